@@ -1,0 +1,229 @@
+/*
+ * quic_b200.h — C ABI of the B200 (sm_100a) W4A16 decode path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * stream handle it is given (a cudaStream_t passed as void*), never
+ * synchronises, never allocates device memory, and returns 0 on success or a
+ * negative QUIC_E_* code.  quic_last_error() returns a static message for the
+ * most recent failure on the calling thread.
+ *
+ * Each declaration cites the interface of the reference project
+ * (hdahroug/quic.cu, paths relative to its root) that it replaces.
+ *
+ * Model constants are fixed at compile time, as in the reference's kernels
+ * (kernels/cuda/rmsnorm.cu:7, swiglu.cu:10, flash_attn_decode.cu:8):
+ * hidden 896, 14 query heads, 2 KV heads, head_dim 64, intermediate 4864,
+ * quantisation group 128.  Layer count, vocabulary size and cache geometry
+ * are run-time arguments.
+ */
+#ifndef QUIC_B200_H
+#define QUIC_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QUIC_HIDDEN 896
+#define QUIC_HEADS 14
+#define QUIC_KV_HEADS 2
+#define QUIC_HEAD_DIM 64
+#define QUIC_INTER 4864
+#define QUIC_GROUP 128
+#define QUIC_QKV_N 1152 /* 896 q + 128 k + 128 v */
+
+#define QUIC_OK 0
+#define QUIC_E_ARG (-1)     /* bad pointer, size or alignment */
+#define QUIC_E_SHAPE (-2)   /* shape not supported by the kernels */
+#define QUIC_E_CUDA (-3)    /* a CUDA runtime call failed */
+#define QUIC_E_LIMIT (-4)   /* size beyond a documented fixed maximum */
+
+const char *quic_last_error(void);
+/* Library ABI version; bumped when a struct below changes. */
+int quic_abi_version(void);
+
+/* ------------------------------------------------------------------------
+ * W4A16 weights.
+ *
+ * Checkpoint layout (reference src/quant/checkpoint.py:23-36):
+ *   weight_packed     int32 [N, K/8]   element k = 8j+i is nibble i of word j
+ *   weight_zero_point int32 [N/8, K/G] row n -> word n/8, nibble n%8
+ *   weight_scale      fp16  [N, K/G]
+ *   w[n,k] = (q - zp[n,k/G]) * scale[n,k/G]
+ *
+ * Device layout used by the kernels ("W4T", K-major so that a warp reads 32
+ * adjacent output columns of one 8-wide k slab with one 128-byte request):
+ *   qw int32 [K/8, N], sc fp16 [K/G, N], zp uint8 [K/G, N/2] (two 4-bit zero
+ *   points per byte, low nibble = even column).
+ * Rows may be permuted on the way (see quic_w4_prepack).  This replaces the
+ * Marlin repack of src/quant/marlin.py:105-125.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const int32_t *qw; /* [K/8, N] */
+  const void *sc;    /* fp16 [K/G, N] */
+  const uint8_t *zp; /* [K/G, N/2] */
+  const void *bias;  /* fp16 [N] in output-row order of this layout, or NULL */
+  int32_t n;
+  int32_t k;
+} quic_w4_t;
+
+/* Row orders accepted by quic_w4_prepack. */
+#define QUIC_ROWS_NATURAL 0
+/* Within every block of 64 rows (one attention head) rows are stored as
+ * (0,32,1,33,...): the two RoPE partners of a pair become neighbours. */
+#define QUIC_ROWS_ROPE_PAIRS 1
+
+/* Repack one checkpoint layer (device pointers) into W4T.  `row_offset` places
+ * the layer's N rows at columns [row_offset, row_offset+N) of a fused matrix
+ * with `n_total` columns (q|k|v, gate|up).  Replaces
+ * src/quant/marlin.py:105 prepack_layer (gptq_repack, marlin_permute_scales,
+ * marlin_zero_points). */
+int quic_w4_prepack(const int32_t *weight_packed, const void *weight_scale,
+                    const int32_t *weight_zero_point, int32_t n, int32_t k,
+                    int32_t row_order, int32_t row_offset, int32_t n_total,
+                    int32_t *qw, void *sc, uint8_t *zp, void *stream);
+
+/* Dequantise a W4T matrix to fp16 [N, K] (natural row order only).  Used by
+ * the bit-exactness tests of the unpack; mirrors
+ * src/quant/checkpoint.py:23 dequantize rounded to fp16. */
+int quic_w4_dequant(const quic_w4_t *w, void *out_f16, void *stream);
+
+/* y[M,N] = x[M,K] · dequant(W)^T + bias, fp16 in/out, fp32 accumulate.
+ * Replaces marlin.forward (kernels/cuda/marlin.cu:4769 marlin_gemm, reached
+ * through src/quant/marlin.py:190 marlin_linear).  M < 16 runs the dequant
+ * GEMV; M >= 16 runs the tcgen05 GEMM when `use_tensor` is non-zero and the
+ * GEMV in row chunks otherwise.  `workspace` (fp32, >= quic_w4a16_workspace
+ * bytes) is needed by the tensor path only. */
+int quic_w4a16_linear(const void *x_f16, const quic_w4_t *w, void *y_f16,
+                      int32_t m, int32_t use_tensor, void *workspace,
+                      void *stream);
+int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k);
+
+/* ------------------------------------------------------------------------
+ * Stand-alone operators with the reference's per-op signatures.
+ * ---------------------------------------------------------------------- */
+
+/* y = x * rsqrt(mean(x^2)+eps) * w over rows of 896; optional residual:
+ * when `residual` is non-NULL, x := x + residual first and the sum is written
+ * to `sum_out`.  Replaces rmsnorm.forward (kernels/cuda/rmsnorm.cu:100) and the
+ * torch residual adds of src/model.py:221,224. */
+int quic_rmsnorm(const void *x_f16, const void *residual_f16, const void *w_f16,
+                 float eps, void *y_f16, void *sum_out_f16, int32_t rows,
+                 void *stream);
+
+/* cos/sin tables fp16 [max_pos, 32].  Replaces rope.init_table
+ * (kernels/cuda/rope.cu:125); uses accurate cosf/sinf. */
+int quic_rope_table_init(const float *inv_freq32, int32_t max_pos, void *cos_f16,
+                         void *sin_f16, void *stream);
+
+/* Rotate-half RoPE on x fp16 [B, H, S, 64]; cos/sin fp16 [S,32] (batch_stride
+ * 0) or [B,S,32].  Replaces rope.forward (kernels/cuda/rope.cu:85). */
+int quic_rope(const void *x_f16, const void *cos_f16, const void *sin_f16,
+              void *y_f16, int32_t b, int32_t h, int32_t s,
+              int32_t trig_batch_stride, void *stream);
+
+/* y = silu(gate) * up, rows of 4864.  Replaces swiglu.forward
+ * (kernels/cuda/swiglu.cu:37). */
+int quic_swiglu(const void *gate_f16, const void *up_f16, void *y_f16,
+                int32_t rows, void *stream);
+
+/* Row argmax of fp16 logits [B, V] -> int64 [B]; ties -> lowest index.
+ * Replaces sampler.forward (kernels/cuda/sampler.cu:52). */
+int quic_argmax(const void *logits_f16, int32_t b, int32_t v, int64_t *out,
+                void *stream);
+
+/* y[M,N] = x[M,K] · w[N,K]^T (+ bias), fp16, fp32 accumulate; K multiple of 8.
+ * Replaces gemm.forward (kernels/cuda/gemm.cu:36, cuBLAS) for the GEMV-shaped
+ * uses on this path (the tied lm_head). */
+int quic_gemm_f16(const void *x_f16, const void *w_f16, const void *bias_f16,
+                  void *y_f16, int32_t m, int32_t n, int32_t k, void *stream);
+
+/* Split-K GQA decode attention.  Replaces flash_attn_decode.forward
+ * (kernels/cuda/flash_attn_decode.cu:133): q fp16 [B,14,64]; K and V fp16 with
+ * explicit element strides (batch, kv head; tokens are 64 contiguous halves
+ * apart); row b attends to tokens [start[b], end[b]) (start == NULL -> 0, the
+ * left pad; end == NULL -> s_max).  A row with no tokens yields zeros
+ * (flash_attn_decode.cu:118-121).  `scratch` holds the split partials and the
+ * arrival counters: quic_attn_scratch_bytes(b, splits) bytes, whose first
+ * b*2*4 bytes (the counters) must be zero before the first call; the kernel
+ * leaves them zero.  `splits` 0 lets the library choose. */
+int quic_attn_decode(const void *q_f16, const void *k_f16, const void *v_f16,
+                     int64_t stride_b, int64_t stride_h, const int32_t *start,
+                     const int32_t *end, int32_t s_max, float scale,
+                     void *out_f16, int32_t b, int32_t splits, void *scratch,
+                     void *stream);
+int32_t quic_attn_pick_splits(int32_t b, int32_t s_max);
+int64_t quic_attn_scratch_bytes(int32_t b, int32_t splits);
+
+/* ------------------------------------------------------------------------
+ * The fused decode step (one token for every active row).
+ * Replaces Engine.step + QUICForCausalLM.forward with seq_len == 1
+ * (src/engine.py:78-107, src/model.py:272-303): embedding gather, 24 decoder
+ * layers, final norm, tied lm_head and greedy argmax, with the KV cache
+ * appended in place and the token / position state kept on the device.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  quic_w4_t qkv;     /* 896 -> 1152, rows in QUIC_ROWS_ROPE_PAIRS order, bias */
+  quic_w4_t o;       /* 896 -> 896 */
+  quic_w4_t gate_up; /* 896 -> 9728 (gate rows then up rows) */
+  quic_w4_t down;    /* 4864 -> 896 */
+  const void *ln1;   /* fp16 [896] input_layernorm */
+  const void *ln2;   /* fp16 [896] post_attention_layernorm */
+} quic_layer_t;
+
+typedef struct {
+  int32_t n_layers;
+  int32_t vocab;
+  float eps;
+  int32_t max_pos;           /* rows of the RoPE tables */
+  const quic_layer_t *layers; /* HOST array of n_layers entries */
+  const void *embed;         /* fp16 [vocab, 896], tied lm_head */
+  const void *final_norm;    /* fp16 [896] */
+  const void *rope_cos;      /* fp16 [max_pos, 32] */
+  const void *rope_sin;
+} quic_model_t;
+
+typedef struct {
+  /* KV cache fp16 [n_layers][2 (K,V)][n_slots][2 kv heads][s_max][64] */
+  void *kv;
+  int32_t n_slots;
+  int32_t s_max;
+  /* Per-slot device state. */
+  int32_t *tok; /* [n_slots] token to feed next */
+  int32_t *pos; /* [n_slots] tokens already cached = position of `tok` */
+  /* Batch rows of this step: slot index per row (device, [batch]). */
+  const int32_t *rows;
+  int32_t batch;
+  /* Generated tokens: out_tokens[(*step_counter % ring) * n_slots + slot]. */
+  int32_t *out_tokens;
+  int32_t ring;
+  int32_t *step_counter; /* device int32, incremented once per step */
+  /* Optional fp16 [batch, vocab] logits of the step (NULL to skip). */
+  void *logits;
+  /* Activation / scratch arena, quic_decode_scratch_bytes() bytes, zeroed
+   * once by the caller before first use. */
+  void *scratch;
+  int32_t attn_splits; /* 0 = choose from ctx_hint */
+  int32_t ctx_hint;    /* upper bound of pos+1 over the rows for this launch */
+} quic_decode_t;
+
+int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32_t attn_splits);
+/* Number of kernels one quic_decode_step launches. */
+int32_t quic_decode_launch_count(const quic_model_t *m, const quic_decode_t *d);
+/* Launch one step (kernels chained with programmatic dependent launch). */
+int quic_decode_step(const quic_model_t *m, const quic_decode_t *d, void *stream);
+
+/* Capture `steps` consecutive decode steps into a CUDA graph owned by the
+ * library; replay with quic_graph_launch.  The same graph stays valid while
+ * the pointers in `d`, the batch size and the split count are unchanged:
+ * tokens, positions and the row->slot map are read from device memory. */
+int quic_decode_graph_create(const quic_model_t *m, const quic_decode_t *d,
+                             int32_t steps, void *stream, void **graph_out);
+int quic_graph_launch(void *graph, void *stream);
+int quic_graph_destroy(void *graph);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUIC_B200_H */

@@ -1,0 +1,21 @@
+"""Engine flags (the reference's EngineConfig, src/config.py:12-18, plus cache geometry)."""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Literal
+
+MODEL_ROOT = os.environ.get("QWEN25_AWQ_PATH", os.environ.get("QWEN25_FP16_PATH", ""))
+
+
+@dataclass(frozen=True)
+class EngineConfig:
+    batching: Literal["static", "continuous"] = "continuous"
+    model_path: str | None = None
+    tokenizer_path: str | None = None
+    use_machete: bool = False  # accepted for compatibility; the Hopper-only backend is not built
+    prefill_backend: Literal["pytorch", "quic"] = "pytorch"
+    # additions (defaults keep reference call sites valid)
+    max_context: int = 2048   # tokens per KV slot (prompt + generated)
+    decode_burst: int = 8     # greedy steps per graph launch between scheduling points

@@ -1,0 +1,312 @@
+// Split-K GQA decode attention over an fp16 K/V cache, head_dim 64, 7 query
+// heads per KV head.
+//
+// Replaces fad_decode_kernel + fad_combine_kernel of the reference
+// (kernels/cuda/flash_attn_decode.cu:12,104).  Same mathematics — fp32 online
+// softmax over the tokens [start_b, end_b) of each row, rows without tokens
+// give zeros (:118-121) — with a different mapping:
+//   * a CTA owns one (split, kv head, batch row); each of its 8 warps walks
+//     tiles of 32 consecutive tokens, ONE TOKEN PER LANE for q·k (no per-token
+//     shuffle chain), all 7 query heads of the group at once;
+//   * K and V tiles are fetched with 16-byte loads issued together, before any
+//     arithmetic, so both are in flight at the same time;
+//   * p·V is done with lanes re-mapped to (token mod 4, 8 dims), probabilities
+//     passing through a per-warp shared-memory tile;
+//   * warps are merged through shared memory, splits through global fp32
+//     partials; the CTA that arrives last at a per-(row, kv head) counter does
+//     the final merge and re-arms the counter, so no second kernel and no
+//     spin-wait is needed.
+#include "decode_kernels.cuh"
+
+namespace quic {
+namespace {
+
+constexpr int kGroupHeads = kHeads / kKvHeads;  // 7
+constexpr int kWarps = 8;
+constexpr int kTile = 32;
+
+__global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs a) {
+  __shared__ __align__(16) float q_s[kGroupHeads * kHeadDim];
+  __shared__ __align__(16) float p_s[kWarps][kGroupHeads][kTile];
+  __shared__ float m_s[kWarps][kGroupHeads];
+  __shared__ float l_s[kWarps][kGroupHeads];
+  __shared__ __align__(16) float o_s[kWarps][kGroupHeads][kHeadDim];
+  __shared__ int last_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+
+  pdl_launch_dependents();
+  pdl_wait();
+
+  int slot = b, t_begin = 0, t_end = a.s_cap;
+  if (a.pos != nullptr) {
+    slot = a.rows[b];
+    t_end = a.pos[slot] + 1;
+  } else {
+    if (a.start != nullptr) t_begin = a.start[b];
+    if (a.end != nullptr) t_end = a.end[b];
+  }
+  if (t_end > a.s_cap) t_end = a.s_cap;
+  if (t_begin < 0) t_begin = 0;
+  const int c_begin = max(t_begin, split * a.chunk);
+  const int c_end = min(t_end, (split + 1) * a.chunk);
+
+  for (int i = tid; i < kGroupHeads * kHeadDim; i += kWarps * 32)
+    q_s[i] = __half2float(a.q[((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim + i]) * a.scale;
+  __syncthreads();
+
+  const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+  const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+
+  float m_run[kGroupHeads], l_run[kGroupHeads];
+  float o[kGroupHeads][8];
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) {
+    m_run[h] = -INFINITY;
+    l_run[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 8; ++d) o[h][d] = 0.f;
+  }
+  const int vt = lane >> 3;        // token (mod 4) this lane covers in p·V
+  const int vd = (lane & 7) * 8;   // first of its 8 dims
+
+  for (int t0 = c_begin + warp * kTile; t0 < c_end; t0 += kWarps * kTile) {
+    const int t = t0 + lane;
+    const bool valid = t < c_end;
+    const int ntok = min(kTile, c_end - t0);
+    // Issue all loads of the tile first.
+    uint4 kr[8];
+    {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)(valid ? t : t0) * kHeadDim);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kr[i] = ldg_nc_u128(kp + i);
+    }
+    uint4 vr[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int tt = 4 * i + vt;
+      const int tc = tt < ntok ? tt : 0;
+      vr[i] = ldg_nc_u128(vbase + (size_t)(t0 + tc) * kHeadDim + vd);
+    }
+
+    float s[kGroupHeads];
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) s[h] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const half2* h2 = reinterpret_cast<const half2*>(&kr[i]);
+      float kf[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h2[j]);
+        kf[2 * j] = f.x;
+        kf[2 * j + 1] = f.y;
+      }
+#pragma unroll
+      for (int h = 0; h < kGroupHeads; ++h) {
+        const float4 qa = *reinterpret_cast<const float4*>(&q_s[h * kHeadDim + 8 * i]);
+        const float4 qb = *reinterpret_cast<const float4*>(&q_s[h * kHeadDim + 8 * i + 4]);
+        s[h] = fmaf(kf[0], qa.x, s[h]);
+        s[h] = fmaf(kf[1], qa.y, s[h]);
+        s[h] = fmaf(kf[2], qa.z, s[h]);
+        s[h] = fmaf(kf[3], qa.w, s[h]);
+        s[h] = fmaf(kf[4], qb.x, s[h]);
+        s[h] = fmaf(kf[5], qb.y, s[h]);
+        s[h] = fmaf(kf[6], qb.z, s[h]);
+        s[h] = fmaf(kf[7], qb.w, s[h]);
+      }
+    }
+    float alpha[kGroupHeads];
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) {
+      const float sv = valid ? s[h] : -INFINITY;
+      const float m_new = fmaxf(m_run[h], warp_max(sv));  // finite: the tile has >= 1 token
+      alpha[h] = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - m_new);
+      const float p = valid ? __expf(sv - m_new) : 0.f;
+      l_run[h] = l_run[h] * alpha[h] + p;  // per-lane partial, summed at the end
+      m_run[h] = m_new;
+      p_s[warp][h][lane] = p;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h)
+#pragma unroll
+      for (int d = 0; d < 8; ++d) o[h][d] *= alpha[h];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int tt = 4 * i + vt;
+      const half2* h2 = reinterpret_cast<const half2*>(&vr[i]);
+      float vf[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h2[j]);
+        vf[2 * j] = f.x;
+        vf[2 * j + 1] = f.y;
+      }
+#pragma unroll
+      for (int h = 0; h < kGroupHeads; ++h) {
+        const float p = p_s[warp][h][tt];  // 0 for tokens past the end
+#pragma unroll
+        for (int d = 0; d < 8; ++d) o[h][d] = fmaf(p, vf[d], o[h][d]);
+      }
+    }
+    __syncwarp();
+  }
+
+  // Warp totals: l over lanes; o over the four token classes (lane bits 3,4).
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) {
+    l_run[h] = warp_sum(l_run[h]);
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+      float v = o[h][d];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      o[h][d] = v;
+    }
+    if (lane < 8) {
+#pragma unroll
+      for (int d = 0; d < 8; ++d) o_s[warp][h][lane * 8 + d] = o[h][d];
+    }
+    if (lane == 0) {
+      m_s[warp][h] = m_run[h];
+      l_s[warp][h] = l_run[h];
+    }
+  }
+  __syncthreads();
+
+  // Merge the 8 warps; thread -> (head, dim).
+  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += kWarps * 32) {
+    const int h = idx >> 6, d = idx & 63;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, m_s[w][h]);
+    float num = 0.f, den = 0.f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float e = (m_s[w][h] == -INFINITY) ? 0.f : __expf(m_s[w][h] - m);
+        den += e * l_s[w][h];
+        num += e * o_s[w][h][d];
+      }
+    }
+    const int qh = kvh * kGroupHeads + h;
+    if (a.splits == 1) {
+      a.out[((size_t)b * kHeads + qh) * kHeadDim + d] =
+          __float2half_rn(m == -INFINITY ? 0.f : num / den);
+    } else {
+      const size_t row = ((size_t)b * kHeads + qh) * a.splits + split;
+      a.o_part[row * kHeadDim + d] = num;
+      if (d == 0) {
+        a.m_part[row] = m;
+        a.l_part[row] = den;
+      }
+    }
+  }
+  if (a.splits == 1) return;
+
+  // Last CTA of this (row, kv head) merges the splits.
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&a.counters[b * kKvHeads + kvh], 1);
+    last_flag = (old == a.splits - 1);
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += kWarps * 32) {
+    const int h = idx >> 6, d = idx & 63;
+    const int qh = kvh * kGroupHeads + h;
+    const size_t row = ((size_t)b * kHeads + qh) * a.splits;
+    float m = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) m = fmaxf(m, __ldcg(a.m_part + row + s));
+    float num = 0.f, den = 0.f;
+    if (m != -INFINITY) {
+      for (int s = 0; s < a.splits; ++s) {
+        const float ms = __ldcg(a.m_part + row + s);
+        const float e = (ms == -INFINITY) ? 0.f : __expf(ms - m);
+        den += e * __ldcg(a.l_part + row + s);
+        num += e * __ldcg(a.o_part + (row + s) * kHeadDim + d);
+      }
+    }
+    a.out[((size_t)b * kHeads + qh) * kHeadDim + d] =
+        __float2half_rn(m == -INFINITY ? 0.f : num / den);
+  }
+  if (tid == 0) a.counters[b * kKvHeads + kvh] = 0;
+}
+
+}  // namespace
+
+cudaError_t launch_attn(const AttnArgs& a, int batch, cudaStream_t s, bool pdl) {
+  dim3 grid(a.splits, kKvHeads, batch);
+  return launch(attn_decode_kernel, grid, dim3(kWarps * 32), 0, s, pdl, a);
+}
+
+}  // namespace quic
+
+using namespace quic;
+
+extern "C" int32_t quic_attn_pick_splits(int32_t b, int32_t s_max) {
+  if (b < 1) b = 1;
+  // Enough CTAs for two per SM where the context allows it, at least one
+  // 256-token pass (8 warps x 32 tokens) per CTA, at most 64 splits.
+  int by_len = (s_max + 255) / 256;
+  int want = (296 + 2 * b - 1) / (2 * b);
+  int s = want < by_len ? want : by_len;
+  if (s < 1) s = 1;
+  if (s > 64) s = 64;
+  return s;
+}
+
+extern "C" int64_t quic_attn_scratch_bytes(int32_t b, int32_t splits) {
+  if (b < 1 || splits < 1) return 0;
+  int64_t counters = ((int64_t)b * kKvHeads * 4 + 255) / 256 * 256;
+  int64_t rows = (int64_t)b * kHeads * splits;
+  return counters + rows * kHeadDim * 4 + 2 * ((rows * 4 + 255) / 256 * 256);
+}
+
+namespace quic {
+// Carves the scratch block; shared with the decode step.
+void attn_carve_scratch(void* scratch, int b, int splits, AttnArgs* a) {
+  char* p = static_cast<char*>(scratch);
+  int64_t counters = ((int64_t)b * kKvHeads * 4 + 255) / 256 * 256;
+  int64_t rows = (int64_t)b * kHeads * splits;
+  int64_t ml = (rows * 4 + 255) / 256 * 256;
+  a->counters = reinterpret_cast<int32_t*>(p);
+  a->o_part = reinterpret_cast<float*>(p + counters);
+  a->m_part = reinterpret_cast<float*>(p + counters + rows * kHeadDim * 4);
+  a->l_part = reinterpret_cast<float*>(p + counters + rows * kHeadDim * 4 + ml);
+}
+}  // namespace quic
+
+extern "C" int quic_attn_decode(const void* q, const void* k, const void* v, int64_t stride_b,
+                                int64_t stride_h, const int32_t* start, const int32_t* end,
+                                int32_t s_max, float scale, void* out, int32_t b, int32_t splits,
+                                void* scratch, void* stream) {
+  QUIC_REQUIRE(q && k && v && out, QUIC_E_ARG, "attn_decode: null tensor");
+  QUIC_REQUIRE(b >= 1 && b <= 65535 && s_max >= 1, QUIC_E_SHAPE, "attn_decode: bad batch or length");
+  QUIC_REQUIRE(((uintptr_t)k % 16 == 0) && ((uintptr_t)v % 16 == 0) && stride_b % 8 == 0 &&
+                   stride_h % 8 == 0,
+               QUIC_E_ARG, "attn_decode: K/V must be 16-byte aligned with strides multiple of 8");
+  if (splits <= 0) splits = quic_attn_pick_splits(b, s_max);
+  QUIC_REQUIRE(splits <= 4096, QUIC_E_SHAPE, "attn_decode: too many splits");
+  QUIC_REQUIRE(splits == 1 || scratch != nullptr, QUIC_E_ARG, "attn_decode: scratch required");
+  AttnArgs a = {};
+  a.q = (const half*)q;
+  a.k = (const half*)k;
+  a.v = (const half*)v;
+  a.stride_b = stride_b;
+  a.stride_h = stride_h;
+  a.start = start;
+  a.end = end;
+  a.s_cap = s_max;
+  a.splits = splits;
+  a.chunk = (s_max + splits - 1) / splits;
+  a.scale = scale > 0.f ? scale : 0.125f;
+  a.out = (half*)out;
+  if (splits > 1) attn_carve_scratch(scratch, b, splits, &a);
+  QUIC_CUDA(launch_attn(a, b, (cudaStream_t)stream, false));
+  return QUIC_OK;
+}

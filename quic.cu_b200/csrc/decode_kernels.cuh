@@ -1,0 +1,120 @@
+// Kernel argument blocks and launchers of the fused decode step.
+#pragma once
+#include "common.cuh"
+
+namespace quic {
+
+// Rows of the down-projection split over kDownSplits CTAs along K (38 groups).
+constexpr int kDownSplits = 5;
+__host__ __device__ __forceinline__ int down_group_begin(int ks) {
+  // 8,8,8,7,7 groups
+  return ks <= 3 ? ks * 8 : 24 + (ks - 3) * 7;
+}
+constexpr int kMaxM = 8;  // batch rows per CTA pass
+
+struct RowState {
+  const int32_t* rows;  // [batch] slot per row
+  const int32_t* tok;   // [n_slots]
+  const int32_t* pos;   // [n_slots]
+  int32_t batch;
+};
+
+struct QkvArgs {
+  quic_w4_t w;
+  const half* ln;
+  const half* embed;      // used when first_layer
+  const half* xres_in;    // [batch][896]
+  half* xres_out;         // [batch][896]
+  const float* partial;   // [kDownSplits][batch][896] or nullptr (first layer)
+  RowState rs;
+  float eps;
+  int32_t first_layer;
+  int32_t vocab;
+  const half* cos_t;
+  const half* sin_t;
+  int32_t max_pos;
+  half* qbuf;    // [batch][14][64]
+  half* kcache;  // this layer: [n_slots][2][s_max][64]
+  half* vcache;
+  int32_t s_max;
+};
+
+struct OProjArgs {
+  quic_w4_t w;
+  const half* attn;     // [batch][896]
+  const half* xres_in;  // [batch][896]
+  half* xres_out;
+  int32_t batch;
+};
+
+struct GateUpArgs {
+  quic_w4_t w;  // n = 9728
+  const half* ln;
+  const half* xres;  // [batch][896]
+  half* act;         // [batch][4864]
+  int32_t batch;
+  float eps;
+};
+
+struct DownArgs {
+  quic_w4_t w;
+  const half* act;  // [batch][4864]
+  float* partial;   // [kDownSplits][batch][896]
+  int32_t batch;
+};
+
+struct AttnArgs {
+  const half* q;  // [batch][14][64]
+  const half* k;
+  const half* v;
+  int64_t stride_b;  // elements between slots / batch rows
+  int64_t stride_h;  // elements between kv heads
+  const int32_t* start;  // [batch] or nullptr
+  const int32_t* end;    // [batch] or nullptr
+  const int32_t* rows;   // decode-step mode: slot per row, end = pos[slot]+1
+  const int32_t* pos;
+  int32_t s_cap;  // token range covered by the grid
+  int32_t chunk;  // tokens per split
+  int32_t splits;
+  float scale;
+  half* out;  // [batch][896]
+  int32_t* counters;  // [batch][2]
+  float* o_part;      // [batch][14][splits][64]
+  float* m_part;      // [batch][14][splits]
+  float* l_part;
+};
+
+struct LmHeadArgs {
+  const half* embed;  // [vocab][896]
+  const half* ln;
+  const half* xres_in;   // [batch][896]
+  const float* partial;  // [kDownSplits][batch][896] or nullptr
+  const half* x_normed;  // stand-alone GEMV mode: rows already normalised, or nullptr
+  int32_t batch;
+  int32_t vocab;
+  float eps;
+  half* logits;  // [batch][vocab] or nullptr
+  // argmax
+  float* best_val;    // [batch][grid]
+  int32_t* best_idx;  // [batch][grid]
+  int32_t* counter;   // single int
+  // state update by the last CTA (all optional)
+  const int32_t* rows;
+  int32_t* tok;
+  int32_t* pos;
+  int32_t* out_tokens;
+  int32_t n_slots;
+  int32_t ring;
+  int32_t* step_counter;
+  int64_t* argmax_out;  // stand-alone mode: [batch]
+};
+
+cudaError_t launch_qkv(const QkvArgs& a, cudaStream_t s, bool pdl);
+cudaError_t launch_oproj(const OProjArgs& a, cudaStream_t s, bool pdl);
+cudaError_t launch_gateup(const GateUpArgs& a, cudaStream_t s, bool pdl);
+cudaError_t launch_down(const DownArgs& a, cudaStream_t s, bool pdl);
+cudaError_t launch_attn(const AttnArgs& a, int batch, cudaStream_t s, bool pdl);
+cudaError_t launch_lm_head(const LmHeadArgs& a, int grid, cudaStream_t s, bool pdl);
+int lm_head_grid(int vocab);
+
+}  // namespace quic

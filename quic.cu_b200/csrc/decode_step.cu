@@ -1,0 +1,267 @@
+// Host side of the fused decode step: carves the scratch arena, chains the
+// kernels of 24 layers + lm_head with programmatic dependent launch, and can
+// capture several consecutive steps into one CUDA graph.
+//
+// One step replaces Engine.step + QUICForCausalLM.forward(seq_len == 1) of the
+// reference (src/engine.py:78-107, src/model.py:272-303).  Token ids, positions
+// and the row -> slot map live in device memory, so a captured graph is valid
+// for any position and consecutive steps need no host round trip.
+#include <new>
+
+#include "decode_kernels.cuh"
+
+namespace quic {
+void attn_carve_scratch(void* scratch, int b, int splits, AttnArgs* a);
+
+namespace {
+
+inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
+
+struct Arena {
+  int64_t lm_counter, attn, xres, qbuf, attn_out, act, partial, best_val, best_idx, total;
+};
+
+// The regions that must start zeroed (arrival counters) come first.
+Arena carve(int batch, int vocab, int splits) {
+  Arena a;
+  int64_t off = 0;
+  a.lm_counter = off;
+  off += 256;
+  a.attn = off;
+  off += align256(quic_attn_scratch_bytes(batch, splits));
+  a.xres = off;
+  off += align256((int64_t)2 * batch * kHidden * 2);
+  a.qbuf = off;
+  off += align256((int64_t)batch * kHidden * 2);
+  a.attn_out = off;
+  off += align256((int64_t)batch * kHidden * 2);
+  a.act = off;
+  off += align256((int64_t)batch * kInter * 2);
+  a.partial = off;
+  off += align256((int64_t)kDownSplits * batch * kHidden * 4);
+  const int grid = lm_head_grid(vocab);
+  a.best_val = off;
+  off += align256((int64_t)batch * grid * 4);
+  a.best_idx = off;
+  off += align256((int64_t)batch * grid * 4);
+  a.total = off;
+  return a;
+}
+
+int pick_splits(const quic_decode_t* d) {
+  if (d->attn_splits > 0) return d->attn_splits;
+  int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
+  if (ctx > d->s_max) ctx = d->s_max;
+  return quic_attn_pick_splits(d->batch, ctx);
+}
+
+int check(const quic_model_t* m, const quic_decode_t* d) {
+  QUIC_REQUIRE(m && d, QUIC_E_ARG, "decode_step: null argument");
+  QUIC_REQUIRE(m->n_layers >= 1 && m->layers, QUIC_E_ARG, "decode_step: no layers");
+  QUIC_REQUIRE(m->vocab >= 2 && m->vocab % 2 == 0, QUIC_E_SHAPE, "decode_step: vocab must be even");
+  QUIC_REQUIRE(m->embed && m->final_norm && m->rope_cos && m->rope_sin && m->max_pos >= 1,
+               QUIC_E_ARG, "decode_step: missing model tensor");
+  QUIC_REQUIRE(d->kv && d->tok && d->pos && d->rows && d->scratch, QUIC_E_ARG,
+               "decode_step: missing state tensor");
+  QUIC_REQUIRE(d->batch >= 1 && d->batch <= 8 * 65535 && d->n_slots >= 1 && d->s_max >= 1,
+               QUIC_E_SHAPE, "decode_step: bad batch / cache geometry");
+  QUIC_REQUIRE(d->out_tokens == nullptr || (d->ring >= 1 && d->step_counter != nullptr),
+               QUIC_E_ARG, "decode_step: out_tokens needs ring >= 1 and a step counter");
+  for (int l = 0; l < m->n_layers; ++l) {
+    const quic_layer_t& L = m->layers[l];
+    QUIC_REQUIRE(L.qkv.n == kQkvN && L.qkv.k == kHidden && L.o.n == kHidden && L.o.k == kHidden &&
+                     L.gate_up.n == 2 * kInter && L.gate_up.k == kHidden && L.down.n == kHidden &&
+                     L.down.k == kInter,
+                 QUIC_E_SHAPE, "decode_step: layer shapes are not Qwen2.5-0.5B's");
+    QUIC_REQUIRE(L.qkv.qw && L.o.qw && L.gate_up.qw && L.down.qw && L.ln1 && L.ln2, QUIC_E_ARG,
+                 "decode_step: missing layer tensor");
+  }
+  return QUIC_OK;
+}
+
+int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st) {
+  const int B = d->batch;
+  const int splits = pick_splits(d);
+  const Arena ar = carve(B, m->vocab, splits);
+  char* base = static_cast<char*>(d->scratch);
+  half* xres[2] = {reinterpret_cast<half*>(base + ar.xres),
+                   reinterpret_cast<half*>(base + ar.xres) + (size_t)B * kHidden};
+  half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
+  half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
+  half* act = reinterpret_cast<half*>(base + ar.act);
+  float* partial = reinterpret_cast<float*>(base + ar.partial);
+
+  const size_t slot_stride = (size_t)kKvHeads * d->s_max * kHeadDim;  // one slot, K or V
+  const size_t kv_plane = (size_t)d->n_slots * slot_stride;           // K (or V) of a layer
+  int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
+  if (ctx > d->s_max) ctx = d->s_max;
+
+  RowState rs;
+  rs.rows = d->rows;
+  rs.tok = d->tok;
+  rs.pos = d->pos;
+  rs.batch = B;
+
+  for (int l = 0; l < m->n_layers; ++l) {
+    const quic_layer_t& L = m->layers[l];
+    half* kc = static_cast<half*>(d->kv) + (size_t)(2 * l) * kv_plane;
+    half* vc = kc + kv_plane;
+
+    QkvArgs qa = {};
+    qa.w = L.qkv;
+    qa.ln = (const half*)L.ln1;
+    qa.embed = (const half*)m->embed;
+    qa.xres_in = xres[1];
+    qa.xres_out = xres[0];
+    qa.partial = partial;
+    qa.rs = rs;
+    qa.eps = m->eps;
+    qa.first_layer = (l == 0);
+    qa.vocab = m->vocab;
+    qa.cos_t = (const half*)m->rope_cos;
+    qa.sin_t = (const half*)m->rope_sin;
+    qa.max_pos = m->max_pos;
+    qa.qbuf = qbuf;
+    qa.kcache = kc;
+    qa.vcache = vc;
+    qa.s_max = d->s_max;
+    QUIC_CUDA(launch_qkv(qa, st, true));
+
+    AttnArgs aa = {};
+    aa.q = qbuf;
+    aa.k = kc;
+    aa.v = vc;
+    aa.stride_b = (int64_t)slot_stride;
+    aa.stride_h = (int64_t)d->s_max * kHeadDim;
+    aa.rows = d->rows;
+    aa.pos = d->pos;
+    aa.s_cap = ctx;
+    aa.splits = splits;
+    aa.chunk = (ctx + splits - 1) / splits;
+    aa.scale = 0.125f;  // 64^-0.5, src/model.py:129
+    aa.out = attn_out;
+    if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
+    QUIC_CUDA(launch_attn(aa, B, st, true));
+
+    OProjArgs oa = {};
+    oa.w = L.o;
+    oa.attn = attn_out;
+    oa.xres_in = xres[0];
+    oa.xres_out = xres[1];
+    oa.batch = B;
+    QUIC_CUDA(launch_oproj(oa, st, true));
+
+    GateUpArgs ga = {};
+    ga.w = L.gate_up;
+    ga.ln = (const half*)L.ln2;
+    ga.xres = xres[1];
+    ga.act = act;
+    ga.batch = B;
+    ga.eps = m->eps;
+    QUIC_CUDA(launch_gateup(ga, st, true));
+
+    DownArgs da = {};
+    da.w = L.down;
+    da.act = act;
+    da.partial = partial;
+    da.batch = B;
+    QUIC_CUDA(launch_down(da, st, true));
+  }
+
+  LmHeadArgs la = {};
+  la.embed = (const half*)m->embed;
+  la.ln = (const half*)m->final_norm;
+  la.xres_in = xres[1];
+  la.partial = partial;
+  la.batch = B;
+  la.vocab = m->vocab;
+  la.eps = m->eps;
+  la.logits = (half*)d->logits;
+  la.best_val = reinterpret_cast<float*>(base + ar.best_val);
+  la.best_idx = reinterpret_cast<int32_t*>(base + ar.best_idx);
+  la.counter = reinterpret_cast<int32_t*>(base + ar.lm_counter);
+  la.rows = d->rows;
+  la.tok = d->tok;
+  la.pos = d->pos;
+  la.out_tokens = d->out_tokens;
+  la.n_slots = d->n_slots;
+  la.ring = d->ring > 0 ? d->ring : 1;
+  la.step_counter = d->step_counter;
+  QUIC_CUDA(launch_lm_head(la, lm_head_grid(m->vocab), st, true));
+  return QUIC_OK;
+}
+
+struct Graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+};
+
+}  // namespace
+}  // namespace quic
+
+using namespace quic;
+
+extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32_t attn_splits) {
+  if (batch < 1 || vocab < 2 || attn_splits < 1) return 0;
+  return carve(batch, vocab, attn_splits).total;
+}
+
+extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_decode_t* d) {
+  (void)d;
+  return m ? 5 * m->n_layers + 1 : 0;
+}
+
+extern "C" int quic_decode_step(const quic_model_t* m, const quic_decode_t* d, void* stream) {
+  int rc = check(m, d);
+  if (rc != QUIC_OK) return rc;
+  return enqueue_step(m, d, (cudaStream_t)stream);
+}
+
+extern "C" int quic_decode_graph_create(const quic_model_t* m, const quic_decode_t* d,
+                                        int32_t steps, void* stream, void** graph_out) {
+  int rc = check(m, d);
+  if (rc != QUIC_OK) return rc;
+  QUIC_REQUIRE(graph_out != nullptr && steps >= 1 && steps <= 4096, QUIC_E_ARG,
+               "decode_graph_create: bad steps / output pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  QUIC_REQUIRE(st != nullptr, QUIC_E_ARG,
+               "decode_graph_create: capture needs a non-default stream");
+  Graph* g = new (std::nothrow) Graph();
+  QUIC_REQUIRE(g != nullptr, QUIC_E_ARG, "decode_graph_create: out of host memory");
+  cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) {
+    delete g;
+    return fail(QUIC_E_CUDA, cudaGetErrorString(e));
+  }
+  for (int s = 0; s < steps && rc == QUIC_OK; ++s) rc = enqueue_step(m, d, st);
+  e = cudaStreamEndCapture(st, &g->graph);
+  if (rc == QUIC_OK && e != cudaSuccess) rc = fail(QUIC_E_CUDA, cudaGetErrorString(e));
+  if (rc == QUIC_OK) {
+    e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) rc = fail(QUIC_E_CUDA, cudaGetErrorString(e));
+  }
+  if (rc != QUIC_OK) {
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    cudaGetLastError();
+    return rc;
+  }
+  *graph_out = g;
+  return QUIC_OK;
+}
+
+extern "C" int quic_graph_launch(void* graph, void* stream) {
+  QUIC_REQUIRE(graph != nullptr, QUIC_E_ARG, "graph_launch: null graph");
+  Graph* g = static_cast<Graph*>(graph);
+  QUIC_CUDA(cudaGraphLaunch(g->exec, (cudaStream_t)stream));
+  return QUIC_OK;
+}
+
+extern "C" int quic_graph_destroy(void* graph) {
+  if (graph == nullptr) return QUIC_OK;
+  Graph* g = static_cast<Graph*>(graph);
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  delete g;
+  return QUIC_OK;
+}

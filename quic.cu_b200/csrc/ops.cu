@@ -1,0 +1,294 @@
+// Stand-alone operators with the reference's per-op call shapes: RMSNorm
+// (+ residual), RoPE and its tables, SwiGLU, argmax, fp16 GEMV.  They serve the
+// prefill path, the per-op parity tests and callers that use the reference's
+// kernel getters one op at a time; the decode step fuses all of them.
+#include <math.h>
+
+#include "decode_kernels.cuh"
+
+namespace quic {
+
+static thread_local char g_err[256] = "";
+void set_error(const char* msg) {
+  int i = 0;
+  for (; msg && msg[i] && i < 255; ++i) g_err[i] = msg[i];
+  g_err[i] = 0;
+}
+int fail(int code, const char* msg) {
+  set_error(msg);
+  return code;
+}
+
+namespace {
+
+// ---- RMSNorm (+ residual) ---------------------------------------------------
+// One warp per row of 896: 28 lanes x 4 x 16 B would leave lanes idle, so each
+// lane takes 28 halves as 3.5 uint4 -> use 8-byte pieces: 896/4 = 224 = 7 x 32.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const half* __restrict__ x,
+                                                      const half* __restrict__ res,
+                                                      const half* __restrict__ w, float eps,
+                                                      half* __restrict__ y,
+                                                      half* __restrict__ sum_out, int rows) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float v[28];
+  float ssq = 0.f;
+#pragma unroll
+  for (int j = 0; j < 7; ++j) {
+    const int c = (j * 32 + lane) * 4;
+    const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * kHidden + c);
+    float2 a = __half22float2(u32_as_half2(u.x)), b = __half22float2(u32_as_half2(u.y));
+    if (res != nullptr) {
+      const uint2 r = *reinterpret_cast<const uint2*>(res + (size_t)row * kHidden + c);
+      const float2 ra = __half22float2(u32_as_half2(r.x)), rb = __half22float2(u32_as_half2(r.y));
+      // the residual stream is an fp16 tensor: round the sum
+      a.x = __half2float(__float2half_rn(a.x + ra.x));
+      a.y = __half2float(__float2half_rn(a.y + ra.y));
+      b.x = __half2float(__float2half_rn(b.x + rb.x));
+      b.y = __half2float(__float2half_rn(b.y + rb.y));
+      if (sum_out != nullptr) {
+        half2 o0 = __floats2half2_rn(a.x, a.y), o1 = __floats2half2_rn(b.x, b.y);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&o0);
+        o.y = *reinterpret_cast<uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(sum_out + (size_t)row * kHidden + c) = o;
+      }
+    }
+    v[4 * j] = a.x; v[4 * j + 1] = a.y; v[4 * j + 2] = b.x; v[4 * j + 3] = b.y;
+    ssq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+  }
+  ssq = warp_sum(ssq);
+  const float r = rsqrtf(ssq * (1.0f / kHidden) + eps);
+#pragma unroll
+  for (int j = 0; j < 7; ++j) {
+    const int c = (j * 32 + lane) * 4;
+    const uint2 u = *reinterpret_cast<const uint2*>(w + c);
+    const float2 wa = __half22float2(u32_as_half2(u.x)), wb = __half22float2(u32_as_half2(u.y));
+    half2 o0 = __floats2half2_rn(v[4 * j] * r * wa.x, v[4 * j + 1] * r * wa.y);
+    half2 o1 = __floats2half2_rn(v[4 * j + 2] * r * wb.x, v[4 * j + 3] * r * wb.y);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&o0);
+    o.y = *reinterpret_cast<uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(y + (size_t)row * kHidden + c) = o;
+  }
+}
+
+// ---- RoPE --------------------------------------------------------------------
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, half* __restrict__ cos_t,
+                                  half* __restrict__ sin_t, int max_pos) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= max_pos * 32) return;
+  const int t = idx >> 5, c = idx & 31;
+  const float ang = (float)t * inv_freq[c];
+  float s, co;
+  sincosf(ang, &s, &co);  // accurate range reduction (no fast-math in this file)
+  cos_t[idx] = __float2half_rn(co);
+  sin_t[idx] = __float2half_rn(s);
+}
+
+// x [B,H,S,64]; one thread per (b,h,s,pair).
+__global__ void rope_kernel(const half* __restrict__ x, const half* __restrict__ cos_t,
+                            const half* __restrict__ sin_t, half* __restrict__ y, int B, int H,
+                            int S, int trig_batch_stride) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)B * H * S * 32;
+  if (idx >= total) return;
+  const int pair = idx & 31;
+  const size_t vec = idx >> 5;  // (b,h,s)
+  const int s = vec % S;
+  const int b = vec / ((size_t)H * S);
+  const size_t trig = (size_t)b * trig_batch_stride + (size_t)s * 32 + pair;
+  const float c = __half2float(cos_t[trig]), sn = __half2float(sin_t[trig]);
+  const float v0 = __half2float(x[vec * 64 + pair]);
+  const float v1 = __half2float(x[vec * 64 + pair + 32]);
+  y[vec * 64 + pair] = __float2half_rn(v0 * c - v1 * sn);
+  y[vec * 64 + pair + 32] = __float2half_rn(v0 * sn + v1 * c);
+}
+
+// ---- SwiGLU -------------------------------------------------------------------
+__global__ void swiglu_kernel(const half2* __restrict__ g, const half2* __restrict__ u,
+                              half2* __restrict__ y, size_t n2) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n2) return;
+  const float2 a = __half22float2(g[i]), b = __half22float2(u[i]);
+  y[i] = __floats2half2_rn(silu_mul(a.x, b.x), silu_mul(a.y, b.y));
+}
+
+// ---- argmax --------------------------------------------------------------------
+// One CTA per row; 16-byte loads when the row start is aligned.
+__global__ void __launch_bounds__(1024) argmax_kernel(const half* __restrict__ logits, int V,
+                                                      int64_t* __restrict__ out) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const half* row = logits + (size_t)blockIdx.x * V;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = __half2float(row[i]);
+    if (v > bv) {  // ascending scan per thread: first maximum kept
+      bv = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sv[warp] = bv;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    bv = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+// ---- fp16 GEMV: y[m,n] = sum_k x[m,k] w[n,k] (+bias) ---------------------------
+// One warp per output row n, up to 8 batch rows per pass, K multiple of 8.
+template <int M>
+__global__ void __launch_bounds__(256) gemv_f16_kernel(const half* __restrict__ x,
+                                                       const half* __restrict__ w,
+                                                       const half* __restrict__ bias,
+                                                       half* __restrict__ y, int m_total, int N,
+                                                       int K) {
+  const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int row0 = blockIdx.y * M;
+  if (n >= N) return;
+  float acc[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) acc[m] = 0.f;
+  const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)n * K);
+  for (int c = lane; c < K / 8; c += 32) {
+    const uint4 wv = ldg_nc_u128(wr + c);
+    const half2* wh = reinterpret_cast<const half2*>(&wv);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      if (row0 + m >= m_total) continue;
+      const uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)(row0 + m) * K + 8 * c);
+      const half2* xh = reinterpret_cast<const half2*>(&xv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __half22float2(wh[e]), b = __half22float2(xh[e]);
+        acc[m] = fmaf(a.x, b.x, acc[m]);
+        acc[m] = fmaf(a.y, b.y, acc[m]);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const float s = warp_sum(acc[m]);
+    if (lane == 0 && row0 + m < m_total) {
+      float v = s;
+      if (bias != nullptr) v = __half2float(__float2half_rn(v)) + __half2float(bias[n]);
+      y[(size_t)(row0 + m) * N + n] = __float2half_rn(v);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace quic
+
+using namespace quic;
+
+extern "C" const char* quic_last_error(void) { return g_err; }
+extern "C" int quic_abi_version(void) { return 1; }
+
+extern "C" int quic_rmsnorm(const void* x, const void* residual, const void* w, float eps, void* y,
+                            void* sum_out, int32_t rows, void* stream) {
+  QUIC_REQUIRE(x && w && y, QUIC_E_ARG, "rmsnorm: null tensor");
+  QUIC_REQUIRE(rows >= 0, QUIC_E_SHAPE, "rmsnorm: negative rows");
+  QUIC_REQUIRE(((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)residual |
+                (uintptr_t)sum_out) % 8 == 0,
+               QUIC_E_ARG, "rmsnorm: tensors must be 8-byte aligned");
+  if (rows == 0) return QUIC_OK;
+  rmsnorm_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(
+      (const half*)x, (const half*)residual, (const half*)w, eps, (half*)y, (half*)sum_out, rows);
+  QUIC_CUDA(cudaGetLastError());
+  return QUIC_OK;
+}
+
+extern "C" int quic_rope_table_init(const float* inv_freq32, int32_t max_pos, void* cos_t,
+                                    void* sin_t, void* stream) {
+  QUIC_REQUIRE(inv_freq32 && cos_t && sin_t, QUIC_E_ARG, "rope_table_init: null tensor");
+  QUIC_REQUIRE(max_pos >= 1, QUIC_E_SHAPE, "rope_table_init: max_pos < 1");
+  const int total = max_pos * 32;
+  rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      inv_freq32, (half*)cos_t, (half*)sin_t, max_pos);
+  QUIC_CUDA(cudaGetLastError());
+  return QUIC_OK;
+}
+
+extern "C" int quic_rope(const void* x, const void* cos_t, const void* sin_t, void* y, int32_t b,
+                         int32_t h, int32_t s, int32_t trig_batch_stride, void* stream) {
+  QUIC_REQUIRE(x && cos_t && sin_t && y, QUIC_E_ARG, "rope: null tensor");
+  QUIC_REQUIRE(b >= 0 && h >= 0 && s >= 0, QUIC_E_SHAPE, "rope: negative size");
+  const size_t total = (size_t)b * h * s * 32;
+  if (total == 0) return QUIC_OK;
+  rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const half*)x, (const half*)cos_t, (const half*)sin_t, (half*)y, b, h, s, trig_batch_stride);
+  QUIC_CUDA(cudaGetLastError());
+  return QUIC_OK;
+}
+
+extern "C" int quic_swiglu(const void* gate, const void* up, void* y, int32_t rows, void* stream) {
+  QUIC_REQUIRE(gate && up && y, QUIC_E_ARG, "swiglu: null tensor");
+  QUIC_REQUIRE(rows >= 0, QUIC_E_SHAPE, "swiglu: negative rows");
+  const size_t n2 = (size_t)rows * kInter / 2;
+  if (n2 == 0) return QUIC_OK;
+  swiglu_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const half2*)gate, (const half2*)up, (half2*)y, n2);
+  QUIC_CUDA(cudaGetLastError());
+  return QUIC_OK;
+}
+
+extern "C" int quic_argmax(const void* logits, int32_t b, int32_t v, int64_t* out, void* stream) {
+  QUIC_REQUIRE(logits && out, QUIC_E_ARG, "argmax: null tensor");
+  QUIC_REQUIRE(b >= 0 && v >= 1, QUIC_E_SHAPE, "argmax: bad shape");
+  if (b == 0) return QUIC_OK;
+  argmax_kernel<<<b, 1024, 0, (cudaStream_t)stream>>>((const half*)logits, v, out);
+  QUIC_CUDA(cudaGetLastError());
+  return QUIC_OK;
+}
+
+extern "C" int quic_gemm_f16(const void* x, const void* w, const void* bias, void* y, int32_t m,
+                             int32_t n, int32_t k, void* stream) {
+  QUIC_REQUIRE(x && w && y, QUIC_E_ARG, "gemm_f16: null tensor");
+  QUIC_REQUIRE(m >= 0 && n >= 1 && k >= 8 && k % 8 == 0, QUIC_E_SHAPE,
+               "gemm_f16: K must be a positive multiple of 8");
+  QUIC_REQUIRE(((uintptr_t)x | (uintptr_t)w) % 16 == 0, QUIC_E_ARG,
+               "gemm_f16: x and w must be 16-byte aligned");
+  if (m == 0) return QUIC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int mchunks = (m + 7) / 8;
+  QUIC_REQUIRE(mchunks <= 65535, QUIC_E_SHAPE, "gemm_f16: too many rows");
+  dim3 grid((n + 7) / 8, mchunks);
+  if (m == 1)
+    gemv_f16_kernel<1><<<grid, 256, 0, st>>>((const half*)x, (const half*)w, (const half*)bias,
+                                             (half*)y, m, n, k);
+  else
+    gemv_f16_kernel<8><<<grid, 256, 0, st>>>((const half*)x, (const half*)w, (const half*)bias,
+                                             (half*)y, m, n, k);
+  QUIC_CUDA(cudaGetLastError());
+  return QUIC_OK;
+}

@@ -1,0 +1,169 @@
+"""Static / continuous batching engine over KV slots.
+
+Keeps the reference's API (src/engine.py:26-168): ``Engine(registry, max_batch_size, config,
+model_module)``, ``add_request(prompt)``, ``step()``, ``run() -> outputs sorted by request id``,
+with the same request semantics:
+
+* FIFO admission decided by the policies of ``scheduler`` before every iteration
+  (src/engine.py:115-160);
+* greedy sampling; the EOS token IS appended and ends the request, ``max_tokens`` caps it
+  (src/engine.py:180-184, src/sequence.py:15-19);
+* under static batching finished rows keep their slot until the whole batch has finished
+  (src/scheduler.py:34-45).
+
+What differs is where the state lives.  The reference keeps one left-padded batch whose
+cache length only grows and rebuilds it with torch.cat on every admission
+(src/engine.py:225-277).  Here every request owns a KV slot that stores real tokens only;
+admission prefills into a free slot, release frees it, and an iteration is a burst of
+``decode_burst`` greedy steps that run on the device from one CUDA graph launch, with one
+device->host copy of the burst's tokens.  Tokens produced by a row after it finished are
+discarded exactly as the reference discards them (src/engine.py:180-182).
+
+``model_module.load(**options)`` must return ``(model, tokenizer)``; the model is driven
+through three calls: ``new_cache(n_slots, s_max)``, ``prefill(cache, slots, prompts)`` and
+``decode(cache, slots, steps)``.
+"""
+
+from __future__ import annotations
+
+import itertools
+from collections import deque
+
+import torch
+
+from .config import EngineConfig
+from .metrics import MetricsRegistry, Span
+from .scheduler import ContinuousAdmissionPolicy, StaticAdmissionPolicy
+from .sequence import SequenceState
+
+BATCHING_POLICIES = {
+    "static": StaticAdmissionPolicy,
+    "continuous": ContinuousAdmissionPolicy,
+}
+
+
+class Engine:
+    def __init__(self, registry: MetricsRegistry | None = None, max_batch_size: int = 8,
+                 config: EngineConfig | None = None, model_module=None) -> None:
+        if config is None:
+            config = EngineConfig()
+        self.config = config
+        self.max_batch_size = max_batch_size
+        self.running: list[SequenceState] = []
+        self.waiting: deque[SequenceState] = deque()
+
+        load_options: dict[str, str | bool] = {}
+        if config.model_path is not None:
+            load_options["path"] = config.model_path
+        if config.tokenizer_path is not None:
+            load_options["tokenizer_path"] = config.tokenizer_path
+        if config.use_machete:
+            load_options["use_machete"] = True
+        if getattr(config, "prefill_backend", None) is not None:
+            load_options["prefill_backend"] = config.prefill_backend
+
+        if model_module is None:
+            from . import model as model_module  # the CUDA model; raises without the library
+        self.model, self.tokenizer = model_module.load(**load_options)
+        self.max_tokens = 256
+        self.registry = registry
+        self.burst = max(1, int(config.decode_burst))
+        self.cache = self.model.new_cache(max_batch_size, config.max_context)
+        self.free_slots: list[int] = list(range(max_batch_size))
+        self._request_id_generator = itertools.count(1)
+        self.batching_policy = BATCHING_POLICIES[config.batching]()
+        self.eos_token_id = getattr(self.tokenizer, "eos_token_id", None)
+        self.decode_steps = 0      # device decode iterations issued
+        self.generated = 0         # tokens kept
+
+    # ---- requests ------------------------------------------------------------------
+    def add_request(self, prompt: str) -> int:
+        """Chat-templated text request (src/engine.py:59-75)."""
+        if self.tokenizer is None:
+            raise RuntimeError("add_request(str) needs a tokenizer; use add_request_ids")
+        encoding = self.tokenizer.apply_chat_template(
+            [{"role": "user", "content": prompt}], add_generation_prompt=True,
+            return_tensors="pt", return_dict=True)
+        return self.add_request_ids(encoding["input_ids"])
+
+    def add_request_ids(self, input_ids, max_tokens: int | None = None) -> int:
+        """Token-id request: ``input_ids`` is a list or a [1, T] / [T] tensor."""
+        ids = torch.as_tensor(input_ids, dtype=torch.long).reshape(1, -1).cpu()
+        if ids.shape[1] < 1:
+            raise ValueError("empty prompt")
+        limit = self.max_tokens if max_tokens is None else max_tokens
+        if ids.shape[1] + limit + self.burst > self.config.max_context:
+            raise ValueError(f"prompt ({ids.shape[1]}) + max_tokens ({limit}) + burst does not fit a "
+                             f"KV slot of {self.config.max_context} tokens")
+        request_id = next(self._request_id_generator)
+        self.waiting.append(SequenceState(prompt_tokens=ids, request_id=request_id, max_tokens=limit))
+        return request_id
+
+    # ---- one iteration ---------------------------------------------------------------
+    def _update_sequence_with_token(self, sequence: SequenceState, token: int) -> None:
+        if not sequence.is_finished:
+            sequence.generated_tokens.append(token)
+            self.generated += 1
+            if self.eos_token_id is not None and token == self.eos_token_id:
+                sequence.finished_at = len(sequence.generated_tokens) - 1
+
+    @torch.inference_mode()
+    def step(self, steps: int | None = None) -> None:
+        """One decode iteration: ``steps`` greedy tokens for every unfinished row."""
+        with Span("step", self.registry):
+            with Span("prepare_decode", self.registry):
+                live = [seq for seq in self.running if not seq.is_finished]
+                if not live:
+                    return
+                if steps is None:
+                    need = max(seq.max_tokens - len(seq.generated_tokens) for seq in live)
+                    steps = max(1, min(self.burst, need))
+                slots = [seq.slot for seq in live]
+            with Span("forward_pass", self.registry):
+                tokens = self.model.decode(self.cache, slots, steps)
+                self.decode_steps += steps
+            with Span("sample_and_update", self.registry):
+                for seq, row in zip(live, tokens):
+                    for token in row:
+                        self._update_sequence_with_token(seq, int(token))
+
+    @torch.inference_mode()
+    def _prefill_sequences(self, sequences: list[SequenceState]) -> None:
+        for seq in sequences:
+            seq.slot = self.free_slots.pop(0)
+        first, _ = self.model.prefill(self.cache, [s.slot for s in sequences],
+                                      [s.prompt_tokens.view(-1) for s in sequences])
+        first = first.tolist() if hasattr(first, "tolist") else list(first)
+        for seq, token in zip(sequences, first):
+            self._update_sequence_with_token(seq, int(token))
+
+    def _finish(self, seq: SequenceState):
+        if self.tokenizer is not None:
+            return self.tokenizer.decode(seq.generated_tokens, skip_special_tokens=True)
+        return list(seq.generated_tokens)
+
+    @torch.inference_mode()
+    def run(self) -> list:
+        """Serves the queue to completion; outputs ordered by request id (src/engine.py:168).
+        Decoded strings with a tokenizer, token-id lists without one."""
+        outputs: dict[int, object] = {}
+        with Span("request run", self.registry):
+            while True:
+                with Span("scheduling", self.registry):
+                    decision = self.batching_policy.decide(self.running, self.waiting, self.max_batch_size)
+                    released = {seq.request_id for seq in decision.release}
+                    for seq in decision.release:
+                        outputs[seq.request_id] = self._finish(seq)
+                        self.free_slots.append(seq.slot)
+                        seq.slot = None
+                    if released:
+                        self.running = [s for s in self.running if s.request_id not in released]
+                if decision.admit:
+                    with Span("prefill", self.registry):
+                        admitted = [self.waiting.popleft() for _ in decision.admit]
+                        self._prefill_sequences(admitted)
+                        self.running.extend(admitted)
+                if not self.running:
+                    break
+                self.step()
+        return [outputs[request_id] for request_id in sorted(outputs)]

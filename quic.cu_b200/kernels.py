@@ -1,0 +1,412 @@
+"""ctypes binding of libquic_b200.so plus per-op wrappers shaped like the reference's
+kernel getters.
+
+The reference loads one JIT torch extension per op through getters that return a module
+with a ``forward`` (kernels/__init__.py:42-115: ``gemm() rmsnorm() rope() swiglu() sampler()
+flash_attn_decode() marlin()``).  Here one ahead-of-time library built for sm_100a carries
+every op behind a C ABI (include/quic_b200.h); the getters below return small objects with
+the same ``forward`` call shapes, so model code written against the reference's loader
+keeps working.  There is no CPU or eager fallback: a missing library or a call with CPU
+tensors raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import functools
+import os
+from types import SimpleNamespace
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libquic_b200.so")
+
+HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, GROUP, QKV_N = 896, 14, 2, 64, 4864, 128, 1152
+ROWS_NATURAL, ROWS_ROPE_PAIRS = 0, 1
+
+
+class W4(C.Structure):
+    """quic_w4_t"""
+
+    _fields_ = [
+        ("qw", C.c_void_p),
+        ("sc", C.c_void_p),
+        ("zp", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("n", C.c_int32),
+        ("k", C.c_int32),
+    ]
+
+
+class Layer(C.Structure):
+    """quic_layer_t"""
+
+    _fields_ = [
+        ("qkv", W4),
+        ("o", W4),
+        ("gate_up", W4),
+        ("down", W4),
+        ("ln1", C.c_void_p),
+        ("ln2", C.c_void_p),
+    ]
+
+
+class Model(C.Structure):
+    """quic_model_t"""
+
+    _fields_ = [
+        ("n_layers", C.c_int32),
+        ("vocab", C.c_int32),
+        ("eps", C.c_float),
+        ("max_pos", C.c_int32),
+        ("layers", C.POINTER(Layer)),
+        ("embed", C.c_void_p),
+        ("final_norm", C.c_void_p),
+        ("rope_cos", C.c_void_p),
+        ("rope_sin", C.c_void_p),
+    ]
+
+
+class Decode(C.Structure):
+    """quic_decode_t"""
+
+    _fields_ = [
+        ("kv", C.c_void_p),
+        ("n_slots", C.c_int32),
+        ("s_max", C.c_int32),
+        ("tok", C.c_void_p),
+        ("pos", C.c_void_p),
+        ("rows", C.c_void_p),
+        ("batch", C.c_int32),
+        ("out_tokens", C.c_void_p),
+        ("ring", C.c_int32),
+        ("step_counter", C.c_void_p),
+        ("logits", C.c_void_p),
+        ("scratch", C.c_void_p),
+        ("attn_splits", C.c_int32),
+        ("ctx_hint", C.c_int32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol declared in include/quic_b200.h
+_P, _I32, _I64, _F = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+SIGNATURES = {
+    "quic_last_error": (C.c_char_p, []),
+    "quic_abi_version": (C.c_int, []),
+    "quic_w4_prepack": (C.c_int, [_P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P]),
+    "quic_w4_dequant": (C.c_int, [C.POINTER(W4), _P, _P]),
+    "quic_w4a16_linear": (C.c_int, [_P, C.POINTER(W4), _P, _I32, _I32, _P, _P]),
+    "quic_w4a16_workspace_bytes": (_I64, [_I32, _I32, _I32]),
+    "quic_rmsnorm": (C.c_int, [_P, _P, _P, _F, _P, _P, _I32, _P]),
+    "quic_rope_table_init": (C.c_int, [_P, _I32, _P, _P, _P]),
+    "quic_rope": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P]),
+    "quic_swiglu": (C.c_int, [_P, _P, _P, _I32, _P]),
+    "quic_argmax": (C.c_int, [_P, _I32, _I32, _P, _P]),
+    "quic_gemm_f16": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P]),
+    "quic_attn_decode": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _I32, _F, _P, _I32, _I32, _P, _P]),
+    "quic_attn_pick_splits": (_I32, [_I32, _I32]),
+    "quic_attn_scratch_bytes": (_I64, [_I32, _I32]),
+    "quic_decode_scratch_bytes": (_I64, [_I32, _I32, _I32]),
+    "quic_decode_launch_count": (_I32, [C.POINTER(Model), C.POINTER(Decode)]),
+    "quic_decode_step": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _P]),
+    "quic_decode_graph_create": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _I32, _P, C.POINTER(_P)]),
+    "quic_graph_launch": (C.c_int, [_P, _P]),
+    "quic_graph_destroy": (C.c_int, [_P]),
+}
+
+
+@functools.cache
+def lib() -> C.CDLL:
+    """Loads the CUDA library; raises if it has not been built (no fallback)."""
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `make -C {os.path.join(_HERE, 'csrc')}` "
+            "(or __graft_entry__.build()); this package has no CPU or eager fallback"
+        )
+    handle = C.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return handle
+
+
+def check(rc: int, what: str = "") -> None:
+    """Turns a negative return code into RuntimeError, the reference's error convention
+    (TORCH_CHECK -> RuntimeError, e.g. kernels/cuda/flash_attn_decode.cu:136-161)."""
+    if rc != 0:
+        msg = lib().quic_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"quic_b200 {what} failed ({rc}): {msg}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("quic_b200: CUDA tensors required (no CPU path)")
+
+
+def _need_half(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and t.dtype != torch.float16:
+            raise RuntimeError("quic_b200: fp16 tensors required")
+
+
+# ---------------------------------------------------------------------------------
+# W4A16 weights on the device
+# ---------------------------------------------------------------------------------
+class W4Weight:
+    """One (possibly fused) W4A16 matrix in the device layout of quic_w4_t.
+
+    Built from checkpoint tensors (reference layout, src/quant/checkpoint.py:23-36) by the
+    GPU repack kernel; replaces MarlinWeight (src/quant/marlin.py:128)."""
+
+    def __init__(self, n: int, k: int, device, bias: torch.Tensor | None = None):
+        if n % 32 or k % GROUP:
+            raise RuntimeError("W4Weight: N must be a multiple of 32 and K of 128")
+        self.size_n, self.size_k = n, k
+        self.qw = torch.empty(k // 8, n, dtype=torch.int32, device=device)
+        self.sc = torch.empty(k // GROUP, n, dtype=torch.float16, device=device)
+        self.zp = torch.empty(k // GROUP, n // 2, dtype=torch.uint8, device=device)
+        self.bias = bias
+        self._workspace: torch.Tensor | None = None
+
+    def put(self, packed: torch.Tensor, scale: torch.Tensor, zero_point: torch.Tensor,
+            row_offset: int = 0, row_order: int = ROWS_NATURAL) -> None:
+        """Repacks one checkpoint layer into columns [row_offset, row_offset + N_layer)."""
+        dev = self.qw.device
+        packed = packed.to(dev, torch.int32).contiguous()
+        scale = scale.to(dev, torch.float16).contiguous()
+        zero_point = zero_point.to(dev, torch.int32).contiguous()
+        n, k8 = packed.shape
+        if k8 * 8 != self.size_k or scale.shape != (n, self.size_k // GROUP) or \
+                zero_point.shape != (n // 8, self.size_k // GROUP):
+            raise RuntimeError("W4Weight.put: checkpoint tensor shapes do not match")
+        check(lib().quic_w4_prepack(ptr(packed), ptr(scale), ptr(zero_point), n, self.size_k,
+                                    row_order, row_offset, self.size_n, ptr(self.qw), ptr(self.sc),
+                                    ptr(self.zp), stream_ptr()), "w4_prepack")
+
+    def struct(self) -> W4:
+        return W4(ptr(self.qw), ptr(self.sc), ptr(self.zp), ptr(self.bias), self.size_n, self.size_k)
+
+    def dequant(self) -> torch.Tensor:
+        out = torch.empty(self.size_n, self.size_k, dtype=torch.float16, device=self.qw.device)
+        s = self.struct()
+        check(lib().quic_w4_dequant(C.byref(s), ptr(out), stream_ptr()), "w4_dequant")
+        return out
+
+    def workspace(self, m: int) -> torch.Tensor:
+        need = lib().quic_w4a16_workspace_bytes(m, self.size_n, self.size_k)
+        if self._workspace is None or self._workspace.numel() * 4 < need:
+            self._workspace = torch.empty((need + 3) // 4, dtype=torch.float32, device=self.qw.device)
+        return self._workspace
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.qw.numel() * 4 + self.sc.numel() * 2 + self.zp.numel()
+
+
+def w4a16_linear(w: W4Weight, x: torch.Tensor, use_tensor: bool | None = None) -> torch.Tensor:
+    """y = x · dequant(W)^T + bias.  Replaces marlin_linear (src/quant/marlin.py:190)."""
+    _need_cuda(x)
+    _need_half(x)
+    x2 = x.contiguous().reshape(-1, w.size_k)
+    m = x2.shape[0]
+    y = torch.empty(m, w.size_n, dtype=torch.float16, device=x.device)
+    if use_tensor is None:
+        use_tensor = m >= 16
+    s = w.struct()
+    check(lib().quic_w4a16_linear(ptr(x2), C.byref(s), ptr(y), m, int(bool(use_tensor)),
+                                  ptr(w.workspace(m)), stream_ptr()), "w4a16_linear")
+    return y.reshape(*x.shape[:-1], w.size_n)
+
+
+# ---------------------------------------------------------------------------------
+# Per-op getters with the reference's forward() call shapes
+# ---------------------------------------------------------------------------------
+def _rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor, eps: float,
+                     residual: torch.Tensor | None = None):
+    """rmsnorm.forward(x fp16 [...,896], weight fp16 [896], eps) -> fp16 (rmsnorm.cu:100).
+    With ``residual`` returns (normed, x + residual)."""
+    _need_cuda(x, weight, residual)
+    _need_half(x, weight, residual)
+    if x.shape[-1] != HIDDEN or weight.numel() != HIDDEN:
+        raise RuntimeError("rmsnorm: hidden size must be 896")
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    rows = x.numel() // HIDDEN
+    total = None
+    if residual is not None:
+        residual = residual.contiguous()
+        total = torch.empty_like(x)
+    check(lib().quic_rmsnorm(ptr(x), ptr(residual), ptr(weight.contiguous()), float(eps), ptr(y),
+                             ptr(total), rows, stream_ptr()), "rmsnorm")
+    return y if residual is None else (y, total)
+
+
+def _rope_init_table(inv_freq: torch.Tensor, max_seq_len: int):
+    """rope.init_table(inv_freq fp32 cuda [32], max_seq_len) -> [cos, sin] fp16 [max,32]
+    (rope.cu:125)."""
+    _need_cuda(inv_freq)
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != 32:
+        raise RuntimeError("rope.init_table: inv_freq must be fp32 with 32 elements")
+    cos = torch.empty(max_seq_len, 32, dtype=torch.float16, device=inv_freq.device)
+    sin = torch.empty_like(cos)
+    check(lib().quic_rope_table_init(ptr(inv_freq.contiguous()), int(max_seq_len), ptr(cos), ptr(sin),
+                                     stream_ptr()), "rope_table_init")
+    return [cos, sin]
+
+
+def _rope_forward(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """rope.forward(x fp16 [B,H,S,64] contiguous, cos, sin fp16 [S,32] or [B,S,32]) (rope.cu:85)."""
+    _need_cuda(x, cos, sin)
+    _need_half(x, cos, sin)
+    if x.dim() != 4 or not x.is_contiguous() or x.shape[3] != HEAD_DIM:
+        raise RuntimeError("rope: x must be contiguous [B, H, S, 64]")
+    b, h, s, _ = x.shape
+    if cos.shape != sin.shape or not (cos.is_contiguous() and sin.is_contiguous()):
+        raise RuntimeError("rope: cos/sin must be contiguous and of equal shape")
+    if cos.dim() == 3:
+        if tuple(cos.shape) != (b, s, 32):
+            raise RuntimeError("rope: per-row cos/sin must be [B, S, 32]")
+        stride = s * 32
+    elif cos.dim() == 2 and tuple(cos.shape) == (s, 32):
+        stride = 0
+    else:
+        raise RuntimeError("rope: shared cos/sin must be [S, 32]")
+    y = torch.empty_like(x)
+    check(lib().quic_rope(ptr(x), ptr(cos), ptr(sin), ptr(y), b, h, s, stride, stream_ptr()), "rope")
+    return y
+
+
+def _swiglu_forward(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """swiglu.forward(gate, up fp16 [rows,4864]) -> fp16 (swiglu.cu:37)."""
+    _need_cuda(gate, up)
+    _need_half(gate, up)
+    if gate.dim() != 2 or gate.shape[1] != INTER or gate.shape != up.shape:
+        raise RuntimeError("swiglu: gate/up must be [rows, 4864] of equal shape")
+    gate, up = gate.contiguous(), up.contiguous()
+    y = torch.empty_like(gate)
+    check(lib().quic_swiglu(ptr(gate), ptr(up), ptr(y), gate.shape[0], stream_ptr()), "swiglu")
+    return y
+
+
+def _sampler_forward(logits: torch.Tensor) -> torch.Tensor:
+    """sampler.forward(logits fp16 [B,1,V]) -> int64 [B,1] (sampler.cu:52)."""
+    _need_cuda(logits)
+    _need_half(logits)
+    if logits.dim() != 3 or logits.shape[1] != 1:
+        raise RuntimeError("sampler: expected [B,1,V]")
+    logits = logits.contiguous()
+    b, _, v = logits.shape
+    out = torch.empty(b, 1, dtype=torch.int64, device=logits.device)
+    check(lib().quic_argmax(ptr(logits), b, v, ptr(out), stream_ptr()), "argmax")
+    return out
+
+
+def _gemm_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """gemm.forward(x fp16 [...,K], w fp16 [N,K], bias fp16 [N] or None) -> [...,N] (gemm.cu:36)."""
+    _need_cuda(x, w, bias)
+    _need_half(x, w, bias)
+    k = x.shape[-1]
+    n = w.shape[0]
+    if w.dim() != 2 or w.shape[1] != k:
+        raise RuntimeError("gemm: weight must be [N, K]")
+    x2 = x.contiguous().reshape(-1, k)
+    y = torch.empty(x2.shape[0], n, dtype=torch.float16, device=x.device)
+    check(lib().quic_gemm_f16(ptr(x2), ptr(w.contiguous()), ptr(bias), ptr(y), x2.shape[0], n, k,
+                              stream_ptr()), "gemm_f16")
+    return y.reshape(*x.shape[:-1], n)
+
+
+_attn_scratch: dict = {}
+
+
+def _flash_attn_decode_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                               softmax_scale: float = -1.0, pad_lens: torch.Tensor | None = None,
+                               splits: int = 0) -> torch.Tensor:
+    """flash_attn_decode.forward(Q fp16 [B,nh,1,64], K, V fp16 [B,n_kv,S,64], softmax_scale,
+    pad_lens int32 [B] or None) -> fp16 [B,nh,1,64] (flash_attn_decode.cu:133-198)."""
+    _need_cuda(q, k, v, pad_lens)
+    _need_half(q, k, v)
+    if q.dim() != 4 or q.shape[2] != 1 or q.shape[3] != HEAD_DIM:
+        raise RuntimeError("flash_attn_decode: Q must be [B, nh, 1, 64]")
+    b, nh = q.shape[0], q.shape[1]
+    if nh != HEADS or k.shape[1] != KV_HEADS:
+        raise RuntimeError("flash_attn_decode: built for 14 query heads / 2 KV heads")
+    if k.shape[0] != b or v.shape != k.shape or k.shape[3] != HEAD_DIM:
+        raise RuntimeError("flash_attn_decode: K/V shape mismatch")
+    s = k.shape[2]
+    if pad_lens is not None and not (pad_lens.dtype == torch.int32 and pad_lens.dim() == 1 and
+                                     pad_lens.shape[0] == b and pad_lens.is_contiguous()):
+        raise RuntimeError("flash_attn_decode: pad_lens must be a contiguous CUDA int32 tensor of shape [B]")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty(b, nh, 1, HEAD_DIM, dtype=torch.float16, device=q.device)
+    if s == 0:
+        return out.zero_()
+    if splits <= 0:
+        splits = lib().quic_attn_pick_splits(b, s)
+    scratch = None
+    if splits > 1:
+        need = lib().quic_attn_scratch_bytes(b, splits)
+        key = (q.device.index, torch.cuda.current_stream().cuda_stream)
+        scratch = _attn_scratch.get(key)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=q.device)
+            _attn_scratch[key] = scratch
+    scale = float(softmax_scale) if softmax_scale and softmax_scale > 0 else HEAD_DIM ** -0.5
+    check(lib().quic_attn_decode(ptr(q), ptr(k), ptr(v), KV_HEADS * s * HEAD_DIM, s * HEAD_DIM,
+                                 ptr(pad_lens), None, s, scale, ptr(out), b, splits, ptr(scratch),
+                                 stream_ptr()), "attn_decode")
+    return out
+
+
+@functools.cache
+def rmsnorm():
+    lib()
+    return SimpleNamespace(forward=_rmsnorm_forward)
+
+
+@functools.cache
+def rope():
+    lib()
+    return SimpleNamespace(forward=_rope_forward, init_table=_rope_init_table)
+
+
+@functools.cache
+def swiglu():
+    lib()
+    return SimpleNamespace(forward=_swiglu_forward)
+
+
+@functools.cache
+def sampler():
+    lib()
+    return SimpleNamespace(forward=_sampler_forward)
+
+
+@functools.cache
+def gemm():
+    lib()
+    return SimpleNamespace(forward=_gemm_forward)
+
+
+@functools.cache
+def flash_attn_decode():
+    lib()
+    return SimpleNamespace(forward=_flash_attn_decode_forward)
+
+
+@functools.cache
+def w4a16():
+    """Replaces the reference's ``marlin()`` getter: ``forward(weight, x)``."""
+    lib()
+    return SimpleNamespace(forward=w4a16_linear)

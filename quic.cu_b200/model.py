@@ -1,0 +1,416 @@
+"""Qwen2.5-0.5B W4A16 model on the B200 kernels, behind the reference's model API.
+
+Mirrors src/model.py of the reference: ``load(path, prefill_backend, use_marlin, use_machete,
+tokenizer_path) -> (QUICForCausalLM, tokenizer)`` (src/model.py:306) and
+``QUICForCausalLM.forward(input_ids, past_key_values, attention_mask, position_ids, use_cache)
+-> CausalLMOutputWithPast`` (src/model.py:272).  Differences that callers can see:
+
+* the cache object handed back is a ``SlotCache`` (slotted fp16 KV that stores real tokens
+  only) instead of HF's ``DynamicCache``; it offers ``get_seq_length()`` and can be passed
+  back in, which is all the reference's callers do with it (run.py:50-61,
+  benchmarks/collect.py:61-92);
+* a prefill returns logits of the last position only unless ``prefill_all_logits`` is set;
+* decode (``seq_len == 1``) is ONE fused call: embedding, 24 layers, final norm, lm_head and
+  argmax run as a chain of kernels with state on the device.  ``decode`` runs several
+  consecutive greedy steps from a captured CUDA graph without a host round trip.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import kernels as K
+from .checkpoint import LAYER_LINEARS, detect_group_size, packed_prefixes
+
+DTYPE = torch.float16
+HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, QKV_N = K.HIDDEN, K.HEADS, K.KV_HEADS, K.HEAD_DIM, K.INTER, K.QKV_N
+
+
+@dataclass
+class CausalLMOutput:
+    """Same two fields callers read from transformers' CausalLMOutputWithPast."""
+
+    logits: torch.Tensor
+    past_key_values: "SlotCache | None" = None
+
+
+class SlotCache:
+    """Slotted KV cache: fp16 [layers][K|V][slots][kv heads][s_max][64] plus the per-slot
+    device state of the decode loop (next token, position) and the decode scratch arena.
+
+    Replaces HF DynamicCache as used by the reference (src/model.py:160, src/engine.py:54):
+    a slot stores only real tokens, so left padding never occupies memory and appending a
+    token is a 512-byte write per layer instead of a torch.cat of the whole cache."""
+
+    def __init__(self, n_layers: int, n_slots: int, s_max: int, vocab: int, device, ring: int = 64):
+        self.n_layers, self.n_slots, self.s_max, self.vocab, self.ring = n_layers, n_slots, s_max, vocab, ring
+        self.device = device
+        self.kv = torch.zeros(n_layers, 2, n_slots, KV_HEADS, s_max, HEAD_DIM, dtype=DTYPE, device=device)
+        self.tok = torch.zeros(n_slots, dtype=torch.int32, device=device)
+        self.pos = torch.zeros(n_slots, dtype=torch.int32, device=device)
+        self.out_tokens = torch.zeros(ring, n_slots, dtype=torch.int32, device=device)
+        self.step_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host_len = [0] * n_slots  # host mirror of pos (tokens cached per slot)
+        self.batch_slots: list[int] = []  # slots of the batch rows, for the forward() API
+        self._rows: dict[tuple, torch.Tensor] = {}
+        self._scratch: dict[tuple, torch.Tensor] = {}
+        self._graphs: dict[tuple, int] = {}
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return max((self.host_len[s] for s in self.batch_slots), default=0)
+
+    def rows_tensor(self, slots: list[int]) -> torch.Tensor:
+        key = tuple(slots)
+        t = self._rows.get(key)
+        if t is None:
+            if len(self._rows) > 256:
+                self._rows.clear()
+            t = torch.tensor(slots, dtype=torch.int32, device=self.device)
+            self._rows[key] = t
+        return t
+
+    def scratch(self, batch: int, splits: int) -> torch.Tensor:
+        key = (batch, splits)
+        t = self._scratch.get(key)
+        if t is None:
+            need = K.lib().quic_decode_scratch_bytes(batch, self.vocab, splits)
+            t = torch.zeros(need, dtype=torch.uint8, device=self.device)
+            self._scratch[key] = t
+        return t
+
+    def release_graphs(self) -> None:
+        for g in self._graphs.values():
+            K.lib().quic_graph_destroy(g)
+        self._graphs.clear()
+
+    def __del__(self):
+        try:
+            self.release_graphs()
+        except Exception:
+            pass
+
+
+def _ctx_bucket(n: int) -> int:
+    b = 256
+    while b < n:
+        b *= 2
+    return b
+
+
+class QUICForCausalLM:
+    """The model: W4A16 weights in device layout + the C structs the kernels read."""
+
+    def __init__(self, config: dict, device="cuda"):
+        self.config = config
+        self.device = torch.device(device)
+        self.n_layers = int(config["num_hidden_layers"])
+        self.vocab = int(config["vocab_size"])
+        self.eps = float(config.get("rms_norm_eps", 1e-6))
+        rp = config.get("rope_parameters") or {}
+        self.theta = float(rp.get("rope_theta", config.get("rope_theta", 1000000.0)))
+        self.max_pos = int(config.get("max_position_embeddings", 32768))
+        if (config["hidden_size"], config["intermediate_size"], config["num_attention_heads"],
+                config["num_key_value_heads"]) != (HIDDEN, INTER, HEADS, KV_HEADS):
+            raise RuntimeError("quic_b200 kernels are built for the Qwen2.5-0.5B layer shapes only")
+        self.prefill_backend = "pytorch"
+        self.prefill_all_logits = False
+        self.layers: list[dict] = []
+        self.embed: torch.Tensor | None = None
+        self.final_norm: torch.Tensor | None = None
+        self._c_layers = None
+        self._c_model = None
+        self.default_slots = 8
+        self.default_context = 4096
+
+    # ---- weights -------------------------------------------------------------
+    def load_state(self, weights: dict) -> None:
+        """Consumes a packed checkpoint state dict (names as in the reference's
+        model.safetensors, src/model.py:332-356) and builds the device layout."""
+        dev = self.device
+        prefixes = packed_prefixes(weights)
+        self.embed = weights["model.embed_tokens.weight"].to(dev, DTYPE).contiguous()
+        self.final_norm = weights["model.norm.weight"].to(dev, DTYPE).contiguous()
+        if self.embed.shape != (self.vocab, HIDDEN):
+            raise RuntimeError("weight mismatch: embed_tokens shape")
+        for i in range(self.n_layers):
+            base = f"model.layers.{i}"
+            for name, _, _, _ in LAYER_LINEARS:
+                if f"{base}.{name}" not in prefixes:
+                    raise RuntimeError(f"no W4A16 kernel for layers: ['{base}.{name}'] (unpacked weights)")
+
+            def get(name, key):
+                return weights[f"{base}.{name}.{key}"]
+
+            bias = torch.empty(QKV_N, dtype=DTYPE, device=dev)
+            qkv = K.W4Weight(QKV_N, HIDDEN, dev, bias=bias)
+            off = 0
+            for name, n in (("self_attn.q_proj", 896), ("self_attn.k_proj", 128), ("self_attn.v_proj", 128)):
+                qkv.put(get(name, "weight_packed"), get(name, "weight_scale"), get(name, "weight_zero_point"),
+                        row_offset=off, row_order=K.ROWS_ROPE_PAIRS)
+                b = get(name, "bias").to(dev, DTYPE)
+                # same row order as the weights: (0,32,1,33,...) inside each head
+                bias[off:off + n] = b.view(-1, 2, 32).transpose(1, 2).reshape(-1)
+                off += n
+            o = K.W4Weight(HIDDEN, HIDDEN, dev)
+            o.put(get("self_attn.o_proj", "weight_packed"), get("self_attn.o_proj", "weight_scale"),
+                  get("self_attn.o_proj", "weight_zero_point"))
+            gu = K.W4Weight(2 * INTER, HIDDEN, dev)
+            gu.put(get("mlp.gate_proj", "weight_packed"), get("mlp.gate_proj", "weight_scale"),
+                   get("mlp.gate_proj", "weight_zero_point"), row_offset=0)
+            gu.put(get("mlp.up_proj", "weight_packed"), get("mlp.up_proj", "weight_scale"),
+                   get("mlp.up_proj", "weight_zero_point"), row_offset=INTER)
+            down = K.W4Weight(HIDDEN, INTER, dev)
+            down.put(get("mlp.down_proj", "weight_packed"), get("mlp.down_proj", "weight_scale"),
+                     get("mlp.down_proj", "weight_zero_point"))
+            self.layers.append({
+                "qkv": qkv, "o": o, "gate_up": gu, "down": down,
+                "ln1": weights[f"{base}.input_layernorm.weight"].to(dev, DTYPE).contiguous(),
+                "ln2": weights[f"{base}.post_attention_layernorm.weight"].to(dev, DTYPE).contiguous(),
+            })
+        exponent = torch.arange(0, HEAD_DIM, 2, dtype=torch.float32) / HEAD_DIM
+        inv_freq = (1.0 / (self.theta ** exponent)).to(dev).contiguous()  # src/model.py:82-84
+        self.rope_cos, self.rope_sin = K.rope().init_table(inv_freq, self.max_pos)
+        self._build_structs()
+        torch.cuda.synchronize(dev)
+
+    def _build_structs(self) -> None:
+        arr = (K.Layer * self.n_layers)()
+        for i, L in enumerate(self.layers):
+            arr[i].qkv, arr[i].o = L["qkv"].struct(), L["o"].struct()
+            arr[i].gate_up, arr[i].down = L["gate_up"].struct(), L["down"].struct()
+            arr[i].ln1, arr[i].ln2 = K.ptr(L["ln1"]), K.ptr(L["ln2"])
+        self._c_layers = arr
+        self._c_model = K.Model(self.n_layers, self.vocab, self.eps, self.max_pos, arr, K.ptr(self.embed),
+                                K.ptr(self.final_norm), K.ptr(self.rope_cos), K.ptr(self.rope_sin))
+
+    def weight_bytes(self) -> int:
+        """Algorithmic bytes one decode step reads from the weights (all layers + lm_head)."""
+        per_layer = sum(L[k].weight_bytes for L in self.layers[:1] for k in ("qkv", "o", "gate_up", "down"))
+        per_layer += QKV_N * 2 + 2 * HIDDEN * 2
+        return per_layer * self.n_layers + self.vocab * HIDDEN * 2 + HIDDEN * 2
+
+    def new_cache(self, n_slots: int | None = None, s_max: int | None = None) -> SlotCache:
+        return SlotCache(self.n_layers, n_slots or self.default_slots, s_max or self.default_context,
+                         self.vocab, self.device)
+
+    def eval(self):
+        return self
+
+    def __call__(self, *args, **kwargs):
+        return self.forward(*args, **kwargs)
+
+    # ---- decode ----------------------------------------------------------------
+    def _decode_struct(self, cache: SlotCache, batch: int, ctx: int, logits: torch.Tensor | None):
+        splits = K.lib().quic_attn_pick_splits(batch, ctx)
+        rows = cache._rows.setdefault(("buf", batch), torch.zeros(batch, dtype=torch.int32, device=self.device))
+        d = K.Decode(K.ptr(cache.kv), cache.n_slots, cache.s_max, K.ptr(cache.tok), K.ptr(cache.pos),
+                     K.ptr(rows), batch, K.ptr(cache.out_tokens), cache.ring, K.ptr(cache.step_counter),
+                     K.ptr(logits), K.ptr(cache.scratch(batch, splits)), splits, ctx)
+        return d, rows
+
+    def _graph(self, cache: SlotCache, batch: int, ctx: int, steps: int, logits: torch.Tensor | None):
+        key = (batch, ctx, steps, K.ptr(logits))
+        g = cache._graphs.get(key)
+        d, rows = self._decode_struct(cache, batch, ctx, logits)
+        if g is None:
+            if not hasattr(self, "_capture_stream"):
+                self._capture_stream = torch.cuda.Stream(device=self.device)
+            out = C.c_void_p()
+            K.check(K.lib().quic_decode_graph_create(C.byref(self._c_model), C.byref(d), steps,
+                                                     self._capture_stream.cuda_stream, C.byref(out)),
+                    "decode_graph_create")
+            g = out.value
+            cache._graphs[key] = g
+        return g, rows
+
+    def launches_per_step(self) -> int:
+        return 5 * self.n_layers + 1
+
+    def decode_async(self, cache: SlotCache, slots: list[int], steps: int,
+                     logits: torch.Tensor | None = None) -> int:
+        """Enqueues ``steps`` greedy decode steps for the rows ``slots`` (no host sync).
+        Returns the ring index of the first generated token row in ``cache.out_tokens``."""
+        if not slots:
+            raise RuntimeError("decode: empty batch")
+        if steps < 1 or steps > cache.ring:
+            raise RuntimeError(f"decode: steps must be in 1..{cache.ring}")
+        longest = max(cache.host_len[s] for s in slots)
+        if longest + steps > cache.s_max or longest + steps > self.max_pos:
+            raise RuntimeError("decode: context would exceed the KV slot length")
+        ctx = min(_ctx_bucket(longest + steps), cache.s_max)
+        g, rows = self._graph(cache, len(slots), ctx, steps, logits)
+        want = cache.rows_tensor(slots)
+        if getattr(cache, "_rows_loaded", {}).get(len(slots)) is not want:
+            rows.copy_(want)
+            cache.__dict__.setdefault("_rows_loaded", {})[len(slots)] = want
+        first = getattr(cache, "host_steps", 0)
+        K.check(K.lib().quic_graph_launch(g, K.stream_ptr()), "graph_launch")
+        cache.host_steps = first + steps
+        for s in slots:
+            cache.host_len[s] += steps
+        return first % cache.ring
+
+    def decode(self, cache: SlotCache, slots: list[int], steps: int) -> list[list[int]]:
+        """``steps`` greedy tokens for every row: result[i][j] is token j of slots[i]."""
+        first = self.decode_async(cache, slots, steps)
+        idx = (torch.arange(steps, device=self.device) + first) % cache.ring
+        toks = cache.out_tokens.index_select(0, idx).index_select(1, cache.rows_tensor(slots).long())
+        return toks.t().cpu().tolist()
+
+    # ---- prefill -----------------------------------------------------------------
+    @torch.inference_mode()
+    def prefill(self, cache: SlotCache, slots: list[int], prompts: list[torch.Tensor],
+                all_logits: bool = False):
+        """Runs the prompts (1-D int64 tensors) through the model, fills their KV slots and
+        returns (first greedy token per prompt [n] int64, logits).  Linear layers run the
+        W4A16 kernels at M = total prompt tokens; attention is torch SDPA per sequence, as the
+        reference's default prefill backend (kernels/flash_attn_prefill_pytorch.py:10)."""
+        dev = self.device
+        lens = [int(p.numel()) for p in prompts]
+        if any(n < 1 for n in lens):
+            raise RuntimeError("prefill: empty prompt")
+        if any(n > cache.s_max or n > self.max_pos for n in lens):
+            raise RuntimeError("prefill: prompt longer than the KV slot")
+        ids = torch.cat([p.reshape(-1) for p in prompts]).to(dev, torch.long)
+        bounds = [0]
+        for n in lens:
+            bounds.append(bounds[-1] + n)
+        pos = torch.cat([torch.arange(n, device=dev) for n in lens])
+        cos, sin = self.rope_cos[pos].contiguous(), self.rope_sin[pos].contiguous()
+        T = ids.numel()
+        h = self.embed[ids]
+        rms, lin = K.rmsnorm().forward, K.w4a16_linear
+        xn = rms(h, self.layers[0]["ln1"], self.eps)
+        for li, L in enumerate(self.layers):
+            qkv = lin(L["qkv"], xn)
+            # stored column order inside each head is (pair, half) -> natural dim = pair + 32*half
+            qkv = qkv.view(T, 18, 32, 2).transpose(2, 3).reshape(T, 18, HEAD_DIM)
+            qk = qkv[:, :16].transpose(0, 1).contiguous().unsqueeze(0)  # [1,16,T,64]
+            qk = K.rope().forward(qk, cos, sin)[0]
+            q, k, v = qk[:14], qk[14:16], qkv[:, 16:18].transpose(0, 1)
+            attn = torch.empty(T, HEADS * HEAD_DIM, dtype=DTYPE, device=dev)
+            for i, s in enumerate(slots):
+                a, b = bounds[i], bounds[i + 1]
+                cache.kv[li, 0, s, :, : b - a] = k[:, a:b]
+                cache.kv[li, 1, s, :, : b - a] = v[:, a:b]
+                o = F.scaled_dot_product_attention(q[None, :, a:b], k[None, :, a:b], v[None, :, a:b],
+                                                   is_causal=True, scale=HEAD_DIM ** -0.5, enable_gqa=True)
+                attn[a:b] = o[0].transpose(0, 1).reshape(b - a, -1)
+            o = lin(L["o"], attn)
+            xn, h = rms(o, L["ln2"], self.eps, residual=h)
+            gu = lin(L["gate_up"], xn)
+            act = K.swiglu().forward(gu[:, :INTER].contiguous(), gu[:, INTER:].contiguous())
+            d = lin(L["down"], act)
+            nxt = self.layers[li + 1]["ln1"] if li + 1 < self.n_layers else self.final_norm
+            xn, h = rms(d, nxt, self.eps, residual=h)
+        last = torch.tensor([b - 1 for b in bounds[1:]], device=dev)
+        rows = xn if all_logits else xn[last]
+        logits = K.gemm().forward(rows, self.embed)
+        picked = logits[last] if all_logits else logits
+        first = K.sampler().forward(picked.unsqueeze(1)).view(-1)
+        st = torch.tensor(slots, device=dev, dtype=torch.long)
+        cache.tok[st] = first.to(torch.int32)
+        cache.pos[st] = torch.tensor(lens, device=dev, dtype=torch.int32)
+        for s, n in zip(slots, lens):
+            cache.host_len[s] = n
+        return first, logits
+
+    # ---- reference-shaped forward ------------------------------------------------------
+    @torch.inference_mode()
+    def forward(self, input_ids: torch.Tensor, past_key_values: SlotCache | None = None,
+                attention_mask: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
+                use_cache: bool = True) -> CausalLMOutput:
+        """Same contract as the reference's forward (src/model.py:272-303): ``input_ids``
+        [B, T]; ``attention_mask`` [B, kv_len] with zeros on the LEFT padding; returns fp16
+        logits and the cache.  ``position_ids`` are implied by the cache (#real tokens so
+        far, exactly what the reference's engine passes, src/engine.py:93-95)."""
+        if input_ids.dim() != 2:
+            raise ValueError("input_ids must be [batch, seq_len]")
+        batch, seq_len = input_ids.shape
+        cache = past_key_values
+        if cache is None:
+            cache = self.new_cache(n_slots=max(batch, self.default_slots))
+        if not cache.batch_slots:
+            cache.batch_slots = list(range(batch))
+        if len(cache.batch_slots) != batch:
+            raise ValueError(f"cache holds {len(cache.batch_slots)} rows, input has {batch}")
+        past_len = cache.get_seq_length()
+        kv_len = past_len + seq_len
+        input_ids = input_ids.to(self.device)
+        if seq_len == 1:
+            if any(cache.host_len[s] == 0 for s in cache.batch_slots) and attention_mask is None:
+                pass  # a one-token prompt: handled by the decode kernels as position 0
+            logits = cache.__dict__.setdefault("_logits", {}).get(batch)
+            if logits is None:
+                logits = torch.empty(batch, self.vocab, dtype=DTYPE, device=self.device)
+                cache._logits[batch] = logits
+            st = cache.rows_tensor(cache.batch_slots).long()
+            cache.tok[st] = input_ids.view(-1).to(torch.int32)
+            self.decode_async(cache, cache.batch_slots, 1, logits=logits)
+            return CausalLMOutput(logits=logits.view(batch, 1, self.vocab),
+                                  past_key_values=cache if use_cache else None)
+        if past_len != 0:
+            raise RuntimeError("forward: multi-token input on a non-empty cache is not supported")
+        if attention_mask is not None:
+            if tuple(attention_mask.shape) != (batch, kv_len):
+                raise ValueError(f"attention_mask {tuple(attention_mask.shape)} does not match "
+                                 f"(batch={batch}, kv_len={kv_len})")
+            lens = attention_mask.to(torch.long).sum(dim=1).tolist()
+        else:
+            lens = [seq_len] * batch
+        prompts = [input_ids[b, seq_len - n:] for b, n in enumerate(lens)]
+        want_all = self.prefill_all_logits
+        _, logits = self.prefill(cache, cache.batch_slots, prompts, all_logits=want_all)
+        if want_all:
+            full = torch.zeros(batch, seq_len, self.vocab, dtype=DTYPE, device=self.device)
+            a = 0
+            for b, n in enumerate(lens):
+                full[b, seq_len - n:] = logits[a:a + n]
+                a += n
+            logits = full
+        else:
+            logits = logits.view(batch, 1, self.vocab)
+        return CausalLMOutput(logits=logits, past_key_values=cache if use_cache else None)
+
+
+# ---- loading ---------------------------------------------------------------------------
+def from_state_dict(weights: dict, config: dict, device="cuda") -> QUICForCausalLM:
+    if not torch.cuda.is_available():
+        raise RuntimeError("quic_b200 needs a CUDA device (no CPU path)")
+    model = QUICForCausalLM(config, device=device)
+    model.load_state(weights)
+    return model
+
+
+def load(path: str, prefill_backend: str = "pytorch", use_marlin: bool = False, use_machete: bool = False,
+         tokenizer_path: str | None = None):
+    """Same signature and return value as the reference's ``model.load`` (src/model.py:306).
+    ``use_marlin`` / ``use_machete`` are accepted for compatibility; every packed layer runs
+    the W4A16 kernels of this package.  The tokenizer is loaded when its files exist."""
+    from safetensors.torch import load_file
+
+    path = os.path.expanduser(path)
+    with open(os.path.join(path, "config.json")) as handle:
+        config = json.load(handle)
+    weights = load_file(os.path.join(path, "model.safetensors"))
+    if not packed_prefixes(weights):
+        raise RuntimeError("quic_b200 runs the quantised (quic_quant) path only: no packed tensors found")
+    group = detect_group_size(config)
+    if group != K.GROUP:
+        raise RuntimeError(f"quic_b200 kernels are built for group size {K.GROUP}, checkpoint has {group}")
+    model = from_state_dict(weights, config)
+    if prefill_backend is not None:
+        model.prefill_backend = prefill_backend
+    tokenizer = None
+    tok_dir = tokenizer_path or path
+    if os.path.exists(os.path.join(tok_dir, "tokenizer.json")):
+        from transformers import AutoTokenizer
+
+        tokenizer = AutoTokenizer.from_pretrained(tok_dir)
+    return model, tokenizer

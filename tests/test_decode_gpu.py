@@ -1,0 +1,85 @@
+"""GPU parity of the fused decode step against the CPU oracle and the reference's
+dequantised-weight Hugging Face path."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+# tolerance of the acceptance gate: logits within rtol 2e-2 / atol 5e-2 per step
+RTOL, ATOL = 2e-2, 5e-2
+
+
+def _close(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return bool(((a - b).abs() <= ATOL + RTOL * b.abs()).all()), (a - b).abs().max().item()
+
+
+def test_token_by_token_matches_oracle(tiny_model):
+    """Prompt and generation both through the fused decode step (positions 0..n)."""
+    net, ref, _, _ = tiny_model
+    prompt = [11, 7, 1999, 42, 0, 512, 77, 1023]
+    ref_tokens, ref_logits = ref.greedy(prompt, 6)
+    cache = net.new_cache(n_slots=4, s_max=256)
+    cache.batch_slots = [2]
+    logits = None
+    for t in prompt:
+        logits = net(torch.tensor([[t]]), past_key_values=cache).logits
+    got_tokens, got_logits = [], []
+    for _ in range(6):
+        got_logits.append(logits[0, 0].clone())
+        nxt = logits[:, -1:, :].argmax(dim=-1)
+        got_tokens.append(int(nxt))
+        logits = net(nxt, past_key_values=cache).logits
+    ok, err = _close(torch.stack(got_logits), ref_logits)
+    assert ok, err
+    assert got_tokens == ref_tokens
+
+
+def test_prefill_then_graph_decode_matches_oracle(tiny_model):
+    net, ref, _, _ = tiny_model
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5, 8, 9, 7, 9]
+    ref_tokens, ref_logits = ref.greedy(prompt, 9)
+    cache = net.new_cache(n_slots=4, s_max=256)
+    first, logits = net.prefill(cache, [3], [torch.tensor(prompt)])
+    ok, err = _close(logits[0], ref_logits[0])
+    assert ok, err
+    tokens = [int(first[0])] + net.decode(cache, [3], 8)[0]
+    assert tokens == ref_tokens
+
+
+def test_batched_rows_are_independent(tiny_model):
+    """Rows of different lengths in one batch give what each gives alone (left-padding
+    semantics of the reference's batch: padded keys never contribute)."""
+    net, ref, _, _ = tiny_model
+    prompts = [[5, 6, 7], [100, 200, 300, 400, 500, 600, 700], [9], [1, 2], [42] * 12]
+    want = [ref.greedy(p, 5)[0] for p in prompts]
+    cache = net.new_cache(n_slots=8, s_max=128)
+    slots = [6, 0, 3, 7, 1]
+    first, _ = net.prefill(cache, slots, [torch.tensor(p) for p in prompts])
+    rest = net.decode(cache, slots, 4)
+    got = [[int(first[i])] + rest[i] for i in range(len(prompts))]
+    assert got == want
+
+
+def test_golden_hf_quant_logits(tiny_model):
+    """Against logits the reference's own model_hf.load produced (tests/golden/make_golden.py)."""
+    net, _, _, _ = tiny_model
+    g = np.load(os.path.join(GOLDEN, "hf_quant_logits.npz"))
+    assert json.loads(str(g["model"])) == {"n_layers": 2, "vocab": 2048, "seed": 1234}
+    prompt, tokens = g["prompt"].tolist(), g["tokens"].tolist()
+    cache = net.new_cache(n_slots=2, s_max=128)
+    cache.batch_slots = [0]
+    out = net(torch.tensor([prompt]), past_key_values=cache)
+    got = [out.logits[0, -1].clone()]
+    for t in tokens[:-1]:  # teacher-forced with the reference's tokens
+        out = net(torch.tensor([[t]]), past_key_values=cache)
+        got.append(out.logits[0, -1].clone())
+    got = torch.stack(got)
+    ok, err = _close(got, torch.from_numpy(g["logits"]))
+    assert ok, err
+    assert got.argmax(-1).tolist() == tokens
