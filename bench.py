@@ -1,0 +1,314 @@
+"""Decode-throughput benchmark of the W4A16 path (and the reference's CPU arm).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload: the full W4A16 decode of the Qwen2.5-0.5B architecture at batch 1 — seeded
+synthetic weights (real weights cannot be downloaded), a 512-token random prompt in an
+fp16 KV slot, greedy decode of 256 tokens.  One *step* is one such 256-token decode.
+``value`` is decode tokens/s with everything resident in HBM (tokens chained on the device
+by CUDA-graph launches); ``e2e`` is the same metric through the per-token public call with
+the token id travelling host -> device and the sampled id device -> host every token, as
+the reference's own generation loop does.  With N > 1 (launched by torch.distributed.run)
+every rank is an independent replica with its own weights and request (weak scaling, no
+collective on the data path).
+
+``--impl reference`` times the reference's Hugging Face eager fp32 path on the host cores
+on a bounded sample of the same workload (oracle/hf_ref.py; the reference project has no
+CPU implementation of its own kernels).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+PROMPT_LEN, GEN_TOKENS, BURST = 512, 256, 64
+METRIC, UNIT = "decode_tokens_per_s_batch1_w4a16", "tokens/s"
+CONFIG = {
+    "workload": "full W4A16 decode, Qwen2.5-0.5B architecture, batch 1, 512-token prompt, 256 greedy tokens",
+    "layers": 24, "vocab": 151936, "kv_cache": "fp16 slots", "weights": "int4 group 128 + fp16 lm_head",
+    "l2_policy": "inputs larger than L2: each token streams 466 MB of weights and KV through a 126 MB L2",
+}
+
+
+def peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            return float(json.load(handle)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        clocks, reasons, max_mhz = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            try:
+                clocks.append(float(row[0]))
+                max_mhz = float(row[1])
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(names, row[3:7]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(clocks)[len(clocks) // 2:] if clocks else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max_mhz,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def build_model(device: str):
+    entry.load_package()
+    from quic_cu_b200 import model as qmodel
+    from quic_cu_b200.checkpoint import qwen_config_dict, synthetic_checkpoint
+
+    state = synthetic_checkpoint(n_layers=24, vocab=151936, seed=0)
+    net = qmodel.from_state_dict(state, qwen_config_dict(24, 151936), device=device)
+    return net, state
+
+
+def cpu_baseline(state, threads: int | None = None, gen: int = 16, repeats: int = 1, warmup: int = 0):
+    """The reference's HF eager fp32 path on the host cores: the 512-token prompt is prefilled
+    untimed, then ``gen`` greedy decode forwards are timed (run.py:49-61's loop)."""
+    from oracle import hf_ref
+    from quic_cu_b200.checkpoint import qwen_config_dict
+
+    if threads:
+        torch.set_num_threads(threads)
+    model = hf_ref.build_hf_model(state, qwen_config_dict(24, 151936), dtype=torch.float32, device="cpu")
+    gen_ids = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, 151936, (1, PROMPT_LEN), generator=gen_ids)
+    times = []
+    with torch.inference_mode():
+        for it in range(warmup + repeats):
+            out = model(prompt, use_cache=True)
+            cache, nxt = out.past_key_values, out.logits[:, -1:, :].argmax(-1)
+            t0 = time.perf_counter()
+            for _ in range(gen):
+                out = model(nxt, past_key_values=cache, use_cache=True)
+                nxt = out.logits[:, -1:, :].argmax(-1)
+            if it >= warmup:
+                times.append(time.perf_counter() - t0)
+    per_step = sum(times) / len(times)
+    return {"value": gen / per_step, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"HF Qwen2ForCausalLM eager fp32, same synthetic weights, 512-token prompt prefilled "
+                      f"untimed, {gen} greedy decode forwards timed x{len(times)}"}, per_step
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    entry.load_package()
+    from quic_cu_b200.checkpoint import synthetic_checkpoint
+
+    state = synthetic_checkpoint(n_layers=24, vocab=151936, seed=0)
+    gen = 16
+    base, per_step = cpu_baseline(state, threads=os.cpu_count(), gen=gen, repeats=args.steps,
+                                  warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": CONFIG,
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_gpu(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the decode path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = f"cuda:{local}"
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(device))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    entry.load_package()
+    from quic_cu_b200 import kernels as K
+
+    net, state = build_model(device)
+    cache = net.new_cache(n_slots=1, s_max=1024)
+    gen_ids = torch.Generator().manual_seed(rank)  # every replica serves its own request
+    prompt = torch.randint(0, 151936, (PROMPT_LEN,), generator=gen_ids)
+    first, _ = net.prefill(cache, [0], [prompt])
+    tok0, pos0 = cache.tok.clone(), cache.pos.clone()
+    torch.cuda.synchronize()
+
+    def reset():
+        cache.tok.copy_(tok0)
+        cache.pos.copy_(pos0)
+        cache.host_len[0] = PROMPT_LEN
+
+    def one_step():
+        reset()
+        for _ in range(GEN_TOKENS // BURST):
+            net.decode_async(cache, [0], BURST)
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        one_step()
+    end.record()
+    barrier()
+    elapsed_ms = start.elapsed_time(end)
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    tokens = args.steps * GEN_TOKENS
+    value = world * tokens / (elapsed_ms / 1e3)
+
+    # ---- end to end: one public decode call per token, token id host <-> device every token
+    pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+    e2e_tokens = GEN_TOKENS
+    reset()
+    pinned[0] = int(first[0])
+    for _ in range(8):
+        cache.tok.copy_(pinned, non_blocking=True)
+        pinned[0] = net.decode(cache, [0], 1)[0][0]
+    reset()
+    pinned[0] = int(first[0])
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_tokens):
+        cache.tok.copy_(pinned, non_blocking=True)      # H2D: the token to feed (pinned host memory)
+        pinned[0] = net.decode(cache, [0], 1)[0][0]      # D2H: the sampled token
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": world * e2e_tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 4 * GEN_TOKENS,
+           "d2h_bytes_per_step": 4 * GEN_TOKENS,
+           "note": "per 256-token step: 256 public decode calls, each with a 4-byte token id H2D from "
+                   "pinned memory and a 4-byte sampled id D2H"}
+
+    # ---- roofline of the dominant kernel (tied lm_head + argmax: 58% of the bytes of a token)
+    peak, peak_kind = peaks()
+    x = torch.randn(1, 896, device=device, dtype=torch.float16)
+    for _ in range(3):
+        K.lm_head_argmax(x, net.embed, net.final_norm, net.eps)
+    reps = 50
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    k0.record()
+    for _ in range(reps):
+        K.lm_head_argmax(x, net.embed, net.final_norm, net.eps)
+    k1.record()
+    torch.cuda.synchronize()
+    lm_us = k0.elapsed_time(k1) * 1e3 / reps
+    lm_bytes = 151936 * 896 * 2 + 896 * 4
+    achieved = lm_bytes / (lm_us * 1e-6) / 1e9
+    roofline = {"bound": "hbm", "kernel": "lm_head_kernel<1> (tied fp16 lm_head GEMV + final RMSNorm + argmax)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_kind": f"of {peak_kind}", "us_per_launch": lm_us, "algorithmic_bytes": lm_bytes,
+                "traffic": LM_HEAD_TRAFFIC_BYTES,
+                "timing": f"{reps} back-to-back launches between CUDA events on the launching stream; the "
+                          "272 MB table exceeds L2"}
+    mean_ctx = PROMPT_LEN + GEN_TOKENS / 2
+    step_bytes = net.weight_bytes() + 12288 * (mean_ctx + 1)
+    us_per_token = elapsed_ms * 1e3 / tokens
+    step_gbs = step_bytes / (us_per_token * 1e-6) / 1e9
+    roofline_step = {"bound": "hbm", "scope": "whole decode step (121 kernels)", "achieved": step_gbs,
+                     "peak": peak, "unit": "GB/s", "frac": step_gbs / peak, "us_per_token": us_per_token,
+                     "algorithmic_bytes": step_bytes}
+
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate",
+        "data": "synthetic", "config": dict(CONFIG, parallelism=f"{world} independent replica(s)"),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * GEN_TOKENS * net.launches_per_step(),
+        "roofline": roofline, "roofline_step": roofline_step,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        del net, cache
+        base, _ = cpu_baseline(state, threads=os.cpu_count(), gen=16, repeats=1, warmup=0)
+        line["cpu_baseline"] = base
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one lm_head_kernel<1> launch at vocab 151936,
+# from the ncu capture summarised in profiles/ (None until a capture exists).
+LM_HEAD_TRAFFIC_BYTES = None
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="quic_b200", choices=["quic_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

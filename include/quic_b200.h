@@ -139,6 +139,20 @@ int quic_argmax(const void *logits_f16, int32_t b, int32_t v, int64_t *out,
 int quic_gemm_f16(const void *x_f16, const void *w_f16, const void *bias_f16,
                   void *y_f16, int32_t m, int32_t n, int32_t k, void *stream);
 
+/* Tied lm_head fused with (optional) final RMSNorm and greedy argmax:
+ * logits[b,:] = norm(x[b,:]) · embed^T, out[b] = argmax (ties -> lowest index, on
+ * the fp16-rounded logits).  Replaces, as one kernel, the final norm
+ * (src/model.py:298), the cuBLAS lm_head (src/model.py:301 -> kernels/cuda/gemm.cu:36)
+ * and torch.argmax (src/engine.py:104).  x fp16 [B,896]; norm_w fp16 [896] or NULL
+ * (x already normalised); embed fp16 [vocab,896], vocab even; logits fp16
+ * [B,vocab] or NULL; out int64 [B] or NULL; scratch >=
+ * quic_lm_head_scratch_bytes(b, vocab) bytes whose first 256 bytes are zero
+ * before the first call (the kernel leaves them zero). */
+int quic_lm_head_argmax(const void *x_f16, const void *norm_w_f16, float eps,
+                        const void *embed_f16, int32_t vocab, int32_t b,
+                        void *logits_f16, int64_t *out, void *scratch, void *stream);
+int64_t quic_lm_head_scratch_bytes(int32_t b, int32_t vocab);
+
 /* Split-K GQA decode attention.  Replaces flash_attn_decode.forward
  * (kernels/cuda/flash_attn_decode.cu:133): q fp16 [B,14,64]; K and V fp16 with
  * explicit element strides (batch, kv head; tokens are 64 contiguous halves

@@ -301,3 +301,43 @@ cudaError_t launch_lm_head(const LmHeadArgs& a, int grid, cudaStream_t s, bool p
 }
 
 }  // namespace quic
+
+using namespace quic;
+
+extern "C" int64_t quic_lm_head_scratch_bytes(int32_t b, int32_t vocab) {
+  if (b < 1 || vocab < 2) return 0;
+  const int64_t per = ((int64_t)b * lm_head_grid(vocab) * 4 + 255) / 256 * 256;
+  return 256 + 2 * per;
+}
+
+extern "C" int quic_lm_head_argmax(const void* x, const void* norm_w, float eps, const void* embed,
+                                   int32_t vocab, int32_t b, void* logits, int64_t* out,
+                                   void* scratch, void* stream) {
+  QUIC_REQUIRE(x && embed && scratch, QUIC_E_ARG, "lm_head_argmax: null tensor");
+  QUIC_REQUIRE(b >= 1 && b <= 8 * 65535 && vocab >= 2 && vocab % 2 == 0, QUIC_E_SHAPE,
+               "lm_head_argmax: batch >= 1 and an even vocabulary are required");
+  QUIC_REQUIRE(((uintptr_t)x % 8 == 0) && ((uintptr_t)embed % 16 == 0), QUIC_E_ARG,
+               "lm_head_argmax: x must be 8-byte and the table 16-byte aligned");
+  const int grid = lm_head_grid(vocab);
+  const int64_t per = ((int64_t)b * grid * 4 + 255) / 256 * 256;
+  char* base = static_cast<char*>(scratch);
+  LmHeadArgs a = {};
+  a.embed = (const half*)embed;
+  a.batch = b;
+  a.vocab = vocab;
+  a.eps = eps;
+  a.logits = (half*)logits;
+  a.counter = reinterpret_cast<int32_t*>(base);
+  a.best_val = reinterpret_cast<float*>(base + 256);
+  a.best_idx = reinterpret_cast<int32_t*>(base + 256 + per);
+  a.argmax_out = out;
+  a.ring = 1;
+  if (norm_w != nullptr) {
+    a.ln = (const half*)norm_w;
+    a.xres_in = (const half*)x;
+  } else {
+    a.x_normed = (const half*)x;
+  }
+  QUIC_CUDA(launch_lm_head(a, grid, (cudaStream_t)stream, false));
+  return QUIC_OK;
+}

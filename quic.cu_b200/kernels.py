@@ -24,6 +24,8 @@ LIB_PATH = os.path.join(_HERE, "libquic_b200.so")
 
 HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, GROUP, QKV_N = 896, 14, 2, 64, 4864, 128, 1152
 ROWS_NATURAL, ROWS_ROPE_PAIRS = 0, 1
+# M >= 16 runs the tcgen05 GEMM when True; the dequant GEMV in row chunks otherwise.
+TENSOR_PATH = False
 
 
 class W4(C.Structure):
@@ -104,6 +106,8 @@ SIGNATURES = {
     "quic_swiglu": (C.c_int, [_P, _P, _P, _I32, _P]),
     "quic_argmax": (C.c_int, [_P, _I32, _I32, _P, _P]),
     "quic_gemm_f16": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P]),
+    "quic_lm_head_argmax": (C.c_int, [_P, _P, _F, _P, _I32, _I32, _P, _P, _P, _P]),
+    "quic_lm_head_scratch_bytes": (_I64, [_I32, _I32]),
     "quic_attn_decode": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _I32, _F, _P, _I32, _I32, _P, _P]),
     "quic_attn_pick_splits": (_I32, [_I32, _I32]),
     "quic_attn_scratch_bytes": (_I64, [_I32, _I32]),
@@ -222,7 +226,7 @@ def w4a16_linear(w: W4Weight, x: torch.Tensor, use_tensor: bool | None = None) -
     m = x2.shape[0]
     y = torch.empty(m, w.size_n, dtype=torch.float16, device=x.device)
     if use_tensor is None:
-        use_tensor = m >= 16
+        use_tensor = TENSOR_PATH and m >= 16
     s = w.struct()
     check(lib().quic_w4a16_linear(ptr(x2), C.byref(s), ptr(y), m, int(bool(use_tensor)),
                                   ptr(w.workspace(m)), stream_ptr()), "w4a16_linear")
@@ -328,6 +332,28 @@ def _gemm_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = 
 
 
 _attn_scratch: dict = {}
+_lm_scratch: dict = {}
+
+
+def lm_head_argmax(x: torch.Tensor, embed: torch.Tensor, norm_weight: torch.Tensor | None = None,
+                   eps: float = 1e-6, want_logits: bool = False):
+    """Final norm (optional) + tied lm_head + greedy argmax in one kernel.
+    x fp16 [B, 896] -> (tokens int64 [B], logits fp16 [B, V] or None)."""
+    _need_cuda(x, embed, norm_weight)
+    _need_half(x, embed, norm_weight)
+    x = x.contiguous().view(-1, HIDDEN)
+    b, vocab = x.shape[0], embed.shape[0]
+    need = lib().quic_lm_head_scratch_bytes(b, vocab)
+    key = (x.device.index, torch.cuda.current_stream().cuda_stream)
+    scratch = _lm_scratch.get(key)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=x.device)
+        _lm_scratch[key] = scratch
+    out = torch.empty(b, dtype=torch.int64, device=x.device)
+    logits = torch.empty(b, vocab, dtype=torch.float16, device=x.device) if want_logits else None
+    check(lib().quic_lm_head_argmax(ptr(x), ptr(norm_weight), float(eps), ptr(embed), vocab, b,
+                                    ptr(logits), ptr(out), ptr(scratch), stream_ptr()), "lm_head_argmax")
+    return out, logits
 
 
 def _flash_attn_decode_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,

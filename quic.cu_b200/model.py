@@ -310,10 +310,11 @@ class QUICForCausalLM:
             nxt = self.layers[li + 1]["ln1"] if li + 1 < self.n_layers else self.final_norm
             xn, h = rms(d, nxt, self.eps, residual=h)
         last = torch.tensor([b - 1 for b in bounds[1:]], device=dev)
-        rows = xn if all_logits else xn[last]
-        logits = K.gemm().forward(rows, self.embed)
-        picked = logits[last] if all_logits else logits
-        first = K.sampler().forward(picked.unsqueeze(1)).view(-1)
+        if all_logits:
+            logits = K.gemm().forward(xn, self.embed)
+            first = K.sampler().forward(logits[last].unsqueeze(1)).view(-1)
+        else:  # xn is already normalised: fused lm_head + argmax on the last positions
+            first, logits = K.lm_head_argmax(xn[last], self.embed, want_logits=True)
         st = torch.tensor(slots, device=dev, dtype=torch.long)
         cache.tok[st] = first.to(torch.int32)
         cache.pos[st] = torch.tensor(lens, device=dev, dtype=torch.int32)

@@ -1,0 +1,75 @@
+"""Split-K GQA decode attention against SDPA (the reference's recipe,
+tests/test_attention.py:57-82: same shapes, pads, seed rule and tolerance) and the oracle."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import quic_ref
+
+pytestmark = pytest.mark.gpu
+BATCH, HEADS, HEAD_DIM = 4, 14, 64
+SCALE = HEAD_DIM ** -0.5
+ATOL = 1e-2
+
+
+def _sdpa(q, k, v, pad_lens):
+    kv_len = k.shape[2]
+    pos = torch.arange(kv_len, device=q.device)
+    not_pad = pos[None, :] >= pad_lens[:, None]
+    mask = not_pad[:, None, None, :].expand(q.shape[0], HEADS, 1, kv_len)
+    return F.scaled_dot_product_attention(q.float(), k.repeat_interleave(7, dim=1).float(),
+                                          v.repeat_interleave(7, dim=1).float(), attn_mask=mask,
+                                          scale=SCALE).to(q.dtype)
+
+
+@pytest.mark.parametrize("kv_len", [16, 64, 256])
+def test_decode_matches_sdpa_with_left_padding(kv_len):
+    from quic_cu_b200 import kernels as K
+
+    generator = torch.Generator(device="cuda").manual_seed(kv_len)
+    q = torch.randn((BATCH, HEADS, 1, HEAD_DIM), device="cuda", generator=generator).half()
+    k = torch.randn((BATCH, 2, kv_len, HEAD_DIM), device="cuda", generator=generator).half()
+    v = torch.randn((BATCH, 2, kv_len, HEAD_DIM), device="cuda", generator=generator).half()
+    pad_lens = torch.tensor([0, 2, kv_len // 4, kv_len - 1], device="cuda", dtype=torch.int32)
+    out = K.flash_attn_decode().forward(q, k, v, SCALE, pad_lens)
+    expected = _sdpa(q, k, v, pad_lens)
+    assert out.shape == (BATCH, HEADS, 1, HEAD_DIM)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.float(), expected.float(), atol=ATOL)
+
+
+@pytest.mark.parametrize("batch,kv_len,splits", [(1, 1, 0), (1, 33, 1), (2, 300, 3), (3, 1000, 0),
+                                                  (1, 8192, 0), (5, 2049, 7), (16, 1024, 0)])
+def test_decode_split_merge_and_ragged(batch, kv_len, splits):
+    """Every split count gives the same answer; pads uniform in [0, S/4]; second call re-uses
+    the scratch (arrival counters must have been re-armed)."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(batch * 100003 + kv_len)
+    q = torch.randn((batch, HEADS, 1, HEAD_DIM), device="cuda", generator=g).half()
+    k = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    v = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    pads = torch.randint(0, kv_len // 4 + 1, (batch,), device="cuda", generator=g).int()
+    expected = _sdpa(q, k, v, pads)
+    for _ in range(2):
+        out = K.flash_attn_decode().forward(q, k, v, SCALE, pads, splits=splits)
+        assert torch.allclose(out.float(), expected.float(), atol=ATOL)
+    out_nopad = K.flash_attn_decode().forward(q, k, v)  # default scale, no pads
+    assert torch.allclose(out_nopad.float(), _sdpa(q, k, v, torch.zeros_like(pads)).float(), atol=ATOL)
+
+
+def test_all_masked_row_gives_zeros_and_oracle_agrees():
+    """flash_attn_decode.cu:118-121: a row whose every key is padding yields 0."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn((3, HEADS, 1, HEAD_DIM), device="cuda", generator=g).half()
+    k = torch.randn((3, 2, 700, HEAD_DIM), device="cuda", generator=g).half()
+    v = torch.randn((3, 2, 700, HEAD_DIM), device="cuda", generator=g).half()
+    pads = torch.tensor([700, 0, 699], device="cuda", dtype=torch.int32)
+    for splits in (1, 4):
+        out = K.flash_attn_decode().forward(q, k, v, SCALE, pads, splits=splits)
+        assert torch.count_nonzero(out[0]) == 0
+        want = quic_ref.attn_decode(q[:, :, 0].cpu(), k.cpu(), v.cpu(), SCALE, start=pads.cpu())
+        assert torch.allclose(out[:, :, 0].cpu().float(), want.float(), atol=2e-3)

@@ -19,6 +19,20 @@ def _close(a, b):
     return bool(((a - b).abs() <= ATOL + RTOL * b.abs()).all()), (a - b).abs().max().item()
 
 
+def _assert_greedy_matches(got_tokens, ref_tokens, ref_logits, near_tie=2e-2):
+    """Greedy sequences must agree up to the first position where the oracle's own top-2
+    margin is below ``near_tie`` (numerical noise may then pick the runner-up, after which
+    the two sequences legitimately differ)."""
+    for i, (g, r) in enumerate(zip(got_tokens, ref_tokens)):
+        if g == r:
+            continue
+        top = torch.topk(ref_logits[i].float(), 2)
+        gap = (top.values[0] - top.values[1]).item()
+        assert gap < near_tie and g == int(top.indices[1]), (i, g, r, gap)
+        return i
+    return len(ref_tokens)
+
+
 def test_token_by_token_matches_oracle(tiny_model):
     """Prompt and generation both through the fused decode step (positions 0..n)."""
     net, ref, _, _ = tiny_model
@@ -35,9 +49,9 @@ def test_token_by_token_matches_oracle(tiny_model):
         nxt = logits[:, -1:, :].argmax(dim=-1)
         got_tokens.append(int(nxt))
         logits = net(nxt, past_key_values=cache).logits
-    ok, err = _close(torch.stack(got_logits), ref_logits)
+    n = _assert_greedy_matches(got_tokens, ref_tokens, ref_logits)
+    ok, err = _close(torch.stack(got_logits)[: n + 1], ref_logits[: n + 1])
     assert ok, err
-    assert got_tokens == ref_tokens
 
 
 def test_prefill_then_graph_decode_matches_oracle(tiny_model):
@@ -49,7 +63,12 @@ def test_prefill_then_graph_decode_matches_oracle(tiny_model):
     ok, err = _close(logits[0], ref_logits[0])
     assert ok, err
     tokens = [int(first[0])] + net.decode(cache, [3], 8)[0]
-    assert tokens == ref_tokens
+    _assert_greedy_matches(tokens, ref_tokens, ref_logits)
+    # the same decode as eight single-step launches gives the same tokens bit for bit
+    cache2 = net.new_cache(n_slots=4, s_max=256)
+    first2, _ = net.prefill(cache2, [1], [torch.tensor(prompt)])
+    again = [int(first2[0])] + [net.decode(cache2, [1], 1)[0][0] for _ in range(8)]
+    assert again == tokens
 
 
 def test_batched_rows_are_independent(tiny_model):
@@ -57,13 +76,13 @@ def test_batched_rows_are_independent(tiny_model):
     semantics of the reference's batch: padded keys never contribute)."""
     net, ref, _, _ = tiny_model
     prompts = [[5, 6, 7], [100, 200, 300, 400, 500, 600, 700], [9], [1, 2], [42] * 12]
-    want = [ref.greedy(p, 5)[0] for p in prompts]
+    want = [ref.greedy(p, 5) for p in prompts]
     cache = net.new_cache(n_slots=8, s_max=128)
     slots = [6, 0, 3, 7, 1]
     first, _ = net.prefill(cache, slots, [torch.tensor(p) for p in prompts])
     rest = net.decode(cache, slots, 4)
-    got = [[int(first[i])] + rest[i] for i in range(len(prompts))]
-    assert got == want
+    for i in range(len(prompts)):
+        _assert_greedy_matches([int(first[i])] + rest[i], want[i][0], want[i][1])
 
 
 def test_golden_hf_quant_logits(tiny_model):
