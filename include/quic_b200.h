@@ -42,6 +42,10 @@ extern "C" {
 const char *quic_last_error(void);
 /* Library ABI version; bumped when a struct below changes. */
 int quic_abi_version(void);
+/* Programmatic dependent launch between the kernels of a decode step is on by
+ * default; 0 turns it off process-wide (plain stream order) for A/B timing.
+ * No counterpart in the reference, which launches every kernel separately. */
+void quic_set_pdl(int enabled);
 
 /* ------------------------------------------------------------------------
  * W4A16 weights.

@@ -9,11 +9,15 @@
 namespace quic {
 
 static thread_local char g_err[256] = "";
+void set_pdl(bool on);
 void set_error(const char* msg) {
   int i = 0;
   for (; msg && msg[i] && i < 255; ++i) g_err[i] = msg[i];
   g_err[i] = 0;
 }
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
+void set_pdl(bool on) { g_pdl = on; }
 int fail(int code, const char* msg) {
   set_error(msg);
   return code;
@@ -213,6 +217,7 @@ using namespace quic;
 
 extern "C" const char* quic_last_error(void) { return g_err; }
 extern "C" int quic_abi_version(void) { return 1; }
+extern "C" void quic_set_pdl(int enabled) { quic::set_pdl(enabled != 0); }
 
 extern "C" int quic_rmsnorm(const void* x, const void* residual, const void* w, float eps, void* y,
                             void* sum_out, int32_t rows, void* stream) {

@@ -96,6 +96,7 @@ _P, _I32, _I64, _F = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 SIGNATURES = {
     "quic_last_error": (C.c_char_p, []),
     "quic_abi_version": (C.c_int, []),
+    "quic_set_pdl": (None, [C.c_int]),
     "quic_w4_prepack": (C.c_int, [_P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P]),
     "quic_w4_dequant": (C.c_int, [C.POINTER(W4), _P, _P]),
     "quic_w4a16_linear": (C.c_int, [_P, C.POINTER(W4), _P, _I32, _I32, _P, _P]),
@@ -247,6 +248,8 @@ def _rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor, eps: float,
     x = x.contiguous()
     y = torch.empty_like(x)
     rows = x.numel() // HIDDEN
+    if rows == 0:
+        return y if residual is None else (y, torch.empty_like(x))
     total = None
     if residual is not None:
         residual = residual.contiguous()

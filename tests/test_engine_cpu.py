@@ -1,0 +1,90 @@
+"""Engine semantics on the CPU with an injected fake model (no CUDA involved)."""
+
+import pytest
+import torch
+
+from quic_cu_b200.config import EngineConfig
+from quic_cu_b200.engine import Engine
+from tests.fake_model import EOS, FakeModule, expected_generation
+
+
+def _engine(batching, max_batch=4, burst=3, tokenizer=None, **kw):
+    module = FakeModule(tokenizer)
+    cfg = EngineConfig(batching=batching, decode_burst=burst, max_context=256, **kw)
+    return Engine(config=cfg, max_batch_size=max_batch, model_module=module), module
+
+
+def test_empty_run_returns_empty_list():  # reference tests/test_engine.py:12
+    engine, _ = _engine("continuous")
+    assert engine.run() == []
+
+
+@pytest.mark.parametrize("batching", ["static", "continuous"])
+@pytest.mark.parametrize("burst", [1, 3, 8])
+def test_outputs_equal_independent_greedy_generation(batching, burst):
+    engine, module = _engine(batching, max_batch=3, burst=burst)
+    engine.max_tokens = 16
+    prompts = [[5, 6, 7], [1], [9, 9, 9, 9], [2, 3], [11] * 10, [4, 5], [8]]
+    limits = [16, 3, 16, 1, 9, 16, 2]
+    for p, lim in zip(prompts, limits):
+        engine.add_request_ids(p, max_tokens=lim)
+    outputs = engine.run()
+    assert len(outputs) == len(prompts)
+    for out, p, lim in zip(outputs, prompts, limits):  # ordered by request id
+        assert out == expected_generation(p, lim, eos=None)
+    assert sorted(engine.free_slots) == [0, 1, 2]
+    assert not engine.running and not engine.waiting
+    if batching == "static":
+        # a new batch is admitted only once every row of the previous one has finished
+        prefills = [c[1] for c in module.model.calls if c[0] == "prefill"]
+        assert [len(p) for p in prefills] == [3, 3, 1]
+
+
+def test_eos_is_appended_and_ends_the_request():  # src/engine.py:180-184
+    class Tok:
+        eos_token_id = EOS
+
+        def decode(self, tokens, skip_special_tokens=True):
+            return " ".join(str(t) for t in tokens)
+
+    engine, _ = _engine("continuous", tokenizer=Tok())
+    found = None
+    for start in range(1, 60):
+        gen = expected_generation([start], 40)
+        if gen[-1] == EOS and 1 < len(gen) < 40:
+            found = (start, gen)
+            break
+    assert found, "no prompt of the fake model reaches EOS"
+    engine.add_request_ids([found[0]], max_tokens=40)
+    out = engine.run()
+    assert out == [" ".join(str(t) for t in found[1])]
+
+
+def test_load_options_follow_the_reference_engine():  # src/engine.py:40-51
+    engine, module = _engine("continuous", model_path="/m", tokenizer_path="/t")
+    assert module.options == {"path": "/m", "tokenizer_path": "/t", "prefill_backend": "pytorch"}
+    engine2, module2 = _engine("static")
+    assert module2.options == {"prefill_backend": "pytorch"}
+
+
+def test_request_that_cannot_fit_a_slot_is_rejected():
+    engine, _ = _engine("continuous")
+    with pytest.raises(ValueError):
+        engine.add_request_ids(list(range(250)), max_tokens=16)
+    with pytest.raises(ValueError):
+        engine.add_request_ids([])
+    with pytest.raises(RuntimeError):
+        engine.add_request("text needs a tokenizer")
+
+
+def test_continuous_refills_vacant_slots_while_others_run():
+    engine, module = _engine("continuous", max_batch=2, burst=2)
+    engine.add_request_ids([1], max_tokens=2)
+    engine.add_request_ids([2], max_tokens=12)
+    engine.add_request_ids([3], max_tokens=2)
+    engine.run()
+    calls = module.model.calls
+    # request 3 is prefilled into the slot request 1 vacated while request 2 is still decoding
+    second_prefill = [i for i, c in enumerate(calls) if c[0] == "prefill"][1]
+    assert calls[second_prefill][1] == [0]
+    assert any(c[0] == "decode" and len(c[1]) == 2 for c in calls[second_prefill:])
