@@ -171,6 +171,26 @@ int quic_attn_decode(const void *q_f16, const void *k_f16, const void *v_f16,
                      const int32_t *end, int32_t s_max, float scale,
                      void *out_f16, int32_t b, int32_t splits, void *scratch,
                      void *stream);
+/* Same operation with no memory from the caller and no allocation anywhere:
+ * the split partials and counters sit in an 8 MiB array built into the library
+ * image (quic_attn_decode_noalloc_max_bytes(); each GPU that loads the library
+ * holds it until the process ends).  This entry point has no counterpart in the
+ * reference.  It is meant for callers that cannot allocate where they call
+ * from: a serving loop that must not hit the device-wide synchronisation of
+ * cudaMalloc/cudaFree, a host runtime that gives a plug-in no allocator, or
+ * code running under its own memory budget.
+ *  - A request whose quic_attn_scratch_bytes(b, splits) exceeds the array is
+ *    refused with QUIC_E_LIMIT; pass a smaller `splits` or use quic_attn_decode.
+ *  - The first call on a device (with that device current) looks up the
+ *    array's device address; make that first call outside any stream capture.
+ *  - All calls share the one array, which keeps the previous call's contents:
+ *    the counters are cleared on `stream` before each launch, and two calls
+ *    whose kernels can overlap on the GPU (different streams) race. */
+int quic_attn_decode_noalloc(const void *q_f16, const void *k_f16, const void *v_f16,
+                             int64_t stride_b, int64_t stride_h, const int32_t *start,
+                             const int32_t *end, int32_t s_max, float scale,
+                             void *out_f16, int32_t b, int32_t splits, void *stream);
+int64_t quic_attn_decode_noalloc_max_bytes(void);
 int32_t quic_attn_pick_splits(int32_t b, int32_t s_max);
 int64_t quic_attn_scratch_bytes(int32_t b, int32_t splits);
 

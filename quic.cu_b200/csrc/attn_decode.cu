@@ -310,3 +310,64 @@ extern "C" int quic_attn_decode(const void* q, const void* k, const void* v, int
   QUIC_CUDA(launch_attn(a, b, (cudaStream_t)stream, false));
   return QUIC_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant: the split partials and arrival counters live in a
+// fixed array inside the library image instead of caller-provided scratch.
+// ---------------------------------------------------------------------------
+namespace {
+
+// 8 MiB: enough for batch x splits up to 2048 (e.g. batch 64 with 32 splits,
+// or batch 1 with the maximum of 64 splits).  Every GPU that loads the library
+// carries this array until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+// In host code `g_attn_static_scratch` is only a handle for the runtime, not an
+// address a kernel may dereference; the device address is looked up once per
+// device, with that device current, and cached here.
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  QUIC_CUDA(cudaGetDevice(&dev));
+  QUIC_REQUIRE(dev >= 0 && dev < kMaxDevices, QUIC_E_LIMIT,
+               "attn_decode_noalloc: device ordinal beyond 63");
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    QUIC_CUDA(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+    QUIC_REQUIRE(p != nullptr, QUIC_E_CUDA, "attn_decode_noalloc: no address for the static scratch");
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return QUIC_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t quic_attn_decode_noalloc_max_bytes(void) { return (int64_t)kStaticScratchBytes; }
+
+extern "C" int quic_attn_decode_noalloc(const void* q, const void* k, const void* v,
+                                        int64_t stride_b, int64_t stride_h, const int32_t* start,
+                                        const int32_t* end, int32_t s_max, float scale, void* out,
+                                        int32_t b, int32_t splits, void* stream) {
+  QUIC_REQUIRE(b >= 1 && s_max >= 1, QUIC_E_SHAPE, "attn_decode_noalloc: bad batch or length");
+  if (splits <= 0) splits = quic_attn_pick_splits(b, s_max);
+  const int64_t need = quic_attn_scratch_bytes(b, splits);
+  if (splits > 1 && need > (int64_t)kStaticScratchBytes)
+    return fail(QUIC_E_LIMIT,
+                "attn_decode_noalloc: batch x splits needs more than the 8 MiB built-in scratch "
+                "(14*64*4 bytes per batch row per split); use fewer splits or quic_attn_decode");
+  void* scratch = nullptr;
+  if (splits > 1) {
+    int rc = static_scratch_for_current_device(&scratch);
+    if (rc != QUIC_OK) return rc;
+    // The array keeps whatever the previous call left.  Only the arrival
+    // counters must start at zero; partials are fully rewritten before use.
+    QUIC_CUDA(cudaMemsetAsync(scratch, 0, (size_t)b * kKvHeads * sizeof(int32_t),
+                              (cudaStream_t)stream));
+  }
+  return quic_attn_decode(q, k, v, stride_b, stride_h, start, end, s_max, scale, out, b, splits,
+                          scratch, stream);
+}

@@ -110,6 +110,8 @@ SIGNATURES = {
     "quic_lm_head_argmax": (C.c_int, [_P, _P, _F, _P, _I32, _I32, _P, _P, _P, _P]),
     "quic_lm_head_scratch_bytes": (_I64, [_I32, _I32]),
     "quic_attn_decode": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _I32, _F, _P, _I32, _I32, _P, _P]),
+    "quic_attn_decode_noalloc": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _I32, _F, _P, _I32, _I32, _P]),
+    "quic_attn_decode_noalloc_max_bytes": (_I64, []),
     "quic_attn_pick_splits": (_I32, [_I32, _I32]),
     "quic_attn_scratch_bytes": (_I64, [_I32, _I32]),
     "quic_decode_scratch_bytes": (_I64, [_I32, _I32, _I32]),
