@@ -246,6 +246,9 @@ typedef struct {
   int32_t ctx_hint;    /* upper bound of pos+1 over the rows for this launch */
 } quic_decode_t;
 
+/* Attention split count the decode step uses for `batch` rows whose contexts are
+ * at most `ctx` tokens (pass the result as attn_splits and to the scratch size). */
+int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx);
 int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32_t attn_splits);
 /* Number of kernels one quic_decode_step launches. */
 int32_t quic_decode_launch_count(const quic_model_t *m, const quic_decode_t *d);

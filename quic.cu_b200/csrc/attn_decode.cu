@@ -36,28 +36,47 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
 
-  pdl_launch_dependents();
+  // The row -> slot map is not written by any kernel of the decode chain.
+  int slot = b;
+  if (a.pos != nullptr) slot = a.rows[b];
+  pdl_trigger_early();
   pdl_wait();
+  QUIC_TLOG_BEGIN(2);
 
-  int slot = b, t_begin = 0, t_end = a.s_cap;
+  const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+  const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+  const int vt = lane >> 3;        // token (mod 4) this lane covers in p·V
+  const int vd = (lane & 7) * 8;   // first of its 8 dims
+  const int last_tok = a.s_cap - 1;
+
+  // One round of global loads: the first K/V tile of this warp is requested
+  // before the row's token range is known (its position in the cache is fixed
+  // by the split; tokens outside the range are masked later, addresses are
+  // clamped into the cache), together with the range itself and q.
+  uint4 kr[8], vr[8];
+  int t0 = split * a.chunk + warp * kTile;
+  {
+    const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(t0 + lane, last_tok) * kHeadDim);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) kr[i] = ldg_nc_u128(kp + i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      vr[i] = ldg_nc_u128(vbase + (size_t)min(t0 + 4 * i + vt, last_tok) * kHeadDim + vd);
+  }
+  int t_begin = 0, t_end = a.s_cap;
   if (a.pos != nullptr) {
-    slot = a.rows[b];
-    t_end = a.pos[slot] + 1;
+    t_end = __ldcg(a.pos + slot) + 1;
   } else {
     if (a.start != nullptr) t_begin = a.start[b];
     if (a.end != nullptr) t_end = a.end[b];
   }
+  for (int i = tid; i < kGroupHeads * kHeadDim; i += kWarps * 32)
+    q_s[i] = __half2float(a.q[((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim + i]) * a.scale;
   if (t_end > a.s_cap) t_end = a.s_cap;
   if (t_begin < 0) t_begin = 0;
   const int c_begin = max(t_begin, split * a.chunk);
   const int c_end = min(t_end, (split + 1) * a.chunk);
-
-  for (int i = tid; i < kGroupHeads * kHeadDim; i += kWarps * 32)
-    q_s[i] = __half2float(a.q[((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim + i]) * a.scale;
   __syncthreads();
-
-  const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
-  const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
 
   float m_run[kGroupHeads], l_run[kGroupHeads];
   float o[kGroupHeads][8];
@@ -68,27 +87,19 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
 #pragma unroll
     for (int d = 0; d < 8; ++d) o[h][d] = 0.f;
   }
-  const int vt = lane >> 3;        // token (mod 4) this lane covers in p·V
-  const int vd = (lane & 7) * 8;   // first of its 8 dims
 
-  for (int t0 = c_begin + warp * kTile; t0 < c_end; t0 += kWarps * kTile) {
-    const int t = t0 + lane;
-    const bool valid = t < c_end;
-    const int ntok = min(kTile, c_end - t0);
-    // Issue all loads of the tile first.
-    uint4 kr[8];
-    {
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)(valid ? t : t0) * kHeadDim);
+  for (bool first = true; t0 < c_end; t0 += kWarps * kTile, first = false) {
+    if (!first) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(t0 + lane, last_tok) * kHeadDim);
 #pragma unroll
       for (int i = 0; i < 8; ++i) kr[i] = ldg_nc_u128(kp + i);
-    }
-    uint4 vr[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int tt = 4 * i + vt;
-      const int tc = tt < ntok ? tt : 0;
-      vr[i] = ldg_nc_u128(vbase + (size_t)(t0 + tc) * kHeadDim + vd);
+      for (int i = 0; i < 8; ++i)
+        vr[i] = ldg_nc_u128(vbase + (size_t)min(t0 + 4 * i + vt, last_tok) * kHeadDim + vd);
     }
+    if (t0 + kTile <= c_begin) continue;  // tile entirely left of the row's first token
+    const int t = t0 + lane;
+    const bool valid = t >= c_begin && t < c_end;
 
     float s[kGroupHeads];
 #pragma unroll
@@ -146,7 +157,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
       }
 #pragma unroll
       for (int h = 0; h < kGroupHeads; ++h) {
-        const float p = p_s[warp][h][tt];  // 0 for tokens past the end
+        const float p = p_s[warp][h][tt];  // 0 for tokens outside the range
 #pragma unroll
         for (int d = 0; d < 8; ++d) o[h][d] = fmaf(p, vf[d], o[h][d]);
       }
@@ -204,7 +215,8 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
       }
     }
   }
-  if (a.splits == 1) return;
+  QUIC_TLOG_END();
+  if (a.splits == 1 || a.consumer_merge) return;
 
   // Last CTA of this (row, kv head) merges the splits.
   __threadfence();
@@ -237,10 +249,167 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
   if (tid == 0) a.counters[b * kKvHeads + kvh] = 0;
 }
 
+
+// ---------------------------------------------------------------------------
+// Latency variant for short contexts at small batch (one decode step of a few
+// rows): a CTA owns 64 tokens of one (row, kv head); FOUR lanes share a token
+// (16 dims each), so a warp covers 8 tokens and does a quarter of the serial
+// work of the kernel above; p·V is done with lane = 2 dims.  Single pass, no
+// running rescale.  Always writes split partials unless there is one split.
+// ---------------------------------------------------------------------------
+constexpr int kSmallChunk = 64;
+
+__global__ void __launch_bounds__(256) attn_decode_small_kernel(const AttnArgs a) {
+  __shared__ __align__(16) float q_s[kGroupHeads * kHeadDim];
+  __shared__ float p_s[kWarps][kGroupHeads][8];
+  __shared__ float m_s[kWarps][kGroupHeads];
+  __shared__ float l_s[kWarps][kGroupHeads];
+  __shared__ __align__(8) float o_s[kWarps][kGroupHeads][kHeadDim];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  int slot = b;
+  if (a.pos != nullptr) slot = a.rows[b];
+  pdl_trigger_early();
+  pdl_wait();
+  QUIC_TLOG_BEGIN(2);
+
+  const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+  const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+  const int last_tok = a.s_cap - 1;
+  const int tw = split * kSmallChunk + warp * 8;  // first token of this warp
+  const int tok = tw + (lane >> 2), part = lane & 3;
+
+  // one round of loads: K (32 B per lane), V (4 B per lane per token), range, q
+  uint4 kr[2];
+  {
+    const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(tok, last_tok) * kHeadDim + 16 * part);
+    kr[0] = ldg_nc_u128(kp);
+    kr[1] = ldg_nc_u128(kp + 1);
+  }
+  uint32_t vr[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t)
+    vr[t] = ldg_nc_u32(vbase + (size_t)min(tw + t, last_tok) * kHeadDim + 2 * lane);
+  int t_begin = 0, t_end = a.s_cap;
+  if (a.pos != nullptr) {
+    t_end = __ldcg(a.pos + slot) + 1;
+  } else {
+    if (a.start != nullptr) t_begin = a.start[b];
+    if (a.end != nullptr) t_end = a.end[b];
+  }
+  for (int i = tid; i < kGroupHeads * kHeadDim; i += 256)
+    q_s[i] = __half2float(a.q[((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim + i]) * a.scale;
+  if (t_end > a.s_cap) t_end = a.s_cap;
+  if (t_begin < 0) t_begin = 0;
+  const bool valid = tok >= t_begin && tok < t_end;
+  __syncthreads();
+
+  float s[kGroupHeads];
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) s[h] = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const half2* h2 = reinterpret_cast<const half2*>(&kr[i]);
+    float kf[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(h2[j]);
+      kf[2 * j] = f.x;
+      kf[2 * j + 1] = f.y;
+    }
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) {
+      const float4 qa = *reinterpret_cast<const float4*>(&q_s[h * kHeadDim + 16 * part + 8 * i]);
+      const float4 qb = *reinterpret_cast<const float4*>(&q_s[h * kHeadDim + 16 * part + 8 * i + 4]);
+      s[h] = fmaf(kf[0], qa.x, s[h]);
+      s[h] = fmaf(kf[1], qa.y, s[h]);
+      s[h] = fmaf(kf[2], qa.z, s[h]);
+      s[h] = fmaf(kf[3], qa.w, s[h]);
+      s[h] = fmaf(kf[4], qb.x, s[h]);
+      s[h] = fmaf(kf[5], qb.y, s[h]);
+      s[h] = fmaf(kf[6], qb.z, s[h]);
+      s[h] = fmaf(kf[7], qb.w, s[h]);
+    }
+  }
+  float m_w[kGroupHeads], l_w[kGroupHeads];
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) {
+    float v = s[h];
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);  // full dot product in all 4 lanes of the token
+    const float sv = valid ? v : -INFINITY;
+    float mx = sv;
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+    const float p = (valid && mx != -INFINITY) ? __expf(sv - mx) : 0.f;
+    float sum = p;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+    m_w[h] = mx;
+    l_w[h] = sum;
+    if (part == 0) p_s[warp][h][lane >> 2] = p;
+  }
+  __syncwarp();
+  float o[kGroupHeads][2];
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) o[h][0] = o[h][1] = 0.f;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    const float2 vf = __half22float2(u32_as_half2(vr[t]));
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) {
+      const float p = p_s[warp][h][t];
+      o[h][0] = fmaf(p, vf.x, o[h][0]);
+      o[h][1] = fmaf(p, vf.y, o[h][1]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) {
+    *reinterpret_cast<float2*>(&o_s[warp][h][2 * lane]) = make_float2(o[h][0], o[h][1]);
+    if (lane == 0) {
+      m_s[warp][h] = m_w[h];
+      l_s[warp][h] = l_w[h];
+    }
+  }
+  __syncthreads();
+
+  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += 256) {
+    const int h = idx >> 6, d = idx & 63;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, m_s[w][h]);
+    float num = 0.f, den = 0.f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float e = (m_s[w][h] == -INFINITY) ? 0.f : __expf(m_s[w][h] - m);
+        den += e * l_s[w][h];
+        num += e * o_s[w][h][d];
+      }
+    }
+    const int qh = kvh * kGroupHeads + h;
+    if (a.splits == 1) {
+      a.out[((size_t)b * kHeads + qh) * kHeadDim + d] = __float2half_rn(m == -INFINITY ? 0.f : num / den);
+    } else {
+      const size_t row = ((size_t)b * kHeads + qh) * a.splits + split;
+      a.o_part[row * kHeadDim + d] = num;
+      if (d == 0) {
+        a.m_part[row] = m;
+        a.l_part[row] = den;
+      }
+    }
+  }
+  QUIC_TLOG_END();
+}
+
 }  // namespace
 
 cudaError_t launch_attn(const AttnArgs& a, int batch, cudaStream_t s, bool pdl) {
   dim3 grid(a.splits, kKvHeads, batch);
+  if (a.small) return launch(attn_decode_small_kernel, grid, dim3(256), 0, s, pdl, a);
   return launch(attn_decode_kernel, grid, dim3(kWarps * 32), 0, s, pdl, a);
 }
 
@@ -371,3 +540,7 @@ extern "C" int quic_attn_decode_noalloc(const void* q, const void* k, const void
   return quic_attn_decode(q, k, v, stride_b, stride_h, start, end, s_max, scale, out, b, splits,
                           scratch, stream);
 }
+
+#ifdef QUIC_TRACE
+QUIC_TRACE_SETTER(attn)
+#endif

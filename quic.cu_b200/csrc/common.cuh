@@ -38,6 +38,19 @@ int fail(int code, const char* msg);
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+// Where a kernel lets its dependent start: at its top (the dependent's weight
+// prefetch then overlaps this whole kernel and dependents cascade several
+// kernels deep) or, with -DQUIC_PDL_LATE, after its main loop (one kernel deep).
+__device__ __forceinline__ void pdl_trigger_early() {
+#ifndef QUIC_PDL_LATE
+  pdl_launch_dependents();
+#endif
+}
+__device__ __forceinline__ void pdl_trigger_late() {
+#ifdef QUIC_PDL_LATE
+  pdl_launch_dependents();
+#endif
+}
 __device__ __forceinline__ void pdl_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
@@ -62,6 +75,42 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// ---- debug timeline (-DQUIC_TRACE) ---------------------------------------------
+// Thread 0 of CTA 0 of every launch logs (kernel id, globaltimer when its wait
+// returned, globaltimer at its end); read back with quic_trace_log().
+#ifdef QUIC_TRACE
+struct TraceRow { unsigned long long id, t_wait, t_end; };
+// one pointer pair per translation unit, installed by QUIC_TRACE_SETTER(name)
+static __device__ TraceRow* g_tlog;
+static __device__ unsigned* g_tlog_n_ptr;
+#define QUIC_TRACE_SETTER(name)                                                      \
+  extern "C" int quic_trace_set_##name(void* rows, void* counter) {                  \
+    cudaMemcpyToSymbol(quic::g_tlog, &rows, sizeof(void*));                          \
+    return (int)cudaMemcpyToSymbol(quic::g_tlog_n_ptr, &counter, sizeof(void*));     \
+  }
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int tlog_begin(int id) {
+  if (threadIdx.x || blockIdx.x || blockIdx.y || blockIdx.z) return -1;
+  if (g_tlog == nullptr) return -1;
+  const int i = atomicAdd(g_tlog_n_ptr, 1u) & 8191;
+  g_tlog[i].id = id;
+  g_tlog[i].t_wait = gtimer();
+  return i;
+}
+__device__ __forceinline__ void tlog_end(int i) {
+  if (i >= 0) g_tlog[i].t_end = gtimer();
+}
+#define QUIC_TLOG_BEGIN(id) const int tlog_i__ = tlog_begin(id)
+#define QUIC_TLOG_END() tlog_end(tlog_i__)
+#else
+#define QUIC_TLOG_BEGIN(id)
+#define QUIC_TLOG_END()
+#endif
 
 // ---- small device utilities -------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
@@ -139,6 +188,26 @@ __device__ __forceinline__ float dot8(const half2 w[4], const float* __restrict_
   acc = fmaf(f.x, b.z, acc);
   acc = fmaf(f.y, b.w, acc);
   return acc;
+}
+
+// acc + a*b with fp16 operands and an fp32 accumulator in ONE instruction (PTX
+// mixed-precision fma, sm_100+): the product of two fp16 numbers is exact in
+// fp32, so this equals convert-then-FFMA without the two conversions.
+__device__ __forceinline__ float fma_h(float acc, half a, half b) {
+  asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)));
+  return acc;
+}
+
+// acc[p] += dot of dequantised pair p with the matching activation pair; xs holds
+// 8 fp16 activations of one k slab in perm8 order (one 16-byte shared load).
+__device__ __forceinline__ void dot8_h(const half2 w[4], const half* __restrict__ xs, float acc[4]) {
+  const uint4 xv = *reinterpret_cast<const uint4*>(xs);
+  const half2* x2 = reinterpret_cast<const half2*>(&xv);
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    acc[p] = fma_h(acc[p], __low2half(w[p]), __low2half(x2[p]));
+    acc[p] = fma_h(acc[p], __high2half(w[p]), __high2half(x2[p]));
+  }
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + __expf(-g))) * u; }

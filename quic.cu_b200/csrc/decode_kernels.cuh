@@ -11,6 +11,8 @@ __host__ __device__ __forceinline__ int down_group_begin(int ks) {
   return ks <= 3 ? ks * 8 : 24 + (ks - 3) * 7;
 }
 constexpr int kMaxM = 8;  // batch rows per CTA pass
+// Up to this many attention splits are merged by the o_proj kernel itself.
+constexpr int kMaxConsumerSplits = 16;
 
 struct RowState {
   const int32_t* rows;  // [batch] slot per row
@@ -41,7 +43,12 @@ struct QkvArgs {
 
 struct OProjArgs {
   quic_w4_t w;
-  const half* attn;     // [batch][896]
+  // splits > 0: merge the attention kernel's split partials here
+  int32_t splits;
+  const float* o_part;  // [batch][14][splits][64]
+  const float* m_part;  // [batch][14][splits]
+  const float* l_part;
+  const half* attn;     // [batch][896] (splits == 0)
   const half* xres_in;  // [batch][896]
   half* xres_out;
   int32_t batch;
@@ -51,15 +58,15 @@ struct GateUpArgs {
   quic_w4_t w;  // n = 9728
   const half* ln;
   const half* xres;  // [batch][896]
-  half* act;         // [batch][4864]
+  float* gu_part;    // [2 parts][gate|up][batch][4864] fp32 partial sums
   int32_t batch;
   float eps;
 };
 
 struct DownArgs {
   quic_w4_t w;
-  const half* act;  // [batch][4864]
-  float* partial;   // [kDownSplits][batch][896]
+  const float* gu_part;  // [2 parts][gate|up][batch][4864]
+  float* partial;        // [kDownSplits][batch][896]
   int32_t batch;
 };
 
@@ -76,6 +83,8 @@ struct AttnArgs {
   int32_t s_cap;  // token range covered by the grid
   int32_t chunk;  // tokens per split
   int32_t splits;
+  int32_t consumer_merge;  // 1: write partials only, the o_proj kernel merges
+  int32_t small;           // 1: latency variant (64 tokens per CTA, consumer merge)
   float scale;
   half* out;  // [batch][896]
   int32_t* counters;  // [batch][2]

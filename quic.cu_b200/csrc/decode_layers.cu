@@ -24,6 +24,19 @@ namespace {
 
 constexpr int kQuarter = kHidden / 4;  // 224 threads cover a 896-wide row, 4 each
 
+// Debug build (-DQUIC_TRACE): SM-clock stamps of the first CTAs of the last launch
+// of each kernel, read back with quic_trace_read().  Compiled out otherwise.
+#ifdef QUIC_TRACE
+__device__ long long g_trace[4][8][8];
+#define QUIC_STAMP(kernel, idx)                                                   \
+  do {                                                                            \
+    if (threadIdx.x == 0 && blockIdx.x < 8 && blockIdx.y == 0 && blockIdx.z == 0) \
+      g_trace[kernel][blockIdx.x][idx] = clock64();                               \
+  } while (0)
+#else
+#define QUIC_STAMP(kernel, idx)
+#endif
+
 struct Half4 {
   half2 a, b;
 };
@@ -58,8 +71,8 @@ __device__ __forceinline__ void block_sum(float (&v)[M], float* red /* [M][32] *
 // un-normalised x is written back by this CTA.
 template <int M>
 __device__ __forceinline__ void residual_norm_to_smem(
-    float* xs, float* red, const half* const (&src)[M], const float* partial, int n_partial,
-    int batch, int row0, const half* ln, float eps, half* xres_out) {
+    half* xs, float* red, const half* const (&src)[M], const float* partial, int n_partial,
+    int batch, int row0, const float4 w, float eps, half* xres_out) {
   const int t = threadIdx.x;
   float4 x[M];
   float ssq[M];
@@ -72,10 +85,14 @@ __device__ __forceinline__ void residual_norm_to_smem(
       float4 v = half4_to_float4(h);
       if (partial != nullptr) {
         float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int j = 0; j < n_partial; ++j) {
-          const float4 q = __ldcg(reinterpret_cast<const float4*>(
+        float4 q[kDownSplits];
+#pragma unroll
+        for (int j = 0; j < kDownSplits; ++j)  // all loads in flight together
+          q[j] = __ldcg(reinterpret_cast<const float4*>(
               partial + ((size_t)j * batch + (row0 + m)) * kHidden + 4 * t));
-          p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
+#pragma unroll
+        for (int j = 0; j < kDownSplits; ++j) {
+          p.x += q[j].x; p.y += q[j].y; p.z += q[j].z; p.w += q[j].w;
         }
         v.x = __half2float(__float2half_rn(v.x + __half2float(__float2half_rn(p.x))));
         v.y = __half2float(__float2half_rn(v.y + __half2float(__float2half_rn(p.y))));
@@ -94,127 +111,194 @@ __device__ __forceinline__ void residual_norm_to_smem(
   }
   block_sum<M>(ssq, red);
   if (t < kQuarter) {
-    const float4 w = half4_to_float4(*reinterpret_cast<const Half4*>(ln + 4 * t));
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       const float r = rsqrtf(ssq[m] * (1.0f / kHidden) + eps);
-      float* dst = xs + m * kHidden;
+      half* dst = xs + m * kHidden;
       const int k = 4 * t;
-      dst[perm_k(k + 0)] = __half2float(__float2half_rn(x[m].x * r * w.x));
-      dst[perm_k(k + 1)] = __half2float(__float2half_rn(x[m].y * r * w.y));
-      dst[perm_k(k + 2)] = __half2float(__float2half_rn(x[m].z * r * w.z));
-      dst[perm_k(k + 3)] = __half2float(__float2half_rn(x[m].w * r * w.w));
+      dst[perm_k(k + 0)] = __float2half_rn(x[m].x * r * w.x);
+      dst[perm_k(k + 1)] = __float2half_rn(x[m].y * r * w.y);
+      dst[perm_k(k + 2)] = __float2half_rn(x[m].z * r * w.z);
+      dst[perm_k(k + 3)] = __float2half_rn(x[m].w * r * w.w);
     }
   }
   __syncthreads();
 }
 
-// Registers of one lane for one quantisation group of one column.
+// Norm weight slice of this thread (4 of 896), loadable before griddepcontrol.wait.
+__device__ __forceinline__ float4 load_ln(const half* ln) {
+  if (threadIdx.x < kQuarter) return half4_to_float4(*reinterpret_cast<const Half4*>(ln + 4 * threadIdx.x));
+  return make_float4(1.f, 1.f, 1.f, 1.f);
+}
+
+// Packed registers of one lane for one quantisation group of one column.  Loading
+// does no arithmetic on the loaded values, so issuing it never stalls.
 struct GroupRegs {
   uint32_t q[kWordsPerGroup];
-  half2 s2;
-  half2 zp;
+  half s;
+  uint8_t zb;
 };
 
 __device__ __forceinline__ void load_group(GroupRegs& r, const quic_w4_t& w, int g, int n) {
   const int32_t* p = w.qw + (size_t)g * kWordsPerGroup * w.n + n;
 #pragma unroll
   for (int j = 0; j < kWordsPerGroup; ++j) r.q[j] = ldg_nc_u32(p + (size_t)j * w.n);
-  const half s = reinterpret_cast<const half*>(w.sc)[(size_t)g * w.n + n];
-  r.s2 = __half2half2(s);
-  const uint8_t zb = w.zp[(size_t)g * (w.n >> 1) + (n >> 1)];
-  r.zp = zp_to_half2((zb >> (4 * (n & 1))) & 15);
+  r.s = reinterpret_cast<const half*>(w.sc)[(size_t)g * w.n + n];
+  r.zb = w.zp[(size_t)g * (w.n >> 1) + (n >> 1)];
 }
 
-// acc[m] += sum over the group of dequant(w) * xs_m ; xs points at the group's
-// first k (perm8 order inside each slab of 8), rows `stride` floats apart.
+// The group's 128 weights as fp16 (q - zp) * s, 64 half2 registers.
+struct GroupF16 {
+  half2 w[kWordsPerGroup][4];
+};
+
+__device__ __forceinline__ void dequant_group(const GroupRegs& r, int n, GroupF16& d) {
+  const half2 s2 = __half2half2(r.s);
+  const half2 zp = zp_to_half2((r.zb >> (4 * (n & 1))) & 15);
+#pragma unroll
+  for (int j = 0; j < kWordsPerGroup; ++j) dequant8(r.q[j], zp, s2, d.w[j]);
+}
+
+// acc[m] += sum over the group of w * xs_m ; xs points at the group's first k
+// (perm8 order inside each slab of 8), rows `stride` halves apart.
 template <int M>
-__device__ __forceinline__ void group_fma(const GroupRegs& r, const float* xs, int stride,
-                                          float (&acc)[M]) {
+__device__ __forceinline__ void group_fma(const GroupF16& d, const half* xs, int stride, float (&acc)[M]) {
+  float a4[M][4];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int p = 0; p < 4; ++p) a4[m][p] = 0.f;
+#pragma unroll
+  for (int j = 0; j < kWordsPerGroup; ++j)
+#pragma unroll
+    for (int m = 0; m < M; ++m) dot8_h(d.w[j], xs + m * stride + 8 * j, a4[m]);
+#pragma unroll
+  for (int m = 0; m < M; ++m) acc[m] += (a4[m][0] + a4[m][1]) + (a4[m][2] + a4[m][3]);
+}
+
+// Same, dequantising on the fly from the packed registers (keeps 16 instead of
+// 64 weight registers; used where two groups per lane are live).
+template <int M>
+__device__ __forceinline__ void group_fma_packed(const GroupRegs& r, int n, const half* xs, int stride,
+                                                 float (&acc)[M]) {
+  const half2 s2 = __half2half2(r.s);
+  const half2 zp = zp_to_half2((r.zb >> (4 * (n & 1))) & 15);
+  float a4[M][4];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int p = 0; p < 4; ++p) a4[m][p] = 0.f;
 #pragma unroll
   for (int j = 0; j < kWordsPerGroup; ++j) {
     half2 w4[4];
-    dequant8(r.q[j], r.zp, r.s2, w4);
+    dequant8(r.q[j], zp, s2, w4);
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[m] = dot8(w4, xs + m * stride + 8 * j, acc[m]);
+    for (int m = 0; m < M; ++m) dot8_h(w4, xs + m * stride + 8 * j, a4[m]);
   }
+#pragma unroll
+  for (int m = 0; m < M; ++m) acc[m] += (a4[m][0] + a4[m][1]) + (a4[m][2] + a4[m][3]);
 }
 
 // ---------------------------------------------------------------------------
 // K1: (residual +) RMSNorm -> QKV GEMV -> bias -> RoPE -> q buffer / KV append.
 // grid (36, ceil(batch/M)), block 224.
+// After the wait there is ONE round of dependent global loads on the critical
+// path: position + residual stream + down partials are requested together; the
+// cos/sin row is requested as soon as the position arrives and lands while the
+// norm and the dot products run.  (Layer 0 adds the token -> embedding row hop.)
 // ---------------------------------------------------------------------------
 template <int M>
 __global__ void __launch_bounds__(224) qkv_kernel(const QkvArgs a) {
-  __shared__ __align__(16) float xs[M * kHidden];
+  __shared__ __align__(16) half xs[M * kHidden];
   __shared__ float red[7 * M * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 32 + lane;
   const int row0 = blockIdx.y * M;
 
+  // ---- before the wait: weights, norm weights, bias, row -> slot map (none of
+  // them is written by a kernel of the decode chain)
   GroupRegs gr;
   load_group(gr, a.w, warp, n);
+  const float4 lnw = load_ln(a.ln);
   const half bias = a.w.bias ? reinterpret_cast<const half*>(a.w.bias)[n] : __float2half(0.f);
-  pdl_launch_dependents();
+  int slot[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) slot[m] = (row0 + m < a.rs.batch) ? a.rs.rows[row0 + m] : -1;
+  GroupF16 gf;
+  dequant_group(gr, n, gf);
+  pdl_trigger_early();
   pdl_wait();
+  QUIC_TLOG_BEGIN(1);
 
   const half* src[M];
-  int slot[M], pos[M];
+  int pos[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) {
-    const int b = row0 + m;
     src[m] = nullptr;
-    slot[m] = -1;
     pos[m] = 0;
-    if (b < a.rs.batch) {
-      slot[m] = a.rs.rows[b];
-      pos[m] = a.rs.pos[slot[m]];
+    if (slot[m] >= 0) {
+      pos[m] = __ldcg(a.rs.pos + slot[m]);
       if (a.first_layer) {
-        int tk = a.rs.tok[slot[m]];
+        int tk = __ldcg(a.rs.tok + slot[m]);
         tk = tk < 0 ? 0 : (tk >= a.vocab ? a.vocab - 1 : tk);
         src[m] = a.embed + (size_t)tk * kHidden;
       } else {
-        src[m] = a.xres_in + (size_t)b * kHidden;
+        src[m] = a.xres_in + (size_t)(row0 + m) * kHidden;
       }
     }
   }
+  // cos/sin of this lane's RoPE pair for the rows this warp will finish
+  const int head = n >> 6;  // 0..13 q, 14..15 k, 16..17 v
+  const int pair = (n & 63) >> 1, hi = n & 1;
+  float cs[(M + 6) / 7], sn[(M + 6) / 7];
+#pragma unroll
+  for (int i = 0; i < (M + 6) / 7; ++i) {
+    cs[i] = 1.f;
+    sn[i] = 0.f;
+    const int m = warp + 7 * i;
+    if (m < M && head < kHeads + kKvHeads) {
+      int p = 0;
+#pragma unroll
+      for (int mm = 0; mm < M; ++mm)
+        if (mm == m) p = pos[mm];
+      p = p < a.max_pos ? p : a.max_pos - 1;
+      cs[i] = __half2float(a.cos_t[(size_t)p * 32 + pair]);
+      sn[i] = __half2float(a.sin_t[(size_t)p * 32 + pair]);
+    }
+  }
   residual_norm_to_smem<M>(xs, red, src, a.first_layer ? nullptr : a.partial, kDownSplits,
-                           a.rs.batch, row0, a.ln, a.eps,
-                           blockIdx.x == 0 ? a.xres_out : nullptr);
+                           a.rs.batch, row0, lnw, a.eps, blockIdx.x == 0 ? a.xres_out : nullptr);
 
   float acc[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) acc[m] = 0.f;
-  group_fma<M>(gr, xs + warp * kGroup, kHidden, acc);
+  group_fma<M>(gf, xs + warp * kGroup, kHidden, acc);
+  pdl_trigger_late();
 #pragma unroll
   for (int m = 0; m < M; ++m) red[(warp * M + m) * 32 + lane] = acc[m];
   __syncthreads();
 
-  // Epilogue: warp `m` finishes batch row m.
-  for (int m = warp; m < M; m += 7) {
+  // Epilogue: warp w finishes batch rows w, w+7.
+#pragma unroll
+  for (int i = 0; i < (M + 6) / 7; ++i) {
+    const int m = warp + 7 * i;
+    if (m >= M) break;
     float v = 0.f;
 #pragma unroll
     for (int g = 0; g < 7; ++g) v += red[(g * M + m) * 32 + lane];
-    const int b = row0 + m;
     // fp16 linear output with bias, as the reference's GEMM writes it.
     v = __half2float(__float2half_rn(v + __half2float(bias)));
-    const int head = n >> 6;        // 0..13 q, 14..15 k, 16..17 v
-    const int i = n & 63;           // stored order: (pair, half)
-    const int pair = i >> 1, hi = i & 1;
     const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-    // slot is warp-uniform per m: recompute from the arrays to stay in registers.
     int sl = -1, p = 0;
 #pragma unroll
     for (int mm = 0; mm < M; ++mm)
       if (mm == m) { sl = slot[mm]; p = pos[mm]; }
-    if (b >= a.rs.batch || sl < 0) continue;
+    if (sl < 0) continue;
+    const int b = row0 + m;
     float out = v;
     if (head < kHeads + kKvHeads) {
-      const int pp = p < a.max_pos ? p : a.max_pos - 1;
-      const float c = __half2float(a.cos_t[(size_t)pp * 32 + pair]);
-      const float s = __half2float(a.sin_t[(size_t)pp * 32 + pair]);
       const float lo = hi ? other : v, up = hi ? v : other;
-      out = hi ? (lo * s + up * c) : (lo * c - up * s);
+      out = hi ? (lo * sn[i] + up * cs[i]) : (lo * cs[i] - up * sn[i]);
     }
     const int dim = pair + 32 * hi;
     const half o16 = __float2half_rn(out);
@@ -226,14 +310,19 @@ __global__ void __launch_bounds__(224) qkv_kernel(const QkvArgs a) {
       base[(((size_t)sl * kKvHeads + kvh) * a.s_max + p) * kHeadDim + dim] = o16;
     }
   }
+  QUIC_TLOG_END();
 }
 
 // ---------------------------------------------------------------------------
-// K3: o_proj GEMV + residual add.  grid (28, ceil(batch/M)), block 224.
+// K3: (merge of the attention splits) -> o_proj GEMV -> residual add.
+// grid (28, ceil(batch/M)), block 224.  With a.splits > 0 the kernel reads the
+// split partials of the attention kernel and merges them itself (every CTA
+// redundantly: 896 values x splits), which saves the attention kernel an atomic
+// round trip and a second pass.
 // ---------------------------------------------------------------------------
 template <int M>
 __global__ void __launch_bounds__(224) oproj_kernel(const OProjArgs a) {
-  __shared__ __align__(16) float xs[M * kHidden];
+  __shared__ __align__(16) half xs[M * kHidden];
   __shared__ float red[7 * M * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 32 + lane;
@@ -241,95 +330,195 @@ __global__ void __launch_bounds__(224) oproj_kernel(const OProjArgs a) {
 
   GroupRegs gr;
   load_group(gr, a.w, warp, n);
-  pdl_launch_dependents();
+  GroupF16 gf;
+  dequant_group(gr, n, gf);
+  pdl_trigger_early();
   pdl_wait();
+  QUIC_TLOG_BEGIN(3);
 
   {
     const int t = threadIdx.x;  // 224 threads x 4 elements
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row0 + m < a.batch)
-        v = half4_to_float4(
-            *reinterpret_cast<const Half4*>(a.attn + (size_t)(row0 + m) * kHidden + 4 * t));
-      float* dst = xs + m * kHidden;
-      dst[perm_k(4 * t + 0)] = v.x;
-      dst[perm_k(4 * t + 1)] = v.y;
-      dst[perm_k(4 * t + 2)] = v.z;
-      dst[perm_k(4 * t + 3)] = v.w;
+      const int b = row0 + m;
+      if (b < a.batch) {
+        if (a.splits > 0) {
+          const int qh = (4 * t) >> 6, d = (4 * t) & 63;
+          const size_t row = ((size_t)b * kHeads + qh) * a.splits;
+          float ms[kMaxConsumerSplits], ls[kMaxConsumerSplits];
+          float4 os[kMaxConsumerSplits];
+#pragma unroll
+          for (int s = 0; s < kMaxConsumerSplits; ++s) {  // every load in flight together
+            ms[s] = -INFINITY;
+            ls[s] = 0.f;
+            os[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s < a.splits) {
+              ms[s] = __ldcg(a.m_part + row + s);
+              ls[s] = __ldcg(a.l_part + row + s);
+              os[s] = __ldcg(reinterpret_cast<const float4*>(a.o_part + (row + s) * kHeadDim + d));
+            }
+          }
+          float mx = -INFINITY;
+#pragma unroll
+          for (int s = 0; s < kMaxConsumerSplits; ++s) mx = fmaxf(mx, ms[s]);
+          if (mx != -INFINITY) {
+            float den = 0.f;
+            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < kMaxConsumerSplits; ++s) {
+              const float e = (ms[s] == -INFINITY) ? 0.f : __expf(ms[s] - mx);
+              den += e * ls[s];
+              num.x += e * os[s].x; num.y += e * os[s].y; num.z += e * os[s].z; num.w += e * os[s].w;
+            }
+            // the attention output is an fp16 tensor in the reference
+            v.x = __half2float(__float2half_rn(num.x / den));
+            v.y = __half2float(__float2half_rn(num.y / den));
+            v.z = __half2float(__float2half_rn(num.z / den));
+            v.w = __half2float(__float2half_rn(num.w / den));
+          }
+        } else {
+          v = half4_to_float4(*reinterpret_cast<const Half4*>(a.attn + (size_t)b * kHidden + 4 * t));
+        }
+      }
+      half* dst = xs + m * kHidden;  // values are fp16 already: exact
+      dst[perm_k(4 * t + 0)] = __float2half_rn(v.x);
+      dst[perm_k(4 * t + 1)] = __float2half_rn(v.y);
+      dst[perm_k(4 * t + 2)] = __float2half_rn(v.z);
+      dst[perm_k(4 * t + 3)] = __float2half_rn(v.w);
     }
+  }
+  // residual values for the epilogue rows of this warp: request them now
+  float resid[(M + 6) / 7];
+#pragma unroll
+  for (int i = 0; i < (M + 6) / 7; ++i) {
+    const int m = warp + 7 * i;
+    resid[i] = (m < M && row0 + m < a.batch) ? __half2float(a.xres_in[(size_t)(row0 + m) * kHidden + n]) : 0.f;
   }
   __syncthreads();
 
   float acc[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) acc[m] = 0.f;
-  group_fma<M>(gr, xs + warp * kGroup, kHidden, acc);
+  group_fma<M>(gf, xs + warp * kGroup, kHidden, acc);
+  pdl_trigger_late();
 #pragma unroll
   for (int m = 0; m < M; ++m) red[(warp * M + m) * 32 + lane] = acc[m];
   __syncthreads();
 
-  for (int m = warp; m < M; m += 7) {
+#pragma unroll
+  for (int i = 0; i < (M + 6) / 7; ++i) {
+    const int m = warp + 7 * i;
+    if (m >= M) break;
     const int b = row0 + m;
     if (b >= a.batch) continue;
     float v = 0.f;
 #pragma unroll
     for (int g = 0; g < 7; ++g) v += red[(g * M + m) * 32 + lane];
     const float o = __half2float(__float2half_rn(v));
-    const float r = __half2float(a.xres_in[(size_t)b * kHidden + n]);
-    a.xres_out[(size_t)b * kHidden + n] = __float2half_rn(r + o);
+    a.xres_out[(size_t)b * kHidden + n] = __float2half_rn(resid[i] + o);
   }
+  QUIC_TLOG_END();
 }
 
 // ---------------------------------------------------------------------------
-// K4: RMSNorm -> gate & up GEMV -> SwiGLU.  grid (152, ceil(batch/M)), block 224.
-// Lane l owns gate column n and up column n + 4864.
+// K4: RMSNorm -> gate & up GEMV (SwiGLU is applied by the consumer).
+// Work unit = (tile of 32 columns, quantisation group): 152 x 7 = 1064 units,
+// dealt 8 per CTA to 133 CTAs of 8 warps, so every SM gets the same amount and
+// the whole kernel is one wave (152 column tiles on 148 SMs would leave four
+// SMs with double work).  The 7 units of a tile span at most two CTAs; each
+// writes its fp32 partial sums to gu_part[part][gate|up][row][4864] (a CTA that
+// owns the whole tile writes zeros to part 1) and the down kernel adds the two
+// parts, rounds to fp16 and applies SwiGLU.  grid (133, ceil(batch/M)), block 256.
 // ---------------------------------------------------------------------------
+constexpr int kGuUnitsPerCta = 8;
+constexpr int kGuCtas = (kInter / 32) * 7 / kGuUnitsPerCta;  // 133
+
 template <int M>
-__global__ void __launch_bounds__(224) gateup_kernel(const GateUpArgs a) {
-  __shared__ __align__(16) float xs[M * kHidden];
-  __shared__ float red[7 * M * 2 * 32];
+__global__ void __launch_bounds__(256) gateup_kernel(const GateUpArgs a) {
+  __shared__ __align__(16) half xs[M * kHidden];
+  __shared__ float red[8 * M * 2 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * 32 + lane;
+  const int unit = blockIdx.x * kGuUnitsPerCta + warp;
+  const int tile = unit / 7, g = unit % 7;
+  const int n = tile * 32 + lane;
   const int row0 = blockIdx.y * M;
 
+  QUIC_STAMP(2, 0);
   GroupRegs gg, gu;
-  load_group(gg, a.w, warp, n);
-  load_group(gu, a.w, warp, n + kInter);
-  pdl_launch_dependents();
+  load_group(gg, a.w, g, n);
+  load_group(gu, a.w, g, n + kInter);
+  const float4 lnw = load_ln(a.ln);
+  // With few batch rows the dequantised weights fit in registers: do it before the wait.
+  GroupF16 fg, fu;
+  if (M <= 2) {
+    dequant_group(gg, n, fg);
+    dequant_group(gu, n + kInter, fu);
+  }
+  QUIC_STAMP(2, 1);
+  pdl_trigger_early();
   pdl_wait();
+  QUIC_TLOG_BEGIN(4);
+  QUIC_STAMP(2, 2);
 
   const half* src[M];
 #pragma unroll
   for (int m = 0; m < M; ++m)
     src[m] = (row0 + m < a.batch) ? a.xres + (size_t)(row0 + m) * kHidden : nullptr;
-  residual_norm_to_smem<M>(xs, red, src, nullptr, 0, a.batch, row0, a.ln, a.eps, nullptr);
+  residual_norm_to_smem<M>(xs, red, src, nullptr, 0, a.batch, row0, lnw, a.eps, nullptr);
+  QUIC_STAMP(2, 3);
 
   float ag[M], au[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) ag[m] = au[m] = 0.f;
-  group_fma<M>(gg, xs + warp * kGroup, kHidden, ag);
-  group_fma<M>(gu, xs + warp * kGroup, kHidden, au);
+  if (M <= 2) {
+    group_fma<M>(fg, xs + g * kGroup, kHidden, ag);
+    group_fma<M>(fu, xs + g * kGroup, kHidden, au);
+  } else {
+    group_fma_packed<M>(gg, n, xs + g * kGroup, kHidden, ag);
+    group_fma_packed<M>(gu, n + kInter, xs + g * kGroup, kHidden, au);
+  }
+  pdl_trigger_late();
 #pragma unroll
   for (int m = 0; m < M; ++m) {
     red[((warp * M + m) * 2 + 0) * 32 + lane] = ag[m];
     red[((warp * M + m) * 2 + 1) * 32 + lane] = au[m];
   }
+  QUIC_STAMP(2, 4);
   __syncthreads();
+  QUIC_STAMP(2, 5);
 
-  for (int m = warp; m < M; m += 7) {
-    const int b = row0 + m;
-    if (b >= a.batch) continue;
-    float g = 0.f, u = 0.f;
-#pragma unroll
-    for (int w = 0; w < 7; ++w) {
-      g += red[((w * M + m) * 2 + 0) * 32 + lane];
-      u += red[((w * M + m) * 2 + 1) * 32 + lane];
+  // Warps 0 and 1 finish the (at most two) tiles this CTA touches.
+  if (warp < 2) {
+    const int first_unit = blockIdx.x * kGuUnitsPerCta;
+    const int t = first_unit / 7 + warp;
+    const int u_lo = max(7 * t, first_unit), u_hi = min(7 * t + 7, first_unit + kGuUnitsPerCta);
+    if (u_lo < u_hi) {
+      const int c_a = (7 * t) / kGuUnitsPerCta, c_b = (7 * t + 6) / kGuUnitsPerCta;
+      const int part = blockIdx.x - c_a;
+      const int col = t * 32 + lane;
+      const size_t plane = (size_t)a.batch * kInter;  // one (part, stream)
+      for (int m = 0; m < M; ++m) {
+        const int b = row0 + m;
+        if (b >= a.batch) continue;
+        float sg = 0.f, su = 0.f;
+        for (int u = u_lo; u < u_hi; ++u) {
+          const int w = u - first_unit;
+          sg += red[((w * M + m) * 2 + 0) * 32 + lane];
+          su += red[((w * M + m) * 2 + 1) * 32 + lane];
+        }
+        float* dst = a.gu_part + (size_t)b * kInter + col;
+        dst[(2 * part + 0) * plane] = sg;
+        dst[(2 * part + 1) * plane] = su;
+        if (c_a == c_b) {
+          dst[2 * plane] = 0.f;
+          dst[3 * plane] = 0.f;
+        }
+      }
     }
-    g = __half2float(__float2half_rn(g));
-    u = __half2float(__float2half_rn(u));
-    a.act[(size_t)b * kInter + n] = __float2half_rn(silu_mul(g, u));
   }
+  QUIC_STAMP(2, 6);
+  QUIC_TLOG_END();
 }
 
 // ---------------------------------------------------------------------------
@@ -339,7 +528,7 @@ __global__ void __launch_bounds__(224) gateup_kernel(const GateUpArgs a) {
 // ---------------------------------------------------------------------------
 template <int M>
 __global__ void __launch_bounds__(256) down_kernel(const DownArgs a) {
-  __shared__ __align__(16) float xs[M * 8 * kGroup];
+  __shared__ __align__(16) half xs[M * 8 * kGroup];
   __shared__ float red[8 * M * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 32 + lane;
@@ -349,29 +538,51 @@ __global__ void __launch_bounds__(256) down_kernel(const DownArgs a) {
   const bool has = g0 + warp < g1;
 
   GroupRegs gr;
-  if (has) load_group(gr, a.w, g0 + warp, n);
-  pdl_launch_dependents();
+  GroupF16 gf;
+  if (has) {
+    load_group(gr, a.w, g0 + warp, n);
+    dequant_group(gr, n, gf);
+  }
+  pdl_trigger_early();
   pdl_wait();
+  QUIC_TLOG_BEGIN(5);
 
+  // Activation slice: add the two gate/up partial planes, round to fp16 (the
+  // reference's linear outputs are fp16), SwiGLU, round again.
   const int kspan = (g1 - g0) * kGroup;
+  const size_t plane = (size_t)a.batch * kInter;
   for (int idx = threadIdx.x; idx < M * (kspan / 4); idx += 256) {
     const int m = idx / (kspan / 4), c = idx % (kspan / 4);
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row0 + m < a.batch)
-      v = half4_to_float4(*reinterpret_cast<const Half4*>(
-          a.act + (size_t)(row0 + m) * kInter + g0 * kGroup + 4 * c));
-    float* dst = xs + m * (8 * kGroup);
-    dst[perm_k(4 * c + 0)] = v.x;
-    dst[perm_k(4 * c + 1)] = v.y;
-    dst[perm_k(4 * c + 2)] = v.z;
-    dst[perm_k(4 * c + 3)] = v.w;
+    if (row0 + m < a.batch) {
+      const float* p = a.gu_part + (size_t)(row0 + m) * kInter + g0 * kGroup + 4 * c;
+      const float4 g0v = __ldcg(reinterpret_cast<const float4*>(p));
+      const float4 u0v = __ldcg(reinterpret_cast<const float4*>(p + plane));
+      const float4 g1v = __ldcg(reinterpret_cast<const float4*>(p + 2 * plane));
+      const float4 u1v = __ldcg(reinterpret_cast<const float4*>(p + 3 * plane));
+      auto act = [](float ga, float gb, float ua, float ub) {
+        const float gg = __half2float(__float2half_rn(ga + gb));
+        const float uu = __half2float(__float2half_rn(ua + ub));
+        return silu_mul(gg, uu);
+      };
+      v.x = act(g0v.x, g1v.x, u0v.x, u1v.x);
+      v.y = act(g0v.y, g1v.y, u0v.y, u1v.y);
+      v.z = act(g0v.z, g1v.z, u0v.z, u1v.z);
+      v.w = act(g0v.w, g1v.w, u0v.w, u1v.w);
+    }
+    half* dst = xs + m * (8 * kGroup);
+    dst[perm_k(4 * c + 0)] = __float2half_rn(v.x);
+    dst[perm_k(4 * c + 1)] = __float2half_rn(v.y);
+    dst[perm_k(4 * c + 2)] = __float2half_rn(v.z);
+    dst[perm_k(4 * c + 3)] = __float2half_rn(v.w);
   }
   __syncthreads();
 
   float acc[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) acc[m] = 0.f;
-  if (has) group_fma<M>(gr, xs + warp * kGroup, 8 * kGroup, acc);
+  if (has) group_fma<M>(gf, xs + warp * kGroup, 8 * kGroup, acc);
+  pdl_trigger_late();
 #pragma unroll
   for (int m = 0; m < M; ++m) red[(warp * M + m) * 32 + lane] = acc[m];
   __syncthreads();
@@ -384,6 +595,7 @@ __global__ void __launch_bounds__(256) down_kernel(const DownArgs a) {
     for (int g = 0; g < 8; ++g) v += red[(g * M + m) * 32 + lane];
     a.partial[((size_t)ks * a.batch + b) * kHidden + n] = v;
   }
+  QUIC_TLOG_END();
 }
 
 template <int M>
@@ -398,8 +610,8 @@ cudaError_t launch_oproj_m(const OProjArgs& a, cudaStream_t s, bool pdl) {
 }
 template <int M>
 cudaError_t launch_gateup_m(const GateUpArgs& a, cudaStream_t s, bool pdl) {
-  dim3 grid(kInter / 32, (a.batch + M - 1) / M);
-  return launch(gateup_kernel<M>, grid, dim3(224), 0, s, pdl, a);
+  dim3 grid(kGuCtas, (a.batch + M - 1) / M);
+  return launch(gateup_kernel<M>, grid, dim3(256), 0, s, pdl, a);
 }
 template <int M>
 cudaError_t launch_down_m(const DownArgs& a, cudaStream_t s, bool pdl) {
@@ -433,3 +645,13 @@ cudaError_t launch_down(const DownArgs& a, cudaStream_t s, bool pdl) {
 }
 
 }  // namespace quic
+
+#ifdef QUIC_TRACE
+extern "C" int quic_trace_read(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, quic::g_trace, sizeof(long long) * 4 * 8 * 8);
+}
+#endif
+
+#ifdef QUIC_TRACE
+QUIC_TRACE_SETTER(layers)
+#endif

@@ -36,7 +36,7 @@ Arena carve(int batch, int vocab, int splits) {
   a.attn_out = off;
   off += align256((int64_t)batch * kHidden * 2);
   a.act = off;
-  off += align256((int64_t)batch * kInter * 2);
+  off += align256((int64_t)4 * batch * kInter * 4);
   a.partial = off;
   off += align256((int64_t)kDownSplits * batch * kHidden * 4);
   const int grid = lm_head_grid(vocab);
@@ -52,7 +52,7 @@ int pick_splits(const quic_decode_t* d) {
   if (d->attn_splits > 0) return d->attn_splits;
   int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
   if (ctx > d->s_max) ctx = d->s_max;
-  return quic_attn_pick_splits(d->batch, ctx);
+  return quic_decode_pick_splits(d->batch, ctx);
 }
 
 int check(const quic_model_t* m, const quic_decode_t* d) {
@@ -88,7 +88,7 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st)
                    reinterpret_cast<half*>(base + ar.xres) + (size_t)B * kHidden};
   half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
   half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
-  half* act = reinterpret_cast<half*>(base + ar.act);
+  float* gu_part = reinterpret_cast<float*>(base + ar.act);
   float* partial = reinterpret_cast<float*>(base + ar.partial);
 
   const size_t slot_stride = (size_t)kKvHeads * d->s_max * kHeadDim;  // one slot, K or V
@@ -140,12 +140,20 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st)
     aa.chunk = (ctx + splits - 1) / splits;
     aa.scale = 0.125f;  // 64^-0.5, src/model.py:129
     aa.out = attn_out;
+    // 64-token CTAs (latency variant) when the split count says so
+    aa.small = (splits <= kMaxConsumerSplits && (int64_t)splits * 64 >= ctx) ? 1 : 0;
+    const bool consumer_merge = splits > 1 && splits <= kMaxConsumerSplits;
+    aa.consumer_merge = consumer_merge ? 1 : 0;
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
     QUIC_CUDA(launch_attn(aa, B, st, true));
 
     OProjArgs oa = {};
     oa.w = L.o;
     oa.attn = attn_out;
+    oa.splits = consumer_merge ? splits : 0;
+    oa.o_part = aa.o_part;
+    oa.m_part = aa.m_part;
+    oa.l_part = aa.l_part;
     oa.xres_in = xres[0];
     oa.xres_out = xres[1];
     oa.batch = B;
@@ -155,14 +163,14 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st)
     ga.w = L.gate_up;
     ga.ln = (const half*)L.ln2;
     ga.xres = xres[1];
-    ga.act = act;
+    ga.gu_part = gu_part;
     ga.batch = B;
     ga.eps = m->eps;
     QUIC_CUDA(launch_gateup(ga, st, true));
 
     DownArgs da = {};
     da.w = L.down;
-    da.act = act;
+    da.gu_part = gu_part;
     da.partial = partial;
     da.batch = B;
     QUIC_CUDA(launch_down(da, st, true));
@@ -200,6 +208,15 @@ struct Graph {
 }  // namespace quic
 
 using namespace quic;
+
+extern "C" int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx) {
+  if (batch < 1) batch = 1;
+  if (ctx < 1) ctx = 1;
+  // Short contexts at small batch: one CTA per 64 tokens, merged by the o_proj kernel.
+  const int small = (ctx + 63) / 64;
+  if (small <= kMaxConsumerSplits && (int64_t)batch * small * kKvHeads <= 1184) return small;
+  return quic_attn_pick_splits(batch, ctx);
+}
 
 extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32_t attn_splits) {
   if (batch < 1 || vocab < 2 || attn_splits < 1) return 0;

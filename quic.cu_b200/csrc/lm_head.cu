@@ -41,8 +41,8 @@ __device__ __forceinline__ Best warp_best(Best x) {
 }
 
 template <int M>
-__global__ void __launch_bounds__(kThreads) lm_head_kernel(const LmHeadArgs a) {
-  __shared__ __align__(16) float xs[M * kHidden];
+__global__ void __launch_bounds__(kThreads, 1) lm_head_kernel(const LmHeadArgs a) {
+  __shared__ __align__(16) half xh[M * kHidden];
   __shared__ float red[M * 32];
   __shared__ float bv_s[M][kThreads / 32];
   __shared__ int bi_s[M][kThreads / 32];
@@ -61,8 +61,9 @@ __global__ void __launch_bounds__(kThreads) lm_head_kernel(const LmHeadArgs a) {
     const char* rowp = reinterpret_cast<const char*>(a.embed) + (size_t)p * 2 * kHidden * 2;
     prefetch_l2(rowp + lane * 112);
   }
-  pdl_launch_dependents();
+  pdl_trigger_early();
   pdl_wait();
+  QUIC_TLOG_BEGIN(6);
 
   // ---- activation: (x + partial sums) -> RMSNorm -> xs (natural order) ----
   {
@@ -130,7 +131,11 @@ __global__ void __launch_bounds__(kThreads) lm_head_kernel(const LmHeadArgs a) {
           v.z = __half2float(__float2half_rn(v.z * r * w.z));
           v.w = __half2float(__float2half_rn(v.w * r * w.w));
         }
-        *reinterpret_cast<float4*>(&xs[m * kHidden + 4 * tid]) = v;
+        half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);  // exact: already fp16 values
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        *reinterpret_cast<uint2*>(&xh[m * kHidden + 4 * tid]) = pk;
       }
     }
     __syncthreads();
@@ -140,13 +145,11 @@ __global__ void __launch_bounds__(kThreads) lm_head_kernel(const LmHeadArgs a) {
   int dim[kVecPerLane];
 #pragma unroll
   for (int j = 0; j < kVecPerLane; ++j) dim[j] = ((lane + 32 * j) % kVecPerRow) * 8;
-  // For one batch row keep the activation in registers.
-  float xr[(M == 1) ? kVecPerLane * 8 : 1];
+  // For one batch row the activation stays in registers (as fp16 pairs).
+  uint4 xr[(M == 1) ? kVecPerLane : 1];
   if (M == 1) {
 #pragma unroll
-    for (int j = 0; j < kVecPerLane; ++j)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) xr[(M == 1) ? j * 8 + e : 0] = xs[dim[j] + e];
+    for (int j = 0; j < kVecPerLane; ++j) xr[(M == 1) ? j : 0] = *reinterpret_cast<const uint4*>(&xh[dim[j]]);
   }
 
   Best best[M];
@@ -156,45 +159,29 @@ __global__ void __launch_bounds__(kThreads) lm_head_kernel(const LmHeadArgs a) {
     best[m].i = 0x7fffffff;
   }
 
-  for (int p = p_begin + warp; p < p_end; p += kThreads / 32) {
-    const uint4* src = reinterpret_cast<const uint4*>(a.embed + (size_t)p * 2 * kHidden);
-    uint4 wv[kVecPerLane];
-#pragma unroll
-    for (int j = 0; j < kVecPerLane; ++j) wv[j] = ldg_nc_u128(src + lane + 32 * j);
+  // One row pair: 7 x 16-byte pieces per lane -> two logits per batch row.
+  auto consume = [&](int p, const uint4 (&wv)[kVecPerLane]) {
     float acc0[M], acc1[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc0[m] = acc1[m] = 0.f;
 #pragma unroll
     for (int j = 0; j < kVecPerLane; ++j) {
-      const half2* h2 = reinterpret_cast<const half2*>(&wv[j]);
-      float wf[8];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __half22float2(h2[e]);
-        wf[2 * e] = f.x;
-        wf[2 * e + 1] = f.y;
-      }
+      const half2* w2 = reinterpret_cast<const half2*>(&wv[j]);
+      // pieces 0..111 of the pair belong to the first row
+      const bool first = (j < 3) || (j == 3 && lane < 16);
 #pragma unroll
       for (int m = 0; m < M; ++m) {
-        float s = 0.f;
-        if (M == 1) {
+        uint4 xv;
+        if (M == 1) xv = xr[(M == 1) ? j : 0];
+        else xv = *reinterpret_cast<const uint4*>(&xh[m * kHidden + dim[j]]);
+        const half2* x2 = reinterpret_cast<const half2*>(&xv);
+        float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) s = fmaf(wf[e], xr[(M == 1) ? j * 8 + e : 0], s);
-        } else {
-          const float4 xa = *reinterpret_cast<const float4*>(&xs[m * kHidden + dim[j]]);
-          const float4 xb = *reinterpret_cast<const float4*>(&xs[m * kHidden + dim[j] + 4]);
-          s = wf[0] * xa.x;
-          s = fmaf(wf[1], xa.y, s);
-          s = fmaf(wf[2], xa.z, s);
-          s = fmaf(wf[3], xa.w, s);
-          s = fmaf(wf[4], xb.x, s);
-          s = fmaf(wf[5], xb.y, s);
-          s = fmaf(wf[6], xb.z, s);
-          s = fmaf(wf[7], xb.w, s);
+        for (int e = 0; e < 4; ++e) {
+          s0 = fma_h(s0, __low2half(w2[e]), __low2half(x2[e]));
+          s1 = fma_h(s1, __high2half(w2[e]), __high2half(x2[e]));
         }
-        // pieces 0..111 of the pair belong to the first row
-        const bool first = (j < 3) || (j == 3 && lane < 16);
-        if (first) acc0[m] += s; else acc1[m] += s;
+        if (first) acc0[m] += s0 + s1; else acc1[m] += s0 + s1;
       }
     }
 #pragma unroll
@@ -211,6 +198,30 @@ __global__ void __launch_bounds__(kThreads) lm_head_kernel(const LmHeadArgs a) {
       c.v = l1;
       c.i = 2 * p + 1;
       best[m] = better(best[m], c);
+    }
+  };
+
+  if (M <= 2) {
+    // Two row pairs (7 KB per warp) are requested before either is consumed.
+    for (int p = p_begin + 2 * warp; p < p_end; p += 2 * (kThreads / 32)) {
+      const bool two = p + 1 < p_end;
+      const uint4* src0 = reinterpret_cast<const uint4*>(a.embed + (size_t)p * 2 * kHidden);
+      const uint4* src1 = reinterpret_cast<const uint4*>(a.embed + (size_t)(two ? p + 1 : p) * 2 * kHidden);
+      uint4 wa[kVecPerLane], wb[kVecPerLane];
+#pragma unroll
+      for (int j = 0; j < kVecPerLane; ++j) wa[j] = ldg_nc_u128(src0 + lane + 32 * j);
+#pragma unroll
+      for (int j = 0; j < kVecPerLane; ++j) wb[j] = ldg_nc_u128(src1 + lane + 32 * j);
+      consume(p, wa);
+      if (two) consume(p + 1, wb);
+    }
+  } else {
+    for (int p = p_begin + warp; p < p_end; p += kThreads / 32) {
+      const uint4* src0 = reinterpret_cast<const uint4*>(a.embed + (size_t)p * 2 * kHidden);
+      uint4 wa[kVecPerLane];
+#pragma unroll
+      for (int j = 0; j < kVecPerLane; ++j) wa[j] = ldg_nc_u128(src0 + lane + 32 * j);
+      consume(p, wa);
     }
   }
 
@@ -235,6 +246,7 @@ __global__ void __launch_bounds__(kThreads) lm_head_kernel(const LmHeadArgs a) {
     }
   }
 
+  QUIC_TLOG_END();
   // Last CTA (over the whole grid) reduces the candidates of every row.
   __threadfence();
   __syncthreads();
@@ -287,7 +299,7 @@ cudaError_t launch_lm_head_m(const LmHeadArgs& a, int grid, cudaStream_t s, bool
 
 int lm_head_grid(int vocab) {
   int pairs = vocab / 2;
-  int g = 148 * 2;
+  int g = 148;  // one persistent CTA per SM
   if (g > pairs) g = pairs > 0 ? pairs : 1;
   return g;
 }
@@ -341,3 +353,7 @@ extern "C" int quic_lm_head_argmax(const void* x, const void* norm_w, float eps,
   QUIC_CUDA(launch_lm_head(a, grid, (cudaStream_t)stream, false));
   return QUIC_OK;
 }
+
+#ifdef QUIC_TRACE
+QUIC_TRACE_SETTER(lm)
+#endif

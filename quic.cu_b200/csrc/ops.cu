@@ -297,3 +297,4 @@ extern "C" int quic_gemm_f16(const void* x, const void* w, const void* bias, voi
   QUIC_CUDA(cudaGetLastError());
   return QUIC_OK;
 }
+

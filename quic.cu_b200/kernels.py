@@ -114,6 +114,7 @@ SIGNATURES = {
     "quic_attn_decode_noalloc_max_bytes": (_I64, []),
     "quic_attn_pick_splits": (_I32, [_I32, _I32]),
     "quic_attn_scratch_bytes": (_I64, [_I32, _I32]),
+    "quic_decode_pick_splits": (_I32, [_I32, _I32]),
     "quic_decode_scratch_bytes": (_I64, [_I32, _I32, _I32]),
     "quic_decode_launch_count": (_I32, [C.POINTER(Model), C.POINTER(Decode)]),
     "quic_decode_step": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _P]),

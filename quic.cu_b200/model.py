@@ -207,7 +207,7 @@ class QUICForCausalLM:
 
     # ---- decode ----------------------------------------------------------------
     def _decode_struct(self, cache: SlotCache, batch: int, ctx: int, logits: torch.Tensor | None):
-        splits = K.lib().quic_attn_pick_splits(batch, ctx)
+        splits = K.lib().quic_decode_pick_splits(batch, ctx)
         rows = cache._rows.setdefault(("buf", batch), torch.zeros(batch, dtype=torch.int32, device=self.device))
         d = K.Decode(K.ptr(cache.kv), cache.n_slots, cache.s_max, K.ptr(cache.tok), K.ptr(cache.pos),
                      K.ptr(rows), batch, K.ptr(cache.out_tokens), cache.ring, K.ptr(cache.step_counter),
