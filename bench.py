@@ -96,13 +96,13 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
-def build_model(device: str):
+def build_model(device: str, layers: int = 24):
     entry.load_package()
     from quic_cu_b200 import model as qmodel
     from quic_cu_b200.checkpoint import qwen_config_dict, synthetic_checkpoint
 
-    state = synthetic_checkpoint(n_layers=24, vocab=151936, seed=0)
-    net = qmodel.from_state_dict(state, qwen_config_dict(24, 151936), device=device)
+    state = synthetic_checkpoint(n_layers=layers, vocab=151936, seed=0)
+    net = qmodel.from_state_dict(state, qwen_config_dict(layers, 151936), device=device)
     return net, state
 
 
@@ -177,7 +177,7 @@ def run_gpu(args) -> None:
     entry.load_package()
     from quic_cu_b200 import kernels as K
 
-    net, state = build_model(device)
+    net, state = build_model(device, args.layers)
     cache = net.new_cache(n_slots=1, s_max=1024)
     gen_ids = torch.Generator().manual_seed(rank)  # every replica serves its own request
     prompt = torch.randint(0, 151936, (PROMPT_LEN,), generator=gen_ids)
@@ -282,7 +282,9 @@ def run_gpu(args) -> None:
         "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * GEN_TOKENS * net.launches_per_step(),
         "roofline": roofline, "roofline_step": roofline_step,
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if args.layers != 24:
+        line["invalid"] = "reduced layer count: profiling run, not a benchmark"
+    if world == 1 and not args.no_cpu_baseline and args.layers == 24:
         del net, cache
         base, _ = cpu_baseline(state, threads=os.cpu_count(), gen=16, repeats=1, warmup=0)
         line["cpu_baseline"] = base
@@ -292,8 +294,8 @@ def run_gpu(args) -> None:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one lm_head_kernel<1> launch at vocab 151936,
-# from the ncu capture summarised in profiles/ (None until a capture exists).
-LM_HEAD_TRAFFIC_BYTES = None
+# from the ncu capture summarised in profiles/lm_head_kernel_batch1_vocab151936.md.
+LM_HEAD_TRAFFIC_BYTES = 276_400_000
 
 
 def main() -> None:
@@ -303,6 +305,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="quic_b200", choices=["quic_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=24,
+                    help="decoder layers of the synthetic model; values below 24 exist only to keep "
+                         "profiler captures small and do not produce a valid benchmark line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -103,6 +103,11 @@ int quic_w4a16_linear(const void *x_f16, const quic_w4_t *w, void *y_f16,
                       int32_t m, int32_t use_tensor, void *workspace,
                       void *stream);
 int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k);
+/* Error word of the tensor path: 0, or a non-zero code if a bounded wait inside
+ * the tcgen05 kernel gave up since the last call (results are then invalid).
+ * Synchronises the device; for tests and debugging.  No reference counterpart
+ * (Marlin's lock spins are unbounded, kernels/cuda/marlin.cu:1467-1476). */
+int quic_w4a16_tensor_status(void);
 
 /* ------------------------------------------------------------------------
  * Stand-alone operators with the reference's per-op signatures.

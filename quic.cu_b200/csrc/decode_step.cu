@@ -19,7 +19,19 @@ inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
 struct Arena {
   int64_t lm_counter, attn, xres, qbuf, attn_out, act, partial, best_val, best_idx, total;
+  // batched step (batch > kMaxM) only
+  int64_t xn, qkv, gu, act16, tcws;
 };
+
+int64_t tc_workspace_bytes(int batch) {
+  int64_t w = w4a16_gemm_tc_workspace(batch, kQkvN, kHidden);
+  const int64_t o = w4a16_gemm_tc_workspace(batch, kHidden, kHidden);
+  const int64_t g = w4a16_gemm_tc_workspace(batch, 2 * kInter, kHidden);
+  const int64_t d = w4a16_gemm_tc_workspace(batch, kHidden, kInter);
+  w = w > o ? w : o;
+  w = w > g ? w : g;
+  return w > d ? w : d;
+}
 
 // The regions that must start zeroed (arrival counters) come first.
 Arena carve(int batch, int vocab, int splits) {
@@ -44,6 +56,19 @@ Arena carve(int batch, int vocab, int splits) {
   off += align256((int64_t)batch * grid * 4);
   a.best_idx = off;
   off += align256((int64_t)batch * grid * 4);
+  a.xn = a.qkv = a.gu = a.act16 = a.tcws = off;
+  if (batch > kMaxM) {
+    a.xn = off;
+    off += align256((int64_t)batch * kHidden * 2);
+    a.qkv = off;
+    off += align256((int64_t)batch * kQkvN * 2);
+    a.gu = off;
+    off += align256((int64_t)batch * 2 * kInter * 2);
+    a.act16 = off;
+    off += align256((int64_t)batch * kInter * 2);
+    a.tcws = off;
+    off += align256(tc_workspace_bytes(batch));
+  }
   a.total = off;
   return a;
 }
@@ -79,8 +104,11 @@ int check(const quic_model_t* m, const quic_decode_t* d) {
   return QUIC_OK;
 }
 
+int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st);
+
 int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st) {
   const int B = d->batch;
+  if (B > kMaxM) return enqueue_step_batched(m, d, st);
   const int splits = pick_splits(d);
   const Arena ar = carve(B, m->vocab, splits);
   char* base = static_cast<char*>(d->scratch);
@@ -199,6 +227,89 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st)
   return QUIC_OK;
 }
 
+// Batch > 8: every linear is the tcgen05 GEMM; norms, RoPE/KV append and SwiGLU are
+// separate small kernels (at these sizes each kernel does microseconds of real work, so
+// the launch chain is no longer what bounds the step).
+int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st) {
+  const int B = d->batch;
+  const int splits = pick_splits(d);
+  const Arena ar = carve(B, m->vocab, splits);
+  char* base = static_cast<char*>(d->scratch);
+  half* h = reinterpret_cast<half*>(base + ar.xres);        // residual stream
+  half* tmp = h + (size_t)B * kHidden;                        // o_proj / down output
+  half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
+  half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
+  half* xn = reinterpret_cast<half*>(base + ar.xn);
+  half* qkv = reinterpret_cast<half*>(base + ar.qkv);
+  half* gu = reinterpret_cast<half*>(base + ar.gu);
+  half* act = reinterpret_cast<half*>(base + ar.act16);
+  float* ws = reinterpret_cast<float*>(base + ar.tcws);
+  const size_t slot_stride = (size_t)kKvHeads * d->s_max * kHeadDim;
+  const size_t kv_plane = (size_t)d->n_slots * slot_stride;
+  int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
+  if (ctx > d->s_max) ctx = d->s_max;
+  const half* embed = (const half*)m->embed;
+
+  QUIC_CUDA(launch_embed_rows(embed, d->rows, d->tok, m->vocab, h, B, st));
+  QUIC_CUDA(launch_rmsnorm(h, nullptr, (const half*)m->layers[0].ln1, m->eps, xn, nullptr, B, st));
+  for (int l = 0; l < m->n_layers; ++l) {
+    const quic_layer_t& L = m->layers[l];
+    half* kc = static_cast<half*>(d->kv) + (size_t)(2 * l) * kv_plane;
+    half* vc = kc + kv_plane;
+    int rc = w4a16_gemm_tc(xn, L.qkv, qkv, B, ws, st);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_qkv_post(qkv, d->rows, d->pos, (const half*)m->rope_cos, (const half*)m->rope_sin,
+                              m->max_pos, qbuf, kc, vc, d->s_max, B, st));
+    AttnArgs aa = {};
+    aa.q = qbuf;
+    aa.k = kc;
+    aa.v = vc;
+    aa.stride_b = (int64_t)slot_stride;
+    aa.stride_h = (int64_t)d->s_max * kHeadDim;
+    aa.rows = d->rows;
+    aa.pos = d->pos;
+    aa.s_cap = ctx;
+    aa.splits = splits;
+    aa.chunk = (ctx + splits - 1) / splits;
+    aa.scale = 0.125f;
+    aa.out = attn_out;
+    aa.small = (splits <= kMaxConsumerSplits && (int64_t)splits * 64 >= ctx) ? 1 : 0;
+    aa.consumer_merge = 0;
+    if (aa.small && splits > 1) aa.small = 0;  // the latency variant leaves the merge to a consumer
+    if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
+    QUIC_CUDA(launch_attn(aa, B, st, false));
+    rc = w4a16_gemm_tc(attn_out, L.o, tmp, B, ws, st);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)L.ln2, m->eps, xn, h, B, st));
+    rc = w4a16_gemm_tc(xn, L.gate_up, gu, B, ws, st);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_swiglu_fused(gu, act, B, st));
+    rc = w4a16_gemm_tc(act, L.down, tmp, B, ws, st);
+    if (rc != QUIC_OK) return rc;
+    const half* next_ln = (l + 1 < m->n_layers) ? (const half*)m->layers[l + 1].ln1 : (const half*)m->final_norm;
+    QUIC_CUDA(launch_rmsnorm(tmp, h, next_ln, m->eps, xn, h, B, st));
+  }
+  LmHeadArgs la = {};
+  la.embed = embed;
+  la.x_normed = xn;
+  la.batch = B;
+  la.vocab = m->vocab;
+  la.eps = m->eps;
+  la.logits = (half*)d->logits;
+  la.best_val = reinterpret_cast<float*>(base + ar.best_val);
+  la.best_idx = reinterpret_cast<int32_t*>(base + ar.best_idx);
+  la.counter = reinterpret_cast<int32_t*>(base + ar.lm_counter);
+  la.rows = d->rows;
+  la.tok = d->tok;
+  la.pos = d->pos;
+  la.out_tokens = d->out_tokens;
+  la.n_slots = d->n_slots;
+  la.ring = d->ring > 0 ? d->ring : 1;
+  la.step_counter = d->step_counter;
+  QUIC_CUDA(launch_lm_head(la, lm_head_grid(m->vocab), st, false));
+  return QUIC_OK;
+}
+
 struct Graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
@@ -224,8 +335,9 @@ extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32
 }
 
 extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_decode_t* d) {
-  (void)d;
-  return m ? 5 * m->n_layers + 1 : 0;
+  if (!m) return 0;
+  if (d && d->batch > kMaxM) return 9 * m->n_layers + 3;  // plus split-K finish kernels
+  return 5 * m->n_layers + 1;
 }
 
 extern "C" int quic_decode_step(const quic_model_t* m, const quic_decode_t* d, void* stream) {

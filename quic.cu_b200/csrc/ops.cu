@@ -210,7 +210,87 @@ __global__ void __launch_bounds__(256) gemv_f16_kernel(const half* __restrict__ 
   }
 }
 
+// ---- pieces of the batched (batch > 8) decode step ------------------------------
+// Embedding rows of the tokens the slots feed next: x[b] = embed[tok[rows[b]]].
+__global__ void embed_rows_kernel(const half* __restrict__ embed, const int32_t* __restrict__ rows,
+                                  const int32_t* __restrict__ tok, int vocab, half* __restrict__ x, int batch) {
+  const int b = blockIdx.x;
+  if (b >= batch) return;
+  int t = tok[rows[b]];
+  t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
+  const uint2* src = reinterpret_cast<const uint2*>(embed + (size_t)t * kHidden);
+  uint2* dst = reinterpret_cast<uint2*>(x + (size_t)b * kHidden);
+  for (int i = threadIdx.x; i < kHidden / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// RoPE + q buffer + KV append from the fused QKV output (columns in rope-pair order,
+// bias already added).  One thread per (row, column pair).
+__global__ void qkv_post_kernel(const half* __restrict__ qkv, const int32_t* __restrict__ rows,
+                                const int32_t* __restrict__ pos, const half* __restrict__ cos_t,
+                                const half* __restrict__ sin_t, int max_pos, half* __restrict__ qbuf,
+                                half* __restrict__ kcache, half* __restrict__ vcache, int s_max, int batch) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= batch * (kQkvN / 2)) return;
+  const int b = idx / (kQkvN / 2), c2 = idx % (kQkvN / 2);
+  const int head = c2 >> 5, pair = c2 & 31;  // stored columns (2*pair, 2*pair+1) = dims (pair, pair+32)
+  const int slot = rows[b];
+  const int p = pos[slot];
+  const float2 v = __half22float2(*reinterpret_cast<const half2*>(qkv + (size_t)b * kQkvN + 2 * c2));
+  float lo = v.x, hi = v.y;
+  if (head < kHeads + kKvHeads) {
+    const int pp = p < max_pos ? p : max_pos - 1;
+    const float c = __half2float(cos_t[(size_t)pp * 32 + pair]), s = __half2float(sin_t[(size_t)pp * 32 + pair]);
+    lo = v.x * c - v.y * s;
+    hi = v.x * s + v.y * c;
+  }
+  half* dst;
+  if (head < kHeads) {
+    dst = qbuf + ((size_t)b * kHeads + head) * kHeadDim;
+  } else {
+    if (p >= s_max) return;
+    const int kvh = (head - kHeads) & 1;
+    half* base = (head < kHeads + kKvHeads) ? kcache : vcache;
+    dst = base + (((size_t)slot * kKvHeads + kvh) * s_max + p) * kHeadDim;
+  }
+  dst[pair] = __float2half_rn(lo);
+  dst[pair + 32] = __float2half_rn(hi);
+}
+
+// act[b][i] = silu(gu[b][i]) * gu[b][4864 + i] on the fused gate|up output.
+__global__ void swiglu_fused_kernel(const half* __restrict__ gu, half* __restrict__ act, int batch) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)batch * (kInter / 2)) return;
+  const int b = idx / (kInter / 2), i2 = idx % (kInter / 2);
+  const half2* row = reinterpret_cast<const half2*>(gu + (size_t)b * 2 * kInter);
+  const float2 g = __half22float2(row[i2]), u = __half22float2(row[kInter / 2 + i2]);
+  reinterpret_cast<half2*>(act + (size_t)b * kInter)[i2] = __floats2half2_rn(silu_mul(g.x, u.x), silu_mul(g.y, u.y));
+}
+
 }  // namespace
+
+cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,
+                              int batch, cudaStream_t st) {
+  embed_rows_kernel<<<batch, 224, 0, st>>>(embed, rows, tok, vocab, x, batch);
+  return cudaGetLastError();
+}
+cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t* pos, const half* cos_t,
+                            const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
+                            int batch, cudaStream_t st) {
+  const int total = batch * (kQkvN / 2);
+  qkv_post_kernel<<<(total + 255) / 256, 256, 0, st>>>(qkv, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache,
+                                                       vcache, s_max, batch);
+  return cudaGetLastError();
+}
+cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream_t st) {
+  const size_t total = (size_t)batch * (kInter / 2);
+  swiglu_fused_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(gu, act, batch);
+  return cudaGetLastError();
+}
+cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
+                           int rows, cudaStream_t st) {
+  rmsnorm_kernel<<<(rows + 7) / 8, 256, 0, st>>>(x, residual, w, eps, y, sum_out, rows);
+  return cudaGetLastError();
+}
 }  // namespace quic
 
 using namespace quic;

@@ -4,8 +4,6 @@
 #include "decode_kernels.cuh"
 
 namespace quic {
-int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace,
-                  cudaStream_t st);  // w4_gemm_tc.cu
 
 namespace {
 
