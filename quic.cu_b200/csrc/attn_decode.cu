@@ -25,6 +25,40 @@ constexpr int kGroupHeads = kHeads / kKvHeads;  // 7
 constexpr int kWarps = 8;
 constexpr int kTile = 32;
 
+// The CTA that arrives last at the per-(row, kv head) counter merges the split partials of
+// the group's 7 heads, writes the fp16 output and re-arms the counter.  No CTA waits.
+__device__ __forceinline__ void merge_splits_last_cta(const AttnArgs& a, int b, int kvh, int split, int* last_flag_s) {
+  const int tid = threadIdx.x;
+  int& last_flag = *last_flag_s;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&a.counters[b * kKvHeads + kvh], 1);
+    last_flag = (old == a.splits - 1);
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += (int)blockDim.x) {
+    const int h = idx >> 6, d = idx & 63;
+    const int qh = kvh * kGroupHeads + h;
+    const size_t row = ((size_t)b * kHeads + qh) * a.splits;
+    float m = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) m = fmaxf(m, __ldcg(a.m_part + row + s));
+    float num = 0.f, den = 0.f;
+    if (m != -INFINITY) {
+      for (int s = 0; s < a.splits; ++s) {
+        const float ms = __ldcg(a.m_part + row + s);
+        const float e = (ms == -INFINITY) ? 0.f : __expf(ms - m);
+        den += e * __ldcg(a.l_part + row + s);
+        num += e * __ldcg(a.o_part + (row + s) * kHeadDim + d);
+      }
+    }
+    a.out[((size_t)b * kHeads + qh) * kHeadDim + d] =
+        __float2half_rn(m == -INFINITY ? 0.f : num / den);
+  }
+  if (tid == 0) a.counters[b * kKvHeads + kvh] = 0;
+}
 __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs a) {
   __shared__ __align__(16) float q_s[kGroupHeads * kHeadDim];
   __shared__ __align__(16) float p_s[kWarps][kGroupHeads][kTile];
@@ -218,35 +252,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
   QUIC_TLOG_END();
   if (a.splits == 1 || a.consumer_merge) return;
 
-  // Last CTA of this (row, kv head) merges the splits.
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(&a.counters[b * kKvHeads + kvh], 1);
-    last_flag = (old == a.splits - 1);
-  }
-  __syncthreads();
-  if (!last_flag) return;
-  __threadfence();
-  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += kWarps * 32) {
-    const int h = idx >> 6, d = idx & 63;
-    const int qh = kvh * kGroupHeads + h;
-    const size_t row = ((size_t)b * kHeads + qh) * a.splits;
-    float m = -INFINITY;
-    for (int s = 0; s < a.splits; ++s) m = fmaxf(m, __ldcg(a.m_part + row + s));
-    float num = 0.f, den = 0.f;
-    if (m != -INFINITY) {
-      for (int s = 0; s < a.splits; ++s) {
-        const float ms = __ldcg(a.m_part + row + s);
-        const float e = (ms == -INFINITY) ? 0.f : __expf(ms - m);
-        den += e * __ldcg(a.l_part + row + s);
-        num += e * __ldcg(a.o_part + (row + s) * kHeadDim + d);
-      }
-    }
-    a.out[((size_t)b * kHeads + qh) * kHeadDim + d] =
-        __float2half_rn(m == -INFINITY ? 0.f : num / den);
-  }
-  if (tid == 0) a.counters[b * kKvHeads + kvh] = 0;
+  merge_splits_last_cta(a, b, kvh, split, &last_flag);
 }
 
 
@@ -265,6 +271,7 @@ __global__ void __launch_bounds__(256) attn_decode_small_kernel(const AttnArgs a
   __shared__ float m_s[kWarps][kGroupHeads];
   __shared__ float l_s[kWarps][kGroupHeads];
   __shared__ __align__(8) float o_s[kWarps][kGroupHeads][kHeadDim];
+  __shared__ int last_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -403,6 +410,8 @@ __global__ void __launch_bounds__(256) attn_decode_small_kernel(const AttnArgs a
     }
   }
   QUIC_TLOG_END();
+  if (a.splits == 1 || a.consumer_merge) return;
+  merge_splits_last_cta(a, b, kvh, split, &last_flag);
 }
 
 }  // namespace

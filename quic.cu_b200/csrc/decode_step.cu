@@ -51,7 +51,8 @@ Arena carve(int batch, int vocab, int splits) {
   off += align256((int64_t)4 * batch * kInter * 4);
   a.partial = off;
   off += align256((int64_t)kDownSplits * batch * kHidden * 4);
-  const int grid = lm_head_grid(vocab);
+  int grid = lm_head_grid(vocab);
+  if (lm_head_tc_supported(batch, vocab) && lm_head_tc_tiles(vocab) > grid) grid = lm_head_tc_tiles(vocab);
   a.best_val = off;
   off += align256((int64_t)batch * grid * 4);
   a.best_idx = off;
@@ -273,9 +274,8 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     aa.chunk = (ctx + splits - 1) / splits;
     aa.scale = 0.125f;
     aa.out = attn_out;
-    aa.small = (splits <= kMaxConsumerSplits && (int64_t)splits * 64 >= ctx) ? 1 : 0;
+    aa.small = ((int64_t)splits * 64 >= ctx) ? 1 : 0;  // 64-token CTAs, merged by the last CTA to arrive
     aa.consumer_merge = 0;
-    if (aa.small && splits > 1) aa.small = 0;  // the latency variant leaves the merge to a consumer
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
     QUIC_CUDA(launch_attn(aa, B, st, false));
     rc = w4a16_gemm_tc(attn_out, L.o, tmp, B, ws, st);
@@ -306,6 +306,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
   la.n_slots = d->n_slots;
   la.ring = d->ring > 0 ? d->ring : 1;
   la.step_counter = d->step_counter;
+  if (lm_head_tc_supported(B, m->vocab)) return launch_lm_head_tc(la, st);
   QUIC_CUDA(launch_lm_head(la, lm_head_grid(m->vocab), st, false));
   return QUIC_OK;
 }
@@ -325,7 +326,7 @@ extern "C" int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx) {
   if (ctx < 1) ctx = 1;
   // Short contexts at small batch: one CTA per 64 tokens, merged by the o_proj kernel.
   const int small = (ctx + 63) / 64;
-  if (small <= kMaxConsumerSplits && (int64_t)batch * small * kKvHeads <= 1184) return small;
+  if (small <= kMaxConsumerSplits && ((int64_t)batch * small * kKvHeads <= 1184 || batch > kMaxM)) return small;
   return quic_attn_pick_splits(batch, ctx);
 }
 

@@ -21,116 +21,81 @@
 // Three stages keep global loads, dequantisation and MMA overlapped.  Split-K CTAs write
 // fp32 partials that a small kernel sums.  Every mbarrier wait is bounded: on a timeout
 // the kernel records an error code, still frees its tensor memory and returns.
-#include "decode_kernels.cuh"
+#include "tc_common.cuh"
 
 namespace quic {
 namespace {
 
-constexpr int kTileN = 128;   // weight rows per CTA (UMMA M)
-constexpr int kBlockK = 64;   // k per stage: 64 fp16 = one 128-byte swizzle row
-constexpr int kStages = 3;
-constexpr int kThreads = 128;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kStages = 8;
+constexpr int kCounterInts = 4096;  // arrival counters at the head of the split-K workspace
 
 __device__ int g_tc_status;  // 0 = ok; otherwise (code << 16) | block of the first failure
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-// Bounded wait for the phase with the given parity; false on timeout.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address
-  d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                    // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-  return d;
-}
-// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t umma_idesc_f16(int n) {
-  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-
-// Byte offset of 16-byte chunk c (0..7) of row r inside a swizzled tile.
-__device__ __forceinline__ uint32_t sw128_offset(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
-
 struct GemmArgs {
-  const half* x;  // [m_total, K]
   quic_w4_t w;
   half* y;         // [m_total, N]    (splits == 1)
   float* part;     // [splits, m_total, N] fp32 (splits > 1)
+  int* counters;   // one per (n tile, m tile), zero on entry, left zero
   int m_total;
   int kblocks_per_split;
 };
 
-template <int MT>  // batch rows per CTA tile (UMMA N): 16, 32, 64, 128 or 256
-__global__ void __launch_bounds__(kThreads) w4a16_gemm_tc_kernel(const GemmArgs a) {
+constexpr int kMaxGroupsPerCta = 40;          // K / 128 of the widest layer (4864) rounded up
+constexpr int kConsumers = 128;               // 4 warps: dequantise, issue MMA, epilogue
+constexpr int kGemmThreads = kConsumers + 32; // + 1 producer warp (one lane issues the TMA loads)
+constexpr uint32_t kRawBytes = 8 * kTileN * 4;  // packed tile: 8 k-words x 128 rows
+
+template <int MT>
+struct Smem {
+  static constexpr uint32_t kB = ((uint32_t)MT * 128u + 1023u) & ~1023u;  // x tile, swizzled by TMA
+  static constexpr uint32_t kStage = kRawBytes + kB;
+  static constexpr uint32_t kA = kTileN * 128;                           // dequantised tile
+  static constexpr uint32_t kTotal = kStages * kStage + 2 * kA + 1024;   // + alignment slack
+};
+
+// Roles: warp 4 lane 0 streams (packed weight tile, x tile) pairs through a kStages-deep TMA
+// ring; warps 0-3 turn each packed tile into the swizzled fp16 A operand (double buffered)
+// and thread 0 issues the MMAs; the same four warps read the accumulator back at the end.
+template <int MT>
+__global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                                     const __grid_constant__ CUtensorMap tm_x,
+                                                                     const GemmArgs a) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bar_free[kStages];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_afree[2];
   __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
+  __shared__ half sc_s[kMaxGroupsPerCta][kTileN];
+  __shared__ uint8_t zp_s[kMaxGroupsPerCta][kTileN];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kTileN;
   const int split = blockIdx.y;
   const int m0 = blockIdx.z * MT;
-  const int K = a.w.k, N = a.w.n;
-  const int kb_total = K / kBlockK;
+  const int N = a.w.n;
+  const int kb_total = a.w.k / kBlockK;
   const int kb0 = split * a.kblocks_per_split;
   const int kb1 = min(kb_total, kb0 + a.kblocks_per_split);
+  const int nkb = kb1 - kb0;
+  // CTAs of different tiles walk their k range from different starting blocks, so CTAs that
+  // run together do not all request the same activation lines from L2 at the same moment.
+  const int rot = nkb > 0 ? (int)(blockIdx.x % nkb) : 0;
 
-  // 1024-byte aligned stage buffers: A (16 KB) then B (MT * 128 bytes) per stage
+  using L = Smem<MT>;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  constexpr uint32_t kABytes = kTileN * 128, kBBytes = MT * 128;
-  constexpr uint32_t kStageBytes = kABytes + ((kBBytes + 1023u) & ~1023u);
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t a_base = base + kStages * L::kStage;
 
   constexpr uint32_t kCols = MT < 32 ? 32 : MT;  // power of two >= 32
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&bar_free[s]), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_afree[0]), 1);
+    mbar_init(smem_u32(&bar_afree[1]), 1);
     mbar_init(smem_u32(&bar_done), 1);
     fail_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -142,108 +107,133 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemm_tc_kernel(const GemmArgs 
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // scales and zero points of this CTA's rows for its whole k range
+  const int g_first = (kb0 * kBlockK) / kGroup, g_last = (kb1 * kBlockK - 1) / kGroup;
+  if (tid < kConsumers) {
+    const half* scp = reinterpret_cast<const half*>(a.w.sc);
+    const int n = n0 + tid;
+    for (int g = g_first; g <= g_last && g - g_first < kMaxGroupsPerCta; ++g) {
+      sc_s[g - g_first][tid] = scp[(size_t)g * N + n];
+      zp_s[g - g_first][tid] = (a.w.zp[(size_t)g * (N >> 1) + (n >> 1)] >> (4 * (n & 1))) & 15;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = tmem_base_s;
   const uint32_t idesc = umma_idesc_f16(MT);
 
-  const half* scp = reinterpret_cast<const half*>(a.w.sc);
-  const int n = n0 + tid;  // this thread's weight row
-  int it = 0;
-  for (int kb = kb0; kb < kb1; ++kb, ++it) {
-    const int stage = it % kStages;
-    const uint32_t a_s = base + stage * kStageBytes, b_s = a_s + kABytes;
-    unsigned char* a_g = gen_base + stage * kStageBytes;
-    unsigned char* b_g = a_g + kABytes;
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      for (int it = 0; it < nkb; ++it) {
+        const int stage = it % kStages;
+        if (it >= kStages && !mbar_wait(smem_u32(&bar_empty[stage]), ((it / kStages) - 1) & 1)) {
+          fail_s = 2;
+          break;
+        }
+        const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        mbar_expect_tx(full, kRawBytes + (uint32_t)MT * 128u);
+        const int kb = kb0 + (it + rot) % nkb;
+        tma_load_2d(raw_s, &tm_w, n0, kb * 8, full);
+        tma_load_2d(b_s, &tm_x, kb * kBlockK, m0, full);
+      }
+    }
+  } else {
+    // ---------------- consumers ----------------
+    for (int it = 0; it < nkb; ++it) {
+      const int stage = it % kStages, buf = it & 1;
+      const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
+      const uint32_t a_s = a_base + buf * L::kA;
+      unsigned char* a_g = gen_base + kStages * L::kStage + buf * L::kA;
+      const uint32_t* raw_g = reinterpret_cast<const uint32_t*>(gen_base + stage * L::kStage);
+      bool ok = mbar_wait(smem_u32(&bar_full[stage]), (it / kStages) & 1);
+      if (ok && it >= 2) ok = mbar_wait(smem_u32(&bar_afree[buf]), ((it / 2) - 1) & 1);
+      // the four warps agree on the outcome of their bounded waits before any of them moves on
+      uint32_t any_bad;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.u32 p, %1, 0;\n\t"
+          "bar.red.or.pred q, 2, %2, p;\n\t"
+          "selp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(any_bad)
+          : "r"(ok ? 0u : 1u), "n"(kConsumers)
+          : "memory");
+      if (any_bad) {
+        if (tid == 0 && !fail_s) fail_s = 1;
+        break;
+      }
 
-    // global loads first (they do not touch the stage)
-    uint32_t q[8];
+      const int g = ((kb0 + (it + rot) % nkb) * kBlockK) / kGroup - g_first;
+      const half2 s2 = __half2half2(sc_s[g][tid]);
+      const half2 zp = zp_to_half2(zp_s[g][tid]);
+#ifndef QUIC_TC_NO_DEQUANT  // timing experiments only
 #pragma unroll
-    for (int j = 0; j < 8; ++j) q[j] = ldg_nc_u32(a.w.qw + ((size_t)kb * 8 + j) * N + n);
-    const int g = (kb * kBlockK) / kGroup;
-    const half2 s2 = __half2half2(scp[(size_t)g * N + n]);
-    const half2 zp = zp_to_half2((a.w.zp[(size_t)g * (N >> 1) + (n >> 1)] >> (4 * (n & 1))) & 15);
-    constexpr int kXChunks = MT * 8;  // 16-byte chunks of the x tile
-    uint4 xv[(kXChunks + kThreads - 1) / kThreads];
+      for (int j = 0; j < 8; ++j) {
+        half2 d[4];
+        dequant8(raw_g[j * kTileN + tid], zp, s2, d);  // d[p] = (k = p, k = p + 4)
+        const uint32_t u0 = *reinterpret_cast<uint32_t*>(&d[0]), u1 = *reinterpret_cast<uint32_t*>(&d[1]);
+        const uint32_t u2 = *reinterpret_cast<uint32_t*>(&d[2]), u3 = *reinterpret_cast<uint32_t*>(&d[3]);
+        uint4 o;
+        o.x = __byte_perm(u0, u1, 0x5410);  // (k0, k1)
+        o.y = __byte_perm(u2, u3, 0x5410);  // (k2, k3)
+        o.z = __byte_perm(u0, u1, 0x7632);  // (k4, k5)
+        o.w = __byte_perm(u2, u3, 0x7632);  // (k6, k7)
+        *reinterpret_cast<uint4*>(a_g + sw128_offset(tid, j)) = o;
+      }
+#endif
+      fence_proxy_async();
+      tc_fence_before();
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+      if (tid == 0) {
+        tc_fence_after();
+#ifndef QUIC_TC_NO_MMA  // timing experiments only
 #pragma unroll
-    for (int i = 0; i < (kXChunks + kThreads - 1) / kThreads; ++i) {
-      const int idx = tid + i * kThreads;
-      const int r = idx >> 3, c = idx & 7;
-      xv[i] = make_uint4(0, 0, 0, 0);
-      if (idx < kXChunks && m0 + r < a.m_total)
-        xv[i] = *reinterpret_cast<const uint4*>(a.x + (size_t)(m0 + r) * K + kb * kBlockK + 8 * c);
-    }
-
-    // the tensor core must have finished reading this stage (MMAs of iteration it - kStages)
-    if (it >= kStages) {
-      const uint32_t parity = ((it / kStages) - 1) & 1;
-      if (!mbar_wait(smem_u32(&bar_free[stage]), parity)) fail_s = 1;
-    }
-
-    // dequantise and store the A row (natural k order inside each 16-byte chunk)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      half2 d[4];
-      dequant8(q[j], zp, s2, d);  // d[p] = (k = p, k = p + 4)
-      const uint32_t u0 = *reinterpret_cast<uint32_t*>(&d[0]), u1 = *reinterpret_cast<uint32_t*>(&d[1]);
-      const uint32_t u2 = *reinterpret_cast<uint32_t*>(&d[2]), u3 = *reinterpret_cast<uint32_t*>(&d[3]);
-      uint4 o;
-      o.x = __byte_perm(u0, u1, 0x5410);  // (k0, k1)
-      o.y = __byte_perm(u2, u3, 0x5410);  // (k2, k3)
-      o.z = __byte_perm(u0, u1, 0x7632);  // (k4, k5)
-      o.w = __byte_perm(u2, u3, 0x7632);  // (k6, k7)
-      *reinterpret_cast<uint4*>(a_g + sw128_offset(tid, j)) = o;
-    }
-#pragma unroll
-    for (int i = 0; i < (kXChunks + kThreads - 1) / kThreads; ++i) {
-      const int idx = tid + i * kThreads;
-      if (idx < kXChunks) *reinterpret_cast<uint4*>(b_g + sw128_offset(idx >> 3, idx & 7)) = xv[i];
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && !fail_s) {
-      tc_fence_after();
-#pragma unroll
-      for (int k = 0; k < kBlockK / 16; ++k)
-        umma_f16(tmem_d, umma_desc_sw128(a_s + k * 32), umma_desc_sw128(b_s + k * 32), idesc,
-                 (it > 0 || k > 0) ? 1u : 0u);
-      umma_commit(smem_u32(&bar_free[stage]));
-      if (kb == kb1 - 1) umma_commit(smem_u32(&bar_done));
+        for (int k = 0; k < kBlockK / 16; ++k)
+          umma_f16(tmem_d, umma_desc_sw128(a_s + k * 32), umma_desc_sw128(b_s + k * 32), idesc,
+                   (it > 0 || k > 0) ? 1u : 0u);
+#endif
+        umma_commit(smem_u32(&bar_empty[stage]));
+        umma_commit(smem_u32(&bar_afree[buf]));
+        if (it == nkb - 1) umma_commit(smem_u32(&bar_done));
+      }
     }
   }
 
   // wait for the whole accumulation, then read the accumulator out of tensor memory
-  bool ok = !fail_s;
-  if (ok && it > 0) ok = mbar_wait(smem_u32(&bar_done), 0);
-  tc_fence_after();
-  if (!ok && tid == 0) atomicCAS(&g_tc_status, 0, (1 << 16) | (int)blockIdx.x);
-
-  if (ok && it > 0) {
-    const int col = n0 + warp * 32 + lane;  // TMEM lane = tile row; warp w reads lanes 32w..32w+31
-    const float bias =
-        (a.w.bias != nullptr && gridDim.y == 1) ? __half2float(reinterpret_cast<const half*>(a.w.bias)[col]) : 0.f;
+  if (warp < 4) {
+    bool ok = !fail_s && nkb > 0;
+    if (ok) ok = mbar_wait(smem_u32(&bar_done), 0);
+    tc_fence_after();
+    if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status, 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
+    if (ok) {
+      const int col = n0 + warp * 32 + lane;  // TMEM lane = tile row; warp w reads lanes 32w..32w+31
+      const float bias = (a.w.bias != nullptr && gridDim.y == 1)
+                             ? __half2float(reinterpret_cast<const half*>(a.w.bias)[col])
+                             : 0.f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < MT; c0 += 8) {
-      uint32_t r[8];
-      const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                   : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                     "=r"(r[7])
-                   : "r"(taddr));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int c0 = 0; c0 < MT; c0 += 8) {
+        if (m0 + c0 >= a.m_total) break;
+        uint32_t r[8];
+        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                       "=r"(r[7])
+                     : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int m = m0 + c0 + j;
-        if (m >= a.m_total) continue;
-        const float v = __uint_as_float(r[j]);
-        if (gridDim.y == 1) {
-          float o = __half2float(__float2half_rn(v));
-          if (a.w.bias != nullptr) o += bias;
-          a.y[(size_t)m * N + col] = __float2half_rn(o);
-        } else {
-          a.part[((size_t)split * a.m_total + m) * N + col] = v;
+        for (int j = 0; j < 8; ++j) {
+          const int m = m0 + c0 + j;
+          if (m >= a.m_total) continue;
+          const float v = __uint_as_float(r[j]);
+          if (gridDim.y == 1) {
+            float o = __half2float(__float2half_rn(v));
+            if (a.w.bias != nullptr) o += bias;
+            a.y[(size_t)m * N + col] = __float2half_rn(o);
+          } else {
+            a.part[((size_t)split * a.m_total + m) * N + col] = v;
+          }
         }
       }
     }
@@ -254,26 +244,40 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemm_tc_kernel(const GemmArgs 
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kCols) : "memory");
 }
 
+// Sums the split-K partials (one thread per output element, all loads of an element in
+// flight together), rounds to fp16 as the un-split epilogue does and adds the bias.
 __global__ void tc_splitk_finish_kernel(const float* __restrict__ part, const half* __restrict__ bias,
                                         half* __restrict__ y, int m_total, int N, int splits) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (size_t)m_total * N) return;
+  const size_t total = (size_t)m_total * N;
+  if (idx >= total) return;
+  float p[16];
+#pragma unroll
+  for (int s = 0; s < 16; ++s) p[s] = s < splits ? __ldcg(part + (size_t)s * total + idx) : 0.f;
   float v = 0.f;
-  for (int s = 0; s < splits; ++s) v += part[(size_t)s * m_total * N + idx];
+#pragma unroll
+  for (int s = 0; s < 16; ++s) v += p[s];
   v = __half2float(__float2half_rn(v));
   if (bias) v += __half2float(bias[idx % N]);
   y[idx] = __float2half_rn(v);
 }
 
 template <int MT>
-int run(const GemmArgs& a, int splits, cudaStream_t st) {
-  constexpr uint32_t kABytes = kTileN * 128, kBBytes = MT * 128;
-  constexpr uint32_t kStageBytes = kABytes + ((kBBytes + 1023u) & ~1023u);
-  const size_t smem = (size_t)kStages * kStageBytes + 1024;
+int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
+  CUtensorMap tm_w, tm_x;
+  // packed weights int32 [K/8, N]: box = 8 k-words x 128 rows; x fp16 [m, K]: box = MT rows x 64 k,
+  // written with the 128-byte swizzle the UMMA descriptor expects (rows past m read as zero)
+  int rc = make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, a.w.qw, (uint64_t)a.w.k / 8, (uint64_t)a.w.n, 8,
+                    kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != QUIC_OK) return rc;
+  rc = make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)a.m_total, (uint64_t)a.w.k, MT, kBlockK,
+                CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != QUIC_OK) return rc;
+  const size_t smem = Smem<MT>::kTotal;
   QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
   dim3 grid(a.w.n / kTileN, splits, (a.m_total + MT - 1) / MT);
-  w4a16_gemm_tc_kernel<MT><<<grid, kThreads, smem, st>>>(a);
+  w4a16_gemm_tc_kernel<MT><<<grid, kGemmThreads, smem, st>>>(tm_w, tm_x, a);
   QUIC_CUDA(cudaGetLastError());
   return QUIC_OK;
 }
@@ -285,9 +289,9 @@ static void tc_plan(int m, int n, int k, int* mt_out, int* splits_out, int* per_
   const int tiles = n / kTileN;
   const int mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   const int mtiles = (m + mt - 1) / mt;
-  // split K until roughly every SM has a CTA, at most 8 ways and at least 2 k blocks per CTA
+  // split K while it at most fills the SMs once, at most 16 ways, at least 2 k blocks per CTA
   int splits = 1;
-  while (splits < 8 && tiles * mtiles * splits * 2 <= 148 && kb_total / (splits * 2) >= 2) splits *= 2;
+  while (splits < 16 && tiles * mtiles * splits * 2 <= 148 && kb_total / (splits * 2) >= 2) splits *= 2;
   const int per = (kb_total + splits - 1) / splits;
   *mt_out = mt;
   *per_out = per;
@@ -297,35 +301,39 @@ static void tc_plan(int m, int n, int k, int* mt_out, int* splits_out, int* per_
 int64_t w4a16_gemm_tc_workspace(int m, int n, int k) {
   int mt, splits, per;
   tc_plan(m, n, k, &mt, &splits, &per);
-  return splits > 1 ? (int64_t)splits * m * n * 4 : 0;
+  return kCounterInts * 4 + (splits > 1 ? (int64_t)splits * m * n * 4 : 0);
 }
 
 int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st) {
   QUIC_REQUIRE(w.n % kTileN == 0 && w.k % kBlockK == 0, QUIC_E_SHAPE,
                "w4a16_linear: the tensor path needs N multiple of 128 and K multiple of 64");
-  QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && w.k % 8 == 0, QUIC_E_ARG, "w4a16_linear: x must be 16-byte aligned");
+  QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0), QUIC_E_ARG,
+               "w4a16_linear: x and the packed weights must be 16-byte aligned");
+  QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16_linear: K beyond 5120 on the tensor path");
   int mt, splits, per;
   tc_plan(m, w.n, w.k, &mt, &splits, &per);
   QUIC_REQUIRE(splits == 1 || workspace != nullptr, QUIC_E_ARG, "w4a16_linear: split-K needs a workspace");
   GemmArgs a = {};
-  a.x = x;
   a.w = w;
   a.y = y;
-  a.part = workspace;
+  a.counters = reinterpret_cast<int*>(workspace);
+  a.part = workspace + kCounterInts;
+  QUIC_REQUIRE((w.n / kTileN) * ((m + mt - 1) / mt) <= kCounterInts, QUIC_E_LIMIT,
+               "w4a16_linear: more than 4096 output tiles on the tensor path");
   a.m_total = m;
   a.kblocks_per_split = per;
   int rc;
   switch (mt) {
-    case 16: rc = run<16>(a, splits, st); break;
-    case 32: rc = run<32>(a, splits, st); break;
-    case 64: rc = run<64>(a, splits, st); break;
-    default: rc = run<128>(a, splits, st); break;
+    case 16: rc = run<16>(x, a, splits, st); break;
+    case 32: rc = run<32>(x, a, splits, st); break;
+    case 64: rc = run<64>(x, a, splits, st); break;
+    default: rc = run<128>(x, a, splits, st); break;
   }
   if (rc != QUIC_OK) return rc;
   if (splits > 1) {
     const size_t total = (size_t)m * w.n;
-    tc_splitk_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-        workspace, (const half*)w.bias, y, m, w.n, splits);
+    tc_splitk_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.part, (const half*)w.bias, y, m,
+                                                                               w.n, splits);
     QUIC_CUDA(cudaGetLastError());
   }
   return QUIC_OK;
@@ -340,5 +348,7 @@ extern "C" int quic_w4a16_tensor_status(void) {
   if (cudaMemcpyFromSymbol(&v, quic::g_tc_status, sizeof(int)) != cudaSuccess) return -1;
   int zero = 0;
   cudaMemcpyToSymbol(quic::g_tc_status, &zero, sizeof(int));
+  const int lm = quic::lm_head_tc_status();
+  if (v == 0) v = lm;
   return v;
 }

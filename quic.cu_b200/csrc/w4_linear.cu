@@ -200,8 +200,8 @@ extern "C" int quic_w4_dequant(const quic_w4_t* w, void* out, void* stream) {
 extern "C" int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   int64_t s = gemv_splits(n, k);
-  if (s < 8) s = 8;  // the tensor path splits K by at most 8 as well
-  return s * (int64_t)m * n * 4;
+  if (s < 16) s = 16;  // the tensor path splits K by at most 16
+  return 16384 + s * (int64_t)m * n * 4;  // arrival counters of the tensor path come first
 }
 
 extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int32_t m,
@@ -216,6 +216,8 @@ extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int
     QUIC_REQUIRE(workspace != nullptr, QUIC_E_ARG, "w4a16_linear: tensor path needs a workspace");
     return w4a16_gemm_tc((const half*)x, *w, (half*)y, m, (float*)workspace, st);
   }
+  // the first 16 KB of the workspace belong to the tensor path's arrival counters
+  float* part = workspace != nullptr ? static_cast<float*>(workspace) + 4096 : nullptr;
   const int ng = w->k / kGroup;
   int splits = (workspace != nullptr && m <= 8) ? gemv_splits(w->n, w->k) : 1;
   int gps = (ng + splits - 1) / splits;
@@ -233,19 +235,17 @@ extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int
   if (M == 1) {
     QUIC_CUDA(cudaFuncSetAttribute(w4_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
-    w4_gemv_kernel<1><<<grid, nwarp * 32, smem, st>>>((const half*)x, *w, (half*)y,
-                                                      (float*)workspace, m, gps);
+    w4_gemv_kernel<1><<<grid, nwarp * 32, smem, st>>>((const half*)x, *w, (half*)y, part, m, gps);
   } else {
     QUIC_CUDA(cudaFuncSetAttribute(w4_gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
-    w4_gemv_kernel<8><<<grid, nwarp * 32, smem, st>>>((const half*)x, *w, (half*)y,
-                                                      (float*)workspace, m, gps);
+    w4_gemv_kernel<8><<<grid, nwarp * 32, smem, st>>>((const half*)x, *w, (half*)y, part, m, gps);
   }
   QUIC_CUDA(cudaGetLastError());
   if (splits > 1) {
     const size_t total = (size_t)m * w->n;
     splitk_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-        (const float*)workspace, (const half*)w->bias, (half*)y, m, w->n, splits);
+        part, (const half*)w->bias, (half*)y, m, w->n, splits);
     QUIC_CUDA(cudaGetLastError());
   }
   return QUIC_OK;

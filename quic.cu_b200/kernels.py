@@ -25,7 +25,7 @@ LIB_PATH = os.path.join(_HERE, "libquic_b200.so")
 HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, GROUP, QKV_N = 896, 14, 2, 64, 4864, 128, 1152
 ROWS_NATURAL, ROWS_ROPE_PAIRS = 0, 1
 # M >= 16 runs the tcgen05 GEMM when True; the dequant GEMV in row chunks otherwise.
-TENSOR_PATH = False
+TENSOR_PATH = True
 
 
 class W4(C.Structure):
@@ -215,7 +215,7 @@ class W4Weight:
     def workspace(self, m: int) -> torch.Tensor:
         need = lib().quic_w4a16_workspace_bytes(m, self.size_n, self.size_k)
         if self._workspace is None or self._workspace.numel() * 4 < need:
-            self._workspace = torch.empty((need + 3) // 4, dtype=torch.float32, device=self.qw.device)
+            self._workspace = torch.zeros((need + 3) // 4, dtype=torch.float32, device=self.qw.device)
         return self._workspace
 
     @property
