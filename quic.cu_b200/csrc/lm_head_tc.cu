@@ -17,7 +17,7 @@
 namespace quic {
 namespace {
 
-constexpr int kLmStages = 6;
+constexpr int kLmStages = 4;  // 4 x 24 KB at 64 rows: two CTAs fit an SM, one loads while the other reduces
 constexpr int kLmThreads = 128 + 32;  // 4 epilogue warps (thread 0 issues MMAs) + 1 TMA warp
 
 struct Best {
@@ -47,8 +47,7 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
   __shared__ int last_flag;
-  __shared__ float cand_v[4][MT];
-  __shared__ int cand_i[4][MT];
+  __shared__ uint32_t cand_key[4][MT];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, ntiles = gridDim.x;
@@ -144,20 +143,14 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
         const int m = c0 + j;
         const half h = __float2half_rn(__uint_as_float(r[j]));
         if (a.logits != nullptr && m < a.batch && ok) a.logits[(size_t)m * a.vocab + row] = h;
-        Best c;
-        c.v = __half2float(h);
-        c.i = row;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          Best y;
-          y.v = __shfl_xor_sync(0xffffffffu, c.v, o);
-          y.i = __shfl_xor_sync(0xffffffffu, c.i, o);
-          c = better(c, y);
-        }
-        if (lane == 0) {
-          cand_v[warp][m] = c.v;
-          cand_i[warp][m] = c.i;
-        }
+        // (fp16 logit, row) as one unsigned key whose order is "larger logit, then lower
+        // row": the warp maximum is a single redux instruction.
+        const uint32_t bits = __half_as_ushort(h);
+        const uint32_t ordered = (bits & 0x8000u) ? (~bits & 0xffffu) : (bits | 0x8000u);
+        const uint32_t nan_safe = ((bits & 0x7fffu) > 0x7c00u) ? 0u : ordered;  // NaN never wins
+        const uint32_t key = (nan_safe << 16) | (uint32_t)(127 - (warp * 32 + lane));
+        const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+        if (lane == 0) cand_key[warp][m] = top;
       }
     }
   }
@@ -168,18 +161,13 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
 
   // tile candidate per batch row
   for (int m = tid; m < MT && m < a.batch; m += kLmThreads) {
-    Best c;
-    c.v = cand_v[0][m];
-    c.i = cand_i[0][m];
+    uint32_t k = cand_key[0][m];
 #pragma unroll
-    for (int w = 1; w < 4; ++w) {
-      Best y;
-      y.v = cand_v[w][m];
-      y.i = cand_i[w][m];
-      c = better(c, y);
-    }
-    a.best_val[(size_t)m * ntiles + tile] = c.v;
-    a.best_idx[(size_t)m * ntiles + tile] = c.i;
+    for (int w = 1; w < 4; ++w) k = max(k, cand_key[w][m]);
+    const uint32_t ordered = k >> 16;
+    const uint32_t bits = (ordered & 0x8000u) ? (ordered & 0x7fffu) : (~ordered & 0xffffu);
+    a.best_val[(size_t)m * ntiles + tile] = ordered == 0u ? -INFINITY : __half2float(__ushort_as_half((unsigned short)bits));
+    a.best_idx[(size_t)m * ntiles + tile] = n0 + 127 - (int)(k & 0xffffu);
   }
 
   // the CTA that arrives last reduces the candidates of all tiles

@@ -26,10 +26,15 @@
 namespace quic {
 namespace {
 
-constexpr int kStages = 8;
 constexpr int kCounterInts = 4096;  // arrival counters at the head of the split-K workspace
 
-__device__ int g_tc_status;  // 0 = ok; otherwise (code << 16) | block of the first failure
+__device__ int g_tc_status;
+#ifdef QUIC_TRACE
+__device__ long long g_gemm_trace[2][20][6];
+#define GSTAMP(it, i) do { if (tid == 0 && blockIdx.x < 2 && blockIdx.y == 0 && (it) < 20) g_gemm_trace[blockIdx.x][it][i] = clock64(); } while (0)
+#else
+#define GSTAMP(it, i)
+#endif  // 0 = ok; otherwise (code << 16) | block of the first failure
 
 struct GemmArgs {
   quic_w4_t w;
@@ -40,30 +45,40 @@ struct GemmArgs {
   int kblocks_per_split;
 };
 
-constexpr int kMaxGroupsPerCta = 40;          // K / 128 of the widest layer (4864) rounded up
-constexpr int kConsumers = 128;               // 4 warps: dequantise, issue MMA, epilogue
-constexpr int kGemmThreads = kConsumers + 32; // + 1 producer warp (one lane issues the TMA loads)
+constexpr int kMaxGroupsPerCta = 40;            // K / 128 of the widest layer (4864) rounded up
+constexpr int kConsumers = 512;                 // 16 warps dequantise (4 per scheduler) and run the epilogue
+constexpr int kGemmThreads = kConsumers + 64;   // + TMA warp + MMA warp (one lane each)
 constexpr uint32_t kRawBytes = 8 * kTileN * 4;  // packed tile: 8 k-words x 128 rows
 
 template <int MT>
 struct Smem {
+  static constexpr int kStages = MT > 64 ? 5 : 6;
   static constexpr uint32_t kB = ((uint32_t)MT * 128u + 1023u) & ~1023u;  // x tile, swizzled by TMA
-  static constexpr uint32_t kStage = kRawBytes + kB;
   static constexpr uint32_t kA = kTileN * 128;                           // dequantised tile
-  static constexpr uint32_t kTotal = kStages * kStage + 2 * kA + 1024;   // + alignment slack
+  static constexpr uint32_t kStage = kRawBytes + kB + kA;
+  static constexpr uint32_t kTotal = kStages * kStage + 1024;            // + alignment slack
 };
 
-// Roles: warp 4 lane 0 streams (packed weight tile, x tile) pairs through a kStages-deep TMA
-// ring; warps 0-3 turn each packed tile into the swizzled fp16 A operand (double buffered)
-// and thread 0 issues the MMAs; the same four warps read the accumulator back at the end.
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Roles.  Warp 16, lane 0: streams (packed weight tile, x tile) pairs through a TMA ring.
+// Warps 0-15: turn each packed tile into the swizzled fp16 A operand of its stage and tell
+// the MMA warp (one mbarrier arrival per warp).  Warp 17, lane 0: issues the MMAs of a stage
+// once its A tile is complete and commits them to the stage's "empty" barrier, which lets
+// the TMA warp refill it.  No role ever waits for another role's instruction issue, only
+// for data.  Warps 0-15 read the accumulator back at the end.
 template <int MT>
 __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                      const __grid_constant__ CUtensorMap tm_x,
                                                                      const GemmArgs a) {
+  using L = Smem<MT>;
+  constexpr int kStages = L::kStages;
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages];
-  __shared__ __align__(8) uint64_t bar_empty[kStages];
-  __shared__ __align__(8) uint64_t bar_afree[2];
+  __shared__ __align__(8) uint64_t bar_full[kStages];    // TMA bytes landed
+  __shared__ __align__(8) uint64_t bar_aready[kStages];  // 16 consumer warps finished the A tile
+  __shared__ __align__(8) uint64_t bar_empty[kStages];   // MMAs that read the stage completed
   __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
@@ -79,23 +94,17 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   const int kb0 = split * a.kblocks_per_split;
   const int kb1 = min(kb_total, kb0 + a.kblocks_per_split);
   const int nkb = kb1 - kb0;
-  // CTAs of different tiles walk their k range from different starting blocks, so CTAs that
-  // run together do not all request the same activation lines from L2 at the same moment.
-  const int rot = nkb > 0 ? (int)(blockIdx.x % nkb) : 0;
 
-  using L = Smem<MT>;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t a_base = base + kStages * L::kStage;
 
   constexpr uint32_t kCols = MT < 32 ? 32 : MT;  // power of two >= 32
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_aready[s]), kConsumers / 32);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    mbar_init(smem_u32(&bar_afree[0]), 1);
-    mbar_init(smem_u32(&bar_afree[1]), 1);
     mbar_init(smem_u32(&bar_done), 1);
     fail_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -109,7 +118,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   }
   // scales and zero points of this CTA's rows for its whole k range
   const int g_first = (kb0 * kBlockK) / kGroup, g_last = (kb1 * kBlockK - 1) / kGroup;
-  if (tid < kConsumers) {
+  if (tid < kTileN) {
     const half* scp = reinterpret_cast<const half*>(a.w.sc);
     const int n = n0 + tid;
     for (int g = g_first; g <= g_last && g - g_first < kMaxGroupsPerCta; ++g) {
@@ -123,8 +132,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   const uint32_t tmem_d = tmem_base_s;
   const uint32_t idesc = umma_idesc_f16(MT);
 
-  if (warp == 4) {
-    // ---------------- producer ----------------
+  if (warp == kConsumers / 32) {
+    // ---------------- TMA producer ----------------
     if (lane == 0) {
       for (int it = 0; it < nkb; ++it) {
         const int stage = it % kStages;
@@ -135,59 +144,21 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
         const uint32_t full = smem_u32(&bar_full[stage]);
         mbar_expect_tx(full, kRawBytes + (uint32_t)MT * 128u);
-        const int kb = kb0 + (it + rot) % nkb;
-        tma_load_2d(raw_s, &tm_w, n0, kb * 8, full);
-        tma_load_2d(b_s, &tm_x, kb * kBlockK, m0, full);
+        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
+        tma_load_2d(b_s, &tm_x, (kb0 + it) * kBlockK, m0, full);
       }
     }
-  } else {
-    // ---------------- consumers ----------------
-    for (int it = 0; it < nkb; ++it) {
-      const int stage = it % kStages, buf = it & 1;
-      const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
-      const uint32_t a_s = a_base + buf * L::kA;
-      unsigned char* a_g = gen_base + kStages * L::kStage + buf * L::kA;
-      const uint32_t* raw_g = reinterpret_cast<const uint32_t*>(gen_base + stage * L::kStage);
-      bool ok = mbar_wait(smem_u32(&bar_full[stage]), (it / kStages) & 1);
-      if (ok && it >= 2) ok = mbar_wait(smem_u32(&bar_afree[buf]), ((it / 2) - 1) & 1);
-      // the four warps agree on the outcome of their bounded waits before any of them moves on
-      uint32_t any_bad;
-      asm volatile(
-          "{\n\t.reg .pred p, q;\n\t"
-          "setp.ne.u32 p, %1, 0;\n\t"
-          "bar.red.or.pred q, 2, %2, p;\n\t"
-          "selp.u32 %0, 1, 0, q;\n\t}"
-          : "=r"(any_bad)
-          : "r"(ok ? 0u : 1u), "n"(kConsumers)
-          : "memory");
-      if (any_bad) {
-        if (tid == 0 && !fail_s) fail_s = 1;
-        break;
-      }
-
-      const int g = ((kb0 + (it + rot) % nkb) * kBlockK) / kGroup - g_first;
-      const half2 s2 = __half2half2(sc_s[g][tid]);
-      const half2 zp = zp_to_half2(zp_s[g][tid]);
-#ifndef QUIC_TC_NO_DEQUANT  // timing experiments only
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        half2 d[4];
-        dequant8(raw_g[j * kTileN + tid], zp, s2, d);  // d[p] = (k = p, k = p + 4)
-        const uint32_t u0 = *reinterpret_cast<uint32_t*>(&d[0]), u1 = *reinterpret_cast<uint32_t*>(&d[1]);
-        const uint32_t u2 = *reinterpret_cast<uint32_t*>(&d[2]), u3 = *reinterpret_cast<uint32_t*>(&d[3]);
-        uint4 o;
-        o.x = __byte_perm(u0, u1, 0x5410);  // (k0, k1)
-        o.y = __byte_perm(u2, u3, 0x5410);  // (k2, k3)
-        o.z = __byte_perm(u0, u1, 0x7632);  // (k4, k5)
-        o.w = __byte_perm(u2, u3, 0x7632);  // (k6, k7)
-        *reinterpret_cast<uint4*>(a_g + sw128_offset(tid, j)) = o;
-      }
-#endif
-      fence_proxy_async();
-      tc_fence_before();
-      asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
-      if (tid == 0) {
+  } else if (warp == kConsumers / 32 + 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      for (int it = 0; it < nkb; ++it) {
+        const int stage = it % kStages;
+        if (!mbar_wait(smem_u32(&bar_aready[stage]), (it / kStages) & 1)) {
+          fail_s = 3;
+          break;
+        }
         tc_fence_after();
+        const uint32_t b_s = base + stage * L::kStage + kRawBytes, a_s = b_s + L::kB;
 #ifndef QUIC_TC_NO_MMA  // timing experiments only
 #pragma unroll
         for (int k = 0; k < kBlockK / 16; ++k)
@@ -195,28 +166,70 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
                    (it > 0 || k > 0) ? 1u : 0u);
 #endif
         umma_commit(smem_u32(&bar_empty[stage]));
-        umma_commit(smem_u32(&bar_afree[buf]));
         if (it == nkb - 1) umma_commit(smem_u32(&bar_done));
       }
     }
+  } else {
+    // ---------------- consumers: dequantise ----------------
+    const int row = tid & (kTileN - 1), part = tid >> 7;  // thread -> (row, two of its eight k-words)
+    for (int it = 0; it < nkb; ++it) {
+      const int stage = it % kStages;
+      // "full" of this phase also means the MMAs of the stage's previous use are complete
+      // (the TMA warp refilled it only after "empty"), so the A tile may be overwritten.
+      if (!mbar_wait(smem_u32(&bar_full[stage]), (it / kStages) & 1)) {
+        fail_s = 1;
+        break;
+      }
+      unsigned char* stage_g = gen_base + stage * L::kStage;
+      const uint32_t* raw_g = reinterpret_cast<const uint32_t*>(stage_g);
+      unsigned char* a_g = stage_g + kRawBytes + L::kB;
+      const int g = ((kb0 + it) * kBlockK) / kGroup - g_first;
+      const half2 s2 = __half2half2(sc_s[g][row]);
+      const half2 zp = zp_to_half2(zp_s[g][row]);
+#ifndef QUIC_TC_NO_DEQUANT  // timing experiments only
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int j = 2 * part + jj;
+        half2 d[4];
+        dequant8(raw_g[j * kTileN + row], zp, s2, d);  // d[p] = (k = p, k = p + 4)
+        const uint32_t u0 = *reinterpret_cast<uint32_t*>(&d[0]), u1 = *reinterpret_cast<uint32_t*>(&d[1]);
+        const uint32_t u2 = *reinterpret_cast<uint32_t*>(&d[2]), u3 = *reinterpret_cast<uint32_t*>(&d[3]);
+        uint4 o;
+        o.x = __byte_perm(u0, u1, 0x5410);  // (k0, k1)
+        o.y = __byte_perm(u2, u3, 0x5410);  // (k2, k3)
+        o.z = __byte_perm(u0, u1, 0x7632);  // (k4, k5)
+        o.w = __byte_perm(u2, u3, 0x7632);  // (k6, k7)
+        *reinterpret_cast<uint4*>(a_g + sw128_offset(row, j)) = o;
+      }
+#endif
+      fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_aready[stage]));
+    }
   }
+  __syncwarp();
 
   // wait for the whole accumulation, then read the accumulator out of tensor memory
-  if (warp < 4) {
+  if (warp < kConsumers / 32) {
     bool ok = !fail_s && nkb > 0;
     if (ok) ok = mbar_wait(smem_u32(&bar_done), 0);
+    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status, 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
     if (ok) {
-      const int col = n0 + warp * 32 + lane;  // TMEM lane = tile row; warp w reads lanes 32w..32w+31
+      // TMEM lane = tile row; a warp may read lanes 32*(warp % 4)..+31, so the four warps that
+      // share a lane quarter split the batch columns between them
+      const int quarter = warp & 3, cgroup = warp >> 2;
+      const int col = n0 + quarter * 32 + lane;
+      constexpr int kColsPerGroup = MT >= 32 ? MT / 4 : 8;
       const float bias = (a.w.bias != nullptr && gridDim.y == 1)
                              ? __half2float(reinterpret_cast<const half*>(a.w.bias)[col])
                              : 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < MT; c0 += 8) {
+      for (int c0 = cgroup * kColsPerGroup; c0 < min(MT, (cgroup + 1) * kColsPerGroup); c0 += 8) {
         if (m0 + c0 >= a.m_total) break;
         uint32_t r[8];
-        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
                        "=r"(r[7])
@@ -352,3 +365,9 @@ extern "C" int quic_w4a16_tensor_status(void) {
   if (v == 0) v = lm;
   return v;
 }
+
+#ifdef QUIC_TRACE
+extern "C" int quic_gemm_trace_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, quic::g_gemm_trace, sizeof(long long) * 2 * 20 * 6);
+}
+#endif
