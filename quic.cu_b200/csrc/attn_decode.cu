@@ -27,6 +27,7 @@ constexpr int kTile = 32;
 
 // The CTA that arrives last at the per-(row, kv head) counter merges the split partials of
 // the group's 7 heads, writes the fp16 output and re-arms the counter.  No CTA waits.
+// Partials are fetched 16 splits at a time with every load in flight before the first use.
 __device__ __forceinline__ void merge_splits_last_cta(const AttnArgs& a, int b, int kvh, int split, int* last_flag_s) {
   const int tid = threadIdx.x;
   int& last_flag = *last_flag_s;
@@ -43,22 +44,36 @@ __device__ __forceinline__ void merge_splits_last_cta(const AttnArgs& a, int b, 
     const int h = idx >> 6, d = idx & 63;
     const int qh = kvh * kGroupHeads + h;
     const size_t row = ((size_t)b * kHeads + qh) * a.splits;
-    float m = -INFINITY;
-    for (int s = 0; s < a.splits; ++s) m = fmaxf(m, __ldcg(a.m_part + row + s));
-    float num = 0.f, den = 0.f;
-    if (m != -INFINITY) {
-      for (int s = 0; s < a.splits; ++s) {
-        const float ms = __ldcg(a.m_part + row + s);
-        const float e = (ms == -INFINITY) ? 0.f : __expf(ms - m);
-        den += e * __ldcg(a.l_part + row + s);
-        num += e * __ldcg(a.o_part + (row + s) * kHeadDim + d);
+    float m = -INFINITY, num = 0.f, den = 0.f;
+    for (int s0 = 0; s0 < a.splits; s0 += 16) {
+      float ms[16], ls[16], os[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const bool in = s0 + j < a.splits;
+        ms[j] = in ? __ldcg(a.m_part + row + s0 + j) : -INFINITY;
+        ls[j] = in ? __ldcg(a.l_part + row + s0 + j) : 0.f;
+        os[j] = in ? __ldcg(a.o_part + (row + s0 + j) * kHeadDim + d) : 0.f;
       }
+      float mc = m;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) mc = fmaxf(mc, ms[j]);
+      if (mc == -INFINITY) continue;
+      const float rescale = (m == -INFINITY) ? 0.f : __expf(m - mc);
+      num *= rescale;
+      den *= rescale;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float e = (ms[j] == -INFINITY) ? 0.f : __expf(ms[j] - mc);
+        den += e * ls[j];
+        num += e * os[j];
+      }
+      m = mc;
     }
-    a.out[((size_t)b * kHeads + qh) * kHeadDim + d] =
-        __float2half_rn(m == -INFINITY ? 0.f : num / den);
+    a.out[((size_t)b * kHeads + qh) * kHeadDim + d] = __float2half_rn(m == -INFINITY ? 0.f : num / den);
   }
   if (tid == 0) a.counters[b * kKvHeads + kvh] = 0;
 }
+
 __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs a) {
   __shared__ __align__(16) float q_s[kGroupHeads * kHeadDim];
   __shared__ __align__(16) float p_s[kWarps][kGroupHeads][kTile];
@@ -280,6 +295,31 @@ __global__ void __launch_bounds__(256) attn_decode_small_kernel(const AttnArgs a
   pdl_trigger_early();
   pdl_wait();
   QUIC_TLOG_BEGIN(2);
+
+  // Throughput mode (the kernel merges the splits itself): a split that lies entirely outside
+  // the row's token range publishes an empty partial without touching the cache.
+  if (!a.consumer_merge && a.splits > 1) {
+    int lo = 0, hi = a.s_cap;
+    if (a.pos != nullptr) {
+      hi = __ldcg(a.pos + slot) + 1;
+    } else {
+      if (a.start != nullptr) lo = a.start[b];
+      if (a.end != nullptr) hi = a.end[b];
+    }
+    if (split * kSmallChunk >= hi || (split + 1) * kSmallChunk <= lo) {
+      for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += 256) {
+        const int h = idx >> 6, d = idx & 63;
+        const size_t row = ((size_t)b * kHeads + kvh * kGroupHeads + h) * a.splits + split;
+        a.o_part[row * kHeadDim + d] = 0.f;
+        if (d == 0) {
+          a.m_part[row] = -INFINITY;
+          a.l_part[row] = 0.f;
+        }
+      }
+      merge_splits_last_cta(a, b, kvh, split, &last_flag);
+      return;
+    }
+  }
 
   const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
   const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;

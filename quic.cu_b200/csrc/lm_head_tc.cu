@@ -17,7 +17,7 @@
 namespace quic {
 namespace {
 
-constexpr int kLmStages = 4;  // 4 x 24 KB at 64 rows: two CTAs fit an SM, one loads while the other reduces
+constexpr int kLmStages = 3;  // 3 x 24 KB at 64 rows: three CTAs share an SM, so loads, MMAs and epilogues of different tiles overlap
 constexpr int kLmThreads = 128 + 32;  // 4 epilogue warps (thread 0 issues MMAs) + 1 TMA warp
 
 struct Best {

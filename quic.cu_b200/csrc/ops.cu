@@ -26,56 +26,49 @@ int fail(int code, const char* msg) {
 namespace {
 
 // ---- RMSNorm (+ residual) ---------------------------------------------------
-// One warp per row of 896: 28 lanes x 4 x 16 B would leave lanes idle, so each
-// lane takes 28 halves as 3.5 uint4 -> use 8-byte pieces: 896/4 = 224 = 7 x 32.
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const half* __restrict__ x,
+// One CTA of 224 threads per row of 896 (4 elements per thread); every global load of the
+// row, the residual and the weight is requested before the first use.
+__global__ void __launch_bounds__(224) rmsnorm_kernel(const half* __restrict__ x,
                                                       const half* __restrict__ res,
                                                       const half* __restrict__ w, float eps,
                                                       half* __restrict__ y,
                                                       half* __restrict__ sum_out, int rows) {
-  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  float v[28];
-  float ssq = 0.f;
-#pragma unroll
-  for (int j = 0; j < 7; ++j) {
-    const int c = (j * 32 + lane) * 4;
-    const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * kHidden + c);
-    float2 a = __half22float2(u32_as_half2(u.x)), b = __half22float2(u32_as_half2(u.y));
-    if (res != nullptr) {
-      const uint2 r = *reinterpret_cast<const uint2*>(res + (size_t)row * kHidden + c);
-      const float2 ra = __half22float2(u32_as_half2(r.x)), rb = __half22float2(u32_as_half2(r.y));
-      // the residual stream is an fp16 tensor: round the sum
-      a.x = __half2float(__float2half_rn(a.x + ra.x));
-      a.y = __half2float(__float2half_rn(a.y + ra.y));
-      b.x = __half2float(__float2half_rn(b.x + rb.x));
-      b.y = __half2float(__float2half_rn(b.y + rb.y));
-      if (sum_out != nullptr) {
-        half2 o0 = __floats2half2_rn(a.x, a.y), o1 = __floats2half2_rn(b.x, b.y);
-        uint2 o;
-        o.x = *reinterpret_cast<uint32_t*>(&o0);
-        o.y = *reinterpret_cast<uint32_t*>(&o1);
-        *reinterpret_cast<uint2*>(sum_out + (size_t)row * kHidden + c) = o;
-      }
+  __shared__ float red[8];
+  const int row = blockIdx.x, t = threadIdx.x, c = 4 * t;
+  const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * kHidden + c);
+  uint2 r = make_uint2(0, 0);
+  if (res != nullptr) r = *reinterpret_cast<const uint2*>(res + (size_t)row * kHidden + c);
+  const uint2 wv = *reinterpret_cast<const uint2*>(w + c);
+  float2 a = __half22float2(u32_as_half2(u.x)), b = __half22float2(u32_as_half2(u.y));
+  if (res != nullptr) {
+    const float2 ra = __half22float2(u32_as_half2(r.x)), rb = __half22float2(u32_as_half2(r.y));
+    // the residual stream is an fp16 tensor: round the sum
+    a.x = __half2float(__float2half_rn(a.x + ra.x));
+    a.y = __half2float(__float2half_rn(a.y + ra.y));
+    b.x = __half2float(__float2half_rn(b.x + rb.x));
+    b.y = __half2float(__float2half_rn(b.y + rb.y));
+    if (sum_out != nullptr) {
+      half2 o0 = __floats2half2_rn(a.x, a.y), o1 = __floats2half2_rn(b.x, b.y);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&o0);
+      o.y = *reinterpret_cast<uint32_t*>(&o1);
+      *reinterpret_cast<uint2*>(sum_out + (size_t)row * kHidden + c) = o;
     }
-    v[4 * j] = a.x; v[4 * j + 1] = a.y; v[4 * j + 2] = b.x; v[4 * j + 3] = b.y;
-    ssq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
   }
-  ssq = warp_sum(ssq);
-  const float r = rsqrtf(ssq * (1.0f / kHidden) + eps);
+  float ssq = warp_sum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y);
+  if ((t & 31) == 0) red[t >> 5] = ssq;
+  __syncthreads();
+  ssq = 0.f;
 #pragma unroll
-  for (int j = 0; j < 7; ++j) {
-    const int c = (j * 32 + lane) * 4;
-    const uint2 u = *reinterpret_cast<const uint2*>(w + c);
-    const float2 wa = __half22float2(u32_as_half2(u.x)), wb = __half22float2(u32_as_half2(u.y));
-    half2 o0 = __floats2half2_rn(v[4 * j] * r * wa.x, v[4 * j + 1] * r * wa.y);
-    half2 o1 = __floats2half2_rn(v[4 * j + 2] * r * wb.x, v[4 * j + 3] * r * wb.y);
-    uint2 o;
-    o.x = *reinterpret_cast<uint32_t*>(&o0);
-    o.y = *reinterpret_cast<uint32_t*>(&o1);
-    *reinterpret_cast<uint2*>(y + (size_t)row * kHidden + c) = o;
-  }
+  for (int i = 0; i < 7; ++i) ssq += red[i];
+  const float rs = rsqrtf(ssq * (1.0f / kHidden) + eps);
+  const float2 wa = __half22float2(u32_as_half2(wv.x)), wb = __half22float2(u32_as_half2(wv.y));
+  half2 o0 = __floats2half2_rn(a.x * rs * wa.x, a.y * rs * wa.y);
+  half2 o1 = __floats2half2_rn(b.x * rs * wb.x, b.y * rs * wb.y);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&o0);
+  o.y = *reinterpret_cast<uint32_t*>(&o1);
+  *reinterpret_cast<uint2*>(y + (size_t)row * kHidden + c) = o;
 }
 
 // ---- RoPE --------------------------------------------------------------------
@@ -288,7 +281,7 @@ cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream
 }
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st) {
-  rmsnorm_kernel<<<(rows + 7) / 8, 256, 0, st>>>(x, residual, w, eps, y, sum_out, rows);
+  rmsnorm_kernel<<<rows, 224, 0, st>>>(x, residual, w, eps, y, sum_out, rows);
   return cudaGetLastError();
 }
 }  // namespace quic
@@ -307,7 +300,7 @@ extern "C" int quic_rmsnorm(const void* x, const void* residual, const void* w, 
                 (uintptr_t)sum_out) % 8 == 0,
                QUIC_E_ARG, "rmsnorm: tensors must be 8-byte aligned");
   if (rows == 0) return QUIC_OK;
-  rmsnorm_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(
+  rmsnorm_kernel<<<rows, 224, 0, (cudaStream_t)stream>>>(
       (const half*)x, (const half*)residual, (const half*)w, eps, (half*)y, (half*)sum_out, rows);
   QUIC_CUDA(cudaGetLastError());
   return QUIC_OK;

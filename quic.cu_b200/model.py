@@ -97,7 +97,11 @@ class SlotCache:
 
 
 def _ctx_bucket(n: int) -> int:
-    b = 256
+    """Context bound a captured graph is valid for: multiples of 128 up to 2048 (so the
+    attention grid tracks the real context closely), powers of two beyond."""
+    if n <= 2048:
+        return max(128, (n + 127) // 128 * 128)
+    b = 4096
     while b < n:
         b *= 2
     return b
