@@ -272,6 +272,14 @@ def run_gpu(args) -> None:
                      "peak": peak, "unit": "GB/s", "frac": step_gbs / peak, "us_per_token": us_per_token,
                      "algorithmic_bytes": step_bytes}
 
+    # ---- batch 64 (the other batch size the metric names): 64 slots, same context, resident state
+    batch64 = None
+    if not args.skip_batch64:
+        batch64 = measure_batch64(net, device, world, dist)
+    serving = None
+    if args.serving_requests > 0:
+        serving = measure_serving(net, device, args.serving_requests, world, dist, rank)
+
     if rank != 0:
         return
     line = {
@@ -280,7 +288,7 @@ def run_gpu(args) -> None:
         "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate",
         "data": "synthetic", "config": dict(CONFIG, parallelism=f"{world} independent replica(s)"),
         "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * GEN_TOKENS * net.launches_per_step(),
-        "roofline": roofline, "roofline_step": roofline_step,
+        "roofline": roofline, "roofline_step": roofline_step, "batch64": batch64, "serving": serving,
     }
     if args.layers != 24:
         line["invalid"] = "reduced layer count: profiling run, not a benchmark"
@@ -291,6 +299,90 @@ def run_gpu(args) -> None:
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def measure_batch64(net, device, world, dist):
+    """Decode tokens/s with 64 rows in flight (64 KV slots, 512 cached tokens each, 128 greedy
+    steps), state resident, CUDA events, max over ranks."""
+    B, ctx, steps, burst = 64, PROMPT_LEN, 128, 32
+    cache = net.new_cache(n_slots=B, s_max=1024)
+    slots = list(range(B))
+    gen = torch.Generator(device=device).manual_seed(1)
+    # random K/V stand in for 512 prefilled tokens per slot (values do not change the work done)
+    cache.kv.normal_(0, 1, generator=gen)
+    cache.tok.copy_(torch.randint(0, 151936, (B,), generator=gen, device=device, dtype=torch.int32))
+
+    def reset():
+        cache.pos.fill_(ctx)
+        for s in slots:
+            cache.host_len[s] = ctx
+
+    def run():
+        reset()
+        for _ in range(steps // burst):
+            net.decode_async(cache, slots, burst)
+
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    us_step = ms * 1e3 / (reps * steps)
+    peak, kind = peaks()
+    step_bytes = net.weight_bytes() + B * 12288 * (ctx + steps / 2 + 1)
+    return {"value": world * B / (us_step * 1e-6), "unit": UNIT, "batch": B, "context": ctx, "us_per_step": us_step,
+            "kernels": "tcgen05 W4A16 GEMM + tcgen05 lm_head/argmax + split-K attention",
+            "hbm_frac": step_bytes / (us_step * 1e-6) / 1e9 / peak, "peak_kind": f"of {kind}",
+            "algorithmic_bytes_per_step": step_bytes}
+
+
+def measure_serving(net, device, n_requests, world, dist, rank):
+    """Continuous batching with 64 KV slots per GPU: prompt lengths uniform in 64..1024, output
+    lengths uniform in 128..512 (forced through max_tokens; random weights never emit EOS), all
+    requests queued at t = 0 (arrivals at saturation), greedy.  The queue is dealt round-robin
+    to the replicas; wall-clock on every rank, max over ranks."""
+    from types import SimpleNamespace
+
+    from quic_cu_b200.config import EngineConfig
+    from quic_cu_b200.engine import Engine
+    from quic_cu_b200.replicas import Request, serve, shard
+
+    gen = torch.Generator().manual_seed(4)
+    plens = torch.randint(64, 1025, (n_requests,), generator=gen).tolist()
+    olens = torch.randint(128, 513, (n_requests,), generator=gen).tolist()
+    reqs = [Request(i, tuple(torch.randint(0, 151936, (plens[i],), generator=gen).tolist()), olens[i])
+            for i in range(n_requests)]
+    mine = shard(reqs, rank, world)
+    module = SimpleNamespace(load=lambda **options: (net, None))
+    engine = Engine(config=EngineConfig(batching="continuous", max_context=2048, decode_burst=8),
+                    max_batch_size=64, model_module=module)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = serve(engine, mine)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    tokens = sum(len(v) for v in out.values())
+    if dist is not None:
+        t = torch.tensor([seconds, float(tokens)], device=device, dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        seconds, tokens = float(tmax[0].item()), int(t[1].item())
+    return {"value": tokens / seconds, "unit": "generated tokens/s (prefill included in the time)",
+            "requests": n_requests, "generated_tokens": tokens, "prompt_tokens": sum(plens), "seconds": seconds,
+            "slots_per_gpu": 64, "replicas": world}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one lm_head_kernel<1> launch at vocab 151936,
@@ -305,6 +397,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="quic_b200", choices=["quic_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-batch64", action="store_true", help="skip the extra batch-64 decode measurement")
+    ap.add_argument("--serving-requests", type=int, default=0,
+                    help="also serve this many synthetic requests with continuous batching (64 slots per GPU); "
+                         "the benchmark configuration uses 4096")
     ap.add_argument("--layers", type=int, default=24,
                     help="decoder layers of the synthetic model; values below 24 exist only to keep "
                          "profiler captures small and do not produce a valid benchmark line")

@@ -68,7 +68,7 @@ Arena carve(int batch, int vocab, int splits) {
     a.act16 = off;
     off += align256((int64_t)batch * kInter * 2);
     a.tcws = off;
-    off += align256(tc_workspace_bytes(batch));
+    off += align256(16384 + tc_workspace_bytes(batch));
   }
   a.total = off;
   return a;

@@ -314,7 +314,7 @@ static void tc_plan(int m, int n, int k, int* mt_out, int* splits_out, int* per_
 int64_t w4a16_gemm_tc_workspace(int m, int n, int k) {
   int mt, splits, per;
   tc_plan(m, n, k, &mt, &splits, &per);
-  return kCounterInts * 4 + (splits > 1 ? (int64_t)splits * m * n * 4 : 0);
+  return splits > 1 ? (int64_t)splits * m * n * 4 : 0;
 }
 
 int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st) {
@@ -331,8 +331,7 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   a.y = y;
   a.counters = reinterpret_cast<int*>(workspace);
   a.part = workspace + kCounterInts;
-  QUIC_REQUIRE((w.n / kTileN) * ((m + mt - 1) / mt) <= kCounterInts, QUIC_E_LIMIT,
-               "w4a16_linear: more than 4096 output tiles on the tensor path");
+  QUIC_REQUIRE((m + mt - 1) / mt <= 65535, QUIC_E_LIMIT, "w4a16_linear: too many rows on the tensor path");
   a.m_total = m;
   a.kblocks_per_split = per;
   int rc;

@@ -199,9 +199,11 @@ extern "C" int quic_w4_dequant(const quic_w4_t* w, void* out, void* stream) {
 
 extern "C" int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  int64_t s = gemv_splits(n, k);
-  if (s < 16) s = 16;  // the tensor path splits K by at most 16
-  return 16384 + s * (int64_t)m * n * 4;  // arrival counters of the tensor path come first
+  // 16 KB reserved head, then split-K partials: of the tensor path for m >= 16 (it stops
+  // splitting once the output tiles fill the SMs, so large m needs none), of the GEMV below.
+  if (m >= 16 && n % 128 == 0 && k % 64 == 0) return 16384 + w4a16_gemm_tc_workspace(m, n, k);
+  if (m > 8) return 16384 + (int64_t)2 * m * n * 4;  // row-chunked GEMV splits only to fit shared memory
+  return 16384 + (int64_t)gemv_splits(n, k) * m * n * 4;
 }
 
 extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int32_t m,

@@ -116,8 +116,10 @@ class Engine:
                 if not live:
                     return
                 if steps is None:
+                    # a full burst whenever some row still needs one (keeps the set of captured
+                    # graphs small); rows that finish inside the burst discard the overshoot
                     need = max(seq.max_tokens - len(seq.generated_tokens) for seq in live)
-                    steps = max(1, min(self.burst, need))
+                    steps = self.burst if need >= self.burst else max(1, need)
                 slots = [seq.slot for seq in live]
             with Span("forward_pass", self.registry):
                 tokens = self.model.decode(self.cache, slots, steps)

@@ -213,14 +213,22 @@ class W4Weight:
         return out
 
     def workspace(self, m: int) -> torch.Tensor:
+        """Split-K workspace, shared by every weight on the device (calls on one stream are ordered)."""
         need = lib().quic_w4a16_workspace_bytes(m, self.size_n, self.size_k)
-        if self._workspace is None or self._workspace.numel() * 4 < need:
-            self._workspace = torch.zeros((need + 3) // 4, dtype=torch.float32, device=self.qw.device)
-        return self._workspace
+        key = self.qw.device.index
+        ws = _linear_workspace.get(key)
+        if ws is None or ws.numel() * 4 < need:
+            ws = torch.zeros((max(need, 1 << 22) + 3) // 4, dtype=torch.float32, device=self.qw.device)
+            _linear_workspace[key] = ws
+        return ws
 
     @property
     def weight_bytes(self) -> int:
         return self.qw.numel() * 4 + self.sc.numel() * 2 + self.zp.numel()
+
+
+_linear_workspace: dict = {}
+MAX_LINEAR_ROWS = 8192  # rows per launch; longer inputs are processed in chunks to bound scratch memory
 
 
 def w4a16_linear(w: W4Weight, x: torch.Tensor, use_tensor: bool | None = None) -> torch.Tensor:
@@ -233,8 +241,10 @@ def w4a16_linear(w: W4Weight, x: torch.Tensor, use_tensor: bool | None = None) -
     if use_tensor is None:
         use_tensor = TENSOR_PATH and m >= 16
     s = w.struct()
-    check(lib().quic_w4a16_linear(ptr(x2), C.byref(s), ptr(y), m, int(bool(use_tensor)),
-                                  ptr(w.workspace(m)), stream_ptr()), "w4a16_linear")
+    for r0 in range(0, m, MAX_LINEAR_ROWS):
+        rows = min(MAX_LINEAR_ROWS, m - r0)
+        check(lib().quic_w4a16_linear(ptr(x2[r0:r0 + rows]), C.byref(s), ptr(y[r0:r0 + rows]), rows,
+                                      int(bool(use_tensor)), ptr(w.workspace(rows)), stream_ptr()), "w4a16_linear")
     return y.reshape(*x.shape[:-1], w.size_n)
 
 

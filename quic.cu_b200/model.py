@@ -96,6 +96,15 @@ class SlotCache:
             pass
 
 
+def _sdpa_backends():
+    """Prefill attention is torch SDPA, as in the reference.  The cuDNN backend builds an
+    execution plan for every new sequence length (~0.1 s each), which a serving loop with
+    ragged prompts pays on almost every admission; the flash / memory-efficient kernels do not."""
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    return sdpa_kernel([SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH])
+
+
 def _ctx_bucket(n: int) -> int:
     """Context bound a captured graph is valid for: multiples of 128 up to 2048 (so the
     attention grid tracks the real context closely), powers of two beyond."""
@@ -299,13 +308,14 @@ class QUICForCausalLM:
             qk = K.rope().forward(qk, cos, sin)[0]
             q, k, v = qk[:14], qk[14:16], qkv[:, 16:18].transpose(0, 1)
             attn = torch.empty(T, HEADS * HEAD_DIM, dtype=DTYPE, device=dev)
-            for i, s in enumerate(slots):
-                a, b = bounds[i], bounds[i + 1]
-                cache.kv[li, 0, s, :, : b - a] = k[:, a:b]
-                cache.kv[li, 1, s, :, : b - a] = v[:, a:b]
-                o = F.scaled_dot_product_attention(q[None, :, a:b], k[None, :, a:b], v[None, :, a:b],
-                                                   is_causal=True, scale=HEAD_DIM ** -0.5, enable_gqa=True)
-                attn[a:b] = o[0].transpose(0, 1).reshape(b - a, -1)
+            with _sdpa_backends():
+                for i, s in enumerate(slots):
+                    a, b = bounds[i], bounds[i + 1]
+                    cache.kv[li, 0, s, :, : b - a] = k[:, a:b]
+                    cache.kv[li, 1, s, :, : b - a] = v[:, a:b]
+                    o = F.scaled_dot_product_attention(q[None, :, a:b], k[None, :, a:b], v[None, :, a:b],
+                                                       is_causal=True, scale=HEAD_DIM ** -0.5, enable_gqa=True)
+                    attn[a:b] = o[0].transpose(0, 1).reshape(b - a, -1)
             o = lin(L["o"], attn)
             xn, h = rms(o, L["ln2"], self.eps, residual=h)
             gu = lin(L["gate_up"], xn)
