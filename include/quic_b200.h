@@ -252,6 +252,12 @@ typedef struct {
   int32_t ctx_hint;    /* upper bound of pos+1 over the rows for this launch */
 } quic_decode_t;
 
+/* Batches of at least this many rows run the decode step on the tensor-core
+ * kernels (tcgen05 GEMM, tensor lm_head); smaller ones on the fused GEMV chain.
+ * Default 5 (measured crossover on B200); accepted range 2..9.  Set it before graphs are captured.  No
+ * reference counterpart (Marlin picks its tile shapes per call,
+ * kernels/cuda/marlin.cu:3795-3805). */
+void quic_set_tensor_min_batch(int32_t batch);
 /* Attention split count the decode step uses for `batch` rows whose contexts are
  * at most `ctx` tokens (pass the result as attn_splits and to the scratch size). */
 int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx);

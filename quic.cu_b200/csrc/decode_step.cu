@@ -58,7 +58,7 @@ Arena carve(int batch, int vocab, int splits) {
   a.best_idx = off;
   off += align256((int64_t)batch * grid * 4);
   a.xn = a.qkv = a.gu = a.act16 = a.tcws = off;
-  if (batch > kMaxM) {
+  if (batch >= 2) {  // the tensor-core step may be selected from batch 2 upwards
     a.xn = off;
     off += align256((int64_t)batch * kHidden * 2);
     a.qkv = off;
@@ -107,9 +107,12 @@ int check(const quic_model_t* m, const quic_decode_t* d) {
 
 int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st);
 
+// Smallest batch that takes the tensor-core step (quic_set_tensor_min_batch); 2..9.
+int g_tensor_min_batch = 5;  // measured: the GEMV chain wins up to 4 rows, the tensor step from 5
+
 int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st) {
   const int B = d->batch;
-  if (B > kMaxM) return enqueue_step_batched(m, d, st);
+  if (B >= g_tensor_min_batch) return enqueue_step_batched(m, d, st);
   const int splits = pick_splits(d);
   const Arena ar = carve(B, m->vocab, splits);
   char* base = static_cast<char*>(d->scratch);
@@ -277,7 +280,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     aa.small = ((int64_t)splits * 64 >= ctx) ? 1 : 0;  // 64-token CTAs, merged by the last CTA to arrive
     aa.consumer_merge = 0;
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
-    QUIC_CUDA(launch_attn(aa, B, st, false));
+    QUIC_CUDA(launch_attn(aa, B, st, true));
     rc = w4a16_gemm_tc(attn_out, L.o, tmp, B, ws, st);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)L.ln2, m->eps, xn, h, B, st));
@@ -307,6 +310,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
   la.ring = d->ring > 0 ? d->ring : 1;
   la.step_counter = d->step_counter;
   if (lm_head_tc_supported(B, m->vocab)) return launch_lm_head_tc(la, st);
+  la.x_normed = xn;
   QUIC_CUDA(launch_lm_head(la, lm_head_grid(m->vocab), st, false));
   return QUIC_OK;
 }
@@ -321,12 +325,16 @@ struct Graph {
 
 using namespace quic;
 
+extern "C" void quic_set_tensor_min_batch(int32_t batch) {
+  g_tensor_min_batch = batch < 2 ? 2 : (batch > kMaxM + 1 ? kMaxM + 1 : batch);
+}
+
 extern "C" int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx) {
   if (batch < 1) batch = 1;
   if (ctx < 1) ctx = 1;
   // Short contexts at small batch: one CTA per 64 tokens, merged by the o_proj kernel.
   const int small = (ctx + 63) / 64;
-  if (small <= kMaxConsumerSplits && ((int64_t)batch * small * kKvHeads <= 1184 || batch > kMaxM)) return small;
+  if (small <= kMaxConsumerSplits && ((int64_t)batch * small * kKvHeads <= 1184 || batch >= g_tensor_min_batch)) return small;
   return quic_attn_pick_splits(batch, ctx);
 }
 
@@ -337,7 +345,7 @@ extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32
 
 extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_decode_t* d) {
   if (!m) return 0;
-  if (d && d->batch > kMaxM) return 9 * m->n_layers + 3;  // plus split-K finish kernels
+  if (d && d->batch >= g_tensor_min_batch) return 9 * m->n_layers + 3;  // plus split-K finish kernels
   return 5 * m->n_layers + 1;
 }
 

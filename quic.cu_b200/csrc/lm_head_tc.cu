@@ -81,6 +81,8 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tmem_d = tmem_base_s;
   const uint32_t idesc = umma_idesc_f16(MT);
+  pdl_launch_dependents();
+  pdl_wait();  // the normalised activations come from the previous kernel
 
   if (warp == 4) {
     if (lane == 0) {
@@ -229,20 +231,20 @@ int run(const LmHeadArgs& a, cudaStream_t st) {
   QUIC_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_lm_tc_status));
   const size_t smem = LmSmem<MT>::kTotal;
   QUIC_CUDA(cudaFuncSetAttribute(lm_head_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  lm_head_tc_kernel<MT><<<a.vocab / kTileN, kLmThreads, smem, st>>>(tm_e, tm_x, a, status);
-  QUIC_CUDA(cudaGetLastError());
+  QUIC_CUDA(launch(lm_head_tc_kernel<MT>, dim3(a.vocab / kTileN), dim3(kLmThreads), smem, st, true, tm_e, tm_x, a,
+                   status));
   return QUIC_OK;
 }
 
 }  // namespace
 
-bool lm_head_tc_supported(int batch, int vocab) { return batch > kMaxM && batch <= 128 && vocab % kTileN == 0; }
+bool lm_head_tc_supported(int batch, int vocab) { return batch >= 2 && batch <= 128 && vocab % kTileN == 0; }
 int lm_head_tc_tiles(int vocab) { return vocab / kTileN; }
 
 // x_normed rows [batch, 896] -> logits / argmax; the best_* arrays hold batch x (vocab / 128) entries.
 int launch_lm_head_tc(const LmHeadArgs& a, cudaStream_t st) {
   QUIC_REQUIRE(a.x_normed != nullptr && lm_head_tc_supported(a.batch, a.vocab), QUIC_E_SHAPE,
-               "lm_head: the tensor path needs 9..128 normalised rows and a vocabulary multiple of 128");
+               "lm_head: the tensor path needs 2..128 normalised rows and a vocabulary multiple of 128");
   QUIC_REQUIRE(((uintptr_t)a.embed % 16 == 0) && ((uintptr_t)a.x_normed % 16 == 0), QUIC_E_ARG,
                "lm_head: tensors must be 16-byte aligned");
   if (a.batch <= 16) return run<16>(a, st);

@@ -35,10 +35,12 @@ __global__ void __launch_bounds__(224) rmsnorm_kernel(const half* __restrict__ x
                                                       half* __restrict__ sum_out, int rows) {
   __shared__ float red[8];
   const int row = blockIdx.x, t = threadIdx.x, c = 4 * t;
+  const uint2 wv = *reinterpret_cast<const uint2*>(w + c);  // weights: not produced by the chain
+  pdl_launch_dependents();
+  pdl_wait();
   const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * kHidden + c);
   uint2 r = make_uint2(0, 0);
   if (res != nullptr) r = *reinterpret_cast<const uint2*>(res + (size_t)row * kHidden + c);
-  const uint2 wv = *reinterpret_cast<const uint2*>(w + c);
   float2 a = __half22float2(u32_as_half2(u.x)), b = __half22float2(u32_as_half2(u.y));
   if (res != nullptr) {
     const float2 ra = __half22float2(u32_as_half2(r.x)), rb = __half22float2(u32_as_half2(r.y));
@@ -208,6 +210,8 @@ __global__ void __launch_bounds__(256) gemv_f16_kernel(const half* __restrict__ 
 __global__ void embed_rows_kernel(const half* __restrict__ embed, const int32_t* __restrict__ rows,
                                   const int32_t* __restrict__ tok, int vocab, half* __restrict__ x, int batch) {
   const int b = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (b >= batch) return;
   int t = tok[rows[b]];
   t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
@@ -223,6 +227,8 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const int32_t* __r
                                 const half* __restrict__ sin_t, int max_pos, half* __restrict__ qbuf,
                                 half* __restrict__ kcache, half* __restrict__ vcache, int s_max, int batch) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (idx >= batch * (kQkvN / 2)) return;
   const int b = idx / (kQkvN / 2), c2 = idx % (kQkvN / 2);
   const int head = c2 >> 5, pair = c2 & 31;  // stored columns (2*pair, 2*pair+1) = dims (pair, pair+32)
@@ -252,6 +258,8 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const int32_t* __r
 // act[b][i] = silu(gu[b][i]) * gu[b][4864 + i] on the fused gate|up output.
 __global__ void swiglu_fused_kernel(const half* __restrict__ gu, half* __restrict__ act, int batch) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (idx >= (size_t)batch * (kInter / 2)) return;
   const int b = idx / (kInter / 2), i2 = idx % (kInter / 2);
   const half2* row = reinterpret_cast<const half2*>(gu + (size_t)b * 2 * kInter);
@@ -263,26 +271,22 @@ __global__ void swiglu_fused_kernel(const half* __restrict__ gu, half* __restric
 
 cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,
                               int batch, cudaStream_t st) {
-  embed_rows_kernel<<<batch, 224, 0, st>>>(embed, rows, tok, vocab, x, batch);
-  return cudaGetLastError();
+  return launch(embed_rows_kernel, dim3(batch), dim3(224), 0, st, true, embed, rows, tok, vocab, x, batch);
 }
 cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t* pos, const half* cos_t,
                             const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
                             int batch, cudaStream_t st) {
   const int total = batch * (kQkvN / 2);
-  qkv_post_kernel<<<(total + 255) / 256, 256, 0, st>>>(qkv, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache,
-                                                       vcache, s_max, batch);
-  return cudaGetLastError();
+  return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, qkv, rows, pos, cos_t, sin_t,
+                max_pos, qbuf, kcache, vcache, s_max, batch);
 }
 cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream_t st) {
   const size_t total = (size_t)batch * (kInter / 2);
-  swiglu_fused_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(gu, act, batch);
-  return cudaGetLastError();
+  return launch(swiglu_fused_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, gu, act, batch);
 }
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st) {
-  rmsnorm_kernel<<<rows, 224, 0, st>>>(x, residual, w, eps, y, sum_out, rows);
-  return cudaGetLastError();
+  return launch(rmsnorm_kernel, dim3(rows), dim3(224), 0, st, true, x, residual, w, eps, y, sum_out, rows);
 }
 }  // namespace quic
 

@@ -131,6 +131,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   tc_fence_after();
   const uint32_t tmem_d = tmem_base_s;
   const uint32_t idesc = umma_idesc_f16(MT);
+  // Everything above touched weights and on-chip state only; the activations come from the
+  // previous kernel of the stream.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == kConsumers / 32) {
     // ---------------- TMA producer ----------------
@@ -263,6 +267,8 @@ __global__ void tc_splitk_finish_kernel(const float* __restrict__ part, const ha
                                         half* __restrict__ y, int m_total, int N, int splits) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)m_total * N;
+  pdl_launch_dependents();
+  pdl_wait();
   if (idx >= total) return;
   float p[16];
 #pragma unroll
@@ -290,8 +296,7 @@ int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
   QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
   dim3 grid(a.w.n / kTileN, splits, (a.m_total + MT - 1) / MT);
-  w4a16_gemm_tc_kernel<MT><<<grid, kGemmThreads, smem, st>>>(tm_w, tm_x, a);
-  QUIC_CUDA(cudaGetLastError());
+  QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
   return QUIC_OK;
 }
 
@@ -344,9 +349,8 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   if (rc != QUIC_OK) return rc;
   if (splits > 1) {
     const size_t total = (size_t)m * w.n;
-    tc_splitk_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.part, (const half*)w.bias, y, m,
-                                                                               w.n, splits);
-    QUIC_CUDA(cudaGetLastError());
+    QUIC_CUDA(launch(tc_splitk_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true,
+                     (const float*)a.part, (const half*)w.bias, y, m, w.n, splits));
   }
   return QUIC_OK;
 }

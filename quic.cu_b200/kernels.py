@@ -115,6 +115,7 @@ SIGNATURES = {
     "quic_attn_decode_noalloc_max_bytes": (_I64, []),
     "quic_attn_pick_splits": (_I32, [_I32, _I32]),
     "quic_attn_scratch_bytes": (_I64, [_I32, _I32]),
+    "quic_set_tensor_min_batch": (None, [_I32]),
     "quic_decode_pick_splits": (_I32, [_I32, _I32]),
     "quic_decode_scratch_bytes": (_I64, [_I32, _I32, _I32]),
     "quic_decode_launch_count": (_I32, [C.POINTER(Model), C.POINTER(Decode)]),
