@@ -129,13 +129,20 @@ int lm_head_grid(int vocab);
 // pieces of the batched (batch > 8) decode step
 cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,
                               int batch, cudaStream_t st);
+// Fused consumers of split-K partial sums [splits][batch][N] (fp32).
+cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
+                                 const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,
+                                 half* kcache, half* vcache, int s_max, int batch, cudaStream_t st);
+cudaError_t launch_rmsnorm_part(const float* part, int splits, const half* residual, const half* w, float eps,
+                                half* y, half* sum_out, int rows, cudaStream_t st);
 cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t* pos, const half* cos_t,
                             const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
                             int batch, cudaStream_t st);
 cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream_t st);
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st);
-int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st);
+int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st,
+                  int* splits_out = nullptr);
 int64_t w4a16_gemm_tc_workspace(int m, int n, int k);
 bool lm_head_tc_supported(int batch, int vocab);
 int lm_head_tc_tiles(int vocab);

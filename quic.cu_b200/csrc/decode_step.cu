@@ -240,11 +240,9 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
   const Arena ar = carve(B, m->vocab, splits);
   char* base = static_cast<char*>(d->scratch);
   half* h = reinterpret_cast<half*>(base + ar.xres);        // residual stream
-  half* tmp = h + (size_t)B * kHidden;                        // o_proj / down output
   half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
   half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
   half* xn = reinterpret_cast<half*>(base + ar.xn);
-  half* qkv = reinterpret_cast<half*>(base + ar.qkv);
   half* gu = reinterpret_cast<half*>(base + ar.gu);
   half* act = reinterpret_cast<half*>(base + ar.act16);
   float* ws = reinterpret_cast<float*>(base + ar.tcws);
@@ -260,10 +258,13 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     const quic_layer_t& L = m->layers[l];
     half* kc = static_cast<half*>(d->kv) + (size_t)(2 * l) * kv_plane;
     half* vc = kc + kv_plane;
-    int rc = w4a16_gemm_tc(xn, L.qkv, qkv, B, ws, st);
+    // linears whose consumer is a small kernel leave split-K partials for it to reduce
+    int sp = 1;
+    const float* part = ws + 4096;
+    int rc = w4a16_gemm_tc(xn, L.qkv, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
-    QUIC_CUDA(launch_qkv_post(qkv, d->rows, d->pos, (const half*)m->rope_cos, (const half*)m->rope_sin,
-                              m->max_pos, qbuf, kc, vc, d->s_max, B, st));
+    QUIC_CUDA(launch_qkv_post_part(part, sp, (const half*)L.qkv.bias, d->rows, d->pos, (const half*)m->rope_cos,
+                                   (const half*)m->rope_sin, m->max_pos, qbuf, kc, vc, d->s_max, B, st));
     AttnArgs aa = {};
     aa.q = qbuf;
     aa.k = kc;
@@ -281,16 +282,16 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     aa.consumer_merge = 0;
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
     QUIC_CUDA(launch_attn(aa, B, st, true));
-    rc = w4a16_gemm_tc(attn_out, L.o, tmp, B, ws, st);
+    rc = w4a16_gemm_tc(attn_out, L.o, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
-    QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)L.ln2, m->eps, xn, h, B, st));
+    QUIC_CUDA(launch_rmsnorm_part(part, sp, h, (const half*)L.ln2, m->eps, xn, h, B, st));
     rc = w4a16_gemm_tc(xn, L.gate_up, gu, B, ws, st);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_swiglu_fused(gu, act, B, st));
-    rc = w4a16_gemm_tc(act, L.down, tmp, B, ws, st);
+    rc = w4a16_gemm_tc(act, L.down, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
     const half* next_ln = (l + 1 < m->n_layers) ? (const half*)m->layers[l + 1].ln1 : (const half*)m->final_norm;
-    QUIC_CUDA(launch_rmsnorm(tmp, h, next_ln, m->eps, xn, h, B, st));
+    QUIC_CUDA(launch_rmsnorm_part(part, sp, h, next_ln, m->eps, xn, h, B, st));
   }
   LmHeadArgs la = {};
   la.embed = embed;

@@ -28,8 +28,10 @@ namespace {
 // ---- RMSNorm (+ residual) ---------------------------------------------------
 // One CTA of 224 threads per row of 896 (4 elements per thread); every global load of the
 // row, the residual and the weight is requested before the first use.
-__global__ void __launch_bounds__(224) rmsnorm_kernel(const half* __restrict__ x,
-                                                      const half* __restrict__ res,
+// With `part` set, the row is the fp16-rounded sum of `splits` fp32 partial planes
+// [splits][rows][896] (split-K output of the GEMM before it) instead of x.
+__global__ void __launch_bounds__(224) rmsnorm_kernel(const half* __restrict__ x, const float* __restrict__ part,
+                                                      int splits, const half* __restrict__ res,
                                                       const half* __restrict__ w, float eps,
                                                       half* __restrict__ y,
                                                       half* __restrict__ sum_out, int rows) {
@@ -38,10 +40,27 @@ __global__ void __launch_bounds__(224) rmsnorm_kernel(const half* __restrict__ x
   const uint2 wv = *reinterpret_cast<const uint2*>(w + c);  // weights: not produced by the chain
   pdl_launch_dependents();
   pdl_wait();
-  const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * kHidden + c);
   uint2 r = make_uint2(0, 0);
   if (res != nullptr) r = *reinterpret_cast<const uint2*>(res + (size_t)row * kHidden + c);
-  float2 a = __half22float2(u32_as_half2(u.x)), b = __half22float2(u32_as_half2(u.y));
+  float2 a, b;
+  if (part != nullptr) {
+    float4 p[16];
+#pragma unroll
+    for (int s = 0; s < 16; ++s)
+      p[s] = s < splits ? __ldcg(reinterpret_cast<const float4*>(part + ((size_t)s * rows + row) * kHidden + c))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+      v.x += p[s].x; v.y += p[s].y; v.z += p[s].z; v.w += p[s].w;
+    }
+    a = make_float2(__half2float(__float2half_rn(v.x)), __half2float(__float2half_rn(v.y)));
+    b = make_float2(__half2float(__float2half_rn(v.z)), __half2float(__float2half_rn(v.w)));
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)row * kHidden + c);
+    a = __half22float2(u32_as_half2(u.x));
+    b = __half22float2(u32_as_half2(u.y));
+  }
   if (res != nullptr) {
     const float2 ra = __half22float2(u32_as_half2(r.x)), rb = __half22float2(u32_as_half2(r.y));
     // the residual stream is an fp16 tensor: round the sum
@@ -222,7 +241,8 @@ __global__ void embed_rows_kernel(const half* __restrict__ embed, const int32_t*
 
 // RoPE + q buffer + KV append from the fused QKV output (columns in rope-pair order,
 // bias already added).  One thread per (row, column pair).
-__global__ void qkv_post_kernel(const half* __restrict__ qkv, const int32_t* __restrict__ rows,
+__global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __restrict__ part, int splits,
+                                const half* __restrict__ bias, const int32_t* __restrict__ rows,
                                 const int32_t* __restrict__ pos, const half* __restrict__ cos_t,
                                 const half* __restrict__ sin_t, int max_pos, half* __restrict__ qbuf,
                                 half* __restrict__ kcache, half* __restrict__ vcache, int s_max, int batch) {
@@ -234,7 +254,25 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const int32_t* __r
   const int head = c2 >> 5, pair = c2 & 31;  // stored columns (2*pair, 2*pair+1) = dims (pair, pair+32)
   const int slot = rows[b];
   const int p = pos[slot];
-  const float2 v = __half22float2(*reinterpret_cast<const half2*>(qkv + (size_t)b * kQkvN + 2 * c2));
+  float2 v;
+  if (part != nullptr) {  // fp16(sum of the split-K partials) + bias, as the GEMM epilogue would do
+    float2 p[16];
+#pragma unroll
+    for (int s = 0; s < 16; ++s)
+      p[s] = s < splits ? __ldcg(reinterpret_cast<const float2*>(part + ((size_t)s * batch + b) * kQkvN + 2 * c2))
+                        : make_float2(0.f, 0.f);
+    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+      acc.x += p[s].x;
+      acc.y += p[s].y;
+    }
+    const float2 bb = __half22float2(*reinterpret_cast<const half2*>(bias + 2 * c2));
+    v.x = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.x)) + bb.x));
+    v.y = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.y)) + bb.y));
+  } else {
+    v = __half22float2(*reinterpret_cast<const half2*>(qkv + (size_t)b * kQkvN + 2 * c2));
+  }
   float lo = v.x, hi = v.y;
   if (head < kHeads + kKvHeads) {
     const int pp = p < max_pos ? p : max_pos - 1;
@@ -277,8 +315,20 @@ cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t*
                             const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
                             int batch, cudaStream_t st) {
   const int total = batch * (kQkvN / 2);
-  return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, qkv, rows, pos, cos_t, sin_t,
-                max_pos, qbuf, kcache, vcache, s_max, batch);
+  return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, qkv, (const float*)nullptr, 0,
+                (const half*)nullptr, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch);
+}
+cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
+                                 const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,
+                                 half* kcache, half* vcache, int s_max, int batch, cudaStream_t st) {
+  const int total = batch * (kQkvN / 2);
+  return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, (const half*)nullptr, part,
+                splits, bias, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch);
+}
+cudaError_t launch_rmsnorm_part(const float* part, int splits, const half* residual, const half* w, float eps,
+                                half* y, half* sum_out, int rows, cudaStream_t st) {
+  return launch(rmsnorm_kernel, dim3(rows), dim3(224), 0, st, true, (const half*)nullptr, part, splits, residual, w,
+                eps, y, sum_out, rows);
 }
 cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream_t st) {
   const size_t total = (size_t)batch * (kInter / 2);
@@ -286,7 +336,8 @@ cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream
 }
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st) {
-  return launch(rmsnorm_kernel, dim3(rows), dim3(224), 0, st, true, x, residual, w, eps, y, sum_out, rows);
+  return launch(rmsnorm_kernel, dim3(rows), dim3(224), 0, st, true, x, (const float*)nullptr, 0, residual, w, eps, y,
+                sum_out, rows);
 }
 }  // namespace quic
 
@@ -305,7 +356,7 @@ extern "C" int quic_rmsnorm(const void* x, const void* residual, const void* w, 
                QUIC_E_ARG, "rmsnorm: tensors must be 8-byte aligned");
   if (rows == 0) return QUIC_OK;
   rmsnorm_kernel<<<rows, 224, 0, (cudaStream_t)stream>>>(
-      (const half*)x, (const half*)residual, (const half*)w, eps, (half*)y, (half*)sum_out, rows);
+      (const half*)x, nullptr, 0, (const half*)residual, (const half*)w, eps, (half*)y, (half*)sum_out, rows);
   QUIC_CUDA(cudaGetLastError());
   return QUIC_OK;
 }

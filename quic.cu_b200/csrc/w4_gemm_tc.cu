@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       const int quarter = warp & 3, cgroup = warp >> 2;
       const int col = n0 + quarter * 32 + lane;
       constexpr int kColsPerGroup = MT >= 32 ? MT / 4 : 8;
-      const float bias = (a.w.bias != nullptr && gridDim.y == 1)
+      const float bias = (a.w.bias != nullptr && gridDim.y == 1 && a.y != nullptr)
                              ? __half2float(reinterpret_cast<const half*>(a.w.bias)[col])
                              : 0.f;
 #pragma unroll 1
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
           const int m = m0 + c0 + j;
           if (m >= a.m_total) continue;
           const float v = __uint_as_float(r[j]);
-          if (gridDim.y == 1) {
+          if (gridDim.y == 1 && a.y != nullptr) {
             float o = __half2float(__float2half_rn(v));
             if (a.w.bias != nullptr) o += bias;
             a.y[(size_t)m * N + col] = __float2half_rn(o);
@@ -322,7 +322,10 @@ int64_t w4a16_gemm_tc_workspace(int m, int n, int k) {
   return splits > 1 ? (int64_t)splits * m * n * 4 : 0;
 }
 
-int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st) {
+// y == nullptr: leave the fp32 partial sums of all `*splits_out` K splits in the workspace
+// (after its 16 KB head) for a fused consumer; no bias is applied.
+int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st,
+                  int* splits_out) {
   QUIC_REQUIRE(w.n % kTileN == 0 && w.k % kBlockK == 0, QUIC_E_SHAPE,
                "w4a16_linear: the tensor path needs N multiple of 128 and K multiple of 64");
   QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0), QUIC_E_ARG,
@@ -330,7 +333,9 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16_linear: K beyond 5120 on the tensor path");
   int mt, splits, per;
   tc_plan(m, w.n, w.k, &mt, &splits, &per);
-  QUIC_REQUIRE(splits == 1 || workspace != nullptr, QUIC_E_ARG, "w4a16_linear: split-K needs a workspace");
+  QUIC_REQUIRE((splits == 1 && y != nullptr) || workspace != nullptr, QUIC_E_ARG,
+               "w4a16_linear: split-K needs a workspace");
+  if (splits_out != nullptr) *splits_out = splits;
   GemmArgs a = {};
   a.w = w;
   a.y = y;
@@ -347,7 +352,7 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
     default: rc = run<128>(x, a, splits, st); break;
   }
   if (rc != QUIC_OK) return rc;
-  if (splits > 1) {
+  if (splits > 1 && y != nullptr) {
     const size_t total = (size_t)m * w.n;
     QUIC_CUDA(launch(tc_splitk_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true,
                      (const float*)a.part, (const half*)w.bias, y, m, w.n, splits));

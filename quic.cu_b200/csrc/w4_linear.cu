@@ -216,7 +216,7 @@ extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int
   cudaStream_t st = (cudaStream_t)stream;
   if (use_tensor && m >= 16) {
     QUIC_REQUIRE(workspace != nullptr, QUIC_E_ARG, "w4a16_linear: tensor path needs a workspace");
-    return w4a16_gemm_tc((const half*)x, *w, (half*)y, m, (float*)workspace, st);
+    return w4a16_gemm_tc((const half*)x, *w, (half*)y, m, (float*)workspace, st, nullptr);
   }
   // the first 16 KB of the workspace belong to the tensor path's arrival counters
   float* part = workspace != nullptr ? static_cast<float*>(workspace) + 4096 : nullptr;
