@@ -278,7 +278,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     aa.chunk = (ctx + splits - 1) / splits;
     aa.scale = 0.125f;
     aa.out = attn_out;
-    aa.small = ((int64_t)splits * 64 >= ctx) ? 1 : 0;  // 64-token CTAs, merged by the last CTA to arrive
+    aa.small = 0;  // throughput regime: lane-per-token CTAs, splits merged by the last CTA to arrive
     aa.consumer_merge = 0;
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
     QUIC_CUDA(launch_attn(aa, B, st, true));
@@ -334,6 +334,14 @@ extern "C" int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx) {
   if (batch < 1) batch = 1;
   if (ctx < 1) ctx = 1;
   // Short contexts at small batch: one CTA per 64 tokens, merged by the o_proj kernel.
+  // Throughput regime: 256-thread CTAs that each walk >= 256 tokens, just enough splits to
+  // give every SM a CTA (one split, hence no merge, from 48 rows up).
+  if (batch >= g_tensor_min_batch && ctx <= 4096) {
+    int s = (120 + batch * kKvHeads - 1) / (batch * kKvHeads);
+    const int by_len = (ctx + 255) / 256;
+    if (s > by_len) s = by_len;
+    return s < 1 ? 1 : s;
+  }
   const int small = (ctx + 63) / 64;
   if (small <= kMaxConsumerSplits && ((int64_t)batch * small * kKvHeads <= 1184 || batch >= g_tensor_min_batch)) return small;
   return quic_attn_pick_splits(batch, ctx);
