@@ -301,6 +301,49 @@ def run_gpu(args) -> None:
         dist.destroy_process_group()
 
 
+def linear_sweep(device: str = "cuda:0", shapes=None, ms=(1, 4, 16, 64, 256), reps: int = 20) -> list[dict]:
+    """The single W4A16 linear-op sweep of the benchmark configuration: the model's four
+    (K, N) shapes at M in {1, 4, 16, 64, 256}; int4 values and zero points uniform in 0..15,
+    scales |N(0, 0.01)| + 1e-3, activations N(0, 1).  Each point is timed as a CUDA graph of
+    ``reps`` launches (device time, no host overhead).  M < 16 runs the dequant GEMV, M >= 16
+    the tcgen05 GEMM."""
+    entry.load_package()
+    from quic_cu_b200 import kernels as K
+    from quic_cu_b200.checkpoint import synthetic_layer
+
+    peak, kind = peaks()
+    shapes = shapes or {"qkv": (896, 1152), "o_proj": (896, 896), "gate_up": (896, 9728), "down": (4864, 896)}
+    out = []
+    for name, (k, n) in shapes.items():
+        layer = synthetic_layer(n, k, torch.Generator().manual_seed(0))
+        w = K.W4Weight(n, k, device)
+        w.put(layer["weight_packed"], layer["weight_scale"], layer["weight_zero_point"])
+        for m in ms:
+            x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).half().to(device)
+            for _ in range(3):
+                K.w4a16_linear(w, x)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(reps):
+                    K.w4a16_linear(w, x)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (5 * reps)
+            nbytes = w.weight_bytes + m * k * 2 + m * n * 2
+            out.append({"layer": name, "k": k, "n": n, "m": m, "kernel": "tcgen05 gemm" if m >= 16 else "gemv",
+                        "us": us, "GB/s": nbytes / us / 1e3, "hbm_frac": nbytes / us / 1e3 / peak,
+                        "TFLOP/s": 2.0 * m * n * k / us / 1e6, "algorithmic_bytes": nbytes,
+                        "note": "weights stay in L2 between the launches of a graph"})
+    return out
+
+
 def measure_batch64(net, device, world, dist):
     """Decode tokens/s with 64 rows in flight (64 KV slots, 512 cached tokens each, 128 greedy
     steps), state resident, CUDA events, max over ranks."""
@@ -404,7 +447,13 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=24,
                     help="decoder layers of the synthetic model; values below 24 exist only to keep "
                          "profiler captures small and do not produce a valid benchmark line")
+    ap.add_argument("--linear-sweep", action="store_true",
+                    help="print the W4A16 linear-op sweep (one JSON line per point) and exit")
     args = ap.parse_args()
+    if args.linear_sweep:
+        for row in linear_sweep():
+            print(json.dumps(row))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
