@@ -287,7 +287,7 @@ def run_gpu(args) -> None:
         "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate",
         "data": "synthetic", "config": dict(CONFIG, parallelism=f"{world} independent replica(s)"),
-        "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * GEN_TOKENS * net.launches_per_step(),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": world * args.steps * GEN_TOKENS * net.launches_per_step(),
         "roofline": roofline, "roofline_step": roofline_step, "batch64": batch64, "serving": serving,
     }
     if args.layers != 24:
@@ -341,6 +341,51 @@ def linear_sweep(device: str = "cuda:0", shapes=None, ms=(1, 4, 16, 64, 256), re
                         "us": us, "GB/s": nbytes / us / 1e3, "hbm_frac": nbytes / us / 1e3 / peak,
                         "TFLOP/s": 2.0 * m * n * k / us / 1e6, "algorithmic_bytes": nbytes,
                         "note": "weights stay in L2 between the launches of a graph"})
+    return out
+
+
+def attention_sweep(device: str = "cuda:0", batches=(1, 16, 64, 256), contexts=(128, 1024, 8192, 32768)) -> list[dict]:
+    """The split-K GQA decode-attention sweep of the benchmark configuration: 14 query / 2 KV
+    heads, head_dim 64, fp16 N(0,1) Q/K/V, every row left-padded by a length uniform in
+    [0, context/4].  Timed as a CUDA graph of launches through the reference-shaped op
+    (flash_attn_decode().forward); bytes = K and V of the unpadded tokens + Q + O."""
+    entry.load_package()
+    from quic_cu_b200 import kernels as K
+
+    peak, kind = peaks()
+    out = []
+    op = K.flash_attn_decode()
+    for b in batches:
+        for s in contexts:
+            g = torch.Generator(device=device).manual_seed(b * 100003 + s)
+            q = torch.randn((b, 14, 1, 64), device=device, generator=g).half()
+            k = torch.randn((b, 2, s, 64), device=device, generator=g).half()
+            v = torch.randn((b, 2, s, 64), device=device, generator=g).half()
+            pads = torch.randint(0, s // 4 + 1, (b,), device=device, generator=g).int()
+            for _ in range(3):
+                op.forward(q, k, v, 0.125, pads)
+            torch.cuda.synchronize()
+            reps = 10 if b * s < (1 << 20) else 3
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(reps):
+                    op.forward(q, k, v, 0.125, pads)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (3 * reps)
+            tokens = int((s - pads.long()).sum().item())
+            nbytes = tokens * 512 + b * 14 * 64 * 2 * 2
+            out.append({"batch": b, "context": s, "splits": K.lib().quic_attn_pick_splits(b, s), "us": us,
+                        "GB/s": nbytes / us / 1e3, "hbm_frac": nbytes / us / 1e3 / peak, "peak_kind": f"of {kind}",
+                        "algorithmic_bytes": nbytes,
+                        "note": "K/V larger than L2 from ~100 MB up; smaller cases are served from L2"})
+            del q, k, v
     return out
 
 
@@ -449,7 +494,13 @@ def main() -> None:
                          "profiler captures small and do not produce a valid benchmark line")
     ap.add_argument("--linear-sweep", action="store_true",
                     help="print the W4A16 linear-op sweep (one JSON line per point) and exit")
+    ap.add_argument("--attention-sweep", action="store_true",
+                    help="print the decode-attention sweep (one JSON line per point) and exit")
     args = ap.parse_args()
+    if args.attention_sweep:
+        for row in attention_sweep():
+            print(json.dumps(row))
+        return
     if args.linear_sweep:
         for row in linear_sweep():
             print(json.dumps(row))

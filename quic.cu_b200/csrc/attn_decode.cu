@@ -18,6 +18,15 @@
 //     spin-wait is needed.
 #include "decode_kernels.cuh"
 
+// Bytes reserved for the arrival counters at the head of the scratch: a fixed 64 KB (8192
+// rows) so that a scratch block shared by calls of different batch sizes keeps its counters
+// apart from the partials whatever the layout of the previous call was.
+static int64_t counter_bytes(int b) {
+  const int64_t need = ((int64_t)b * QUIC_KV_HEADS * 4 + 255) / 256 * 256;
+  return need > 65536 ? need : 65536;
+}
+
+
 namespace quic {
 namespace {
 
@@ -454,11 +463,211 @@ __global__ void __launch_bounds__(256) attn_decode_small_kernel(const AttnArgs a
   merge_splits_last_cta(a, b, kvh, split, &last_flag);
 }
 
+
+// ---------------------------------------------------------------------------
+// Throughput variant on the warp-level tensor cores.  With 7 query heads per KV
+// head, q·K and p·V cost 7 FMA per byte of cache, more than the fp32 pipes can
+// issue at HBM speed, so here both products are mma.m16n8k16 (fp16 in, fp32
+// accumulate): heads on the M side (7 of 16 rows used), tokens / dims on N.
+// No operand goes through shared memory:
+//   * K: a lane loads 32 contiguous bytes of one token row (coalesced 16-byte
+//     loads).  The mma's k index is mapped to head dims so that those 32 bytes
+//     are exactly the lane's B fragments of the four k steps; the Q fragments
+//     use the same mapping.
+//   * P: the score fragment of two 8-token blocks is already the A fragment of
+//     one 16-token k step (scores stay in registers).
+//   * V: a lane loads 16 bytes (8 dims) of four token rows and pairs the rows
+//     with byte permutes into B fragments; the n index is mapped to dims so the
+//     eight mma of a k step cover all 64 dims.
+// Softmax bookkeeping is fp32 per head (online rescale per 32-token tile).
+// 4 warps per CTA, tiles of 32 tokens strided over the warps.
+// ---------------------------------------------------------------------------
+constexpr int kMmaWarps = 4;
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kMmaWarps * 32) attn_decode_mma_kernel(const AttnArgs a) {
+  __shared__ float m_s[kMmaWarps][kGroupHeads];
+  __shared__ float l_s[kMmaWarps][kGroupHeads];
+  __shared__ __align__(16) float o_s[kMmaWarps][kGroupHeads][kHeadDim];
+  __shared__ int last_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;  // fragment row (head) and column pair
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  int slot = b;
+  if (a.pos != nullptr) slot = a.rows[b];
+  pdl_trigger_early();
+  pdl_wait();
+  QUIC_TLOG_BEGIN(2);
+
+  int t_begin = 0, t_end = a.s_cap;
+  if (a.pos != nullptr) {
+    t_end = __ldcg(a.pos + slot) + 1;
+  } else {
+    if (a.start != nullptr) t_begin = a.start[b];
+    if (a.end != nullptr) t_end = a.end[b];
+  }
+  if (t_end > a.s_cap) t_end = a.s_cap;
+  if (t_begin < 0) t_begin = 0;
+  const int c_begin = max(t_begin, split * a.chunk);
+  const int c_end = min(t_end, (split + 1) * a.chunk);
+  const int last_tok = a.s_cap - 1;
+
+  // Q fragments: head g (rows 7..15 of the tile are zero), dims 16c + 4ks + {0,1} | {2,3}
+  uint32_t qa0[4], qa2[4];
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    qa0[ks] = qa2[ks] = 0u;
+    if (g < kGroupHeads) {
+      const half* qp = a.q + ((size_t)b * kHeads + kvh * kGroupHeads + g) * kHeadDim + 16 * c + 4 * ks;
+      const uint2 u = *reinterpret_cast<const uint2*>(qp);
+      qa0[ks] = u.x;
+      qa2[ks] = u.y;
+    }
+  }
+  const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+  const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
+
+  float m_run = -INFINITY, l_run = 0.f;  // head g (replicated over the 4 lanes of the row)
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  const int tile0 = (split * a.chunk) & ~31;  // tiles are aligned to 32 tokens
+  for (int t0 = tile0 + warp * 32; t0 < c_end; t0 += kMmaWarps * 32) {
+    if (t0 + 32 <= c_begin) continue;
+    // ---- loads: K rows t0 + 8nb + g, bytes [32c, 32c+32); V rows t0 + 16j + 2c + {0,1,8,9}, dims 8g..8g+7
+    uint4 kr[4][2], vr[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(t0 + 8 * nb + g, last_tok) * kHeadDim + 16 * c);
+      kr[nb][0] = ldg_nc_u128(kp);
+      kr[nb][1] = ldg_nc_u128(kp + 1);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int tb = t0 + 16 * j + 2 * c;
+      vr[j][0] = ldg_nc_u128(vbase + (size_t)min(tb, last_tok) * kHeadDim + 8 * g);
+      vr[j][1] = ldg_nc_u128(vbase + (size_t)min(tb + 1, last_tok) * kHeadDim + 8 * g);
+      vr[j][2] = ldg_nc_u128(vbase + (size_t)min(tb + 8, last_tok) * kHeadDim + 8 * g);
+      vr[j][3] = ldg_nc_u128(vbase + (size_t)min(tb + 9, last_tok) * kHeadDim + 8 * g);
+    }
+    // ---- scores: S[head g][token t0 + 8nb + 2c + {0,1}]
+    float sc[4][2];
+    float m_tile = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      float d[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&kr[nb][0]);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) mma16816(d, qa0[ks], 0u, qa2[ks], 0u, u[2 * ks], u[2 * ks + 1]);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int t = t0 + 8 * nb + 2 * c + e;
+        const float v = (t >= c_begin && t < c_end) ? d[e] * a.scale : -INFINITY;
+        sc[nb][e] = v;
+        m_tile = fmaxf(m_tile, v);
+      }
+    }
+    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
+    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
+    const float m_new = fmaxf(m_run, m_tile);  // the tile holds at least one token of the range
+    const float alpha = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
+    uint32_t pa[2][2];  // P as A fragments: [k step of 16 tokens][a0 | a2]
+    float l_add = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      const float p0 = (sc[nb][0] == -INFINITY) ? 0.f : __expf(sc[nb][0] - m_new);
+      const float p1 = (sc[nb][1] == -INFINITY) ? 0.f : __expf(sc[nb][1] - m_new);
+      const half2 ph = __floats2half2_rn(p0, p1);
+      // the row sum uses the rounded probabilities that multiply V
+      l_add += __low2float(ph) + __high2float(ph);
+      pa[nb >> 1][nb & 1] = *reinterpret_cast<const uint32_t*>(&ph);
+    }
+    l_run = l_run * alpha + l_add;
+    m_run = m_new;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j][0] *= alpha;
+      o[j][1] *= alpha;
+    }
+    // ---- O[head g][dims] += P V ; mma j covers dims {8n + j}: lane n = g supplies dim 8g + j
+#pragma unroll
+    for (int jk = 0; jk < 2; ++jk) {
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vr[jk][0]);  // token 2c
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vr[jk][1]);  // token 2c + 1
+      const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vr[jk][2]);  // token 2c + 8
+      const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vr[jk][3]);  // token 2c + 9
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {  // word w holds dims 8g + 2w, 8g + 2w + 1
+        const uint32_t b0_lo = __byte_perm(r0[w], r1[w], 0x5410), b0_hi = __byte_perm(r0[w], r1[w], 0x7632);
+        const uint32_t b1_lo = __byte_perm(r2[w], r3[w], 0x5410), b1_hi = __byte_perm(r2[w], r3[w], 0x7632);
+        mma16816(o[2 * w], pa[jk][0], 0u, pa[jk][1], 0u, b0_lo, b1_lo);
+        mma16816(o[2 * w + 1], pa[jk][0], 0u, pa[jk][1], 0u, b0_hi, b1_hi);
+      }
+    }
+  }
+
+  // ---- warp state -> shared memory in the layout of the scalar kernels
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (g < kGroupHeads) {
+    if (c == 0) {
+      m_s[warp][g] = m_run;
+      l_s[warp][g] = l_run;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j
+      o_s[warp][g][16 * c + j] = o[j][0];
+      o_s[warp][g][16 * c + 8 + j] = o[j][1];
+    }
+  }
+  __syncthreads();
+
+  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += kMmaWarps * 32) {
+    const int h = idx >> 6, d = idx & 63;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) m = fmaxf(m, m_s[w][h]);
+    float num = 0.f, den = 0.f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) {
+        const float e = (m_s[w][h] == -INFINITY) ? 0.f : __expf(m_s[w][h] - m);
+        den += e * l_s[w][h];
+        num += e * o_s[w][h][d];
+      }
+    }
+    const int qh = kvh * kGroupHeads + h;
+    if (a.splits == 1) {
+      a.out[((size_t)b * kHeads + qh) * kHeadDim + d] = __float2half_rn(m == -INFINITY ? 0.f : num / den);
+    } else {
+      const size_t row = ((size_t)b * kHeads + qh) * a.splits + split;
+      a.o_part[row * kHeadDim + d] = num;
+      if (d == 0) {
+        a.m_part[row] = m;
+        a.l_part[row] = den;
+      }
+    }
+  }
+  QUIC_TLOG_END();
+  if (a.splits == 1 || a.consumer_merge) return;
+  merge_splits_last_cta(a, b, kvh, split, &last_flag);
+}
+
 }  // namespace
 
 cudaError_t launch_attn(const AttnArgs& a, int batch, cudaStream_t s, bool pdl) {
   dim3 grid(a.splits, kKvHeads, batch);
   if (a.small) return launch(attn_decode_small_kernel, grid, dim3(256), 0, s, pdl, a);
+  if (a.use_mma) return launch(attn_decode_mma_kernel, grid, dim3(kMmaWarps * 32), 0, s, pdl, a);
   return launch(attn_decode_kernel, grid, dim3(kWarps * 32), 0, s, pdl, a);
 }
 
@@ -480,7 +689,7 @@ extern "C" int32_t quic_attn_pick_splits(int32_t b, int32_t s_max) {
 
 extern "C" int64_t quic_attn_scratch_bytes(int32_t b, int32_t splits) {
   if (b < 1 || splits < 1) return 0;
-  int64_t counters = ((int64_t)b * kKvHeads * 4 + 255) / 256 * 256;
+  int64_t counters = counter_bytes(b);
   int64_t rows = (int64_t)b * kHeads * splits;
   return counters + rows * kHeadDim * 4 + 2 * ((rows * 4 + 255) / 256 * 256);
 }
@@ -489,7 +698,7 @@ namespace quic {
 // Carves the scratch block; shared with the decode step.
 void attn_carve_scratch(void* scratch, int b, int splits, AttnArgs* a) {
   char* p = static_cast<char*>(scratch);
-  int64_t counters = ((int64_t)b * kKvHeads * 4 + 255) / 256 * 256;
+  int64_t counters = counter_bytes(b);
   int64_t rows = (int64_t)b * kHeads * splits;
   int64_t ml = (rows * 4 + 255) / 256 * 256;
   a->counters = reinterpret_cast<int32_t*>(p);
@@ -524,6 +733,7 @@ extern "C" int quic_attn_decode(const void* q, const void* k, const void* v, int
   a.chunk = (s_max + splits - 1) / splits;
   a.scale = scale > 0.f ? scale : 0.125f;
   a.out = (half*)out;
+  a.use_mma = ((int64_t)b * s_max >= 8192) ? 1 : 0;  // enough work for the throughput variant
   if (splits > 1) attn_carve_scratch(scratch, b, splits, &a);
   QUIC_CUDA(launch_attn(a, b, (cudaStream_t)stream, false));
   return QUIC_OK;

@@ -85,6 +85,7 @@ struct AttnArgs {
   int32_t splits;
   int32_t consumer_merge;  // 1: write partials only, the o_proj kernel merges
   int32_t small;           // 1: latency variant (64 tokens per CTA, consumer merge)
+  int32_t use_mma;         // 1: throughput variant on mma.m16n8k16
   float scale;
   half* out;  // [batch][896]
   int32_t* counters;  // [batch][2]

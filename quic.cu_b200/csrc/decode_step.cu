@@ -278,7 +278,8 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     aa.chunk = (ctx + splits - 1) / splits;
     aa.scale = 0.125f;
     aa.out = attn_out;
-    aa.small = 0;  // throughput regime: lane-per-token CTAs, splits merged by the last CTA to arrive
+    aa.small = 0;  // throughput regime: tensor-core CTAs, splits merged by the last CTA to arrive
+    aa.use_mma = 1;
     aa.consumer_merge = 0;
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
     QUIC_CUDA(launch_attn(aa, B, st, true));

@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   using L = Smem<MT>;
   constexpr int kStages = L::kStages;
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages];    // TMA bytes landed
+  __shared__ __align__(8) uint64_t bar_full[kStages];    // packed weight tile landed (TMA bytes)
+  __shared__ __align__(8) uint64_t bar_xfull[kStages];   // x tile landed (TMA bytes)
   __shared__ __align__(8) uint64_t bar_aready[kStages];  // 16 consumer warps finished the A tile
   __shared__ __align__(8) uint64_t bar_empty[kStages];   // MMAs that read the stage completed
   __shared__ __align__(8) uint64_t bar_done;
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_xfull[s]), 1);
       mbar_init(smem_u32(&bar_aready[s]), kConsumers / 32);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
@@ -131,25 +133,40 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   tc_fence_after();
   const uint32_t tmem_d = tmem_base_s;
   const uint32_t idesc = umma_idesc_f16(MT);
-  // Everything above touched weights and on-chip state only; the activations come from the
-  // previous kernel of the stream.
+  // Everything above touched weights and on-chip state only.  The activations (and the
+  // buffers the epilogue writes) belong to the previous kernels of the stream: the producer
+  // requests the packed weight tiles of the first ring pass, THEN waits for the predecessor
+  // and requests the x tiles; the other roles wait before they touch global memory.
   pdl_launch_dependents();
-  pdl_wait();
 
   if (warp == kConsumers / 32) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (int it = 0; it < nkb; ++it) {
+      const int first = nkb < kStages ? nkb : kStages;
+      for (int it = 0; it < first; ++it) {
+        const uint32_t raw_s = base + it * L::kStage;
+        const uint32_t full = smem_u32(&bar_full[it]);
+        mbar_expect_tx(full, kRawBytes);
+        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
+      }
+      pdl_wait();
+      for (int it = 0; it < first; ++it) {
+        const uint32_t xfull = smem_u32(&bar_xfull[it]);
+        mbar_expect_tx(xfull, (uint32_t)MT * 128u);
+        tma_load_2d(base + it * L::kStage + kRawBytes, &tm_x, (kb0 + it) * kBlockK, m0, xfull);
+      }
+      for (int it = first; it < nkb; ++it) {
         const int stage = it % kStages;
-        if (it >= kStages && !mbar_wait(smem_u32(&bar_empty[stage]), ((it / kStages) - 1) & 1)) {
+        if (!mbar_wait(smem_u32(&bar_empty[stage]), ((it / kStages) - 1) & 1)) {
           fail_s = 2;
           break;
         }
         const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
-        const uint32_t full = smem_u32(&bar_full[stage]);
-        mbar_expect_tx(full, kRawBytes + (uint32_t)MT * 128u);
+        const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_xfull[stage]);
+        mbar_expect_tx(full, kRawBytes);
         tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
-        tma_load_2d(b_s, &tm_x, (kb0 + it) * kBlockK, m0, full);
+        mbar_expect_tx(xfull, (uint32_t)MT * 128u);
+        tma_load_2d(b_s, &tm_x, (kb0 + it) * kBlockK, m0, xfull);
       }
     }
   } else if (warp == kConsumers / 32 + 1) {
@@ -157,7 +174,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     if (lane == 0) {
       for (int it = 0; it < nkb; ++it) {
         const int stage = it % kStages;
-        if (!mbar_wait(smem_u32(&bar_aready[stage]), (it / kStages) & 1)) {
+        if (!mbar_wait(smem_u32(&bar_aready[stage]), (it / kStages) & 1) ||
+            !mbar_wait(smem_u32(&bar_xfull[stage]), (it / kStages) & 1)) {
           fail_s = 3;
           break;
         }
@@ -215,6 +233,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
 
   // wait for the whole accumulation, then read the accumulator out of tensor memory
   if (warp < kConsumers / 32) {
+    pdl_wait();  // the output / partial buffers may still be read by earlier kernels of the chain
     bool ok = !fail_s && nkb > 0;
     if (ok) ok = mbar_wait(smem_u32(&bar_done), 0);
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective

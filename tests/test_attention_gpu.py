@@ -73,3 +73,23 @@ def test_all_masked_row_gives_zeros_and_oracle_agrees():
         assert torch.count_nonzero(out[0]) == 0
         want = quic_ref.attn_decode(q[:, :, 0].cpu(), k.cpu(), v.cpu(), SCALE, start=pads.cpu())
         assert torch.allclose(out[:, :, 0].cpu().float(), want.float(), atol=2e-3)
+
+
+@pytest.mark.parametrize("batch,kv_len", [(4, 32768), (256, 1024), (64, 8192)])
+def test_decode_sweep_corners(batch, kv_len):
+    """Corners of the benchmark's attention sweep (maximum context, maximum batch): against
+    SDPA on the rows that fit in memory, and split-count invariance on all rows."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(batch + kv_len)
+    q = torch.randn((batch, HEADS, 1, HEAD_DIM), device="cuda", generator=g).half()
+    k = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    v = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    pads = torch.randint(0, kv_len // 4 + 1, (batch,), device="cuda", generator=g).int()
+    out = K.flash_attn_decode().forward(q, k, v, SCALE, pads)
+    rows = slice(0, min(batch, 4))
+    expected = _sdpa(q[rows], k[rows], v[rows], pads[rows])
+    assert torch.allclose(out[rows].float(), expected.float(), atol=ATOL)
+    other = K.flash_attn_decode().forward(q, k, v, SCALE, pads, splits=1 if kv_len <= 8192 else 7)
+    assert torch.allclose(out.float(), other.float(), atol=2e-3)
+    assert torch.isfinite(out).all()
