@@ -677,10 +677,10 @@ using namespace quic;
 
 extern "C" int32_t quic_attn_pick_splits(int32_t b, int32_t s_max) {
   if (b < 1) b = 1;
-  // Enough CTAs for two per SM where the context allows it, at least one
-  // 256-token pass (8 warps x 32 tokens) per CTA, at most 64 splits.
+  // Enough CTAs for several per SM (the kernels keep 3-4 CTAs of 4-8 warps resident), at
+  // least 256 tokens per CTA, at most 64 splits.
   int by_len = (s_max + 255) / 256;
-  int want = (296 + 2 * b - 1) / (2 * b);
+  int want = (1184 + 2 * b - 1) / (2 * b);
   int s = want < by_len ? want : by_len;
   if (s < 1) s = 1;
   if (s > 64) s = 64;

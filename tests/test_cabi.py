@@ -31,7 +31,8 @@ def test_host_only_queries():
     assert lib.quic_abi_version() == 1
     assert lib.quic_attn_pick_splits(1, 128) == 1
     assert lib.quic_attn_pick_splits(1, 32768) == 64
-    assert lib.quic_attn_pick_splits(256, 32768) == 1
+    assert lib.quic_attn_pick_splits(256, 32768) == 3
+    assert lib.quic_attn_pick_splits(4096, 32768) == 1
     assert lib.quic_attn_scratch_bytes(4, 8) > 4 * 14 * 8 * 64 * 4
     assert lib.quic_decode_scratch_bytes(1, 151936, 4) > 0
     assert lib.quic_w4a16_workspace_bytes(1, 896, 4864) >= 896 * 4
