@@ -217,20 +217,20 @@ def run_gpu(args) -> None:
     value = world * tokens / (elapsed_ms / 1e3)
 
     # ---- end to end: one public decode call per token, token id host <-> device every token
-    pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+    pinned_t = torch.zeros(1, dtype=torch.int32).pin_memory()
+    pinned = pinned_t.numpy()  # same page-locked memory, cheap element writes
     e2e_tokens = GEN_TOKENS
     reset()
     pinned[0] = int(first[0])
     for _ in range(8):
-        cache.tok.copy_(pinned, non_blocking=True)
-        pinned[0] = net.decode(cache, [0], 1)[0][0]
+        pinned[0] = net.decode(cache, [0], 1, feed=pinned_t)[0][0]
     reset()
     pinned[0] = int(first[0])
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_tokens):
-        cache.tok.copy_(pinned, non_blocking=True)      # H2D: the token to feed (pinned host memory)
-        pinned[0] = net.decode(cache, [0], 1)[0][0]      # D2H: the sampled token
+        # H2D: the token to feed (pinned host memory); D2H: the sampled token
+        pinned[0] = net.decode(cache, [0], 1, feed=pinned_t)[0][0]
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     if dist is not None:
@@ -496,9 +496,15 @@ def main() -> None:
                     help="print the W4A16 linear-op sweep (one JSON line per point) and exit")
     ap.add_argument("--attention-sweep", action="store_true",
                     help="print the decode-attention sweep (one JSON line per point) and exit")
+    ap.add_argument("--attention-point", default="",
+                    help="with --attention-sweep: measure the single point 'batch,context' (profiler captures)")
     args = ap.parse_args()
     if args.attention_sweep:
-        for row in attention_sweep():
+        kw = {}
+        if args.attention_point:
+            b, s_ = (int(v) for v in args.attention_point.split(","))
+            kw = {"batches": (b,), "contexts": (s_,)}
+        for row in attention_sweep(**kw):
             print(json.dumps(row))
         return
     if args.linear_sweep:

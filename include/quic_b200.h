@@ -274,6 +274,15 @@ int quic_decode_step(const quic_model_t *m, const quic_decode_t *d, void *stream
 int quic_decode_graph_create(const quic_model_t *m, const quic_decode_t *d,
                              int32_t steps, void *stream, void **graph_out);
 int quic_graph_launch(void *graph, void *stream);
+/* One host-driven call of a captured graph, the form the reference's token loop
+ * has (src/engine.py:82-84 builds the next-token tensor on the host and copies
+ * it to the device, src/engine.py:98-104 synchronises and reads the sampled ids
+ * back with .tolist()): copies n_in int32 from host_in to dev_in (skipped when
+ * n_in == 0), launches the graph, copies n_out int32 from dev_out to host_out
+ * and waits for the stream.  Host buffers should be page-locked. */
+int quic_graph_run_host(void *graph, void *stream, const int32_t *host_in,
+                        int32_t *dev_in, int32_t n_in, const int32_t *dev_out,
+                        int32_t *host_out, int32_t n_out);
 int quic_graph_destroy(void *graph);
 
 #ifdef __cplusplus

@@ -405,6 +405,24 @@ extern "C" int quic_graph_launch(void* graph, void* stream) {
   return QUIC_OK;
 }
 
+extern "C" int quic_graph_run_host(void* graph, void* stream, const int32_t* host_in, int32_t* dev_in,
+                                   int32_t n_in, const int32_t* dev_out, int32_t* host_out, int32_t n_out) {
+  QUIC_REQUIRE(graph != nullptr, QUIC_E_ARG, "graph_run_host: null graph");
+  QUIC_REQUIRE(n_in >= 0 && n_out >= 0, QUIC_E_ARG, "graph_run_host: negative count");
+  QUIC_REQUIRE(n_in == 0 || (host_in != nullptr && dev_in != nullptr), QUIC_E_ARG,
+               "graph_run_host: null input buffer");
+  QUIC_REQUIRE(n_out == 0 || (host_out != nullptr && dev_out != nullptr), QUIC_E_ARG,
+               "graph_run_host: null output buffer");
+  Graph* g = static_cast<Graph*>(graph);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n_in > 0) QUIC_CUDA(cudaMemcpyAsync(dev_in, host_in, sizeof(int32_t) * n_in, cudaMemcpyHostToDevice, st));
+  QUIC_CUDA(cudaGraphLaunch(g->exec, st));
+  if (n_out > 0)
+    QUIC_CUDA(cudaMemcpyAsync(host_out, dev_out, sizeof(int32_t) * n_out, cudaMemcpyDeviceToHost, st));
+  QUIC_CUDA(cudaStreamSynchronize(st));
+  return QUIC_OK;
+}
+
 extern "C" int quic_graph_destroy(void* graph) {
   if (graph == nullptr) return QUIC_OK;
   Graph* g = static_cast<Graph*>(graph);

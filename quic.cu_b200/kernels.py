@@ -122,6 +122,7 @@ SIGNATURES = {
     "quic_decode_step": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _P]),
     "quic_decode_graph_create": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _I32, _P, C.POINTER(_P)]),
     "quic_graph_launch": (C.c_int, [_P, _P]),
+    "quic_graph_run_host": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P, _P, C.c_int32]),
     "quic_graph_destroy": (C.c_int, [_P]),
 }
 
@@ -151,7 +152,11 @@ def check(rc: int, what: str = "") -> None:
 
 
 def stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of torch's current CUDA stream on the current device."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+    except AttributeError:
+        return torch.cuda.current_stream().cuda_stream
 
 
 def ptr(t: torch.Tensor | None) -> int | None:

@@ -61,6 +61,9 @@ class SlotCache:
         self._rows: dict[tuple, torch.Tensor] = {}
         self._scratch: dict[tuple, torch.Tensor] = {}
         self._graphs: dict[tuple, int] = {}
+        self._plans: dict[tuple, tuple] = {}       # decode(): per (rows, steps) launch plan
+        self._rows_loaded: dict[int, torch.Tensor] = {}  # row->slot map now on the device, per batch size
+        self.host_steps = 0                        # host mirror of step_counter
 
     def get_seq_length(self, layer_idx: int = 0) -> int:
         return max((self.host_len[s] for s in self.batch_slots), default=0)
@@ -82,6 +85,14 @@ class SlotCache:
             need = K.lib().quic_decode_scratch_bytes(batch, self.vocab, splits)
             t = torch.zeros(need, dtype=torch.uint8, device=self.device)
             self._scratch[key] = t
+        return t
+
+    def host_out(self) -> torch.Tensor:
+        """Page-locked host mirror of ``out_tokens`` (filled by decode())."""
+        t = self.__dict__.get("_host_out")
+        if t is None:
+            t = torch.zeros(self.ring, self.n_slots, dtype=torch.int32).pin_memory()
+            self._host_out = t
         return t
 
     def release_graphs(self) -> None:
@@ -245,10 +256,9 @@ class QUICForCausalLM:
     def launches_per_step(self) -> int:
         return 5 * self.n_layers + 1
 
-    def decode_async(self, cache: SlotCache, slots: list[int], steps: int,
-                     logits: torch.Tensor | None = None) -> int:
-        """Enqueues ``steps`` greedy decode steps for the rows ``slots`` (no host sync).
-        Returns the ring index of the first generated token row in ``cache.out_tokens``."""
+    def _prepare_decode(self, cache: SlotCache, slots: list[int], steps: int, logits):
+        """Checks the request, loads the row->slot map and returns (graph handle, ring index
+        of the first generated token row) after advancing the host mirrors."""
         if not slots:
             raise RuntimeError("decode: empty batch")
         if steps < 1 or steps > cache.ring:
@@ -259,22 +269,79 @@ class QUICForCausalLM:
         ctx = min(_ctx_bucket(longest + steps), cache.s_max)
         g, rows = self._graph(cache, len(slots), ctx, steps, logits)
         want = cache.rows_tensor(slots)
-        if getattr(cache, "_rows_loaded", {}).get(len(slots)) is not want:
+        if cache._rows_loaded.get(len(slots)) is not want:
             rows.copy_(want)
-            cache.__dict__.setdefault("_rows_loaded", {})[len(slots)] = want
-        first = getattr(cache, "host_steps", 0)
-        K.check(K.lib().quic_graph_launch(g, K.stream_ptr()), "graph_launch")
+            cache._rows_loaded[len(slots)] = want
+        first = cache.host_steps
         cache.host_steps = first + steps
         for s in slots:
             cache.host_len[s] += steps
-        return first % cache.ring
+        return g, first % cache.ring
 
-    def decode(self, cache: SlotCache, slots: list[int], steps: int) -> list[list[int]]:
-        """``steps`` greedy tokens for every row: result[i][j] is token j of slots[i]."""
-        first = self.decode_async(cache, slots, steps)
-        idx = (torch.arange(steps, device=self.device) + first) % cache.ring
-        toks = cache.out_tokens.index_select(0, idx).index_select(1, cache.rows_tensor(slots).long())
-        return toks.t().cpu().tolist()
+    def decode_async(self, cache: SlotCache, slots: list[int], steps: int,
+                     logits: torch.Tensor | None = None) -> int:
+        """Enqueues ``steps`` greedy decode steps for the rows ``slots`` (no host sync).
+        Returns the ring index of the first generated token row in ``cache.out_tokens``."""
+        g, first = self._prepare_decode(cache, slots, steps, logits)
+        K.check(K.lib().quic_graph_launch(g, K.stream_ptr()), "graph_launch")
+        return first
+
+    def decode(self, cache: SlotCache, slots: list[int], steps: int,
+               feed: torch.Tensor | None = None) -> list[list[int]]:
+        """``steps`` greedy tokens for every row: result[i][j] is token j of slots[i].
+
+        The host-driven form of the reference's token loop (src/engine.py:82-104) in one
+        library call: the optional ``feed`` (page-locked int32 [len(slots)], the token each
+        row consumes first; ``slots`` must then be consecutive) travels host -> device, the
+        captured steps run, the generated ids travel device -> host into a page-locked
+        buffer, and the call returns when they have arrived."""
+        n_in = 0
+        if feed is not None:
+            if feed.dtype != torch.int32 or feed.numel() != len(slots) or feed.is_cuda:
+                raise ValueError("decode: feed must be a host int32 tensor with one token per row")
+            n_in = len(slots)
+        # A plan keeps everything that stays the same between calls for the same rows while
+        # the context stays inside the captured graph's bound.
+        key = (tuple(slots), steps)
+        plan = cache._plans.get(key)
+        first = cache.host_steps % cache.ring
+        host_len = cache.host_len
+        if (plan is not None and first + steps <= cache.ring
+                and max(host_len[s] for s in slots) + steps <= plan[1]
+                and cache._rows_loaded.get(len(slots)) is plan[2]):
+            g = plan[0]
+            cache.host_steps += steps
+            for s in slots:
+                host_len[s] += steps
+        else:
+            if n_in and any(b - a != 1 for a, b in zip(slots, slots[1:])):
+                raise ValueError("decode: feed needs consecutive slots")
+            g, first = self._prepare_decode(cache, slots, steps, None)
+            longest = max(host_len[s] for s in slots)  # already advanced by `steps`
+            bound = min(_ctx_bucket(longest), cache.s_max, self.max_pos)
+            host = cache.host_out()
+            plan = (g, bound, cache.rows_tensor(slots), cache.tok.data_ptr() + 4 * slots[0],
+                    cache.out_tokens.data_ptr(), host.data_ptr(), host.numpy())
+            if len(cache._plans) > 64:
+                cache._plans.clear()
+            cache._plans[key] = plan
+            if first + steps > cache.ring:  # the block of rows wraps around the ring
+                if n_in:
+                    cache.tok[slots[0]: slots[0] + n_in].copy_(feed, non_blocking=True)
+                K.check(K.lib().quic_graph_launch(g, K.stream_ptr()), "graph_launch")
+                idx = (torch.arange(steps, device=self.device) + first) % cache.ring
+                toks = cache.out_tokens.index_select(0, idx).index_select(1, cache.rows_tensor(slots).long())
+                return toks.t().cpu().tolist()
+        n = cache.n_slots
+        offset = 4 * first * n
+        rc = K.lib().quic_graph_run_host(g, K.stream_ptr(), feed.data_ptr() if n_in else None, plan[3], n_in,
+                                         plan[4] + offset, plan[5] + offset, steps * n)
+        if rc != 0:
+            K.check(rc, "graph_run_host")
+        host_np = plan[6]
+        if steps == 1 and len(slots) == 1:
+            return [[int(host_np[first, slots[0]])]]
+        return host_np[first: first + steps][:, slots].T.tolist()
 
     # ---- prefill -----------------------------------------------------------------
     @torch.inference_mode()
