@@ -31,6 +31,19 @@ namespace quic {
 namespace {
 
 constexpr int kGroupHeads = kHeads / kKvHeads;  // 7
+
+// Debug build (-DQUIC_TRACE): SM-clock stamps of the first CTAs of the last launch of the
+// latency kernel, read back with quic_trace_read_attn().  Compiled out otherwise.
+#ifdef QUIC_TRACE
+__device__ long long g_trace_attn[8][8];
+#define ATTN_STAMP(idx)                                                          \
+  do {                                                                            \
+    if (threadIdx.x == 0 && blockIdx.x < 8 && blockIdx.y == 0 && blockIdx.z == 0) \
+      g_trace_attn[blockIdx.x][idx] = clock64();                                  \
+  } while (0)
+#else
+#define ATTN_STAMP(idx)
+#endif
 constexpr int kWarps = 8;
 constexpr int kTile = 32;
 
@@ -280,189 +293,236 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
 }
 
 
+constexpr int kMmaWarps = 4;
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+
+__device__ __forceinline__ uint4 ld_cg_u128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t pack_half2(float x, float y) {
+  const half2 h = __floats2half2_rn(x, y);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ int ld_acquire_s32(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------------------
 // Latency variant for short contexts at small batch (one decode step of a few
-// rows): a CTA owns 64 tokens of one (row, kv head); FOUR lanes share a token
-// (16 dims each), so a warp covers 8 tokens and does a quarter of the serial
-// work of the kernel above; p·V is done with lane = 2 dims.  Single pass, no
-// running rescale.  Always writes split partials unless there is one split.
+// rows): ONE WARP owns 64 tokens of one (row, kv head) and does both products
+// on mma.m16n8k16 with the fragment mappings of the throughput kernel below
+// (heads on M; K fragments are the lane's own 32 contiguous bytes of a token
+// row; probabilities go from the score fragments straight into the A operand
+// of p·V).  No shared memory, no CTA barrier, one softmax pass: the row maximum
+// and sum cost four shuffles.
+//
+// Inside the decode chain (a.prefetch) the cache tile is requested BEFORE the
+// dependency wait, so it is in registers when the query arrives.  That is sound
+// for every row except the one the preceding qkv kernel appends in this very
+// step, which the lanes that hold it fetch again after the wait.  Rows appended
+// by earlier steps are complete as soon as the step counter (advanced by the
+// last CTA of the lm_head kernel) shows the current step; the counter is read
+// with acquire semantics before the tile is requested and again after the wait,
+// and if the two differ the whole tile is fetched again.
 // ---------------------------------------------------------------------------
-constexpr int kSmallChunk = 64;
+constexpr int kWarpChunk = 64;
 
-__global__ void __launch_bounds__(256) attn_decode_small_kernel(const AttnArgs a) {
-  __shared__ __align__(16) float q_s[kGroupHeads * kHeadDim];
-  __shared__ float p_s[kWarps][kGroupHeads][8];
-  __shared__ float m_s[kWarps][kGroupHeads];
-  __shared__ float l_s[kWarps][kGroupHeads];
-  __shared__ __align__(8) float o_s[kWarps][kGroupHeads][kHeadDim];
+__global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) {
   __shared__ int last_flag;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lane = threadIdx.x;
+  const int g = lane >> 2, c = lane & 3;  // fragment row (head) and column pair
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   int slot = b;
-  if (a.pos != nullptr) slot = a.rows[b];
-  pdl_trigger_early();
-  pdl_wait();
-  QUIC_TLOG_BEGIN(2);
-
-  // Throughput mode (the kernel merges the splits itself): a split that lies entirely outside
-  // the row's token range publishes an empty partial without touching the cache.
-  if (!a.consumer_merge && a.splits > 1) {
-    int lo = 0, hi = a.s_cap;
-    if (a.pos != nullptr) {
-      hi = __ldcg(a.pos + slot) + 1;
-    } else {
-      if (a.start != nullptr) lo = a.start[b];
-      if (a.end != nullptr) hi = a.end[b];
-    }
-    if (split * kSmallChunk >= hi || (split + 1) * kSmallChunk <= lo) {
-      for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += 256) {
-        const int h = idx >> 6, d = idx & 63;
-        const size_t row = ((size_t)b * kHeads + kvh * kGroupHeads + h) * a.splits + split;
-        a.o_part[row * kHeadDim + d] = 0.f;
-        if (d == 0) {
-          a.m_part[row] = -INFINITY;
-          a.l_part[row] = 0.f;
-        }
-      }
-      merge_splits_last_cta(a, b, kvh, split, &last_flag);
-      return;
-    }
-  }
-
+  if (a.pos != nullptr) slot = a.rows[b];  // the row -> slot map is not written inside the chain
   const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
   const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
   const int last_tok = a.s_cap - 1;
-  const int tw = split * kSmallChunk + warp * 8;  // first token of this warp
-  const int tok = tw + (lane >> 2), part = lane & 3;
+  const int t0 = split * kWarpChunk;
+  ATTN_STAMP(0);
+  pdl_trigger_early();
 
-  // one round of loads: K (32 B per lane), V (4 B per lane per token), range, q
-  uint4 kr[2];
-  {
-    const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(tok, last_tok) * kHeadDim + 16 * part);
-    kr[0] = ldg_nc_u128(kp);
-    kr[1] = ldg_nc_u128(kp + 1);
-  }
-  uint32_t vr[8];
+  // K rows t0 + 8nb + g, bytes [32c, 32c + 32); V rows t0 + 16j + 2c + {0,1,8,9}, dims 8g .. 8g+7
+  uint4 kr[8][2], vr[4][4];
+  int epoch0 = 0;
+  const bool prefetch = a.prefetch != 0 && a.epoch != nullptr;
+  if (prefetch) {
+    epoch0 = ld_acquire_s32(a.epoch);
 #pragma unroll
-  for (int t = 0; t < 8; ++t)
-    vr[t] = ldg_nc_u32(vbase + (size_t)min(tw + t, last_tok) * kHeadDim + 2 * lane);
+    for (int nb = 0; nb < 8; ++nb) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(t0 + 8 * nb + g, last_tok) * kHeadDim + 16 * c);
+      kr[nb][0] = ldg_nc_u128(kp);
+      kr[nb][1] = ldg_nc_u128(kp + 1);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int tb = t0 + 16 * j + 2 * c;
+      vr[j][0] = ldg_nc_u128(vbase + (size_t)min(tb, last_tok) * kHeadDim + 8 * g);
+      vr[j][1] = ldg_nc_u128(vbase + (size_t)min(tb + 1, last_tok) * kHeadDim + 8 * g);
+      vr[j][2] = ldg_nc_u128(vbase + (size_t)min(tb + 8, last_tok) * kHeadDim + 8 * g);
+      vr[j][3] = ldg_nc_u128(vbase + (size_t)min(tb + 9, last_tok) * kHeadDim + 8 * g);
+    }
+  }
+  pdl_wait();
+  QUIC_TLOG_BEGIN(2);
+  ATTN_STAMP(1);
+
   int t_begin = 0, t_end = a.s_cap;
+  int fresh = -1;        // row appended by the preceding kernel of the chain
+  bool refetch = !prefetch;
   if (a.pos != nullptr) {
     t_end = __ldcg(a.pos + slot) + 1;
+    fresh = t_end - 1;
+    if (prefetch) refetch = __ldcg(a.epoch) != epoch0;
   } else {
     if (a.start != nullptr) t_begin = a.start[b];
     if (a.end != nullptr) t_end = a.end[b];
   }
-  for (int i = tid; i < kGroupHeads * kHeadDim; i += 256)
-    q_s[i] = __half2float(a.q[((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim + i]) * a.scale;
+  // Q fragments: head g (rows 7..15 of the tile are zero), dims 16c + 4ks + {0,1} | {2,3}
+  uint32_t qa0[4], qa2[4];
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    qa0[ks] = qa2[ks] = 0u;
+    if (g < kGroupHeads) {
+      const half* qp = a.q + ((size_t)b * kHeads + kvh * kGroupHeads + g) * kHeadDim + 16 * c + 4 * ks;
+      const uint2 u = __ldcg(reinterpret_cast<const uint2*>(qp));
+      qa0[ks] = u.x;
+      qa2[ks] = u.y;
+    }
+  }
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb) {
+    const int row = t0 + 8 * nb + g;
+    if (refetch || row == fresh) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(row, last_tok) * kHeadDim + 16 * c);
+      kr[nb][0] = ld_cg_u128(kp);
+      kr[nb][1] = ld_cg_u128(kp + 1);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = t0 + 16 * j + 2 * c + (r & 1) + 8 * (r >> 1);
+      if (refetch || row == fresh) vr[j][r] = ld_cg_u128(vbase + (size_t)min(row, last_tok) * kHeadDim + 8 * g);
+    }
+  }
   if (t_end > a.s_cap) t_end = a.s_cap;
   if (t_begin < 0) t_begin = 0;
-  const bool valid = tok >= t_begin && tok < t_end;
-  __syncthreads();
+  const int c_begin = max(t_begin, t0);
+  const int c_end = min(t_end, t0 + kWarpChunk);
+  ATTN_STAMP(2);
 
-  float s[kGroupHeads];
+  // ---- scores: S[head g][token t0 + 8nb + 2c + {0,1}]
+  // (k steps outermost: consecutive mma belong to different accumulators)
+  float sc[8][2];
+  float m = -INFINITY;
+  {
+    float d[8][4];
 #pragma unroll
-  for (int h = 0; h < kGroupHeads; ++h) s[h] = 0.f;
+    for (int nb = 0; nb < 8; ++nb) d[nb][0] = d[nb][1] = d[nb][2] = d[nb][3] = 0.f;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const half2* h2 = reinterpret_cast<const half2*>(&kr[i]);
-    float kf[8];
+    for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(h2[j]);
-      kf[2 * j] = f.x;
-      kf[2 * j + 1] = f.y;
-    }
-#pragma unroll
-    for (int h = 0; h < kGroupHeads; ++h) {
-      const float4 qa = *reinterpret_cast<const float4*>(&q_s[h * kHeadDim + 16 * part + 8 * i]);
-      const float4 qb = *reinterpret_cast<const float4*>(&q_s[h * kHeadDim + 16 * part + 8 * i + 4]);
-      s[h] = fmaf(kf[0], qa.x, s[h]);
-      s[h] = fmaf(kf[1], qa.y, s[h]);
-      s[h] = fmaf(kf[2], qa.z, s[h]);
-      s[h] = fmaf(kf[3], qa.w, s[h]);
-      s[h] = fmaf(kf[4], qb.x, s[h]);
-      s[h] = fmaf(kf[5], qb.y, s[h]);
-      s[h] = fmaf(kf[6], qb.z, s[h]);
-      s[h] = fmaf(kf[7], qb.w, s[h]);
-    }
-  }
-  float m_w[kGroupHeads], l_w[kGroupHeads];
-#pragma unroll
-  for (int h = 0; h < kGroupHeads; ++h) {
-    float v = s[h];
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);  // full dot product in all 4 lanes of the token
-    const float sv = valid ? v : -INFINITY;
-    float mx = sv;
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-    const float p = (valid && mx != -INFINITY) ? __expf(sv - mx) : 0.f;
-    float sum = p;
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-    m_w[h] = mx;
-    l_w[h] = sum;
-    if (part == 0) p_s[warp][h][lane >> 2] = p;
-  }
-  __syncwarp();
-  float o[kGroupHeads][2];
-#pragma unroll
-  for (int h = 0; h < kGroupHeads; ++h) o[h][0] = o[h][1] = 0.f;
-#pragma unroll
-  for (int t = 0; t < 8; ++t) {
-    const float2 vf = __half22float2(u32_as_half2(vr[t]));
-#pragma unroll
-    for (int h = 0; h < kGroupHeads; ++h) {
-      const float p = p_s[warp][h][t];
-      o[h][0] = fmaf(p, vf.x, o[h][0]);
-      o[h][1] = fmaf(p, vf.y, o[h][1]);
-    }
-  }
-#pragma unroll
-  for (int h = 0; h < kGroupHeads; ++h) {
-    *reinterpret_cast<float2*>(&o_s[warp][h][2 * lane]) = make_float2(o[h][0], o[h][1]);
-    if (lane == 0) {
-      m_s[warp][h] = m_w[h];
-      l_s[warp][h] = l_w[h];
-    }
-  }
-  __syncthreads();
-
-  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += 256) {
-    const int h = idx >> 6, d = idx & 63;
-    float m = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, m_s[w][h]);
-    float num = 0.f, den = 0.f;
-    if (m != -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        const float e = (m_s[w][h] == -INFINITY) ? 0.f : __expf(m_s[w][h] - m);
-        den += e * l_s[w][h];
-        num += e * o_s[w][h][d];
+      for (int nb = 0; nb < 8; ++nb) {
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(&kr[nb][0]);
+        mma16816(d[nb], qa0[ks], 0u, qa2[ks], 0u, u[2 * ks], u[2 * ks + 1]);
       }
     }
-    const int qh = kvh * kGroupHeads + h;
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int t = t0 + 8 * nb + 2 * c + e;
+        const float v = (t >= c_begin && t < c_end) ? d[nb][e] * a.scale : -INFINITY;
+        sc[nb][e] = v;
+        m = fmaxf(m, v);
+      }
+    }
+  }
+  ATTN_STAMP(3);
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+  uint32_t pa[4][2];  // P as A fragments: [k step of 16 tokens][a0 | a2]
+  float l = 0.f;
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb) {
+    const float p0 = (sc[nb][0] == -INFINITY) ? 0.f : __expf(sc[nb][0] - m);
+    const float p1 = (sc[nb][1] == -INFINITY) ? 0.f : __expf(sc[nb][1] - m);
+    const half2 ph = __floats2half2_rn(p0, p1);
+    l += __low2float(ph) + __high2float(ph);  // the sum uses the rounded probabilities that multiply V
+    pa[nb >> 1][nb & 1] = *reinterpret_cast<const uint32_t*>(&ph);
+  }
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  ATTN_STAMP(4);
+
+  // ---- O[head g][dims] = P V ; mma j covers dims {8n + j}: lane n = g supplies dim 8g + j
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+#pragma unroll
+  for (int jk = 0; jk < 4; ++jk) {
+    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vr[jk][0]);  // token 2c
+    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vr[jk][1]);  // token 2c + 1
+    const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vr[jk][2]);  // token 2c + 8
+    const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vr[jk][3]);  // token 2c + 9
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {  // word w holds dims 8g + 2w, 8g + 2w + 1
+      const uint32_t b0_lo = __byte_perm(r0[w], r1[w], 0x5410), b0_hi = __byte_perm(r0[w], r1[w], 0x7632);
+      const uint32_t b1_lo = __byte_perm(r2[w], r3[w], 0x5410), b1_hi = __byte_perm(r2[w], r3[w], 0x7632);
+      mma16816(o[2 * w], pa[jk][0], 0u, pa[jk][1], 0u, b0_lo, b1_lo);
+      mma16816(o[2 * w + 1], pa[jk][0], 0u, pa[jk][1], 0u, b0_hi, b1_hi);
+    }
+  }
+  ATTN_STAMP(5);
+
+  // ---- C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j of head g
+  if (g < kGroupHeads) {
+    const int qh = kvh * kGroupHeads + g;
     if (a.splits == 1) {
-      a.out[((size_t)b * kHeads + qh) * kHeadDim + d] = __float2half_rn(m == -INFINITY ? 0.f : num / den);
+      const float inv = (m == -INFINITY || l == 0.f) ? 0.f : 1.f / l;
+      half* op = a.out + ((size_t)b * kHeads + qh) * kHeadDim + 16 * c;
+      uint4 lo, hi;
+      lo.x = pack_half2(o[0][0] * inv, o[1][0] * inv);
+      lo.y = pack_half2(o[2][0] * inv, o[3][0] * inv);
+      lo.z = pack_half2(o[4][0] * inv, o[5][0] * inv);
+      lo.w = pack_half2(o[6][0] * inv, o[7][0] * inv);
+      hi.x = pack_half2(o[0][1] * inv, o[1][1] * inv);
+      hi.y = pack_half2(o[2][1] * inv, o[3][1] * inv);
+      hi.z = pack_half2(o[4][1] * inv, o[5][1] * inv);
+      hi.w = pack_half2(o[6][1] * inv, o[7][1] * inv);
+      *reinterpret_cast<uint4*>(op) = lo;
+      *reinterpret_cast<uint4*>(op + 8) = hi;
     } else {
       const size_t row = ((size_t)b * kHeads + qh) * a.splits + split;
-      a.o_part[row * kHeadDim + d] = num;
-      if (d == 0) {
+      float4* op = reinterpret_cast<float4*>(a.o_part + row * kHeadDim + 16 * c);
+      op[0] = make_float4(o[0][0], o[1][0], o[2][0], o[3][0]);
+      op[1] = make_float4(o[4][0], o[5][0], o[6][0], o[7][0]);
+      op[2] = make_float4(o[0][1], o[1][1], o[2][1], o[3][1]);
+      op[3] = make_float4(o[4][1], o[5][1], o[6][1], o[7][1]);
+      if (c == 0) {
         a.m_part[row] = m;
-        a.l_part[row] = den;
+        a.l_part[row] = l;
       }
     }
   }
+  ATTN_STAMP(7);
   QUIC_TLOG_END();
   if (a.splits == 1 || a.consumer_merge) return;
   merge_splits_last_cta(a, b, kvh, split, &last_flag);
 }
-
 
 // ---------------------------------------------------------------------------
 // Throughput variant on the warp-level tensor cores.  With 7 query heads per KV
@@ -482,16 +542,6 @@ __global__ void __launch_bounds__(256) attn_decode_small_kernel(const AttnArgs a
 // Softmax bookkeeping is fp32 per head (online rescale per 32-token tile).
 // 4 warps per CTA, tiles of 32 tokens strided over the warps.
 // ---------------------------------------------------------------------------
-constexpr int kMmaWarps = 4;
-
-__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 __global__ void __launch_bounds__(kMmaWarps * 32) attn_decode_mma_kernel(const AttnArgs a) {
   __shared__ float m_s[kMmaWarps][kGroupHeads];
   __shared__ float l_s[kMmaWarps][kGroupHeads];
@@ -562,18 +612,27 @@ __global__ void __launch_bounds__(kMmaWarps * 32) attn_decode_mma_kernel(const A
     // ---- scores: S[head g][token t0 + 8nb + 2c + {0,1}]
     float sc[4][2];
     float m_tile = -INFINITY;
+    {
+      float d[4][4];
 #pragma unroll
-    for (int nb = 0; nb < 4; ++nb) {
-      float d[4] = {0.f, 0.f, 0.f, 0.f};
-      const uint32_t* u = reinterpret_cast<const uint32_t*>(&kr[nb][0]);
+      for (int nb = 0; nb < 4; ++nb) d[nb][0] = d[nb][1] = d[nb][2] = d[nb][3] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) mma16816(d, qa0[ks], 0u, qa2[ks], 0u, u[2 * ks], u[2 * ks + 1]);
+      for (int ks = 0; ks < 4; ++ks) {  // k steps outermost: consecutive mma are independent
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int t = t0 + 8 * nb + 2 * c + e;
-        const float v = (t >= c_begin && t < c_end) ? d[e] * a.scale : -INFINITY;
-        sc[nb][e] = v;
-        m_tile = fmaxf(m_tile, v);
+        for (int nb = 0; nb < 4; ++nb) {
+          const uint32_t* u = reinterpret_cast<const uint32_t*>(&kr[nb][0]);
+          mma16816(d[nb], qa0[ks], 0u, qa2[ks], 0u, u[2 * ks], u[2 * ks + 1]);
+        }
+      }
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int t = t0 + 8 * nb + 2 * c + e;
+          const float v = (t >= c_begin && t < c_end) ? d[nb][e] * a.scale : -INFINITY;
+          sc[nb][e] = v;
+          m_tile = fmaxf(m_tile, v);
+        }
       }
     }
     m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
@@ -666,7 +725,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32) attn_decode_mma_kernel(const A
 
 cudaError_t launch_attn(const AttnArgs& a, int batch, cudaStream_t s, bool pdl) {
   dim3 grid(a.splits, kKvHeads, batch);
-  if (a.small) return launch(attn_decode_small_kernel, grid, dim3(256), 0, s, pdl, a);
+  if (a.small) return launch(attn_decode_warp_kernel, grid, dim3(32), 0, s, pdl, a);
   if (a.use_mma) return launch(attn_decode_mma_kernel, grid, dim3(kMmaWarps * 32), 0, s, pdl, a);
   return launch(attn_decode_kernel, grid, dim3(kWarps * 32), 0, s, pdl, a);
 }
@@ -734,6 +793,7 @@ extern "C" int quic_attn_decode(const void* q, const void* k, const void* v, int
   a.scale = scale > 0.f ? scale : 0.125f;
   a.out = (half*)out;
   a.use_mma = ((int64_t)b * s_max >= 8192) ? 1 : 0;  // enough work for the throughput variant
+  a.small = (!a.use_mma && (int64_t)splits * kWarpChunk >= s_max) ? 1 : 0;
   if (splits > 1) attn_carve_scratch(scratch, b, splits, &a);
   QUIC_CUDA(launch_attn(a, b, (cudaStream_t)stream, false));
   return QUIC_OK;
@@ -802,4 +862,9 @@ extern "C" int quic_attn_decode_noalloc(const void* q, const void* k, const void
 
 #ifdef QUIC_TRACE
 QUIC_TRACE_SETTER(attn)
+#endif
+#ifdef QUIC_TRACE
+extern "C" int quic_trace_read_attn(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, quic::g_trace_attn, sizeof(long long) * 8 * 8);
+}
 #endif

@@ -84,7 +84,9 @@ struct AttnArgs {
   int32_t chunk;  // tokens per split
   int32_t splits;
   int32_t consumer_merge;  // 1: write partials only, the o_proj kernel merges
-  int32_t small;           // 1: latency variant (64 tokens per CTA, consumer merge)
+  int32_t small;           // 1: latency variant (one warp per 64 tokens)
+  int32_t prefetch;        // latency variant inside the decode chain: cache tile requested before the wait
+  const int32_t* epoch;    // step counter that guards the early request (advanced once per decode step)
   int32_t use_mma;         // 1: throughput variant on mma.m16n8k16
   float scale;
   half* out;  // [batch][896]

@@ -110,7 +110,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
 // Smallest batch that takes the tensor-core step (quic_set_tensor_min_batch); 2..9.
 int g_tensor_min_batch = 5;  // measured: the GEMV chain wins up to 4 rows, the tensor step from 5
 
-int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st) {
+int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
   const int B = d->batch;
   if (B >= g_tensor_min_batch) return enqueue_step_batched(m, d, st);
   const int splits = pick_splits(d);
@@ -157,7 +157,10 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st)
     qa.kcache = kc;
     qa.vcache = vc;
     qa.s_max = d->s_max;
-    QUIC_CUDA(launch_qkv(qa, st, true));
+    // The first kernel of a sequence starts only after everything enqueued before it has
+    // completed (no programmatic overlap), so later kernels of the chain may read the cache
+    // before their own dependency wait.
+    QUIC_CUDA(launch_qkv(qa, st, !(chain_head && l == 0)));
 
     AttnArgs aa = {};
     aa.q = qbuf;
@@ -176,6 +179,8 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st)
     aa.small = (splits <= kMaxConsumerSplits && (int64_t)splits * 64 >= ctx) ? 1 : 0;
     const bool consumer_merge = splits > 1 && splits <= kMaxConsumerSplits;
     aa.consumer_merge = consumer_merge ? 1 : 0;
+    aa.epoch = d->step_counter;
+    aa.prefetch = (aa.small && d->step_counter != nullptr) ? 1 : 0;
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
     QUIC_CUDA(launch_attn(aa, B, st, true));
 
@@ -362,7 +367,7 @@ extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_de
 extern "C" int quic_decode_step(const quic_model_t* m, const quic_decode_t* d, void* stream) {
   int rc = check(m, d);
   if (rc != QUIC_OK) return rc;
-  return enqueue_step(m, d, (cudaStream_t)stream);
+  return enqueue_step(m, d, (cudaStream_t)stream, true);
 }
 
 extern "C" int quic_decode_graph_create(const quic_model_t* m, const quic_decode_t* d,
@@ -381,7 +386,7 @@ extern "C" int quic_decode_graph_create(const quic_model_t* m, const quic_decode
     delete g;
     return fail(QUIC_E_CUDA, cudaGetErrorString(e));
   }
-  for (int s = 0; s < steps && rc == QUIC_OK; ++s) rc = enqueue_step(m, d, st);
+  for (int s = 0; s < steps && rc == QUIC_OK; ++s) rc = enqueue_step(m, d, st, s == 0);
   e = cudaStreamEndCapture(st, &g->graph);
   if (rc == QUIC_OK && e != cudaSuccess) rc = fail(QUIC_E_CUDA, cudaGetErrorString(e));
   if (rc == QUIC_OK) {

@@ -285,6 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_kernel(const LmHeadArgs a
   __syncthreads();
   if (tid == 0) {
     *a.counter = 0;
+    __threadfence();  // the new positions and tokens are visible before the step counter moves
     if (a.step_counter != nullptr) *a.step_counter = step + 1;
   }
 }

@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   __syncthreads();
   if (tid == 0) {
     *a.counter = 0;
+    __threadfence();  // the new positions and tokens are visible before the step counter moves
     if (a.step_counter != nullptr) *a.step_counter = step + 1;
   }
 }

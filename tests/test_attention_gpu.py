@@ -59,6 +59,29 @@ def test_decode_split_merge_and_ragged(batch, kv_len, splits):
     assert torch.allclose(out_nopad.float(), _sdpa(q, k, v, torch.zeros_like(pads)).float(), atol=ATOL)
 
 
+@pytest.mark.parametrize("batch,kv_len", [(1, 1), (1, 64), (1, 65), (2, 300), (3, 1000), (1, 1024), (4, 1537)])
+def test_decode_latency_variant(batch, kv_len):
+    """One split per 64 tokens selects the single-warp tensor-core variant the decode chain
+    uses at small batch: left pads (one row fully padded where there are several rows), keys
+    beyond the last split masked, the splits merged by the last CTA to arrive; twice, so the
+    arrival counters must have been re-armed."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(batch * 7919 + kv_len)
+    q = torch.randn((batch, HEADS, 1, HEAD_DIM), device="cuda", generator=g).half()
+    k = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    v = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    pads = torch.randint(0, kv_len // 2 + 1, (batch,), device="cuda", generator=g).int()
+    if batch > 2:
+        pads[1] = kv_len
+    want = quic_ref.attn_decode(q[:, :, 0].cpu(), k.cpu(), v.cpu(), SCALE, start=pads.cpu())
+    splits = (kv_len + 63) // 64
+    for _ in range(2):
+        out = K.flash_attn_decode().forward(q, k, v, SCALE, pads, splits=splits)
+        assert torch.isfinite(out).all()
+        assert torch.allclose(out[:, :, 0].cpu().float(), want.float(), atol=ATOL)
+
+
 def test_all_masked_row_gives_zeros_and_oracle_agrees():
     """flash_attn_decode.cu:118-121: a row whose every key is padding yields 0."""
     from quic_cu_b200 import kernels as K
