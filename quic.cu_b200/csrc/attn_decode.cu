@@ -96,6 +96,77 @@ __device__ __forceinline__ void merge_splits_last_cta(const AttnArgs& a, int b, 
   if (tid == 0) a.counters[b * kKvHeads + kvh] = 0;
 }
 
+// The same merge for single-warp CTAs and at most 32 splits.  Lane s owns split s for the
+// softmax statistics (one coalesced load per head), every lane owns two dims of the output;
+// all partial loads of four heads are in flight together, so the merge costs three memory
+// round trips whatever the split count.
+__device__ __forceinline__ void merge_splits_warp(const AttnArgs& a, int b, int kvh) {
+  const int lane = threadIdx.x;
+  __threadfence();
+  __syncwarp();
+  int old = 0;
+  if (lane == 0) old = atomicAdd(&a.counters[b * kKvHeads + kvh], 1);
+  old = __shfl_sync(0xffffffffu, old, 0);
+  if (old != a.splits - 1) return;
+  __threadfence();
+  const size_t row0 = ((size_t)b * kHeads + kvh * kGroupHeads) * a.splits;
+  float e[kGroupHeads], inv[kGroupHeads];
+  {
+    float ms[kGroupHeads], ls[kGroupHeads];
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) {
+      const bool in = lane < a.splits;
+      ms[h] = in ? __ldcg(a.m_part + row0 + (size_t)h * a.splits + lane) : -INFINITY;
+      ls[h] = in ? __ldcg(a.l_part + row0 + (size_t)h * a.splits + lane) : 0.f;
+    }
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) {
+      const float mx = warp_max(ms[h]);
+      e[h] = (ms[h] == -INFINITY) ? 0.f : __expf(ms[h] - mx);
+      const float den = warp_sum(e[h] * ls[h]);
+      inv[h] = den > 0.f ? 1.f / den : 0.f;
+    }
+  }
+  constexpr int kBatchHeads = 4;
+#pragma unroll
+  for (int h0 = 0; h0 < kGroupHeads; h0 += kBatchHeads) {
+    float2 acc[kBatchHeads];
+#pragma unroll
+    for (int hh = 0; hh < kBatchHeads; ++hh) acc[hh] = make_float2(0.f, 0.f);
+    for (int s0 = 0; s0 < a.splits; s0 += 8) {
+      float2 v[kBatchHeads][8];
+#pragma unroll
+      for (int hh = 0; hh < kBatchHeads; ++hh) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const bool in = (h0 + hh < kGroupHeads) && (s0 + j < a.splits);
+          v[hh][j] = in ? __ldcg(reinterpret_cast<const float2*>(
+                              a.o_part + (row0 + (size_t)(h0 + hh) * a.splits + s0 + j) * kHeadDim) + lane)
+                        : make_float2(0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < kBatchHeads; ++hh) {
+        if (h0 + hh >= kGroupHeads) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float w = __shfl_sync(0xffffffffu, e[h0 + hh], (s0 + j) & 31);
+          acc[hh].x = fmaf(w, v[hh][j].x, acc[hh].x);
+          acc[hh].y = fmaf(w, v[hh][j].y, acc[hh].y);
+        }
+      }
+    }
+#pragma unroll
+    for (int hh = 0; hh < kBatchHeads; ++hh) {
+      if (h0 + hh >= kGroupHeads) continue;
+      const int qh = kvh * kGroupHeads + h0 + hh;
+      *reinterpret_cast<half2*>(a.out + ((size_t)b * kHeads + qh) * kHeadDim + 2 * lane) =
+          __floats2half2_rn(acc[hh].x * inv[h0 + hh], acc[hh].y * inv[h0 + hh]);
+    }
+  }
+  if (lane == 0) a.counters[b * kKvHeads + kvh] = 0;
+}
+
 __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs a) {
   __shared__ __align__(16) float q_s[kGroupHeads * kHeadDim];
   __shared__ __align__(16) float p_s[kWarps][kGroupHeads][kTile];
@@ -521,7 +592,11 @@ __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) 
   ATTN_STAMP(7);
   QUIC_TLOG_END();
   if (a.splits == 1 || a.consumer_merge) return;
-  merge_splits_last_cta(a, b, kvh, split, &last_flag);
+  if (a.splits <= 32) {
+    merge_splits_warp(a, b, kvh);
+  } else {
+    merge_splits_last_cta(a, b, kvh, split, &last_flag);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -736,6 +811,8 @@ using namespace quic;
 
 extern "C" int32_t quic_attn_pick_splits(int32_t b, int32_t s_max) {
   if (b < 1) b = 1;
+  // Small problems: the latency variant, one warp per 64 tokens.
+  if ((int64_t)b * s_max < 8192 && s_max <= 32 * kWarpChunk) return (s_max + kWarpChunk - 1) / kWarpChunk;
   // Enough CTAs for several per SM (the kernels keep 3-4 CTAs of 4-8 warps resident), at
   // least 256 tokens per CTA, at most 64 splits.
   int by_len = (s_max + 255) / 256;

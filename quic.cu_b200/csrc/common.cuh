@@ -107,7 +107,14 @@ __device__ __forceinline__ void tlog_end(int i) {
 }
 #define QUIC_TLOG_BEGIN(id) const int tlog_i__ = tlog_begin(id)
 #define QUIC_TLOG_END() tlog_end(tlog_i__)
+struct TlogScope {
+  int i;
+  __device__ explicit TlogScope(int id) : i(tlog_begin(id)) {}
+  __device__ ~TlogScope() { tlog_end(i); }
+};
+#define QUIC_TLOG_SCOPE(id) TlogScope tlog_scope__(id)
 #else
+#define QUIC_TLOG_SCOPE(id)
 #define QUIC_TLOG_BEGIN(id)
 #define QUIC_TLOG_END()
 #endif

@@ -131,7 +131,7 @@ int lm_head_grid(int vocab);
 
 // pieces of the batched (batch > 8) decode step
 cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,
-                              int batch, cudaStream_t st);
+                              int batch, cudaStream_t st, bool pdl);
 // Fused consumers of split-K partial sums [splits][batch][N] (fp32).
 cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
                                  const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,

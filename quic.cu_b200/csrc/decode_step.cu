@@ -105,14 +105,14 @@ int check(const quic_model_t* m, const quic_decode_t* d) {
   return QUIC_OK;
 }
 
-int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st);
+int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head);
 
 // Smallest batch that takes the tensor-core step (quic_set_tensor_min_batch); 2..9.
 int g_tensor_min_batch = 5;  // measured: the GEMV chain wins up to 4 rows, the tensor step from 5
 
 int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
   const int B = d->batch;
-  if (B >= g_tensor_min_batch) return enqueue_step_batched(m, d, st);
+  if (B >= g_tensor_min_batch) return enqueue_step_batched(m, d, st, chain_head);
   const int splits = pick_splits(d);
   const Arena ar = carve(B, m->vocab, splits);
   char* base = static_cast<char*>(d->scratch);
@@ -239,7 +239,7 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st,
 // Batch > 8: every linear is the tcgen05 GEMM; norms, RoPE/KV append and SwiGLU are
 // separate small kernels (at these sizes each kernel does microseconds of real work, so
 // the launch chain is no longer what bounds the step).
-int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st) {
+int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
   const int B = d->batch;
   const int splits = pick_splits(d);
   const Arena ar = carve(B, m->vocab, splits);
@@ -257,7 +257,8 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
   if (ctx > d->s_max) ctx = d->s_max;
   const half* embed = (const half*)m->embed;
 
-  QUIC_CUDA(launch_embed_rows(embed, d->rows, d->tok, m->vocab, h, B, st));
+  // (the head of a sequence starts only after everything enqueued before it has completed)
+  QUIC_CUDA(launch_embed_rows(embed, d->rows, d->tok, m->vocab, h, B, st, !chain_head));
   QUIC_CUDA(launch_rmsnorm(h, nullptr, (const half*)m->layers[0].ln1, m->eps, xn, nullptr, B, st));
   for (int l = 0; l < m->n_layers; ++l) {
     const quic_layer_t& L = m->layers[l];
@@ -283,9 +284,14 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     aa.chunk = (ctx + splits - 1) / splits;
     aa.scale = 0.125f;
     aa.out = attn_out;
-    aa.small = 0;  // throughput regime: tensor-core CTAs, splits merged by the last CTA to arrive
+    // One warp per 64 tokens with the cache tile requested ahead of the dependency wait while
+    // that needs at most 32 splits; 4-warp CTAs walking longer ranges beyond.  Either way the
+    // splits are merged by the last CTA to arrive.
+    aa.small = (splits <= 32 && (int64_t)splits * 64 >= ctx) ? 1 : 0;
     aa.use_mma = 1;
     aa.consumer_merge = 0;
+    aa.epoch = d->step_counter;
+    aa.prefetch = (aa.small && d->step_counter != nullptr) ? 1 : 0;
     if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
     QUIC_CUDA(launch_attn(aa, B, st, true));
     rc = w4a16_gemm_tc(attn_out, L.o, nullptr, B, ws, st, &sp);
@@ -339,15 +345,17 @@ extern "C" void quic_set_tensor_min_batch(int32_t batch) {
 extern "C" int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx) {
   if (batch < 1) batch = 1;
   if (ctx < 1) ctx = 1;
-  // Short contexts at small batch: one CTA per 64 tokens, merged by the o_proj kernel.
-  // Throughput regime: 256-thread CTAs that each walk >= 256 tokens, just enough splits to
-  // give every SM a CTA (one split, hence no merge, from 48 rows up).
-  if (batch >= g_tensor_min_batch && ctx <= 4096) {
-    int s = (120 + batch * kKvHeads - 1) / (batch * kKvHeads);
-    const int by_len = (ctx + 255) / 256;
+  // Throughput regime (tensor-core step): 4-warp CTAs that cover 128 tokens per pass; one
+  // pass per CTA while that still leaves at most two waves of four CTAs per SM.
+  if (batch >= g_tensor_min_batch) {
+    if (ctx <= 2048) return (ctx + 63) / 64;  // single-warp CTAs, every cache tile in flight at once
+    const int by_len = (ctx + 127) / 128;
+    int s = 1184 / (batch * kKvHeads);
     if (s > by_len) s = by_len;
+    if (s > 64) s = 64;
     return s < 1 ? 1 : s;
   }
+  // Short contexts at small batch: one warp per 64 tokens, merged by the o_proj kernel.
   const int small = (ctx + 63) / 64;
   if (small <= kMaxConsumerSplits && ((int64_t)batch * small * kKvHeads <= 1184 || batch >= g_tensor_min_batch)) return small;
   return quic_attn_pick_splits(batch, ctx);

@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   const uint32_t idesc = umma_idesc_f16(MT);
   pdl_launch_dependents();
   pdl_wait();  // the normalised activations come from the previous kernel
+  QUIC_TLOG_SCOPE(12);
 
   if (warp == 4) {
     if (lane == 0) {
@@ -263,3 +264,7 @@ int lm_head_tc_status() {
 }
 
 }  // namespace quic
+
+#ifdef QUIC_TRACE
+QUIC_TRACE_SETTER(lmtc)
+#endif

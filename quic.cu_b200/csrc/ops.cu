@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(224) rmsnorm_kernel(const half* __restrict__ x
   const uint2 wv = *reinterpret_cast<const uint2*>(w + c);  // weights: not produced by the chain
   pdl_launch_dependents();
   pdl_wait();
+  QUIC_TLOG_SCOPE(8);
   uint2 r = make_uint2(0, 0);
   if (res != nullptr) r = *reinterpret_cast<const uint2*>(res + (size_t)row * kHidden + c);
   float2 a, b;
@@ -231,6 +232,7 @@ __global__ void embed_rows_kernel(const half* __restrict__ embed, const int32_t*
   const int b = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
+  QUIC_TLOG_SCOPE(11);
   if (b >= batch) return;
   int t = tok[rows[b]];
   t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
@@ -249,6 +251,7 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
+  QUIC_TLOG_SCOPE(9);
   if (idx >= batch * (kQkvN / 2)) return;
   const int b = idx / (kQkvN / 2), c2 = idx % (kQkvN / 2);
   const int head = c2 >> 5, pair = c2 & 31;  // stored columns (2*pair, 2*pair+1) = dims (pair, pair+32)
@@ -298,6 +301,7 @@ __global__ void swiglu_fused_kernel(const half* __restrict__ gu, half* __restric
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
+  QUIC_TLOG_SCOPE(10);
   if (idx >= (size_t)batch * (kInter / 2)) return;
   const int b = idx / (kInter / 2), i2 = idx % (kInter / 2);
   const half2* row = reinterpret_cast<const half2*>(gu + (size_t)b * 2 * kInter);
@@ -308,8 +312,8 @@ __global__ void swiglu_fused_kernel(const half* __restrict__ gu, half* __restric
 }  // namespace
 
 cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,
-                              int batch, cudaStream_t st) {
-  return launch(embed_rows_kernel, dim3(batch), dim3(224), 0, st, true, embed, rows, tok, vocab, x, batch);
+                              int batch, cudaStream_t st, bool pdl) {
+  return launch(embed_rows_kernel, dim3(batch), dim3(224), 0, st, pdl, embed, rows, tok, vocab, x, batch);
 }
 cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t* pos, const half* cos_t,
                             const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
@@ -426,3 +430,7 @@ extern "C" int quic_gemm_f16(const void* x, const void* w, const void* bias, voi
   return QUIC_OK;
 }
 
+
+#ifdef QUIC_TRACE
+QUIC_TRACE_SETTER(ops)
+#endif

@@ -234,6 +234,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   // wait for the whole accumulation, then read the accumulator out of tensor memory
   if (warp < kConsumers / 32) {
     pdl_wait();  // the output / partial buffers may still be read by earlier kernels of the chain
+    QUIC_TLOG_SCOPE(7);
     bool ok = !fail_s && nkb > 0;
     if (ok) ok = mbar_wait(smem_u32(&bar_done), 0);
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
@@ -397,4 +398,8 @@ extern "C" int quic_w4a16_tensor_status(void) {
 extern "C" int quic_gemm_trace_read(long long* out) {
   return (int)cudaMemcpyFromSymbol(out, quic::g_gemm_trace, sizeof(long long) * 2 * 20 * 6);
 }
+#endif
+
+#ifdef QUIC_TRACE
+QUIC_TRACE_SETTER(gemm)
 #endif

@@ -29,7 +29,8 @@ def test_every_declared_symbol_is_exported_and_bound():
 def test_host_only_queries():
     lib = K.lib()
     assert lib.quic_abi_version() == 1
-    assert lib.quic_attn_pick_splits(1, 128) == 1
+    assert lib.quic_attn_pick_splits(1, 128) == 2
+    assert lib.quic_attn_pick_splits(1, 64) == 1
     assert lib.quic_attn_pick_splits(1, 32768) == 64
     assert lib.quic_attn_pick_splits(256, 32768) == 3
     assert lib.quic_attn_pick_splits(4096, 32768) == 1
