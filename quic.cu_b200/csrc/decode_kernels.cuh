@@ -110,6 +110,7 @@ struct LmHeadArgs {
   float* best_val;    // [batch][grid]
   int32_t* best_idx;  // [batch][grid]
   int32_t* counter;   // single int
+  unsigned long long* keys;  // tensor path: [batch] packed (logit, index) maxima, zero when idle
   // state update by the last CTA (all optional)
   const int32_t* rows;
   int32_t* tok;

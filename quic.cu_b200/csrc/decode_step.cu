@@ -37,8 +37,8 @@ int64_t tc_workspace_bytes(int batch) {
 Arena carve(int batch, int vocab, int splits) {
   Arena a;
   int64_t off = 0;
-  a.lm_counter = off;
-  off += 256;
+  a.lm_counter = off;  // arrival counter, then the lm_head's per-row maxima (up to 128 rows)
+  off += 256 + 128 * 8;
   a.attn = off;
   off += align256(quic_attn_scratch_bytes(batch, splits));
   a.xres = off;
@@ -225,6 +225,7 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st,
   la.best_val = reinterpret_cast<float*>(base + ar.best_val);
   la.best_idx = reinterpret_cast<int32_t*>(base + ar.best_idx);
   la.counter = reinterpret_cast<int32_t*>(base + ar.lm_counter);
+  la.keys = reinterpret_cast<unsigned long long*>(base + ar.lm_counter + 256);
   la.rows = d->rows;
   la.tok = d->tok;
   la.pos = d->pos;
@@ -315,6 +316,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
   la.best_val = reinterpret_cast<float*>(base + ar.best_val);
   la.best_idx = reinterpret_cast<int32_t*>(base + ar.best_idx);
   la.counter = reinterpret_cast<int32_t*>(base + ar.lm_counter);
+  la.keys = reinterpret_cast<unsigned long long*>(base + ar.lm_counter + 256);
   la.rows = d->rows;
   la.tok = d->tok;
   la.pos = d->pos;

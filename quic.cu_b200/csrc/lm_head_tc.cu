@@ -20,14 +20,6 @@ namespace {
 constexpr int kLmStages = 3;  // 3 x 24 KB at 64 rows: three CTAs share an SM, so loads, MMAs and epilogues of different tiles overlap
 constexpr int kLmThreads = 128 + 32;  // 4 epilogue warps (thread 0 issues MMAs) + 1 TMA warp
 
-struct Best {
-  float v;
-  int i;
-};
-__device__ __forceinline__ Best better(Best a, Best b) {
-  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
-}
-
 template <int MT>
 struct LmSmem {
   static constexpr uint32_t kA = kTileN * 128;
@@ -162,18 +154,20 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kCols) : "memory");
 
-  // tile candidate per batch row
+  // Tile candidate per batch row -> one 64-bit atomic maximum per row.  The key orders by
+  // "larger logit, then lower vocabulary index" (argmax_kernel's tie rule, sampler.cu:38-40);
+  // zero means "no finite logit yet".
   for (int m = tid; m < MT && m < a.batch; m += kLmThreads) {
     uint32_t k = cand_key[0][m];
 #pragma unroll
     for (int w = 1; w < 4; ++w) k = max(k, cand_key[w][m]);
     const uint32_t ordered = k >> 16;
-    const uint32_t bits = (ordered & 0x8000u) ? (ordered & 0x7fffu) : (~ordered & 0xffffu);
-    a.best_val[(size_t)m * ntiles + tile] = ordered == 0u ? -INFINITY : __half2float(__ushort_as_half((unsigned short)bits));
-    a.best_idx[(size_t)m * ntiles + tile] = n0 + 127 - (int)(k & 0xffffu);
+    const uint32_t index = (uint32_t)n0 + 127u - (k & 0xffffu);
+    if (ordered != 0u)
+      atomicMax(a.keys + m, ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - index));
   }
 
-  // the CTA that arrives last reduces the candidates of all tiles
+  // the CTA that arrives last turns the keys into tokens and re-arms them
   __threadfence();
   __syncthreads();
   if (tid == 0) last_flag = (atomicAdd(a.counter, 1) == ntiles - 1);
@@ -182,32 +176,16 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   __threadfence();
   int step = 0;
   if (a.step_counter != nullptr) step = *a.step_counter;
-  for (int b = warp; b < a.batch; b += kLmThreads / 32) {
-    Best c;
-    c.v = -INFINITY;
-    c.i = 0x7fffffff;
-    for (int i = lane; i < ntiles; i += 32) {
-      Best y;
-      y.v = __ldcg(a.best_val + (size_t)b * ntiles + i);
-      y.i = __ldcg(a.best_idx + (size_t)b * ntiles + i);
-      c = better(c, y);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      Best y;
-      y.v = __shfl_xor_sync(0xffffffffu, c.v, o);
-      y.i = __shfl_xor_sync(0xffffffffu, c.i, o);
-      c = better(c, y);
-    }
-    if (lane == 0) {
-      const int token = c.i == 0x7fffffff ? 0 : c.i;
-      if (a.argmax_out != nullptr) a.argmax_out[b] = token;
-      if (a.rows != nullptr) {
-        const int slot = a.rows[b];
-        a.tok[slot] = token;
-        a.pos[slot] = a.pos[slot] + 1;
-        if (a.out_tokens != nullptr) a.out_tokens[(size_t)(step % a.ring) * a.n_slots + slot] = token;
-      }
+  for (int b = tid; b < a.batch; b += kLmThreads) {
+    const unsigned long long key = __ldcg(a.keys + b);
+    a.keys[b] = 0ull;
+    const int token = key == 0ull ? 0 : (int)(0xffffffffu - (uint32_t)(key & 0xffffffffull));
+    if (a.argmax_out != nullptr) a.argmax_out[b] = token;
+    if (a.rows != nullptr) {
+      const int slot = a.rows[b];
+      a.tok[slot] = token;
+      a.pos[slot] = a.pos[slot] + 1;
+      if (a.out_tokens != nullptr) a.out_tokens[(size_t)(step % a.ring) * a.n_slots + slot] = token;
     }
   }
   __syncthreads();
