@@ -32,8 +32,23 @@ __device__ int g_tc_status;
 #ifdef QUIC_TRACE
 __device__ long long g_gemm_trace[2][20][6];
 #define GSTAMP(it, i) do { if (tid == 0 && blockIdx.x < 2 && blockIdx.y == 0 && (it) < 20) g_gemm_trace[blockIdx.x][it][i] = clock64(); } while (0)
+// role stamps of CTA (0,0,0) of the last launch of each weight shape
+__device__ long long g_gemm_roles[4][8];
+__device__ long long g_gemm_mma[4][16][3];
+#define GMMA(it, i)                                                                      \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 16)               \
+      g_gemm_mma[a.w.n == 1152 ? 0 : (a.w.n == 9728 ? 2 : (a.w.k == 896 ? 1 : 3))][it][i] = clock64(); \
+  } while (0)
+#define GROLE(i)                                                                         \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)                            \
+      g_gemm_roles[a.w.n == 1152 ? 0 : (a.w.n == 9728 ? 2 : (a.w.k == 896 ? 1 : 3))][i] = clock64(); \
+  } while (0)
 #else
 #define GSTAMP(it, i)
+#define GROLE(i)
+#define GMMA(it, i)
 #endif  // 0 = ok; otherwise (code << 16) | block of the first failure
 
 struct GemmArgs {
@@ -77,8 +92,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   constexpr int kStages = L::kStages;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStages];    // packed weight tile landed (TMA bytes)
-  __shared__ __align__(8) uint64_t bar_xfull[kStages];   // x tile landed (TMA bytes)
-  __shared__ __align__(8) uint64_t bar_aready[kStages];  // 16 consumer warps finished the A tile
+  __shared__ __align__(8) uint64_t bar_aready[kStages];  // 16 consumer warps finished the A tile AND the x tile landed
   __shared__ __align__(8) uint64_t bar_empty[kStages];   // MMAs that read the stage completed
   __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t tmem_base_s;
@@ -95,6 +109,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   const int kb0 = split * a.kblocks_per_split;
   const int kb1 = min(kb_total, kb0 + a.kblocks_per_split);
   const int nkb = kb1 - kb0;
+  if (tid == 0) GROLE(0);
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -103,8 +118,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
-      mbar_init(smem_u32(&bar_xfull[s]), 1);
-      mbar_init(smem_u32(&bar_aready[s]), kConsumers / 32);
+      mbar_init(smem_u32(&bar_aready[s]), kConsumers / 32 + 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     mbar_init(smem_u32(&bar_done), 1);
@@ -138,6 +152,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   // requests the packed weight tiles of the first ring pass, THEN waits for the predecessor
   // and requests the x tiles; the other roles wait before they touch global memory.
   pdl_launch_dependents();
+  if (tid == 0) GROLE(1);
 
   if (warp == kConsumers / 32) {
     // ---------------- TMA producer ----------------
@@ -150,8 +165,9 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
       }
       pdl_wait();
+      GROLE(2);
       for (int it = 0; it < first; ++it) {
-        const uint32_t xfull = smem_u32(&bar_xfull[it]);
+        const uint32_t xfull = smem_u32(&bar_aready[it]);
         mbar_expect_tx(xfull, (uint32_t)MT * 128u);
         tma_load_2d(base + it * L::kStage + kRawBytes, &tm_x, (kb0 + it) * kBlockK, m0, xfull);
       }
@@ -162,7 +178,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
           break;
         }
         const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
-        const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_xfull[stage]);
+        const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_aready[stage]);
         mbar_expect_tx(full, kRawBytes);
         tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
         mbar_expect_tx(xfull, (uint32_t)MT * 128u);
@@ -172,14 +188,25 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   } else if (warp == kConsumers / 32 + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
+#ifdef QUIC_TC_WARMUP
+      // One throw-away MMA before the operands exist (its result is overwritten by the first
+      // real one, which does not accumulate): the tensor pipe is busy once before the
+      // dependency wait instead of after it.
+      umma_f16(tmem_d, umma_desc_sw128(base + kRawBytes + L::kB), umma_desc_sw128(base + kRawBytes), idesc, 0u);
+#endif
+      // One wait per k block (operand A written by the consumer warps and operand B landed by
+      // TMA arrive on the same barrier) and a commit only where somebody waits for it: each
+      // of these costs the issuing thread a round trip, and at these sizes the loop is bound
+      // by that, not by the tensor pipe.
       for (int it = 0; it < nkb; ++it) {
         const int stage = it % kStages;
-        if (!mbar_wait(smem_u32(&bar_aready[stage]), (it / kStages) & 1) ||
-            !mbar_wait(smem_u32(&bar_xfull[stage]), (it / kStages) & 1)) {
+        if (!mbar_wait(smem_u32(&bar_aready[stage]), (it / kStages) & 1)) {
           fail_s = 3;
           break;
         }
-        tc_fence_after();
+        if (it == 0) tc_fence_after();
+        if (it == 0) GROLE(3);
+        GMMA(it, 0);
         const uint32_t b_s = base + stage * L::kStage + kRawBytes, a_s = b_s + L::kB;
 #ifndef QUIC_TC_NO_MMA  // timing experiments only
 #pragma unroll
@@ -187,9 +214,12 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
           umma_f16(tmem_d, umma_desc_sw128(a_s + k * 32), umma_desc_sw128(b_s + k * 32), idesc,
                    (it > 0 || k > 0) ? 1u : 0u);
 #endif
-        umma_commit(smem_u32(&bar_empty[stage]));
+        GMMA(it, 1);
+        if (it + kStages < nkb) umma_commit(smem_u32(&bar_empty[stage]));
         if (it == nkb - 1) umma_commit(smem_u32(&bar_done));
+        GMMA(it, 2);
       }
+      GROLE(4);
     }
   } else {
     // ---------------- consumers: dequantise ----------------
@@ -230,13 +260,15 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     }
   }
   __syncwarp();
+  if (tid == 0) GROLE(5);
 
   // wait for the whole accumulation, then read the accumulator out of tensor memory
   if (warp < kConsumers / 32) {
     pdl_wait();  // the output / partial buffers may still be read by earlier kernels of the chain
     QUIC_TLOG_SCOPE(7);
     bool ok = !fail_s && nkb > 0;
-    if (ok) ok = mbar_wait(smem_u32(&bar_done), 0);
+    if (ok) ok = mbar_wait_relaxed(smem_u32(&bar_done), 0, 64);
+    if (tid == 0) GROLE(6);
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status, 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
@@ -275,6 +307,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       }
     }
   }
+  if (tid == 0) GROLE(7);
   tc_fence_before();
   __syncthreads();
   if (warp == 0)
@@ -402,4 +435,10 @@ extern "C" int quic_gemm_trace_read(long long* out) {
 
 #ifdef QUIC_TRACE
 QUIC_TRACE_SETTER(gemm)
+extern "C" int quic_trace_read_gemm_mma(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, quic::g_gemm_mma, sizeof(long long) * 4 * 16 * 3);
+}
+extern "C" int quic_trace_read_gemm_roles(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, quic::g_gemm_roles, sizeof(long long) * 4 * 8);
+}
 #endif
