@@ -296,16 +296,44 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
   dst[pair + 32] = __float2half_rn(hi);
 }
 
-// act[b][i] = silu(gu[b][i]) * gu[b][4864 + i] on the fused gate|up output.
-__global__ void swiglu_fused_kernel(const half* __restrict__ gu, half* __restrict__ act, int batch) {
+// act[b][i] = silu(gu[b][i]) * gu[b][4864 + i] on the fused gate|up output, which comes
+// either as fp16 rows or as `splits` fp32 split-K partial sums [splits][batch][9728]; the
+// summed linear output is rounded to fp16 first, as the un-split epilogue does.
+__global__ void swiglu_fused_kernel(const half* __restrict__ gu, const float* __restrict__ part, int splits,
+                                    half* __restrict__ act, int batch) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
   QUIC_TLOG_SCOPE(10);
   if (idx >= (size_t)batch * (kInter / 2)) return;
   const int b = idx / (kInter / 2), i2 = idx % (kInter / 2);
-  const half2* row = reinterpret_cast<const half2*>(gu + (size_t)b * 2 * kInter);
-  const float2 g = __half22float2(row[i2]), u = __half22float2(row[kInter / 2 + i2]);
+  float2 g, u;
+  if (part != nullptr) {
+    const size_t plane = (size_t)batch * 2 * kInter;
+    const float* row = part + (size_t)b * 2 * kInter;
+    float2 gs[16], us[16];
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+      gs[s] = s < splits ? __ldcg(reinterpret_cast<const float2*>(row + s * plane) + i2) : make_float2(0.f, 0.f);
+      us[s] = s < splits ? __ldcg(reinterpret_cast<const float2*>(row + s * plane + kInter) + i2)
+                         : make_float2(0.f, 0.f);
+    }
+    g = gs[0];
+    u = us[0];
+#pragma unroll
+    for (int s = 1; s < 16; ++s) {
+      g.x += gs[s].x;
+      g.y += gs[s].y;
+      u.x += us[s].x;
+      u.y += us[s].y;
+    }
+    g = __half22float2(__floats2half2_rn(g.x, g.y));
+    u = __half22float2(__floats2half2_rn(u.x, u.y));
+  } else {
+    const half2* row = reinterpret_cast<const half2*>(gu + (size_t)b * 2 * kInter);
+    g = __half22float2(row[i2]);
+    u = __half22float2(row[kInter / 2 + i2]);
+  }
   reinterpret_cast<half2*>(act + (size_t)b * kInter)[i2] = __floats2half2_rn(silu_mul(g.x, u.x), silu_mul(g.y, u.y));
 }
 
@@ -336,7 +364,13 @@ cudaError_t launch_rmsnorm_part(const float* part, int splits, const half* resid
 }
 cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream_t st) {
   const size_t total = (size_t)batch * (kInter / 2);
-  return launch(swiglu_fused_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, gu, act, batch);
+  return launch(swiglu_fused_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, gu,
+                (const float*)nullptr, 0, act, batch);
+}
+cudaError_t launch_swiglu_fused_part(const float* part, int splits, half* act, int batch, cudaStream_t st) {
+  const size_t total = (size_t)batch * (kInter / 2);
+  return launch(swiglu_fused_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true,
+                (const half*)nullptr, part, splits, act, batch);
 }
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st) {

@@ -58,6 +58,7 @@ struct GemmArgs {
   int* counters;   // one per (n tile, m tile), zero on entry, left zero
   int m_total;
   int kblocks_per_split;
+  int stages;  // depth of the operand ring (3 lets two CTAs share an SM, 5-6 is the deep ring)
 };
 
 constexpr int kMaxGroupsPerCta = 40;            // K / 128 of the widest layer (4864) rounded up
@@ -84,16 +85,16 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // once its A tile is complete and commits them to the stage's "empty" barrier, which lets
 // the TMA warp refill it.  No role ever waits for another role's instruction issue, only
 // for data.  Warps 0-15 read the accumulator back at the end.
-template <int MT>
+template <int MT, int kStages>
 __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                      const __grid_constant__ CUtensorMap tm_x,
                                                                      const GemmArgs a) {
   using L = Smem<MT>;
-  constexpr int kStages = L::kStages;
+  constexpr int kMaxStages = kStages;
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages];    // packed weight tile landed (TMA bytes)
-  __shared__ __align__(8) uint64_t bar_aready[kStages];  // 16 consumer warps finished the A tile AND the x tile landed
-  __shared__ __align__(8) uint64_t bar_empty[kStages];   // MMAs that read the stage completed
+  __shared__ __align__(8) uint64_t bar_full[kMaxStages];    // packed weight tile landed (TMA bytes)
+  __shared__ __align__(8) uint64_t bar_aready[kMaxStages];  // 16 consumer warps finished the A tile AND the x tile landed
+  __shared__ __align__(8) uint64_t bar_empty[kMaxStages];   // MMAs that read the stage completed
   __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
@@ -171,9 +172,9 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         mbar_expect_tx(xfull, (uint32_t)MT * 128u);
         tma_load_2d(base + it * L::kStage + kRawBytes, &tm_x, (kb0 + it) * kBlockK, m0, xfull);
       }
-      for (int it = first; it < nkb; ++it) {
-        const int stage = it % kStages;
-        if (!mbar_wait(smem_u32(&bar_empty[stage]), ((it / kStages) - 1) & 1)) {
+      // (ring position and phase are carried along: the depth is a run-time value)
+      for (int it = first, stage = 0, pass = 1; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&bar_empty[stage]), (pass - 1) & 1)) {
           fail_s = 2;
           break;
         }
@@ -183,6 +184,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
         mbar_expect_tx(xfull, (uint32_t)MT * 128u);
         tma_load_2d(b_s, &tm_x, (kb0 + it) * kBlockK, m0, xfull);
+        if (++stage == kStages) {
+          stage = 0;
+          ++pass;
+        }
       }
     }
   } else if (warp == kConsumers / 32 + 1) {
@@ -198,9 +203,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       // TMA arrive on the same barrier) and a commit only where somebody waits for it: each
       // of these costs the issuing thread a round trip, and at these sizes the loop is bound
       // by that, not by the tensor pipe.
-      for (int it = 0; it < nkb; ++it) {
-        const int stage = it % kStages;
-        if (!mbar_wait(smem_u32(&bar_aready[stage]), (it / kStages) & 1)) {
+      for (int it = 0, stage = 0, pass = 0; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&bar_aready[stage]), pass & 1)) {
           fail_s = 3;
           break;
         }
@@ -218,17 +222,20 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         if (it + kStages < nkb) umma_commit(smem_u32(&bar_empty[stage]));
         if (it == nkb - 1) umma_commit(smem_u32(&bar_done));
         GMMA(it, 2);
+        if (++stage == kStages) {
+          stage = 0;
+          ++pass;
+        }
       }
       GROLE(4);
     }
   } else {
     // ---------------- consumers: dequantise ----------------
     const int row = tid & (kTileN - 1), part = tid >> 7;  // thread -> (row, two of its eight k-words)
-    for (int it = 0; it < nkb; ++it) {
-      const int stage = it % kStages;
+    for (int it = 0, stage = 0, pass = 0; it < nkb; ++it) {
       // "full" of this phase also means the MMAs of the stage's previous use are complete
       // (the TMA warp refilled it only after "empty"), so the A tile may be overwritten.
-      if (!mbar_wait(smem_u32(&bar_full[stage]), (it / kStages) & 1)) {
+      if (!mbar_wait(smem_u32(&bar_full[stage]), pass & 1)) {
         fail_s = 1;
         break;
       }
@@ -257,6 +264,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_aready[stage]));
+      if (++stage == kStages) {
+        stage = 0;
+        ++pass;
+      }
     }
   }
   __syncwarp();
@@ -345,34 +356,59 @@ int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
   rc = make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)a.m_total, (uint64_t)a.w.k, MT, kBlockK,
                 CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != QUIC_OK) return rc;
-  const size_t smem = Smem<MT>::kTotal;
-  QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
   dim3 grid(a.w.n / kTileN, splits, (a.m_total + MT - 1) / MT);
-  QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
+  if (a.stages == 3) {
+    const size_t smem = 3 * Smem<MT>::kStage + 1024;
+    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, 3>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
+  } else {
+    constexpr int kDeep = Smem<MT>::kStages;
+    const size_t smem = Smem<MT>::kTotal;
+    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
+  }
   return QUIC_OK;
 }
 
 }  // namespace
 
-static void tc_plan(int m, int n, int k, int* mt_out, int* splits_out, int* per_out) {
+// `fused_consumer`: the caller's next kernel sums the split-K partials itself, so splitting
+// costs no extra launch.
+static void tc_plan(int m, int n, int k, bool fused_consumer, int* mt_out, int* splits_out, int* per_out,
+                    int* stages_out) {
   const int kb_total = k / kBlockK;
   const int tiles = n / kTileN;
   const int mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   const int mtiles = (m + mt - 1) / mt;
+  const int ctas = tiles * mtiles;
+  int stages = mt > 64 ? 5 : 6;
   // split K while it at most fills the SMs once, at most 16 ways, at least 2 k blocks per CTA
   int splits = 1;
-  while (splits < 16 && tiles * mtiles * splits * 2 <= 148 && kb_total / (splits * 2) >= 2) splits *= 2;
+  while (splits < 16 && ctas * splits * 2 <= 148 && kb_total / (splits * 2) >= 2) splits *= 2;
+  if (splits == 1 && fused_consumer && mt <= 64 && ctas * 2 > 148 && ctas * 2 <= 296) {
+    // More than half the SMs but not two CTAs on each: a 3-deep ring lets two CTAs share an
+    // SM, so K can still be split until every SM holds two.
+    stages = 3;
+    splits = 296 / ctas;
+    if (splits > kb_total / 2) splits = kb_total / 2;
+    if (splits < 1) splits = 1;
+  }
   const int per = (kb_total + splits - 1) / splits;
   *mt_out = mt;
   *per_out = per;
   *splits_out = (kb_total + per - 1) / per;
+  *stages_out = stages;
 }
 
 int64_t w4a16_gemm_tc_workspace(int m, int n, int k) {
-  int mt, splits, per;
-  tc_plan(m, n, k, &mt, &splits, &per);
-  return splits > 1 ? (int64_t)splits * m * n * 4 : 0;
+  int mt, splits, per, stages;
+  tc_plan(m, n, k, true, &mt, &splits, &per, &stages);
+  int64_t need = splits > 1 ? (int64_t)splits * m * n * 4 : 0;
+  tc_plan(m, n, k, false, &mt, &splits, &per, &stages);
+  const int64_t plain = splits > 1 ? (int64_t)splits * m * n * 4 : 0;
+  return need > plain ? need : plain;
 }
 
 // y == nullptr: leave the fp32 partial sums of all `*splits_out` K splits in the workspace
@@ -384,8 +420,8 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0), QUIC_E_ARG,
                "w4a16_linear: x and the packed weights must be 16-byte aligned");
   QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16_linear: K beyond 5120 on the tensor path");
-  int mt, splits, per;
-  tc_plan(m, w.n, w.k, &mt, &splits, &per);
+  int mt, splits, per, stages;
+  tc_plan(m, w.n, w.k, y == nullptr, &mt, &splits, &per, &stages);
   QUIC_REQUIRE((splits == 1 && y != nullptr) || workspace != nullptr, QUIC_E_ARG,
                "w4a16_linear: split-K needs a workspace");
   if (splits_out != nullptr) *splits_out = splits;
@@ -397,6 +433,7 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   QUIC_REQUIRE((m + mt - 1) / mt <= 65535, QUIC_E_LIMIT, "w4a16_linear: too many rows on the tensor path");
   a.m_total = m;
   a.kblocks_per_split = per;
+  a.stages = stages;
   int rc;
   switch (mt) {
     case 16: rc = run<16>(x, a, splits, st); break;
