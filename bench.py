@@ -287,7 +287,7 @@ def run_gpu(args) -> None:
         "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate",
         "data": "synthetic", "config": dict(CONFIG, parallelism=f"{world} independent replica(s)"),
-        "clocks": clocks, "e2e": e2e, "gpu_launches": world * args.steps * GEN_TOKENS * net.launches_per_step(),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": world * args.steps * GEN_TOKENS * net.launches_per_step(cache, 1, PROMPT_LEN + GEN_TOKENS),
         "roofline": roofline, "roofline_step": roofline_step, "batch64": batch64, "serving": serving,
     }
     if args.layers != 24:

@@ -17,6 +17,7 @@
 //     the final merge and re-arms the counter, so no second kernel and no
 //     spin-wait is needed.
 #include "decode_kernels.cuh"
+#include "attn_warp.cuh"
 
 // Bytes reserved for the arrival counters at the head of the scratch: a fixed 64 KB (8192
 // rows) so that a scratch block shared by calls of different batch sizes keeps its counters
@@ -366,38 +367,10 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
 
 constexpr int kMmaWarps = 4;
 
-__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-
-__device__ __forceinline__ uint4 ld_cg_u128(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint32_t pack_half2(float x, float y) {
-  const half2 h = __floats2half2_rn(x, y);
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
-__device__ __forceinline__ int ld_acquire_s32(const int32_t* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
 // ---------------------------------------------------------------------------
 // Latency variant for short contexts at small batch (one decode step of a few
-// rows): ONE WARP owns 64 tokens of one (row, kv head) and does both products
-// on mma.m16n8k16 with the fragment mappings of the throughput kernel below
-// (heads on M; K fragments are the lane's own 32 contiguous bytes of a token
-// row; probabilities go from the score fragments straight into the A operand
-// of p·V).  No shared memory, no CTA barrier, one softmax pass: the row maximum
-// and sum cost four shuffles.
+// rows): ONE WARP owns 64 tokens of one (row, kv head); the arithmetic is in
+// attn_warp.cuh.
 //
 // Inside the decode chain (a.prefetch) the cache tile is requested BEFORE the
 // dependency wait, so it is in registers when the query arrives.  That is sound
@@ -408,8 +381,6 @@ __device__ __forceinline__ int ld_acquire_s32(const int32_t* p) {
 // with acquire semantics before the tile is requested and again after the wait,
 // and if the two differ the whole tile is fetched again.
 // ---------------------------------------------------------------------------
-constexpr int kWarpChunk = 64;
-
 __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) {
   __shared__ int last_flag;
   const int lane = threadIdx.x;
@@ -424,33 +395,19 @@ __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) 
   ATTN_STAMP(0);
   pdl_trigger_early();
 
-  // K rows t0 + 8nb + g, bytes [32c, 32c + 32); V rows t0 + 16j + 2c + {0,1,8,9}, dims 8g .. 8g+7
-  uint4 kr[8][2], vr[4][4];
+  WarpTile tile;
   int epoch0 = 0;
   const bool prefetch = a.prefetch != 0 && a.epoch != nullptr;
   if (prefetch) {
     epoch0 = ld_acquire_s32(a.epoch);
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb) {
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(t0 + 8 * nb + g, last_tok) * kHeadDim + 16 * c);
-      kr[nb][0] = ldg_nc_u128(kp);
-      kr[nb][1] = ldg_nc_u128(kp + 1);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int tb = t0 + 16 * j + 2 * c;
-      vr[j][0] = ldg_nc_u128(vbase + (size_t)min(tb, last_tok) * kHeadDim + 8 * g);
-      vr[j][1] = ldg_nc_u128(vbase + (size_t)min(tb + 1, last_tok) * kHeadDim + 8 * g);
-      vr[j][2] = ldg_nc_u128(vbase + (size_t)min(tb + 8, last_tok) * kHeadDim + 8 * g);
-      vr[j][3] = ldg_nc_u128(vbase + (size_t)min(tb + 9, last_tok) * kHeadDim + 8 * g);
-    }
+    warp_tile_request(tile, kbase, vbase, t0, last_tok, g, c);
   }
   pdl_wait();
   QUIC_TLOG_BEGIN(2);
   ATTN_STAMP(1);
 
   int t_begin = 0, t_end = a.s_cap;
-  int fresh = -1;        // row appended by the preceding kernel of the chain
+  int fresh = -1;  // row appended by the preceding kernel of the chain
   bool refetch = !prefetch;
   if (a.pos != nullptr) {
     t_end = __ldcg(a.pos + slot) + 1;
@@ -460,103 +417,17 @@ __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) 
     if (a.start != nullptr) t_begin = a.start[b];
     if (a.end != nullptr) t_end = a.end[b];
   }
-  // Q fragments: head g (rows 7..15 of the tile are zero), dims 16c + 4ks + {0,1} | {2,3}
   uint32_t qa0[4], qa2[4];
-#pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    qa0[ks] = qa2[ks] = 0u;
-    if (g < kGroupHeads) {
-      const half* qp = a.q + ((size_t)b * kHeads + kvh * kGroupHeads + g) * kHeadDim + 16 * c + 4 * ks;
-      const uint2 u = __ldcg(reinterpret_cast<const uint2*>(qp));
-      qa0[ks] = u.x;
-      qa2[ks] = u.y;
-    }
-  }
-#pragma unroll
-  for (int nb = 0; nb < 8; ++nb) {
-    const int row = t0 + 8 * nb + g;
-    if (refetch || row == fresh) {
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(row, last_tok) * kHeadDim + 16 * c);
-      kr[nb][0] = ld_cg_u128(kp);
-      kr[nb][1] = ld_cg_u128(kp + 1);
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int row = t0 + 16 * j + 2 * c + (r & 1) + 8 * (r >> 1);
-      if (refetch || row == fresh) vr[j][r] = ld_cg_u128(vbase + (size_t)min(row, last_tok) * kHeadDim + 8 * g);
-    }
-  }
+  warp_q_fragments(qa0, qa2, a.q + ((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim, g, c);
+  warp_tile_refetch(tile, kbase, vbase, t0, last_tok, g, c, refetch, fresh);
   if (t_end > a.s_cap) t_end = a.s_cap;
   if (t_begin < 0) t_begin = 0;
   const int c_begin = max(t_begin, t0);
   const int c_end = min(t_end, t0 + kWarpChunk);
   ATTN_STAMP(2);
 
-  // ---- scores: S[head g][token t0 + 8nb + 2c + {0,1}]
-  // (k steps outermost: consecutive mma belong to different accumulators)
-  float sc[8][2];
-  float m = -INFINITY;
-  {
-    float d[8][4];
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb) d[nb][0] = d[nb][1] = d[nb][2] = d[nb][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-      for (int nb = 0; nb < 8; ++nb) {
-        const uint32_t* u = reinterpret_cast<const uint32_t*>(&kr[nb][0]);
-        mma16816(d[nb], qa0[ks], 0u, qa2[ks], 0u, u[2 * ks], u[2 * ks + 1]);
-      }
-    }
-#pragma unroll
-    for (int nb = 0; nb < 8; ++nb) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int t = t0 + 8 * nb + 2 * c + e;
-        const float v = (t >= c_begin && t < c_end) ? d[nb][e] * a.scale : -INFINITY;
-        sc[nb][e] = v;
-        m = fmaxf(m, v);
-      }
-    }
-  }
-  ATTN_STAMP(3);
-  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-  uint32_t pa[4][2];  // P as A fragments: [k step of 16 tokens][a0 | a2]
-  float l = 0.f;
-#pragma unroll
-  for (int nb = 0; nb < 8; ++nb) {
-    const float p0 = (sc[nb][0] == -INFINITY) ? 0.f : __expf(sc[nb][0] - m);
-    const float p1 = (sc[nb][1] == -INFINITY) ? 0.f : __expf(sc[nb][1] - m);
-    const half2 ph = __floats2half2_rn(p0, p1);
-    l += __low2float(ph) + __high2float(ph);  // the sum uses the rounded probabilities that multiply V
-    pa[nb >> 1][nb & 1] = *reinterpret_cast<const uint32_t*>(&ph);
-  }
-  l += __shfl_xor_sync(0xffffffffu, l, 1);
-  l += __shfl_xor_sync(0xffffffffu, l, 2);
-  ATTN_STAMP(4);
-
-  // ---- O[head g][dims] = P V ; mma j covers dims {8n + j}: lane n = g supplies dim 8g + j
-  float o[8][4];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-#pragma unroll
-  for (int jk = 0; jk < 4; ++jk) {
-    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vr[jk][0]);  // token 2c
-    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vr[jk][1]);  // token 2c + 1
-    const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vr[jk][2]);  // token 2c + 8
-    const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vr[jk][3]);  // token 2c + 9
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {  // word w holds dims 8g + 2w, 8g + 2w + 1
-      const uint32_t b0_lo = __byte_perm(r0[w], r1[w], 0x5410), b0_hi = __byte_perm(r0[w], r1[w], 0x7632);
-      const uint32_t b1_lo = __byte_perm(r2[w], r3[w], 0x5410), b1_hi = __byte_perm(r2[w], r3[w], 0x7632);
-      mma16816(o[2 * w], pa[jk][0], 0u, pa[jk][1], 0u, b0_lo, b1_lo);
-      mma16816(o[2 * w + 1], pa[jk][0], 0u, pa[jk][1], 0u, b0_hi, b1_hi);
-    }
-  }
+  float m, l, o[8][4];
+  warp_tile_attend(tile, qa0, qa2, t0, c_begin, c_end, a.scale, c, m, l, o);
   ATTN_STAMP(5);
 
   // ---- C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j of head g

@@ -430,12 +430,17 @@ __global__ void __launch_bounds__(224) oproj_kernel(const OProjArgs a) {
 // writes its fp32 partial sums to gu_part[part][gate|up][row][4864] (a CTA that
 // owns the whole tile writes zeros to part 1) and the down kernel adds the two
 // parts, rounds to fp16 and applies SwiGLU.  grid (133, ceil(batch/M)), block 256.
+// At one row the kernel is held to 128 registers: with 156 a CTA of this kernel
+// and a CTA of the down kernel (127 registers, launched early by programmatic
+// dependent launch to fetch its weights) did not fit one SM's register file
+// together, so most of the down kernel's weight loads started only after this
+// kernel had finished.
 // ---------------------------------------------------------------------------
 constexpr int kGuUnitsPerCta = 8;
 constexpr int kGuCtas = (kInter / 32) * 7 / kGuUnitsPerCta;  // 133
 
 template <int M>
-__global__ void __launch_bounds__(256) gateup_kernel(const GateUpArgs a) {
+__global__ void __launch_bounds__(256, M == 1 ? 2 : 1) gateup_kernel(const GateUpArgs a) {
   __shared__ __align__(16) half xs[M * kHidden];
   __shared__ float red[8 * M * 2 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

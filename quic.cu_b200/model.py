@@ -253,8 +253,12 @@ class QUICForCausalLM:
             cache._graphs[key] = g
         return g, rows
 
-    def launches_per_step(self) -> int:
-        return 5 * self.n_layers + 1
+    def launches_per_step(self, cache: SlotCache | None = None, batch: int = 1, ctx: int = 1024) -> int:
+        """Kernels one decode step launches for ``batch`` rows at a context bound of ``ctx``."""
+        if cache is None:
+            return 5 * self.n_layers + 1
+        d, _ = self._decode_struct(cache, batch, ctx, None)
+        return int(K.lib().quic_decode_launch_count(C.byref(self._c_model), C.byref(d)))
 
     def _prepare_decode(self, cache: SlotCache, slots: list[int], steps: int, logits):
         """Checks the request, loads the row->slot map and returns (graph handle, ring index
