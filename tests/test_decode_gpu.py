@@ -71,6 +71,42 @@ def test_prefill_then_graph_decode_matches_oracle(tiny_model):
     assert again == tokens
 
 
+def test_bursts_single_steps_and_host_fed_steps_agree(tiny_model):
+    """150 tokens three ways: graph bursts of 64 steps (the ring of generated tokens wraps),
+    single-step calls, and single-step calls that feed the previous token back from pinned
+    host memory.  Bit-identical tokens: the kernels read cache rows written one step earlier
+    ahead of their dependency wait, and with a two-layer model consecutive steps sit only a
+    few kernels apart."""
+    net, _, _, _ = tiny_model
+    prompt = torch.tensor([17, 4, 256, 1000, 31, 8, 8, 1203, 77])
+    n = 150
+
+    cache = net.new_cache(n_slots=2, s_max=256)
+    first, _ = net.prefill(cache, [1], [prompt])
+    bursts, left = [int(first[0])], n
+    while left:
+        k = min(64, left)
+        bursts += net.decode(cache, [1], k)[0]
+        left -= k
+
+    cache = net.new_cache(n_slots=2, s_max=256)
+    first, _ = net.prefill(cache, [0], [prompt])
+    singles = [int(first[0])] + [net.decode(cache, [0], 1)[0][0] for _ in range(n)]
+
+    cache = net.new_cache(n_slots=2, s_max=256)
+    first, _ = net.prefill(cache, [1], [prompt])
+    pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+    fed = [int(first[0])]
+    for _ in range(n):
+        pinned[0] = fed[-1]
+        fed.append(net.decode(cache, [1], 1, feed=pinned)[0][0])
+
+    assert singles == bursts
+    assert fed == bursts
+    with pytest.raises(ValueError):
+        net.decode(cache, [1], 1, feed=torch.zeros(2, dtype=torch.int32))
+
+
 def test_batched_rows_are_independent(tiny_model):
     """Rows of different lengths in one batch give what each gives alone (left-padding
     semantics of the reference's batch: padded keys never contribute)."""
