@@ -254,7 +254,7 @@ typedef struct {
 
 /* Batches of at least this many rows run the decode step on the tensor-core
  * kernels (tcgen05 GEMM, tensor lm_head); smaller ones on the fused GEMV chain.
- * Default 5 (measured crossover on B200); accepted range 2..9.  Set it before graphs are captured.  No
+ * Default 4 (measured crossover on B200); accepted range 2..9.  Set it before graphs are captured.  No
  * reference counterpart (Marlin picks its tile shapes per call,
  * kernels/cuda/marlin.cu:3795-3805). */
 void quic_set_tensor_min_batch(int32_t batch);

@@ -41,9 +41,9 @@ def test_tensor_gemm_matches_gemv_and_oracle(name):
     assert K.lib().quic_w4a16_tensor_status() == 0
 
 
-@pytest.mark.parametrize("batch", [9, 12, 40])
+@pytest.mark.parametrize("batch", [4, 9, 12, 40])
 def test_batched_decode_step_matches_oracle(tiny_model, batch):
-    """Batch > 8 switches the decode step to the tensor-core kernels; every row must still give
+    """From 4 rows the decode step runs on the tensor-core kernels; every row must still give
     what the oracle gives for that request alone."""
     from quic_cu_b200 import kernels as K
 
@@ -58,6 +58,30 @@ def test_batched_decode_step_matches_oracle(tiny_model, batch):
     for i in range(0, batch, max(1, batch // 6)):
         ref_tokens, ref_logits = ref.greedy(prompts[i].tolist(), 5)
         _near_tie_ok([int(first[i])] + rest[i], ref_tokens, ref_logits)
+    assert K.lib().quic_w4a16_tensor_status() == 0
+
+
+@pytest.mark.parametrize("batch", [3, 5, 8])
+def test_gemv_chain_and_tensor_step_agree_with_oracle(tiny_model, batch):
+    """The same rows through the fused GEMV chain (forced up to 8 rows per step) and through
+    the tensor-core step (forced from 2 rows): both must match the oracle row by row."""
+    from quic_cu_b200 import kernels as K
+
+    net, ref, _, _ = tiny_model
+    gen = torch.Generator().manual_seed(100 + batch)
+    prompts = [torch.randint(0, 2048, (int(n),), generator=gen) for n in torch.randint(1, 30, (batch,), generator=gen)]
+    want = [ref.greedy(p.tolist(), 5) for p in prompts]
+    try:
+        for threshold in (9, 2):
+            K.lib().quic_set_tensor_min_batch(threshold)
+            cache = net.new_cache(n_slots=8, s_max=128)  # new cache: graphs are captured per threshold
+            slots = list(range(batch))
+            first, _ = net.prefill(cache, slots, prompts)
+            rest = net.decode(cache, slots, 4)
+            for i in range(batch):
+                _near_tie_ok([int(first[i])] + rest[i], want[i][0], want[i][1])
+    finally:
+        K.lib().quic_set_tensor_min_batch(4)
     assert K.lib().quic_w4a16_tensor_status() == 0
 
 
