@@ -58,7 +58,8 @@ class SlotCache:
         self.step_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.host_len = [0] * n_slots  # host mirror of pos (tokens cached per slot)
         self.batch_slots: list[int] = []  # slots of the batch rows, for the forward() API
-        self._rows: dict[tuple, torch.Tensor] = {}
+        self._rows: dict[tuple, torch.Tensor] = {}      # row->slot maps by slot tuple (evictable)
+        self._row_bufs: dict[int, torch.Tensor] = {}    # per batch size: the buffer captured graphs read
         self._scratch: dict[tuple, torch.Tensor] = {}
         self._graphs: dict[tuple, int] = {}
         self._plans: dict[tuple, tuple] = {}       # decode(): per (rows, steps) launch plan
@@ -232,7 +233,10 @@ class QUICForCausalLM:
     # ---- decode ----------------------------------------------------------------
     def _decode_struct(self, cache: SlotCache, batch: int, ctx: int, logits: torch.Tensor | None):
         splits = K.lib().quic_decode_pick_splits(batch, ctx)
-        rows = cache._rows.setdefault(("buf", batch), torch.zeros(batch, dtype=torch.int32, device=self.device))
+        # captured graphs keep this buffer's address: it lives as long as the cache
+        rows = cache._row_bufs.get(batch)
+        if rows is None:
+            rows = cache._row_bufs[batch] = torch.zeros(batch, dtype=torch.int32, device=self.device)
         d = K.Decode(K.ptr(cache.kv), cache.n_slots, cache.s_max, K.ptr(cache.tok), K.ptr(cache.pos),
                      K.ptr(rows), batch, K.ptr(cache.out_tokens), cache.ring, K.ptr(cache.step_counter),
                      K.ptr(logits), K.ptr(cache.scratch(batch, splits)), splits, ctx)
