@@ -133,10 +133,30 @@ int quic_rope(const void *x_f16, const void *cos_f16, const void *sin_f16,
               void *y_f16, int32_t b, int32_t h, int32_t s,
               int32_t trig_batch_stride, void *stream);
 
+/* Prefill form of "split heads, rotate, append": qkv fp16 [rows, 1152] is the
+ * output of the fused QKV linear (columns in the prepacked order: inside every
+ * head, rotation pairs adjacent); row r belongs to KV slot slots[r] at position
+ * positions[r].  Writes the rotated queries head-major, q_out fp16
+ * [14, rows, 64], and the rotated keys / plain values into the layer's cache
+ * planes [n_slots, 2, s_max, 64] at (slot, head, position).  Replaces
+ * _heads + rope.forward x2 + DynamicCache.update of the reference's attention
+ * (src/model.py:138-160). */
+int quic_qkv_rope_append(const void *qkv_f16, const int32_t *slots,
+                         const int32_t *positions, const void *cos_f16,
+                         const void *sin_f16, int32_t max_pos, void *q_out_f16,
+                         void *kcache_f16, void *vcache_f16, int32_t s_max,
+                         int32_t rows, void *stream);
+
 /* y = silu(gate) * up, rows of 4864.  Replaces swiglu.forward
  * (kernels/cuda/swiglu.cu:37). */
 int quic_swiglu(const void *gate_f16, const void *up_f16, void *y_f16,
                 int32_t rows, void *stream);
+/* The same on the output of the fused gate|up linear, gu [rows, 9728]:
+ * y = silu(gu[:, :4864]) * gu[:, 4864:].  The reference runs gate and up as
+ * two linears and hands both to swiglu.forward (src/model.py:96-105); here
+ * they are one linear, and this form saves slicing its output. */
+int quic_swiglu_fused(const void *gu_f16, void *y_f16, int32_t rows,
+                      void *stream);
 
 /* Row argmax of fp16 logits [B, V] -> int64 [B]; ties -> lowest index.
  * Replaces sampler.forward (kernels/cuda/sampler.cu:52). */

@@ -247,7 +247,8 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
                                 const half* __restrict__ bias, const int32_t* __restrict__ rows,
                                 const int32_t* __restrict__ pos, const half* __restrict__ cos_t,
                                 const half* __restrict__ sin_t, int max_pos, half* __restrict__ qbuf,
-                                half* __restrict__ kcache, half* __restrict__ vcache, int s_max, int batch) {
+                                half* __restrict__ kcache, half* __restrict__ vcache, int s_max, int batch,
+                                const int32_t* __restrict__ row_pos, int q_head_major) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
@@ -256,7 +257,8 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
   const int b = idx / (kQkvN / 2), c2 = idx % (kQkvN / 2);
   const int head = c2 >> 5, pair = c2 & 31;  // stored columns (2*pair, 2*pair+1) = dims (pair, pair+32)
   const int slot = rows[b];
-  const int p = pos[slot];
+  // decode: the row's position is its slot's; prefill: every row (token) brings its own
+  const int p = row_pos != nullptr ? row_pos[b] : pos[slot];
   float2 v;
   if (part != nullptr) {  // fp16(sum of the split-K partials) + bias, as the GEMM epilogue would do
     float2 p[16];
@@ -285,9 +287,9 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
   }
   half* dst;
   if (head < kHeads) {
-    dst = qbuf + ((size_t)b * kHeads + head) * kHeadDim;
+    dst = q_head_major ? qbuf + ((size_t)head * batch + b) * kHeadDim : qbuf + ((size_t)b * kHeads + head) * kHeadDim;
   } else {
-    if (p >= s_max) return;
+    if (p >= s_max || p < 0) return;
     const int kvh = (head - kHeads) & 1;
     half* base = (head < kHeads + kKvHeads) ? kcache : vcache;
     dst = base + (((size_t)slot * kKvHeads + kvh) * s_max + p) * kHeadDim;
@@ -348,14 +350,16 @@ cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t*
                             int batch, cudaStream_t st) {
   const int total = batch * (kQkvN / 2);
   return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, qkv, (const float*)nullptr, 0,
-                (const half*)nullptr, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch);
+                (const half*)nullptr, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch,
+                (const int32_t*)nullptr, 0);
 }
 cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
                                  const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,
                                  half* kcache, half* vcache, int s_max, int batch, cudaStream_t st) {
   const int total = batch * (kQkvN / 2);
   return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, (const half*)nullptr, part,
-                splits, bias, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch);
+                splits, bias, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch,
+                (const int32_t*)nullptr, 0);
 }
 cudaError_t launch_rmsnorm_part(const float* part, int splits, const half* residual, const half* w, float eps,
                                 half* y, half* sum_out, int rows, cudaStream_t st) {
@@ -430,6 +434,32 @@ extern "C" int quic_swiglu(const void* gate, const void* up, void* y, int32_t ro
   swiglu_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       (const half2*)gate, (const half2*)up, (half2*)y, n2);
   QUIC_CUDA(cudaGetLastError());
+  return QUIC_OK;
+}
+
+extern "C" int quic_qkv_rope_append(const void* qkv, const int32_t* slots, const int32_t* positions,
+                                    const void* cos_t, const void* sin_t, int32_t max_pos, void* q_out,
+                                    void* kcache, void* vcache, int32_t s_max, int32_t rows, void* stream) {
+  QUIC_REQUIRE(qkv && slots && positions && cos_t && sin_t && q_out && kcache && vcache, QUIC_E_ARG,
+               "qkv_rope_append: null tensor");
+  QUIC_REQUIRE(rows >= 0 && rows <= (1 << 20) && s_max >= 1 && max_pos >= 1, QUIC_E_SHAPE,
+               "qkv_rope_append: bad row count or cache length");
+  if (rows == 0) return QUIC_OK;
+  const int total = rows * (kQkvN / 2);
+  QUIC_CUDA(launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, false,
+                   (const half*)qkv, (const float*)nullptr, 0, (const half*)nullptr, slots, (const int32_t*)nullptr,
+                   (const half*)cos_t, (const half*)sin_t, (int)max_pos, (half*)q_out, (half*)kcache, (half*)vcache,
+                   (int)s_max, (int)rows, positions, 1));
+  return QUIC_OK;
+}
+
+extern "C" int quic_swiglu_fused(const void* gu, void* y, int32_t rows, void* stream) {
+  QUIC_REQUIRE(gu && y, QUIC_E_ARG, "swiglu_fused: null tensor");
+  QUIC_REQUIRE(rows >= 0, QUIC_E_SHAPE, "swiglu_fused: negative rows");
+  if (rows == 0) return QUIC_OK;
+  const size_t total = (size_t)rows * (kInter / 2);
+  QUIC_CUDA(launch(swiglu_fused_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                   false, (const half*)gu, (const float*)nullptr, 0, (half*)y, (int)rows));
   return QUIC_OK;
 }
 

@@ -59,6 +59,7 @@ struct GemmArgs {
   int m_total;
   int kblocks_per_split;
   int stages;  // depth of the operand ring (3 lets two CTAs share an SM, 5-6 is the deep ring)
+  int mtl;     // batch-row tiles per CTA (2 from 129 rows up)
 };
 
 constexpr int kMaxGroupsPerCta = 40;            // K / 128 of the widest layer (4864) rounded up
@@ -66,10 +67,13 @@ constexpr int kConsumers = 512;                 // 16 warps dequantise (4 per sc
 constexpr int kGemmThreads = kConsumers + 64;   // + TMA warp + MMA warp (one lane each)
 constexpr uint32_t kRawBytes = 8 * kTileN * 4;  // packed tile: 8 k-words x 128 rows
 
-template <int MT>
+// MTL = batch-row tiles per CTA: one dequantised weight tile feeds MTL MMAs groups, so the
+// dequantisation work per flop drops MTL-fold (large M: prefill).
+template <int MT, int MTL = 1>
 struct Smem {
-  static constexpr int kStages = MT > 64 ? 5 : 6;
-  static constexpr uint32_t kB = ((uint32_t)MT * 128u + 1023u) & ~1023u;  // x tile, swizzled by TMA
+  static constexpr int kStages = MTL > 1 ? 4 : (MT > 64 ? 5 : 6);
+  static constexpr uint32_t kBTile = ((uint32_t)MT * 128u + 1023u) & ~1023u;  // one x tile, swizzled by TMA
+  static constexpr uint32_t kB = kBTile * MTL;
   static constexpr uint32_t kA = kTileN * 128;                           // dequantised tile
   static constexpr uint32_t kStage = kRawBytes + kB + kA;
   static constexpr uint32_t kTotal = kStages * kStage + 1024;            // + alignment slack
@@ -85,11 +89,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // once its A tile is complete and commits them to the stage's "empty" barrier, which lets
 // the TMA warp refill it.  No role ever waits for another role's instruction issue, only
 // for data.  Warps 0-15 read the accumulator back at the end.
-template <int MT, int kStages>
+template <int MT, int kStages, int MTL>
 __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                      const __grid_constant__ CUtensorMap tm_x,
                                                                      const GemmArgs a) {
-  using L = Smem<MT>;
+  using L = Smem<MT, MTL>;
   constexpr int kMaxStages = kStages;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];    // packed weight tile landed (TMA bytes)
@@ -104,7 +108,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kTileN;
   const int split = blockIdx.y;
-  const int m0 = blockIdx.z * MT;
+  const int m0 = blockIdx.z * MT * MTL;
   const int N = a.w.n;
   const int kb_total = a.w.k / kBlockK;
   const int kb0 = split * a.kblocks_per_split;
@@ -115,7 +119,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
 
-  constexpr uint32_t kCols = MT < 32 ? 32 : MT;  // power of two >= 32
+  constexpr uint32_t kCols = MT * MTL < 32 ? 32 : MT * MTL;  // power of two >= 32
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
@@ -169,8 +173,11 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       GROLE(2);
       for (int it = 0; it < first; ++it) {
         const uint32_t xfull = smem_u32(&bar_aready[it]);
-        mbar_expect_tx(xfull, (uint32_t)MT * 128u);
-        tma_load_2d(base + it * L::kStage + kRawBytes, &tm_x, (kb0 + it) * kBlockK, m0, xfull);
+        mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL);
+#pragma unroll
+        for (int i = 0; i < MTL; ++i)  // rows past the end of x read as zero
+          tma_load_2d(base + it * L::kStage + kRawBytes + i * L::kBTile, &tm_x, (kb0 + it) * kBlockK, m0 + i * MT,
+                      xfull);
       }
       // (ring position and phase are carried along: the depth is a run-time value)
       for (int it = first, stage = 0, pass = 1; it < nkb; ++it) {
@@ -182,8 +189,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_aready[stage]);
         mbar_expect_tx(full, kRawBytes);
         tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
-        mbar_expect_tx(xfull, (uint32_t)MT * 128u);
-        tma_load_2d(b_s, &tm_x, (kb0 + it) * kBlockK, m0, xfull);
+        mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL);
+#pragma unroll
+        for (int i = 0; i < MTL; ++i)
+          tma_load_2d(b_s + i * L::kBTile, &tm_x, (kb0 + it) * kBlockK, m0 + i * MT, xfull);
         if (++stage == kStages) {
           stage = 0;
           ++pass;
@@ -214,9 +223,13 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         const uint32_t b_s = base + stage * L::kStage + kRawBytes, a_s = b_s + L::kB;
 #ifndef QUIC_TC_NO_MMA  // timing experiments only
 #pragma unroll
-        for (int k = 0; k < kBlockK / 16; ++k)
-          umma_f16(tmem_d, umma_desc_sw128(a_s + k * 32), umma_desc_sw128(b_s + k * 32), idesc,
-                   (it > 0 || k > 0) ? 1u : 0u);
+        for (int i = 0; i < MTL; ++i) {
+          if (i > 0 && m0 + i * MT >= a.m_total) break;  // tile of rows beyond the end
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k)
+            umma_f16(tmem_d + (uint32_t)(i * MT), umma_desc_sw128(a_s + k * 32),
+                     umma_desc_sw128(b_s + i * L::kBTile + k * 32), idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
 #endif
         GMMA(it, 1);
         if (it + kStages < nkb) umma_commit(smem_u32(&bar_empty[stage]));
@@ -293,26 +306,31 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
                              ? __half2float(reinterpret_cast<const half*>(a.w.bias)[col])
                              : 0.f;
 #pragma unroll 1
-      for (int c0 = cgroup * kColsPerGroup; c0 < min(MT, (cgroup + 1) * kColsPerGroup); c0 += 8) {
-        if (m0 + c0 >= a.m_total) break;
-        uint32_t r[8];
-        const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                       "=r"(r[7])
-                     : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int i = 0; i < MTL; ++i) {
+        if (m0 + i * MT >= a.m_total) break;
+#pragma unroll 1
+        for (int c = cgroup * kColsPerGroup; c < min(MT, (cgroup + 1) * kColsPerGroup); c += 8) {
+          const int c0 = i * MT + c;  // accumulator column = tile * MT + row inside the tile
+          if (m0 + c0 >= a.m_total) break;
+          uint32_t r[8];
+          const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                         "=r"(r[7])
+                       : "r"(taddr));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int m = m0 + c0 + j;
-          if (m >= a.m_total) continue;
-          const float v = __uint_as_float(r[j]);
-          if (gridDim.y == 1 && a.y != nullptr) {
-            float o = __half2float(__float2half_rn(v));
-            if (a.w.bias != nullptr) o += bias;
-            a.y[(size_t)m * N + col] = __float2half_rn(o);
-          } else {
-            a.part[((size_t)split * a.m_total + m) * N + col] = v;
+          for (int j = 0; j < 8; ++j) {
+            const int m = m0 + c0 + j;
+            if (m >= a.m_total) continue;
+            const float v = __uint_as_float(r[j]);
+            if (gridDim.y == 1 && a.y != nullptr) {
+              float o = __half2float(__float2half_rn(v));
+              if (a.w.bias != nullptr) o += bias;
+              a.y[(size_t)m * N + col] = __float2half_rn(o);
+            } else {
+              a.part[((size_t)split * a.m_total + m) * N + col] = v;
+            }
           }
         }
       }
@@ -325,24 +343,40 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kCols) : "memory");
 }
 
-// Sums the split-K partials (one thread per output element, all loads of an element in
+// Sums the split-K partials (one thread per four consecutive output elements, all loads in
 // flight together), rounds to fp16 as the un-split epilogue does and adds the bias.
+// N is a multiple of 128, so a group of four never straddles a row.
 __global__ void tc_splitk_finish_kernel(const float* __restrict__ part, const half* __restrict__ bias,
                                         half* __restrict__ y, int m_total, int N, int splits) {
-  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   const size_t total = (size_t)m_total * N;
   pdl_launch_dependents();
   pdl_wait();
   if (idx >= total) return;
-  float p[16];
+  float4 p[16];
 #pragma unroll
-  for (int s = 0; s < 16; ++s) p[s] = s < splits ? __ldcg(part + (size_t)s * total + idx) : 0.f;
-  float v = 0.f;
+  for (int s = 0; s < 16; ++s)
+    p[s] = s < splits ? __ldcg(reinterpret_cast<const float4*>(part + (size_t)s * total + idx))
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 v = p[0];
 #pragma unroll
-  for (int s = 0; s < 16; ++s) v += p[s];
-  v = __half2float(__float2half_rn(v));
-  if (bias) v += __half2float(bias[idx % N]);
-  y[idx] = __float2half_rn(v);
+  for (int s = 1; s < 16; ++s) {
+    v.x += p[s].x;
+    v.y += p[s].y;
+    v.z += p[s].z;
+    v.w += p[s].w;
+  }
+  half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+  if (bias) {
+    const half2* b2 = reinterpret_cast<const half2*>(bias + idx % N);
+    const float2 l = __half22float2(lo), h = __half22float2(hi), bl = __half22float2(b2[0]), bh = __half22float2(b2[1]);
+    lo = __floats2half2_rn(l.x + bl.x, l.y + bl.y);
+    hi = __floats2half2_rn(h.x + bh.x, h.y + bh.y);
+  }
+  uint2 out;
+  out.x = *reinterpret_cast<const uint32_t*>(&lo);
+  out.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(y + idx) = out;
 }
 
 template <int MT>
@@ -356,18 +390,30 @@ int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
   rc = make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)a.m_total, (uint64_t)a.w.k, MT, kBlockK,
                 CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != QUIC_OK) return rc;
-  dim3 grid(a.w.n / kTileN, splits, (a.m_total + MT - 1) / MT);
+  const int mtiles = (a.m_total + MT - 1) / MT;
+  if (a.mtl == 2) {
+    if constexpr (MT == 128) {
+      constexpr int kDeep = Smem<MT, 2>::kStages;
+      const size_t smem = Smem<MT, 2>::kTotal;
+      dim3 grid(a.w.n / kTileN, splits, (mtiles + 1) / 2);
+      QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
+      QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, 2>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
+      return QUIC_OK;
+    }
+  }
+  dim3 grid(a.w.n / kTileN, splits, mtiles);
   if (a.stages == 3) {
     const size_t smem = 3 * Smem<MT>::kStage + 1024;
-    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, 3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
-    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, 3>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
+    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, 3, 1>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
   } else {
     constexpr int kDeep = Smem<MT>::kStages;
     const size_t smem = Smem<MT>::kTotal;
-    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
-    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
+    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, 1>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
   }
   return QUIC_OK;
 }
@@ -377,12 +423,14 @@ int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
 // `fused_consumer`: the caller's next kernel sums the split-K partials itself, so splitting
 // costs no extra launch.
 static void tc_plan(int m, int n, int k, bool fused_consumer, int* mt_out, int* splits_out, int* per_out,
-                    int* stages_out) {
+                    int* stages_out, int* mtl_out = nullptr) {
   const int kb_total = k / kBlockK;
   const int tiles = n / kTileN;
   const int mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   const int mtiles = (m + mt - 1) / mt;
-  const int ctas = tiles * mtiles;
+  // two row tiles share one dequantised weight tile once there is more than a wave of CTAs
+  const int mtl = (mtiles >= 2 && tiles * mtiles > 148) ? 2 : 1;
+  const int ctas = tiles * ((mtiles + mtl - 1) / mtl);
   int stages = mt > 64 ? 5 : 6;
   // split K while it at most fills the SMs once, at most 16 ways, at least 2 k blocks per CTA
   int splits = 1;
@@ -400,6 +448,7 @@ static void tc_plan(int m, int n, int k, bool fused_consumer, int* mt_out, int* 
   *per_out = per;
   *splits_out = (kb_total + per - 1) / per;
   *stages_out = stages;
+  if (mtl_out != nullptr) *mtl_out = mtl;
 }
 
 int64_t w4a16_gemm_tc_workspace(int m, int n, int k) {
@@ -420,8 +469,8 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0), QUIC_E_ARG,
                "w4a16_linear: x and the packed weights must be 16-byte aligned");
   QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16_linear: K beyond 5120 on the tensor path");
-  int mt, splits, per, stages;
-  tc_plan(m, w.n, w.k, y == nullptr, &mt, &splits, &per, &stages);
+  int mt, splits, per, stages, mtl;
+  tc_plan(m, w.n, w.k, y == nullptr, &mt, &splits, &per, &stages, &mtl);
   QUIC_REQUIRE((splits == 1 && y != nullptr) || workspace != nullptr, QUIC_E_ARG,
                "w4a16_linear: split-K needs a workspace");
   if (splits_out != nullptr) *splits_out = splits;
@@ -434,6 +483,7 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   a.m_total = m;
   a.kblocks_per_split = per;
   a.stages = stages;
+  a.mtl = mtl;
   int rc;
   switch (mt) {
     case 16: rc = run<16>(x, a, splits, st); break;
@@ -444,7 +494,7 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   if (rc != QUIC_OK) return rc;
   if (splits > 1 && y != nullptr) {
     const size_t total = (size_t)m * w.n;
-    QUIC_CUDA(launch(tc_splitk_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true,
+    QUIC_CUDA(launch(tc_splitk_finish_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, st, true,
                      (const float*)a.part, (const half*)w.bias, y, m, w.n, splits));
   }
   return QUIC_OK;

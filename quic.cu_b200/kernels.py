@@ -105,7 +105,9 @@ SIGNATURES = {
     "quic_rmsnorm": (C.c_int, [_P, _P, _P, _F, _P, _P, _I32, _P]),
     "quic_rope_table_init": (C.c_int, [_P, _I32, _P, _P, _P]),
     "quic_rope": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P]),
+    "quic_qkv_rope_append": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _I32, _I32, _P]),
     "quic_swiglu": (C.c_int, [_P, _P, _P, _I32, _P]),
+    "quic_swiglu_fused": (C.c_int, [_P, _P, _I32, _P]),
     "quic_argmax": (C.c_int, [_P, _I32, _I32, _P, _P]),
     "quic_gemm_f16": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P]),
     "quic_lm_head_argmax": (C.c_int, [_P, _P, _F, _P, _I32, _I32, _P, _P, _P, _P]),
@@ -323,6 +325,42 @@ def _swiglu_forward(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     gate, up = gate.contiguous(), up.contiguous()
     y = torch.empty_like(gate)
     check(lib().quic_swiglu(ptr(gate), ptr(up), ptr(y), gate.shape[0], stream_ptr()), "swiglu")
+    return y
+
+
+def qkv_rope_append(qkv: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor,
+                    sin: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor) -> torch.Tensor:
+    """Prefill: rotates and scatters the fused QKV output of ``rows`` tokens.  ``slots`` /
+    ``positions`` int32 [rows]; ``kcache`` / ``vcache`` one layer's planes [n_slots, 2, s_max,
+    64].  Returns the rotated queries fp16 [14, rows, 64] (the reference's _heads + rope +
+    cache update, src/model.py:138-160, in one kernel)."""
+    _need_cuda(qkv, slots, positions, cos, sin, kcache, vcache)
+    _need_half(qkv, cos, sin, kcache, vcache)
+    rows = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.shape[1] != QKV_N or slots.numel() != rows or positions.numel() != rows:
+        raise RuntimeError("qkv_rope_append: qkv must be [rows, 1152] with one slot and position per row")
+    if slots.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise RuntimeError("qkv_rope_append: slots / positions must be int32")
+    if not (kcache.is_contiguous() and vcache.is_contiguous()) or kcache.shape[1:] != (KV_HEADS, kcache.shape[2], HEAD_DIM):
+        raise RuntimeError("qkv_rope_append: cache planes must be contiguous [n_slots, 2, s_max, 64]")
+    q = torch.empty(HEADS, rows, HEAD_DIM, dtype=torch.float16, device=qkv.device)
+    check(lib().quic_qkv_rope_append(ptr(qkv.contiguous()), ptr(slots), ptr(positions), ptr(cos), ptr(sin),
+                                     cos.shape[0], ptr(q), ptr(kcache), ptr(vcache), kcache.shape[2], rows,
+                                     stream_ptr()), "qkv_rope_append")
+    return q
+
+
+def swiglu_fused(gu: torch.Tensor) -> torch.Tensor:
+    """silu(gu[:, :4864]) * gu[:, 4864:] on the fused gate|up linear output, fp16 [rows, 9728]
+    -> fp16 [rows, 4864] (the reference's _MLP, src/model.py:96-105, without slicing copies)."""
+    _need_cuda(gu)
+    _need_half(gu)
+    if gu.dim() != 2 or gu.shape[1] != 2 * INTER:
+        raise RuntimeError("swiglu_fused: expected [rows, 9728]")
+    gu = gu.contiguous()
+    y = torch.empty(gu.shape[0], INTER, dtype=torch.float16, device=gu.device)
+    if gu.shape[0]:
+        check(lib().quic_swiglu_fused(ptr(gu), ptr(y), gu.shape[0], stream_ptr()), "swiglu_fused")
     return y
 
 

@@ -369,32 +369,30 @@ class QUICForCausalLM:
         bounds = [0]
         for n in lens:
             bounds.append(bounds[-1] + n)
-        pos = torch.cat([torch.arange(n, device=dev) for n in lens])
-        cos, sin = self.rope_cos[pos].contiguous(), self.rope_sin[pos].contiguous()
+        # per token: its KV slot and its position (one small host -> device copy each)
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev, non_blocking=True)
+        slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32),
+                                          torch.tensor(lens)).to(dev, non_blocking=True)
         T = ids.numel()
         h = self.embed[ids]
         rms, lin = K.rmsnorm().forward, K.w4a16_linear
         xn = rms(h, self.layers[0]["ln1"], self.eps)
         for li, L in enumerate(self.layers):
             qkv = lin(L["qkv"], xn)
-            # stored column order inside each head is (pair, half) -> natural dim = pair + 32*half
-            qkv = qkv.view(T, 18, 32, 2).transpose(2, 3).reshape(T, 18, HEAD_DIM)
-            qk = qkv[:, :16].transpose(0, 1).contiguous().unsqueeze(0)  # [1,16,T,64]
-            qk = K.rope().forward(qk, cos, sin)[0]
-            q, k, v = qk[:14], qk[14:16], qkv[:, 16:18].transpose(0, 1)
+            # heads split, RoPE applied and K/V written into their slots by one kernel
+            q = K.qkv_rope_append(qkv, slot_of, pos, self.rope_cos, self.rope_sin, cache.kv[li, 0], cache.kv[li, 1])
             attn = torch.empty(T, HEADS * HEAD_DIM, dtype=DTYPE, device=dev)
             with _sdpa_backends():
                 for i, s in enumerate(slots):
                     a, b = bounds[i], bounds[i + 1]
-                    cache.kv[li, 0, s, :, : b - a] = k[:, a:b]
-                    cache.kv[li, 1, s, :, : b - a] = v[:, a:b]
-                    o = F.scaled_dot_product_attention(q[None, :, a:b], k[None, :, a:b], v[None, :, a:b],
+                    k, v = cache.kv[li, 0, s, :, : b - a], cache.kv[li, 1, s, :, : b - a]
+                    o = F.scaled_dot_product_attention(q[None, :, a:b], k[None], v[None],
                                                        is_causal=True, scale=HEAD_DIM ** -0.5, enable_gqa=True)
                     attn[a:b] = o[0].transpose(0, 1).reshape(b - a, -1)
             o = lin(L["o"], attn)
             xn, h = rms(o, L["ln2"], self.eps, residual=h)
             gu = lin(L["gate_up"], xn)
-            act = K.swiglu().forward(gu[:, :INTER].contiguous(), gu[:, INTER:].contiguous())
+            act = K.swiglu_fused(gu)
             d = lin(L["down"], act)
             nxt = self.layers[li + 1]["ln1"] if li + 1 < self.n_layers else self.final_norm
             xn, h = rms(d, nxt, self.eps, residual=h)

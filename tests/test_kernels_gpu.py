@@ -47,6 +47,10 @@ def test_swiglu(K):  # reference tests/test_kernels.py:26
     out = K.swiglu().forward(gate, up)
     expected = (F.silu(gate.float()) * up.float()).half()
     assert torch.allclose(out, expected, atol=1e-2)
+    # the same on the fused gate|up layout: bit-identical to the two-tensor form
+    fused = K.swiglu_fused(torch.cat([gate, up], dim=1))
+    assert torch.equal(fused, out)
+    assert K.swiglu_fused(torch.empty(0, 9728, device="cuda", dtype=torch.float16)).shape == (0, 4864)
 
 
 def test_gemm(K):  # reference tests/test_kernels.py:38
@@ -110,6 +114,37 @@ def test_rope_table_and_rotation(K):
     y2 = K.rope().forward(x, cos[pos].contiguous(), sin[pos].contiguous())
     want2 = quic_ref.rope(x.cpu(), cos[pos].cpu()[:, None], sin[pos].cpu()[:, None])
     assert torch.allclose(y2.cpu().float(), want2.float(), atol=2e-3)
+
+
+def test_qkv_rope_append_matches_split_rope_and_cache_update(K):
+    """Prefill form: one kernel instead of the reference's _heads + rope.forward x2 +
+    DynamicCache.update (src/model.py:138-160).  Stored columns hold rotation pairs side by
+    side inside every head; tokens of two sequences go to different slots."""
+    torch.manual_seed(3)
+    exponent = torch.arange(0, 64, 2, dtype=torch.float32) / 64
+    cos, sin = K.rope().init_table((1.0 / (1e6 ** exponent)).cuda(), 4096)
+    lens, slots = [37, 5], [3, 0]
+    rows = sum(lens)
+    qkv = torch.randn(rows, 1152, device="cuda", dtype=torch.float16)
+    pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).cuda()
+    slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32), torch.tensor(lens)).cuda()
+    kc = torch.zeros(4, 2, 64, 64, device="cuda", dtype=torch.float16)
+    vc = torch.zeros_like(kc)
+    q = K.qkv_rope_append(qkv, slot_of, pos, cos, sin, kc, vc)
+    assert q.shape == (14, rows, 64)
+    natural = qkv.cpu().view(rows, 18, 32, 2).transpose(2, 3).reshape(rows, 18, 64)
+    c, s_ = cos.cpu()[pos.cpu().long()][:, None], sin.cpu()[pos.cpu().long()][:, None]
+    rotated = quic_ref.rope(natural[:, :16], c, s_)  # [rows, 16, 64]
+    # fp32 rotation with or without a fused multiply-add: at most one fp16 ulp apart
+    assert torch.allclose(q.cpu().float(), rotated[:, :14].transpose(0, 1).float(), atol=2e-3, rtol=1e-3)
+    start = 0
+    for n, slot in zip(lens, slots):
+        assert torch.allclose(kc[slot, :, :n].cpu().float(), rotated[start:start + n, 14:16].transpose(0, 1).float(),
+                              atol=2e-3, rtol=1e-3)
+        assert torch.equal(vc[slot, :, :n].cpu(), natural[start:start + n, 16:18].transpose(0, 1))
+        assert torch.count_nonzero(kc[slot, :, n:]) == 0
+        start += n
+    assert torch.count_nonzero(kc[1]) == 0 and torch.count_nonzero(vc[2]) == 0
 
 
 def test_errors_are_runtime_errors(K):
