@@ -202,12 +202,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   } else if (warp == kConsumers / 32 + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-#ifdef QUIC_TC_WARMUP
-      // One throw-away MMA before the operands exist (its result is overwritten by the first
-      // real one, which does not accumulate): the tensor pipe is busy once before the
-      // dependency wait instead of after it.
-      umma_f16(tmem_d, umma_desc_sw128(base + kRawBytes + L::kB), umma_desc_sw128(base + kRawBytes), idesc, 0u);
-#endif
       // One wait per k block (operand A written by the consumer warps and operand B landed by
       // TMA arrive on the same barrier) and a commit only where somebody waits for it: each
       // of these costs the issuing thread a round trip, and at these sizes the loop is bound
