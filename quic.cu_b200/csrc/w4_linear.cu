@@ -197,11 +197,19 @@ extern "C" int quic_w4_dequant(const quic_w4_t* w, void* out, void* stream) {
   return QUIC_OK;
 }
 
+// Rows from which the tcgen05 GEMM beats the dequant GEMV (measured per layer shape: 5-9 us
+// against 10-19 us at 4 rows).
+static constexpr int kTensorMinRows = 4;
+
 extern "C" int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  // 16 KB reserved head, then split-K partials: of the tensor path for m >= 16 (it stops
+  // 16 KB reserved head, then split-K partials: of the tensor path from 4 rows (it stops
   // splitting once the output tiles fill the SMs, so large m needs none), of the GEMV below.
-  if (m >= 16 && n % 128 == 0 && k % 64 == 0) return 16384 + w4a16_gemm_tc_workspace(m, n, k);
+  if (m >= kTensorMinRows && n % 128 == 0 && k % 64 == 0) {
+    const int64_t tc = 16384 + w4a16_gemm_tc_workspace(m, n, k);
+    const int64_t gv = m > 8 ? 16384 + (int64_t)2 * m * n * 4 : 16384 + (int64_t)gemv_splits(n, k) * m * n * 4;
+    return tc > gv ? tc : gv;  // the caller may force either path
+  }
   if (m > 8) return 16384 + (int64_t)2 * m * n * 4;  // row-chunked GEMV splits only to fit shared memory
   return 16384 + (int64_t)gemv_splits(n, k) * m * n * 4;
 }
@@ -214,7 +222,7 @@ extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int
   QUIC_REQUIRE(m >= 0, QUIC_E_SHAPE, "w4a16_linear: negative M");
   if (m == 0) return QUIC_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_tensor && m >= 16) {
+  if (use_tensor && m >= kTensorMinRows && w->n % 128 == 0 && w->k % 64 == 0) {
     QUIC_REQUIRE(workspace != nullptr, QUIC_E_ARG, "w4a16_linear: tensor path needs a workspace");
     return w4a16_gemm_tc((const half*)x, *w, (half*)y, m, (float*)workspace, st, nullptr);
   }

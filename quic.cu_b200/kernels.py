@@ -24,8 +24,9 @@ LIB_PATH = os.path.join(_HERE, "libquic_b200.so")
 
 HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, GROUP, QKV_N = 896, 14, 2, 64, 4864, 128, 1152
 ROWS_NATURAL, ROWS_ROPE_PAIRS = 0, 1
-# M >= 16 runs the tcgen05 GEMM when True; the dequant GEMV in row chunks otherwise.
+# M >= TENSOR_MIN_ROWS runs the tcgen05 GEMM when True; the dequant GEMV in row chunks otherwise.
 TENSOR_PATH = True
+TENSOR_MIN_ROWS = 4
 
 
 class W4(C.Structure):
@@ -247,7 +248,7 @@ def w4a16_linear(w: W4Weight, x: torch.Tensor, use_tensor: bool | None = None) -
     m = x2.shape[0]
     y = torch.empty(m, w.size_n, dtype=torch.float16, device=x.device)
     if use_tensor is None:
-        use_tensor = TENSOR_PATH and m >= 16
+        use_tensor = TENSOR_PATH and m >= TENSOR_MIN_ROWS
     s = w.struct()
     for r0 in range(0, m, MAX_LINEAR_ROWS):
         rows = min(MAX_LINEAR_ROWS, m - r0)
