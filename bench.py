@@ -437,8 +437,9 @@ def measure_batch64(net, device, world, dist):
 def measure_serving(net, device, n_requests, world, dist, rank):
     """Continuous batching with 64 KV slots per GPU: prompt lengths uniform in 64..1024, output
     lengths uniform in 128..512 (forced through max_tokens; random weights never emit EOS), all
-    requests queued at t = 0 (arrivals at saturation), greedy.  The queue is dealt round-robin
-    to the replicas; wall-clock on every rank, max over ranks."""
+    requests queued at t = 0 (arrivals at saturation), greedy, prefill attention by the
+    library's own kernel (prefill_backend "quic").  The queue is dealt round-robin to the
+    replicas; wall-clock on every rank, max over ranks."""
     from types import SimpleNamespace
 
     from quic_cu_b200.config import EngineConfig
@@ -452,7 +453,8 @@ def measure_serving(net, device, n_requests, world, dist, rank):
             for i in range(n_requests)]
     mine = shard(reqs, rank, world)
     module = SimpleNamespace(load=lambda **options: (net, None))
-    engine = Engine(config=EngineConfig(batching="continuous", max_context=2048, decode_burst=8),
+    engine = Engine(config=EngineConfig(batching="continuous", max_context=2048, decode_burst=8,
+                                        prefill_backend="quic"),
                     max_batch_size=64, model_module=module)
     if dist is not None:
         dist.barrier()

@@ -147,6 +147,20 @@ int quic_qkv_rope_append(const void *qkv_f16, const int32_t *slots,
                          void *kcache_f16, void *vcache_f16, int32_t s_max,
                          int32_t rows, void *stream);
 
+/* Causal prefill attention of n_seq sequences in one launch (GQA 14:2,
+ * head_dim 64).  q_f16 [14, rows, 64] as written by quic_qkv_rope_append;
+ * sequence i owns rows seq_start[i] .. seq_start[i] + seq_len[i] - 1, its keys
+ * and values are positions 0 .. seq_len[i] - 1 of KV slot seq_slot[i] in the
+ * layer's cache planes [n_slots, 2, s_max, 64] (no padding is stored, so no pad
+ * mask exists); out_f16 [rows, 896] token-major.  Replaces the reference's
+ * prefill attention (kernels/flash_attn_prefill_pytorch.py:10 = torch SDPA with
+ * a causal + left-pad mask; kernels/cuda/flash_attn_prefill.cu:87). */
+int quic_attn_prefill(const void *q_f16, const void *kcache_f16,
+                      const void *vcache_f16, const int32_t *seq_start,
+                      const int32_t *seq_len, const int32_t *seq_slot,
+                      int32_t n_seq, int32_t max_len, int32_t rows,
+                      int32_t s_max, float scale, void *out_f16, void *stream);
+
 /* y = silu(gate) * up, rows of 4864.  Replaces swiglu.forward
  * (kernels/cuda/swiglu.cu:37). */
 int quic_swiglu(const void *gate_f16, const void *up_f16, void *y_f16,

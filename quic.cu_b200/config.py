@@ -15,6 +15,8 @@ class EngineConfig:
     model_path: str | None = None
     tokenizer_path: str | None = None
     use_machete: bool = False  # accepted for compatibility; the Hopper-only backend is not built
+    # "pytorch": torch SDPA per sequence (the reference's default); "quic": the library's causal
+    # prefill kernel, all admitted sequences in one launch (the reference's name for its own kernel)
     prefill_backend: Literal["pytorch", "quic"] = "pytorch"
     # additions (defaults keep reference call sites valid)
     max_context: int = 2048   # tokens per KV slot (prompt + generated)

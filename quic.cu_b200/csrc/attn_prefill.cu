@@ -1,0 +1,227 @@
+// Causal prefill attention over KV slots (GQA 14:2, head_dim 64), all admitted sequences in
+// one launch.  Queries come head-major from quic_qkv_rope_append, keys and values are read
+// from the slots that kernel has just filled, and the output is written token-major
+// [rows, 896], which is the layout the o_proj GEMM consumes.
+//
+// Flash-attention-2 style on mma.sync.m16n8k16: a warp owns 16 consecutive query rows of
+// one head and walks the keys 32 at a time up to its causal bound with an online softmax.
+// The fragment mappings are those of attn_warp.cuh (K fragments are the lane's own 32
+// contiguous bytes of a key row, probabilities go from the score fragments straight into the
+// A operand of p.V, V pairs are built with byte permutes); the difference to decode is that
+// all 16 rows of the M tile are real queries, so every lane carries two rows (g and g + 8).
+// No shared memory: K/V tiles are re-read through L2 by the warps that need them.
+#include "attn_warp.cuh"
+#include "decode_kernels.cuh"
+
+namespace quic {
+namespace {
+
+// Read-only load that allocates in L1: the four warps of a CTA walk the same K/V tiles at
+// about the same time, so three of four reads of a tile are L1 hits.  (The cache rows were
+// written by an earlier kernel; L1 holds nothing stale at kernel start.)
+__device__ __forceinline__ uint4 ldg_l1_u128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+constexpr int kPfWarps = 4;
+constexpr int kPfRows = 16 * kPfWarps;  // query rows per CTA
+constexpr int kGroupHeads = kHeads / kKvHeads;
+
+struct PrefillAttnArgs {
+  const half* q;        // [14][rows][64]
+  const half* kcache;   // [n_slots][2][s_max][64]
+  const half* vcache;
+  const int32_t* seq_start;  // [n_seq] first row of the sequence in q / out
+  const int32_t* seq_len;    // [n_seq]
+  const int32_t* seq_slot;   // [n_seq]
+  half* out;            // [rows][896]
+  int32_t rows;
+  int32_t s_max;
+  float scale;
+};
+
+__global__ void __launch_bounds__(kPfWarps * 32) attn_prefill_kernel(const PrefillAttnArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int len = a.seq_len[seq];
+  // the longest key ranges first: CTAs of late query rows are launched before the short ones
+  const int r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kPfRows + warp * 16;  // first query position of this warp
+  if (r0 >= len) return;
+  const int start = a.seq_start[seq];
+  const int slot = a.seq_slot[seq];
+  const int kvh = head / kGroupHeads;
+  const half* kbase = a.kcache + ((size_t)slot * kKvHeads + kvh) * a.s_max * kHeadDim;
+  const half* vbase = a.vcache + ((size_t)slot * kKvHeads + kvh) * a.s_max * kHeadDim;
+  const int last_tok = len - 1;
+
+  // Q fragments of rows r0 + g (a0, a2) and r0 + g + 8 (a1, a3): dims 16c + 4ks + {0,1} | {2,3}
+  uint32_t qa[4][4];
+  {
+    const int ra = min(r0 + g, last_tok), rb = min(r0 + g + 8, last_tok);  // rows past the end mirror the last
+    const half* qa_p = a.q + ((size_t)head * a.rows + start + ra) * kHeadDim + 16 * c;
+    const half* qb_p = a.q + ((size_t)head * a.rows + start + rb) * kHeadDim + 16 * c;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      const uint2 ua = *reinterpret_cast<const uint2*>(qa_p + 4 * ks);
+      const uint2 ub = *reinterpret_cast<const uint2*>(qb_p + 4 * ks);
+      qa[ks][0] = ua.x;
+      qa[ks][1] = ub.x;
+      qa[ks][2] = ua.y;
+      qa[ks][3] = ub.y;
+    }
+  }
+  const int pos_a = r0 + g, pos_b = r0 + g + 8;  // causal bounds of the lane's two rows
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  const int t_stop = min(r0 + 16, len);  // keys 0 .. t_stop - 1 are visible to some row of the warp
+  for (int t0 = 0; t0 < t_stop; t0 += 32) {
+    // ---- loads: K rows t0 + 8nb + g, bytes [32c, 32c+32); V rows t0 + 16j + 2c + {0,1,8,9}, dims 8g..8g+7
+    uint4 kr[4][2], vr[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)min(t0 + 8 * nb + g, last_tok) * kHeadDim + 16 * c);
+      kr[nb][0] = ldg_l1_u128(kp);
+      kr[nb][1] = ldg_l1_u128(kp + 1);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int tb = t0 + 16 * j + 2 * c;
+      vr[j][0] = ldg_l1_u128(vbase + (size_t)min(tb, last_tok) * kHeadDim + 8 * g);
+      vr[j][1] = ldg_l1_u128(vbase + (size_t)min(tb + 1, last_tok) * kHeadDim + 8 * g);
+      vr[j][2] = ldg_l1_u128(vbase + (size_t)min(tb + 8, last_tok) * kHeadDim + 8 * g);
+      vr[j][3] = ldg_l1_u128(vbase + (size_t)min(tb + 9, last_tok) * kHeadDim + 8 * g);
+    }
+    // ---- scores: d[nb][0..1] row g, d[nb][2..3] row g + 8, tokens t0 + 8nb + 2c + {0,1}
+    float d[4][4];
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) d[nb][0] = d[nb][1] = d[nb][2] = d[nb][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {  // k steps outermost: consecutive mma are independent
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(&kr[nb][0]);
+        mma16816(d[nb], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], u[2 * ks], u[2 * ks + 1]);
+      }
+    }
+    float mt[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int t = t0 + 8 * nb + 2 * c + e;
+        d[nb][e] = (t <= pos_a && t < len) ? d[nb][e] * a.scale : -INFINITY;
+        d[nb][2 + e] = (t <= pos_b && t < len) ? d[nb][2 + e] * a.scale : -INFINITY;
+        mt[0] = fmaxf(mt[0], d[nb][e]);
+        mt[1] = fmaxf(mt[1], d[nb][2 + e]);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mt[r] = fmaxf(mt[r], __shfl_xor_sync(0xffffffffu, mt[r], 1));
+      mt[r] = fmaxf(mt[r], __shfl_xor_sync(0xffffffffu, mt[r], 2));
+      const float m_new = fmaxf(m_run[r], mt[r]);
+      alpha[r] = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - m_new);  // m_new finite whenever m_run is
+      m_run[r] = m_new;
+    }
+    uint32_t pa[2][4];  // P as A fragments per 16-token k step: a0 (row g), a1 (row g+8), a2, a3 (second 8 tokens)
+    float l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float s0 = d[nb][2 * r], s1 = d[nb][2 * r + 1];
+        const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_run[r]);
+        const float p1 = (s1 == -INFINITY) ? 0.f : __expf(s1 - m_run[r]);
+        const half2 ph = __floats2half2_rn(p0, p1);
+        l_add[r] += __low2float(ph) + __high2float(ph);  // the sum uses the rounded probabilities that multiply V
+        pa[nb >> 1][2 * (nb & 1) + r] = *reinterpret_cast<const uint32_t*>(&ph);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + l_add[r];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j][0] *= alpha[0];
+      o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1];
+      o[j][3] *= alpha[1];
+    }
+    // ---- O += P V ; mma j covers dims {8n + j}: lane n = g supplies dim 8g + j
+#pragma unroll
+    for (int jk = 0; jk < 2; ++jk) {
+      const uint32_t* v0 = reinterpret_cast<const uint32_t*>(&vr[jk][0]);  // token 2c
+      const uint32_t* v1 = reinterpret_cast<const uint32_t*>(&vr[jk][1]);  // token 2c + 1
+      const uint32_t* v2 = reinterpret_cast<const uint32_t*>(&vr[jk][2]);  // token 2c + 8
+      const uint32_t* v3 = reinterpret_cast<const uint32_t*>(&vr[jk][3]);  // token 2c + 9
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {  // word w holds dims 8g + 2w, 8g + 2w + 1
+        const uint32_t b0_lo = __byte_perm(v0[w], v1[w], 0x5410), b0_hi = __byte_perm(v0[w], v1[w], 0x7632);
+        const uint32_t b1_lo = __byte_perm(v2[w], v3[w], 0x5410), b1_hi = __byte_perm(v2[w], v3[w], 0x7632);
+        mma16816(o[2 * w], pa[jk][0], pa[jk][1], pa[jk][2], pa[jk][3], b0_lo, b1_lo);
+        mma16816(o[2 * w + 1], pa[jk][0], pa[jk][1], pa[jk][2], pa[jk][3], b0_hi, b1_hi);
+      }
+    }
+  }
+
+  // ---- C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j; rows g (o[j][0..1]) and g + 8 (o[j][2..3])
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = r0 + g + 8 * r;
+    if (row >= len) continue;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    half* op = a.out + (size_t)(start + row) * kHidden + head * kHeadDim + 16 * c;
+    uint4 lo, hi;
+    lo.x = pack_half2(o[0][2 * r] * inv, o[1][2 * r] * inv);
+    lo.y = pack_half2(o[2][2 * r] * inv, o[3][2 * r] * inv);
+    lo.z = pack_half2(o[4][2 * r] * inv, o[5][2 * r] * inv);
+    lo.w = pack_half2(o[6][2 * r] * inv, o[7][2 * r] * inv);
+    hi.x = pack_half2(o[0][2 * r + 1] * inv, o[1][2 * r + 1] * inv);
+    hi.y = pack_half2(o[2][2 * r + 1] * inv, o[3][2 * r + 1] * inv);
+    hi.z = pack_half2(o[4][2 * r + 1] * inv, o[5][2 * r + 1] * inv);
+    hi.w = pack_half2(o[6][2 * r + 1] * inv, o[7][2 * r + 1] * inv);
+    *reinterpret_cast<uint4*>(op) = lo;
+    *reinterpret_cast<uint4*>(op + 8) = hi;
+  }
+}
+
+}  // namespace
+}  // namespace quic
+
+using namespace quic;
+
+extern "C" int quic_attn_prefill(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
+                                 const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len,
+                                 int32_t rows, int32_t s_max, float scale, void* out, void* stream) {
+  QUIC_REQUIRE(q && kcache && vcache && seq_start && seq_len && seq_slot && out, QUIC_E_ARG,
+               "attn_prefill: null tensor");
+  QUIC_REQUIRE(n_seq >= 0 && n_seq <= 65535 && rows >= 0 && max_len >= 0 && s_max >= 1 && max_len <= s_max,
+               QUIC_E_SHAPE, "attn_prefill: bad sequence count or lengths");
+  QUIC_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)kcache % 16 == 0) && ((uintptr_t)vcache % 16 == 0) &&
+                   ((uintptr_t)out % 16 == 0),
+               QUIC_E_ARG, "attn_prefill: tensors must be 16-byte aligned");
+  if (n_seq == 0 || rows == 0 || max_len == 0) return QUIC_OK;
+  PrefillAttnArgs a = {};
+  a.q = (const half*)q;
+  a.kcache = (const half*)kcache;
+  a.vcache = (const half*)vcache;
+  a.seq_start = seq_start;
+  a.seq_len = seq_len;
+  a.seq_slot = seq_slot;
+  a.out = (half*)out;
+  a.rows = rows;
+  a.s_max = s_max;
+  a.scale = scale > 0.f ? scale : 0.125f;
+  dim3 grid((max_len + kPfRows - 1) / kPfRows, kHeads, n_seq);
+  QUIC_CUDA(launch(attn_prefill_kernel, grid, dim3(kPfWarps * 32), 0, (cudaStream_t)stream, false, a));
+  return QUIC_OK;
+}

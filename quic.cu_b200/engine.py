@@ -65,6 +65,8 @@ class Engine:
         if model_module is None:
             from . import model as model_module  # the CUDA model; raises without the library
         self.model, self.tokenizer = model_module.load(**load_options)
+        if getattr(config, "prefill_backend", None) is not None and hasattr(self.model, "prefill_backend"):
+            self.model.prefill_backend = config.prefill_backend  # also for a model handed in ready-made
         self.max_tokens = 256
         self.registry = registry
         self.burst = max(1, int(config.decode_burst))

@@ -107,6 +107,7 @@ SIGNATURES = {
     "quic_rope_table_init": (C.c_int, [_P, _I32, _P, _P, _P]),
     "quic_rope": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P]),
     "quic_qkv_rope_append": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _I32, _I32, _P]),
+    "quic_attn_prefill": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, C.c_float, _P, _P]),
     "quic_swiglu": (C.c_int, [_P, _P, _P, _I32, _P]),
     "quic_swiglu_fused": (C.c_int, [_P, _P, _I32, _P]),
     "quic_argmax": (C.c_int, [_P, _I32, _I32, _P, _P]),
@@ -349,6 +350,25 @@ def qkv_rope_append(qkv: torch.Tensor, slots: torch.Tensor, positions: torch.Ten
                                      cos.shape[0], ptr(q), ptr(kcache), ptr(vcache), kcache.shape[2], rows,
                                      stream_ptr()), "qkv_rope_append")
     return q
+
+
+def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, seq_start: torch.Tensor,
+                 seq_len: torch.Tensor, seq_slot: torch.Tensor, max_len: int, scale: float = -1.0) -> torch.Tensor:
+    """Causal prefill attention of several sequences in one launch.  ``q`` fp16 [14, rows, 64]
+    (from qkv_rope_append); ``seq_start`` / ``seq_len`` / ``seq_slot`` int32 [n_seq] on the
+    device; keys and values are read from the slots.  Returns fp16 [rows, 896]."""
+    _need_cuda(q, kcache, vcache, seq_start, seq_len, seq_slot)
+    _need_half(q, kcache, vcache)
+    if q.dim() != 3 or q.shape[0] != HEADS or q.shape[2] != HEAD_DIM or not q.is_contiguous():
+        raise RuntimeError("attn_prefill: q must be contiguous [14, rows, 64]")
+    if any(t.dtype != torch.int32 for t in (seq_start, seq_len, seq_slot)):
+        raise RuntimeError("attn_prefill: sequence tables must be int32")
+    rows, n_seq = q.shape[1], seq_len.numel()
+    out = torch.empty(rows, HEADS * HEAD_DIM, dtype=torch.float16, device=q.device)
+    check(lib().quic_attn_prefill(ptr(q), ptr(kcache), ptr(vcache), ptr(seq_start), ptr(seq_len), ptr(seq_slot),
+                                  n_seq, int(max_len), rows, kcache.shape[2], float(scale), ptr(out), stream_ptr()),
+          "attn_prefill")
+    return out
 
 
 def swiglu_fused(gu: torch.Tensor) -> torch.Tensor:

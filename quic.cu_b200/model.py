@@ -374,6 +374,9 @@ class QUICForCausalLM:
         slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32),
                                           torch.tensor(lens)).to(dev, non_blocking=True)
         T = ids.numel()
+        if self.prefill_backend != "pytorch":
+            table = torch.tensor([bounds[:-1], lens, slots], dtype=torch.int32).to(dev, non_blocking=True)
+            seq_start, seq_len, seq_slot = table[0], table[1], table[2]
         h = self.embed[ids]
         rms, lin = K.rmsnorm().forward, K.w4a16_linear
         xn = rms(h, self.layers[0]["ln1"], self.eps)
@@ -381,14 +384,17 @@ class QUICForCausalLM:
             qkv = lin(L["qkv"], xn)
             # heads split, RoPE applied and K/V written into their slots by one kernel
             q = K.qkv_rope_append(qkv, slot_of, pos, self.rope_cos, self.rope_sin, cache.kv[li, 0], cache.kv[li, 1])
-            attn = torch.empty(T, HEADS * HEAD_DIM, dtype=DTYPE, device=dev)
-            with _sdpa_backends():
-                for i, s in enumerate(slots):
-                    a, b = bounds[i], bounds[i + 1]
-                    k, v = cache.kv[li, 0, s, :, : b - a], cache.kv[li, 1, s, :, : b - a]
-                    o = F.scaled_dot_product_attention(q[None, :, a:b], k[None], v[None],
-                                                       is_causal=True, scale=HEAD_DIM ** -0.5, enable_gqa=True)
-                    attn[a:b] = o[0].transpose(0, 1).reshape(b - a, -1)
+            if self.prefill_backend == "pytorch":  # the reference's default: torch SDPA per sequence
+                attn = torch.empty(T, HEADS * HEAD_DIM, dtype=DTYPE, device=dev)
+                with _sdpa_backends():
+                    for i, s in enumerate(slots):
+                        a, b = bounds[i], bounds[i + 1]
+                        k, v = cache.kv[li, 0, s, :, : b - a], cache.kv[li, 1, s, :, : b - a]
+                        o = F.scaled_dot_product_attention(q[None, :, a:b], k[None], v[None],
+                                                           is_causal=True, scale=HEAD_DIM ** -0.5, enable_gqa=True)
+                        attn[a:b] = o[0].transpose(0, 1).reshape(b - a, -1)
+            else:  # "quic": every sequence in one launch of the causal prefill kernel
+                attn = K.attn_prefill(q, cache.kv[li, 0], cache.kv[li, 1], seq_start, seq_len, seq_slot, max(lens))
             o = lin(L["o"], attn)
             xn, h = rms(o, L["ln2"], self.eps, residual=h)
             gu = lin(L["gate_up"], xn)

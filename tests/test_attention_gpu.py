@@ -116,3 +116,29 @@ def test_decode_sweep_corners(batch, kv_len):
     other = K.flash_attn_decode().forward(q, k, v, SCALE, pads, splits=1 if kv_len <= 8192 else 7)
     assert torch.allclose(out.float(), other.float(), atol=2e-3)
     assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("lens", [[1], [16], [17, 64], [65, 3, 130], [560], [1024, 300]])
+def test_prefill_attention_matches_causal_sdpa(lens):
+    """quic_attn_prefill against causal torch SDPA per sequence (the reference's default
+    prefill attention, kernels/flash_attn_prefill_pytorch.py:10): sequences of ragged
+    lengths in one launch, keys and values read from scattered KV slots."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(sum(lens))
+    rows, n_slots, s_max = sum(lens), 5, 1024
+    slots = [4, 0, 2][: len(lens)]
+    q = torch.randn((HEADS, rows, HEAD_DIM), device="cuda", generator=g).half()
+    kc = torch.randn((n_slots, 2, s_max, HEAD_DIM), device="cuda", generator=g).half()
+    vc = torch.randn((n_slots, 2, s_max, HEAD_DIM), device="cuda", generator=g).half()
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    dev = dict(device="cuda", dtype=torch.int32)
+    out = K.attn_prefill(q, kc, vc, torch.tensor(starts, **dev), torch.tensor(lens, **dev),
+                         torch.tensor(slots, **dev), max(lens), SCALE)
+    assert out.shape == (rows, HEADS * HEAD_DIM) and torch.isfinite(out).all()
+    for a, n, s in zip(starts, lens, slots):
+        want = torch.nn.functional.scaled_dot_product_attention(
+            q[None, :, a:a + n].float(), kc[None, s, :, :n].float(), vc[None, s, :, :n].float(),
+            is_causal=True, scale=SCALE, enable_gqa=True)[0]  # [14, n, 64]
+        got = out[a:a + n].view(n, HEADS, HEAD_DIM).transpose(0, 1).float()
+        assert torch.allclose(got, want, atol=ATOL), (n, (got - want).abs().max().item())
