@@ -389,6 +389,43 @@ def attention_sweep(device: str = "cuda:0", batches=(1, 16, 64, 256), contexts=(
     return out
 
 
+def ttft_sweep(device: str = "cuda:0", grid=((1, 128), (1, 512), (4, 128), (4, 512), (16, 128), (16, 512)),
+               gen_tokens: int = 32) -> list[dict]:
+    """Time to first token and decode rate on the reference's own grid (benchmarks/collect.py:
+    batch x context, CUDA events around the prefill, then around gen_tokens - 1 decode
+    forwards; decode_tps = batch * (gen_tokens - 1) / decode seconds).  Prefill attention by
+    the library's kernel; synthetic weights and random prompts."""
+    net, _ = build_model(device, 24)
+    net.prefill_backend = "quic"
+    out = []
+    for batch, ctx in grid:
+        gen = torch.Generator().manual_seed(batch * 1000 + ctx)
+        prompts = [torch.randint(0, 151936, (ctx,), generator=gen) for _ in range(batch)]
+        slots = list(range(batch))
+        cache = net.new_cache(n_slots=batch, s_max=1024)
+        for _ in range(2):
+            net.prefill(cache, slots, prompts)
+            net.decode_async(cache, slots, gen_tokens - 1)
+        torch.cuda.synchronize()
+        ttft, dec = [], []
+        for _ in range(5):
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            net.prefill(cache, slots, prompts)
+            e[1].record()
+            net.decode_async(cache, slots, gen_tokens - 1)
+            e[2].record()
+            torch.cuda.synchronize()
+            ttft.append(e[0].elapsed_time(e[1]))
+            dec.append(e[1].elapsed_time(e[2]))
+        out.append({"batch": batch, "context": ctx, "ttft_ms": sum(ttft) / len(ttft),
+                    "decode_tps": batch * (gen_tokens - 1) / (sum(dec) / len(dec) / 1e3),
+                    "peak_vram_mb": torch.cuda.max_memory_allocated() / 2 ** 20,
+                    "note": "W4A16, prefill_backend quic; the reference's H100 figures for this grid: "
+                            "TTFT 13.1 / 20.2 / 18.8 / 40.0 / 53.6 / 52.5 ms"})
+    return out
+
+
 def measure_batch64(net, device, world, dist):
     """Decode tokens/s with 64 rows in flight (64 KV slots, 512 cached tokens each, 128 greedy
     steps), state resident, CUDA events, max over ranks."""
@@ -498,6 +535,8 @@ def main() -> None:
                     help="print the W4A16 linear-op sweep (one JSON line per point) and exit")
     ap.add_argument("--attention-sweep", action="store_true",
                     help="print the decode-attention sweep (one JSON line per point) and exit")
+    ap.add_argument("--ttft-sweep", action="store_true",
+                    help="print time-to-first-token and decode rate on the reference's batch x context grid and exit")
     ap.add_argument("--attention-point", default="",
                     help="with --attention-sweep: measure the single point 'batch,context' (profiler captures)")
     args = ap.parse_args()
@@ -507,6 +546,10 @@ def main() -> None:
             b, s_ = (int(v) for v in args.attention_point.split(","))
             kw = {"batches": (b,), "contexts": (s_,)}
         for row in attention_sweep(**kw):
+            print(json.dumps(row))
+        return
+    if args.ttft_sweep:
+        for row in ttft_sweep():
             print(json.dumps(row))
         return
     if args.linear_sweep:
