@@ -143,7 +143,6 @@ cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t*
                             const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
                             int batch, cudaStream_t st);
 cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream_t st);
-cudaError_t launch_swiglu_fused_part(const float* part, int splits, half* act, int batch, cudaStream_t st);
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st);
 int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st,

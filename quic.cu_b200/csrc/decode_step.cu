@@ -298,17 +298,9 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     rc = w4a16_gemm_tc(attn_out, L.o, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_rmsnorm_part(part, sp, h, (const half*)L.ln2, m->eps, xn, h, B, st));
-    if (B <= 32) {
-      // few rows: K split three ways over two CTAs per SM, SwiGLU sums the fp32 partials
-      rc = w4a16_gemm_tc(xn, L.gate_up, nullptr, B, ws, st, &sp);
-      if (rc != QUIC_OK) return rc;
-      QUIC_CUDA(launch_swiglu_fused_part(part, sp, act, B, st));
-    } else {
-      // more rows: the partials would cost more traffic than the split saves
-      rc = w4a16_gemm_tc(xn, L.gate_up, gu, B, ws, st);
-      if (rc != QUIC_OK) return rc;
-      QUIC_CUDA(launch_swiglu_fused(gu, act, B, st));
-    }
+    rc = w4a16_gemm_tc(xn, L.gate_up, gu, B, ws, st);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_swiglu_fused(gu, act, B, st));
     rc = w4a16_gemm_tc(act, L.down, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
     const half* next_ln = (l + 1 < m->n_layers) ? (const half*)m->layers[l + 1].ln1 : (const half*)m->final_norm;

@@ -371,11 +371,6 @@ cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream
   return launch(swiglu_fused_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, gu,
                 (const float*)nullptr, 0, act, batch);
 }
-cudaError_t launch_swiglu_fused_part(const float* part, int splits, half* act, int batch, cudaStream_t st) {
-  const size_t total = (size_t)batch * (kInter / 2);
-  return launch(swiglu_fused_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true,
-                (const half*)nullptr, part, splits, act, batch);
-}
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st) {
   return launch(rmsnorm_kernel, dim3(rows), dim3(224), 0, st, true, x, (const float*)nullptr, 0, residual, w, eps, y,

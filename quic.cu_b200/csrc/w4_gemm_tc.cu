@@ -58,24 +58,30 @@ struct GemmArgs {
   int* counters;   // one per (n tile, m tile), zero on entry, left zero
   int m_total;
   int kblocks_per_split;
-  int stages;  // depth of the operand ring (3 lets two CTAs share an SM, 5-6 is the deep ring)
   int mtl;     // batch-row tiles per CTA (2 from 129 rows up)
 };
 
 constexpr int kMaxGroupsPerCta = 40;            // K / 128 of the widest layer (4864) rounded up
 constexpr int kConsumers = 512;                 // 16 warps dequantise (4 per scheduler) and run the epilogue
 constexpr int kGemmThreads = kConsumers + 64;   // + TMA warp + MMA warp (one lane each)
-constexpr uint32_t kRawBytes = 8 * kTileN * 4;  // packed tile: 8 k-words x 128 rows
+// A pipeline stage covers kSub swizzle atoms of K (2 x 64 = 128 = one quantisation group): the
+// fixed per-stage costs of every role (a barrier round trip, a fence, a commit) are paid
+// half as often as with one atom per stage.
+constexpr int kSub = 2;
+constexpr int kStageK = kBlockK * kSub;
+constexpr uint32_t kRawBytes = 8 * kSub * kTileN * 4;  // packed tile: 16 k-words x 128 rows
 
 // MTL = batch-row tiles per CTA: one dequantised weight tile feeds MTL MMAs groups, so the
 // dequantisation work per flop drops MTL-fold (large M: prefill).
 template <int MT, int MTL = 1>
 struct Smem {
-  static constexpr int kStages = MTL > 1 ? 4 : (MT > 64 ? 5 : 6);
-  static constexpr uint32_t kBTile = ((uint32_t)MT * 128u + 1023u) & ~1023u;  // one x tile, swizzled by TMA
-  static constexpr uint32_t kB = kBTile * MTL;
-  static constexpr uint32_t kA = kTileN * 128;                           // dequantised tile
+  static constexpr uint32_t kBTile = ((uint32_t)MT * 128u + 1023u) & ~1023u;  // one x tile (MT rows x 64 k), swizzled by TMA
+  static constexpr uint32_t kB = kBTile * MTL * kSub;
+  static constexpr uint32_t kASub = kTileN * 128;                        // dequantised 128 rows x 64 k
+  static constexpr uint32_t kA = kASub * kSub;
   static constexpr uint32_t kStage = kRawBytes + kB + kA;
+  // as many stages as fit beside ~16 KB of static shared memory
+  static constexpr int kStages = (int)((210u * 1024u) / kStage) > 4 ? 4 : (int)((210u * 1024u) / kStage);
   static constexpr uint32_t kTotal = kStages * kStage + 1024;            // + alignment slack
 };
 
@@ -110,7 +116,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   const int split = blockIdx.y;
   const int m0 = blockIdx.z * MT * MTL;
   const int N = a.w.n;
-  const int kb_total = a.w.k / kBlockK;
+  const int kb_total = a.w.k / kStageK;
   const int kb0 = split * a.kblocks_per_split;
   const int kb1 = min(kb_total, kb0 + a.kblocks_per_split);
   const int nkb = kb1 - kb0;
@@ -138,7 +144,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // scales and zero points of this CTA's rows for its whole k range
-  const int g_first = (kb0 * kBlockK) / kGroup, g_last = (kb1 * kBlockK - 1) / kGroup;
+  const int g_first = (kb0 * kStageK) / kGroup, g_last = (kb1 * kStageK - 1) / kGroup;
   if (tid < kTileN) {
     const half* scp = reinterpret_cast<const half*>(a.w.sc);
     const int n = n0 + tid;
@@ -167,17 +173,17 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         const uint32_t raw_s = base + it * L::kStage;
         const uint32_t full = smem_u32(&bar_full[it]);
         mbar_expect_tx(full, kRawBytes);
-        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
+        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
       }
       pdl_wait();
       GROLE(2);
       for (int it = 0; it < first; ++it) {
         const uint32_t xfull = smem_u32(&bar_aready[it]);
-        mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL);
+        mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL * kSub);
 #pragma unroll
-        for (int i = 0; i < MTL; ++i)  // rows past the end of x read as zero
-          tma_load_2d(base + it * L::kStage + kRawBytes + i * L::kBTile, &tm_x, (kb0 + it) * kBlockK, m0 + i * MT,
-                      xfull);
+        for (int i = 0; i < MTL * kSub; ++i)  // tile i: rows of row tile i / kSub, k atom i % kSub; rows past the end read as zero
+          tma_load_2d(base + it * L::kStage + kRawBytes + i * L::kBTile, &tm_x,
+                      ((kb0 + it) * kSub + i % kSub) * kBlockK, m0 + (i / kSub) * MT, xfull);
       }
       // (ring position and phase are carried along: the depth is a run-time value)
       for (int it = first, stage = 0, pass = 1; it < nkb; ++it) {
@@ -188,11 +194,11 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
         const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_aready[stage]);
         mbar_expect_tx(full, kRawBytes);
-        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8, full);
-        mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL);
+        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+        mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL * kSub);
 #pragma unroll
-        for (int i = 0; i < MTL; ++i)
-          tma_load_2d(b_s + i * L::kBTile, &tm_x, (kb0 + it) * kBlockK, m0 + i * MT, xfull);
+        for (int i = 0; i < MTL * kSub; ++i)
+          tma_load_2d(b_s + i * L::kBTile, &tm_x, ((kb0 + it) * kSub + i % kSub) * kBlockK, m0 + (i / kSub) * MT, xfull);
         if (++stage == kStages) {
           stage = 0;
           ++pass;
@@ -220,9 +226,12 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         for (int i = 0; i < MTL; ++i) {
           if (i > 0 && m0 + i * MT >= a.m_total) break;  // tile of rows beyond the end
 #pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k)
-            umma_f16(tmem_d + (uint32_t)(i * MT), umma_desc_sw128(a_s + k * 32),
-                     umma_desc_sw128(b_s + i * L::kBTile + k * 32), idesc, (it > 0 || k > 0) ? 1u : 0u);
+          for (int sub = 0; sub < kSub; ++sub)
+#pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k)
+              umma_f16(tmem_d + (uint32_t)(i * MT), umma_desc_sw128(a_s + sub * L::kASub + k * 32),
+                       umma_desc_sw128(b_s + (i * kSub + sub) * L::kBTile + k * 32), idesc,
+                       (it > 0 || sub > 0 || k > 0) ? 1u : 0u);
         }
 #endif
         GMMA(it, 1);
@@ -238,7 +247,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     }
   } else {
     // ---------------- consumers: dequantise ----------------
-    const int row = tid & (kTileN - 1), part = tid >> 7;  // thread -> (row, two of its eight k-words)
+    const int row = tid & (kTileN - 1), part = tid >> 7;  // thread -> (row, four of its sixteen k-words)
     for (int it = 0, stage = 0, pass = 0; it < nkb; ++it) {
       // "full" of this phase also means the MMAs of the stage's previous use are complete
       // (the TMA warp refilled it only after "empty"), so the A tile may be overwritten.
@@ -249,13 +258,13 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       unsigned char* stage_g = gen_base + stage * L::kStage;
       const uint32_t* raw_g = reinterpret_cast<const uint32_t*>(stage_g);
       unsigned char* a_g = stage_g + kRawBytes + L::kB;
-      const int g = ((kb0 + it) * kBlockK) / kGroup - g_first;
+      const int g = ((kb0 + it) * kStageK) / kGroup - g_first;
       const half2 s2 = __half2half2(sc_s[g][row]);
       const half2 zp = zp_to_half2(zp_s[g][row]);
 #ifndef QUIC_TC_NO_DEQUANT  // timing experiments only
 #pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const int j = 2 * part + jj;
+      for (int jj = 0; jj < 2 * kSub; ++jj) {
+        const int j = 2 * kSub * part + jj;  // k-word 0..15 of the stage: atom j / 8, 16-byte chunk j % 8
         half2 d[4];
         dequant8(raw_g[j * kTileN + row], zp, s2, d);  // d[p] = (k = p, k = p + 4)
         const uint32_t u0 = *reinterpret_cast<uint32_t*>(&d[0]), u1 = *reinterpret_cast<uint32_t*>(&d[1]);
@@ -265,7 +274,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         o.y = __byte_perm(u2, u3, 0x5410);  // (k2, k3)
         o.z = __byte_perm(u0, u1, 0x7632);  // (k4, k5)
         o.w = __byte_perm(u2, u3, 0x7632);  // (k6, k7)
-        *reinterpret_cast<uint4*>(a_g + sw128_offset(row, j)) = o;
+        *reinterpret_cast<uint4*>(a_g + (j >> 3) * L::kASub + sw128_offset(row, j & 7)) = o;
       }
 #endif
       fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
@@ -378,7 +387,7 @@ int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
   CUtensorMap tm_w, tm_x;
   // packed weights int32 [K/8, N]: box = 8 k-words x 128 rows; x fp16 [m, K]: box = MT rows x 64 k,
   // written with the 128-byte swizzle the UMMA descriptor expects (rows past m read as zero)
-  int rc = make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, a.w.qw, (uint64_t)a.w.k / 8, (uint64_t)a.w.n, 8,
+  int rc = make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, a.w.qw, (uint64_t)a.w.k / 8, (uint64_t)a.w.n, 8 * kSub,
                     kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != QUIC_OK) return rc;
   rc = make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)a.m_total, (uint64_t)a.w.k, MT, kBlockK,
@@ -397,74 +406,51 @@ int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
     }
   }
   dim3 grid(a.w.n / kTileN, splits, mtiles);
-  if (a.stages == 3) {
-    const size_t smem = 3 * Smem<MT>::kStage + 1024;
-    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, 3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)smem));
-    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, 3, 1>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
-  } else {
-    constexpr int kDeep = Smem<MT>::kStages;
-    const size_t smem = Smem<MT>::kTotal;
-    QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)smem));
-    QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, 1>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
-  }
+  constexpr int kDeep = Smem<MT>::kStages;
+  const size_t smem = Smem<MT>::kTotal;
+  QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+  QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, 1>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
   return QUIC_OK;
 }
 
 }  // namespace
 
-// `fused_consumer`: the caller's next kernel sums the split-K partials itself, so splitting
-// costs no extra launch.
-static void tc_plan(int m, int n, int k, bool fused_consumer, int* mt_out, int* splits_out, int* per_out,
-                    int* stages_out, int* mtl_out = nullptr) {
-  const int kb_total = k / kBlockK;
+static void tc_plan(int m, int n, int k, int* mt_out, int* splits_out, int* per_out, int* mtl_out = nullptr) {
+  const int kb_total = k / kStageK;
   const int tiles = n / kTileN;
   const int mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
   const int mtiles = (m + mt - 1) / mt;
   // two row tiles share one dequantised weight tile once there is more than a wave of CTAs
   const int mtl = (mtiles >= 2 && tiles * mtiles > 148) ? 2 : 1;
   const int ctas = tiles * ((mtiles + mtl - 1) / mtl);
-  int stages = mt > 64 ? 5 : 6;
-  // split K while it at most fills the SMs once, at most 16 ways, at least 2 k blocks per CTA
+  // split K while it at most fills the SMs once, at most 16 ways, at least one stage per CTA
   int splits = 1;
-  while (splits < 16 && ctas * splits * 2 <= 148 && kb_total / (splits * 2) >= 2) splits *= 2;
-  if (splits == 1 && fused_consumer && mt <= 64 && ctas * 2 > 148 && ctas * 2 <= 296) {
-    // More than half the SMs but not two CTAs on each: a 3-deep ring lets two CTAs share an
-    // SM, so K can still be split until every SM holds two.
-    stages = 3;
-    splits = 296 / ctas;
-    if (splits > kb_total / 2) splits = kb_total / 2;
-    if (splits < 1) splits = 1;
-  }
+  while (splits < 16 && ctas * splits * 2 <= 148 && kb_total / (splits * 2) >= 1) splits *= 2;
   const int per = (kb_total + splits - 1) / splits;
   *mt_out = mt;
   *per_out = per;
   *splits_out = (kb_total + per - 1) / per;
-  *stages_out = stages;
   if (mtl_out != nullptr) *mtl_out = mtl;
 }
 
 int64_t w4a16_gemm_tc_workspace(int m, int n, int k) {
-  int mt, splits, per, stages;
-  tc_plan(m, n, k, true, &mt, &splits, &per, &stages);
-  int64_t need = splits > 1 ? (int64_t)splits * m * n * 4 : 0;
-  tc_plan(m, n, k, false, &mt, &splits, &per, &stages);
-  const int64_t plain = splits > 1 ? (int64_t)splits * m * n * 4 : 0;
-  return need > plain ? need : plain;
+  int mt, splits, per;
+  tc_plan(m, n, k, &mt, &splits, &per);
+  return splits > 1 ? (int64_t)splits * m * n * 4 : 0;
 }
 
 // y == nullptr: leave the fp32 partial sums of all `*splits_out` K splits in the workspace
 // (after its 16 KB head) for a fused consumer; no bias is applied.
 int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st,
                   int* splits_out) {
-  QUIC_REQUIRE(w.n % kTileN == 0 && w.k % kBlockK == 0, QUIC_E_SHAPE,
-               "w4a16_linear: the tensor path needs N multiple of 128 and K multiple of 64");
+  QUIC_REQUIRE(w.n % kTileN == 0 && w.k % kStageK == 0, QUIC_E_SHAPE,
+               "w4a16_linear: the tensor path needs N and K multiples of 128");
   QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0), QUIC_E_ARG,
                "w4a16_linear: x and the packed weights must be 16-byte aligned");
   QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16_linear: K beyond 5120 on the tensor path");
-  int mt, splits, per, stages, mtl;
-  tc_plan(m, w.n, w.k, y == nullptr, &mt, &splits, &per, &stages, &mtl);
+  int mt, splits, per, mtl;
+  tc_plan(m, w.n, w.k, &mt, &splits, &per, &mtl);
   QUIC_REQUIRE((splits == 1 && y != nullptr) || workspace != nullptr, QUIC_E_ARG,
                "w4a16_linear: split-K needs a workspace");
   if (splits_out != nullptr) *splits_out = splits;
@@ -476,7 +462,6 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
   QUIC_REQUIRE((m + mt - 1) / mt <= 65535, QUIC_E_LIMIT, "w4a16_linear: too many rows on the tensor path");
   a.m_total = m;
   a.kblocks_per_split = per;
-  a.stages = stages;
   a.mtl = mtl;
   int rc;
   switch (mt) {
