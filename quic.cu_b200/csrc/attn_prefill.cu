@@ -9,7 +9,7 @@
 // contiguous bytes of a key row, probabilities go from the score fragments straight into the
 // A operand of p.V, V pairs are built with byte permutes); the difference to decode is that
 // all 16 rows of the M tile are real queries, so every lane carries two rows (g and g + 8).
-// No shared memory: K/V tiles are re-read through L2 by the warps that need them.
+// No shared memory: K/V tiles are re-read through L1 / L2 by the warps that need them.
 #include "attn_warp.cuh"
 #include "decode_kernels.cuh"
 
