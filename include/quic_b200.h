@@ -286,6 +286,37 @@ typedef struct {
   int32_t ctx_hint;    /* upper bound of pos+1 over the rows for this launch */
 } quic_decode_t;
 
+/* ---- fused prefill --------------------------------------------------------
+ * Every admitted prompt through the whole model in one call: embedding gather,
+ * 24 x (RMSNorm, W4A16 GEMM, quic_qkv_rope_append, quic_attn_prefill, o_proj,
+ * residual + RMSNorm, gate_up, SwiGLU, down, residual + RMSNorm), then the tied
+ * lm_head + argmax on the last token of every sequence; fills the KV slots and
+ * sets tok[slot] = first generated token, pos[slot] = prompt length.  Replaces
+ * the prefill branch of the reference's forward and its splice into the batch
+ * (src/model.py:164-199, 272-303; src/engine.py:187-222).  Rows are the tokens
+ * of all sequences back to back.  All pointers are device pointers. */
+typedef struct {
+  const int32_t *ids;       /* [rows] token ids */
+  const int32_t *row_slot;  /* [rows] KV slot of the row's sequence */
+  const int32_t *row_pos;   /* [rows] position of the row inside its sequence */
+  const int32_t *seq_start; /* [n_seq] first row of the sequence */
+  const int32_t *seq_len;   /* [n_seq] */
+  const int32_t *seq_slot;  /* [n_seq] */
+  int32_t rows;
+  int32_t n_seq;
+  int32_t max_len; /* longest sequence */
+  void *kv;        /* cache as in quic_decode_t */
+  int32_t n_slots;
+  int32_t s_max;
+  int32_t *tok; /* [n_slots] */
+  int32_t *pos; /* [n_slots] */
+  int64_t *first_tokens; /* [n_seq] out */
+  void *logits;          /* optional fp16 [n_seq, vocab] of the last positions */
+  void *scratch;         /* quic_prefill_scratch_bytes() bytes, zeroed once by the caller */
+} quic_prefill_t;
+int64_t quic_prefill_scratch_bytes(int32_t rows, int32_t n_seq, int32_t vocab);
+int quic_prefill(const quic_model_t *m, const quic_prefill_t *p, void *stream);
+
 /* Batches of at least this many rows run the decode step on the tensor-core
  * kernels (tcgen05 GEMM, tensor lm_head); smaller ones on the fused GEMV chain.
  * Default 4 (measured crossover on B200); accepted range 2..9.  Set it before graphs are captured.  No

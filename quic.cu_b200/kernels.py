@@ -92,6 +92,30 @@ class Decode(C.Structure):
     ]
 
 
+class Prefill(C.Structure):
+    """quic_prefill_t"""
+
+    _fields_ = [
+        ("ids", C.c_void_p),
+        ("row_slot", C.c_void_p),
+        ("row_pos", C.c_void_p),
+        ("seq_start", C.c_void_p),
+        ("seq_len", C.c_void_p),
+        ("seq_slot", C.c_void_p),
+        ("rows", C.c_int32),
+        ("n_seq", C.c_int32),
+        ("max_len", C.c_int32),
+        ("kv", C.c_void_p),
+        ("n_slots", C.c_int32),
+        ("s_max", C.c_int32),
+        ("tok", C.c_void_p),
+        ("pos", C.c_void_p),
+        ("first_tokens", C.c_void_p),
+        ("logits", C.c_void_p),
+        ("scratch", C.c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol declared in include/quic_b200.h
 _P, _I32, _I64, _F = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 SIGNATURES = {
@@ -124,6 +148,8 @@ SIGNATURES = {
     "quic_decode_scratch_bytes": (_I64, [_I32, _I32, _I32]),
     "quic_decode_launch_count": (_I32, [C.POINTER(Model), C.POINTER(Decode)]),
     "quic_decode_step": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _P]),
+    "quic_prefill_scratch_bytes": (_I64, [_I32, _I32, _I32]),
+    "quic_prefill": (C.c_int, [C.POINTER(Model), C.POINTER(Prefill), _P]),
     "quic_decode_graph_create": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _I32, _P, C.POINTER(_P)]),
     "quic_graph_launch": (C.c_int, [_P, _P]),
     "quic_graph_run_host": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P, _P, C.c_int32]),

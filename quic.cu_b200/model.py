@@ -365,10 +365,12 @@ class QUICForCausalLM:
             raise RuntimeError("prefill: empty prompt")
         if any(n > cache.s_max or n > self.max_pos for n in lens):
             raise RuntimeError("prefill: prompt longer than the KV slot")
-        ids = torch.cat([p.reshape(-1) for p in prompts]).to(dev, torch.long)
         bounds = [0]
         for n in lens:
             bounds.append(bounds[-1] + n)
+        if self.prefill_backend != "pytorch" and not all_logits:
+            return self._prefill_fused(cache, slots, prompts, lens, bounds)
+        ids = torch.cat([p.reshape(-1) for p in prompts]).to(dev, torch.long)
         # per token: its KV slot and its position (one small host -> device copy each)
         pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev, non_blocking=True)
         slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32),
@@ -413,6 +415,35 @@ class QUICForCausalLM:
         cache.pos[st] = torch.tensor(lens, device=dev, dtype=torch.int32)
         for s, n in zip(slots, lens):
             cache.host_len[s] = n
+        return first, logits
+
+    def _prefill_fused(self, cache: SlotCache, slots: list[int], prompts: list[torch.Tensor], lens: list[int],
+                       bounds: list[int]):
+        """prefill_backend "quic": the whole prefill as ONE library call (quic_prefill): the
+        host builds one int32 table (token ids, slot and position per row, start / length /
+        slot per sequence), copies it once, and reads nothing back."""
+        dev = self.device
+        rows, n_seq = bounds[-1], len(lens)
+        table = torch.empty(3 * rows + 3 * n_seq, dtype=torch.int32)
+        table[:rows] = torch.cat([p.reshape(-1) for p in prompts])
+        table[rows:2 * rows] = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32), torch.tensor(lens))
+        table[2 * rows:3 * rows] = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+        table[3 * rows:] = torch.tensor([bounds[:-1], lens, slots], dtype=torch.int32).reshape(-1)
+        t = table.to(dev, non_blocking=True)
+        need = K.lib().quic_prefill_scratch_bytes(rows, n_seq, self.vocab)
+        scratch = cache.__dict__.get("_prefill_scratch")
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.zeros(int(need * 1.25), dtype=torch.uint8, device=dev)
+            cache._prefill_scratch = scratch
+        first = torch.empty(n_seq, dtype=torch.int64, device=dev)
+        logits = torch.empty(n_seq, self.vocab, dtype=DTYPE, device=dev)
+        base = t.data_ptr()
+        p = K.Prefill(base, base + 4 * rows, base + 8 * rows, base + 12 * rows, base + 12 * rows + 4 * n_seq,
+                      base + 12 * rows + 8 * n_seq, rows, n_seq, max(lens), K.ptr(cache.kv), cache.n_slots,
+                      cache.s_max, K.ptr(cache.tok), K.ptr(cache.pos), K.ptr(first), K.ptr(logits), K.ptr(scratch))
+        K.check(K.lib().quic_prefill(C.byref(self._c_model), C.byref(p), K.stream_ptr()), "prefill")
+        for s_, n in zip(slots, lens):
+            cache.host_len[s_] = n
         return first, logits
 
     # ---- reference-shaped forward ------------------------------------------------------
