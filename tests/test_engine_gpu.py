@@ -20,11 +20,13 @@ def _prefix_ok(got, ref_tokens, ref_logits, near_tie=2e-2):
     assert len(got) == len(ref_tokens)
 
 
-@pytest.mark.parametrize("batching", ["static", "continuous"])
-def test_engine_multirequest_generation(tiny_model, batching):  # reference tests/test_engine.py:20
+@pytest.mark.parametrize("batching,prefill_backend", [("static", "pytorch"), ("continuous", "pytorch"),
+                                                      ("continuous", "quic")])
+def test_engine_multirequest_generation(tiny_model, batching, prefill_backend):  # reference tests/test_engine.py:20
     net, ref, _, _ = tiny_model
     module = SimpleNamespace(load=lambda **options: (net, None))
-    engine = Engine(config=EngineConfig(batching=batching, max_context=128, decode_burst=4),
+    engine = Engine(config=EngineConfig(batching=batching, max_context=128, decode_burst=4,
+                                        prefill_backend=prefill_backend),
                     max_batch_size=4, model_module=module)
     engine.max_tokens = 10
     gen = torch.Generator().manual_seed(3)
@@ -39,6 +41,7 @@ def test_engine_multirequest_generation(tiny_model, batching):  # reference test
         assert len(out) == lim
         _prefix_ok(out, ref_tokens, ref_logits)
     assert engine.run() == []
+    net.prefill_backend = "pytorch"  # the fixture is shared
 
 
 def test_load_from_checkpoint_directory(tmp_path, tiny_model):
