@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(kPfWarps * 32) attn_prefill_kernel(const Prefi
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int head = blockIdx.y, seq = blockIdx.z;
+  pdl_trigger_early();
+  pdl_wait();  // queries and cache rows come from the kernels before this one
   const int len = a.seq_len[seq];
   // the longest key ranges first: CTAs of late query rows are launched before the short ones
   const int r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kPfRows + warp * 16;  // first query position of this warp
@@ -197,11 +199,10 @@ __global__ void __launch_bounds__(kPfWarps * 32) attn_prefill_kernel(const Prefi
 }  // namespace
 }  // namespace quic
 
-using namespace quic;
-
-extern "C" int quic_attn_prefill(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
-                                 const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len,
-                                 int32_t rows, int32_t s_max, float scale, void* out, void* stream) {
+namespace quic {
+int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
+                        const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len, int32_t rows,
+                        int32_t s_max, float scale, void* out, cudaStream_t stream, bool pdl) {
   QUIC_REQUIRE(q && kcache && vcache && seq_start && seq_len && seq_slot && out, QUIC_E_ARG,
                "attn_prefill: null tensor");
   QUIC_REQUIRE(n_seq >= 0 && n_seq <= 65535 && rows >= 0 && max_len >= 0 && s_max >= 1 && max_len <= s_max,
@@ -222,6 +223,14 @@ extern "C" int quic_attn_prefill(const void* q, const void* kcache, const void* 
   a.s_max = s_max;
   a.scale = scale > 0.f ? scale : 0.125f;
   dim3 grid((max_len + kPfRows - 1) / kPfRows, kHeads, n_seq);
-  QUIC_CUDA(launch(attn_prefill_kernel, grid, dim3(kPfWarps * 32), 0, (cudaStream_t)stream, false, a));
+  QUIC_CUDA(launch(attn_prefill_kernel, grid, dim3(kPfWarps * 32), 0, stream, pdl, a));
   return QUIC_OK;
+}
+}  // namespace quic
+
+extern "C" int quic_attn_prefill(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
+                                 const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len,
+                                 int32_t rows, int32_t s_max, float scale, void* out, void* stream) {
+  return quic::attn_prefill_launch(q, kcache, vcache, seq_start, seq_len, seq_slot, n_seq, max_len, rows, s_max,
+                                   scale, out, (cudaStream_t)stream, false);
 }

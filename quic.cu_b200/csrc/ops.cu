@@ -353,6 +353,14 @@ cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t*
                 (const half*)nullptr, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch,
                 (const int32_t*)nullptr, 0);
 }
+cudaError_t launch_qkv_rope_append(const half* qkv, const int32_t* slots, const int32_t* positions, const half* cos_t,
+                                   const half* sin_t, int max_pos, half* q_out, half* kcache, half* vcache, int s_max,
+                                   int rows, cudaStream_t st, bool pdl) {
+  const int total = rows * (kQkvN / 2);
+  return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, pdl, qkv, (const float*)nullptr, 0,
+                (const half*)nullptr, slots, (const int32_t*)nullptr, cos_t, sin_t, max_pos, q_out, kcache, vcache,
+                s_max, rows, positions, 1);
+}
 cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
                                  const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,
                                  half* kcache, half* vcache, int s_max, int batch, cudaStream_t st) {
@@ -440,11 +448,9 @@ extern "C" int quic_qkv_rope_append(const void* qkv, const int32_t* slots, const
   QUIC_REQUIRE(rows >= 0 && rows <= (1 << 20) && s_max >= 1 && max_pos >= 1, QUIC_E_SHAPE,
                "qkv_rope_append: bad row count or cache length");
   if (rows == 0) return QUIC_OK;
-  const int total = rows * (kQkvN / 2);
-  QUIC_CUDA(launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, false,
-                   (const half*)qkv, (const float*)nullptr, 0, (const half*)nullptr, slots, (const int32_t*)nullptr,
-                   (const half*)cos_t, (const half*)sin_t, (int)max_pos, (half*)q_out, (half*)kcache, (half*)vcache,
-                   (int)s_max, (int)rows, positions, 1));
+  QUIC_CUDA(launch_qkv_rope_append((const half*)qkv, slots, positions, (const half*)cos_t, (const half*)sin_t,
+                                   (int)max_pos, (half*)q_out, (half*)kcache, (half*)vcache, (int)s_max, (int)rows,
+                                   (cudaStream_t)stream, false));
   return QUIC_OK;
 }
 

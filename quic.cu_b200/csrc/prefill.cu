@@ -138,27 +138,28 @@ extern "C" int quic_prefill(const quic_model_t* m, const quic_prefill_t* p, void
 
   embed_tokens_kernel<<<rows, 224, 0, st>>>((const half*)m->embed, p->ids, m->vocab, h);
   QUIC_CUDA(cudaGetLastError());
-  int rc = quic_rmsnorm(h, nullptr, m->layers[0].ln1, m->eps, xn, nullptr, rows, stream);
-  if (rc != QUIC_OK) return rc;
+  // From here on the kernels are chained with programmatic dependent launch: each one does
+  // its set-up (and the GEMMs request their weight tiles) while its predecessor drains.
+  QUIC_CUDA(launch_rmsnorm(h, nullptr, (const half*)m->layers[0].ln1, m->eps, xn, nullptr, rows, st));
+  int rc = QUIC_OK;
   for (int l = 0; l < m->n_layers; ++l) {
     const quic_layer_t& L = m->layers[l];
     half* kc = static_cast<half*>(p->kv) + (size_t)(2 * l) * kv_plane;
     half* vc = kc + kv_plane;
     if ((rc = linear_rows(xn, L.qkv, qkv, rows, ws, stream)) != QUIC_OK) return rc;
-    if ((rc = quic_qkv_rope_append(qkv, p->row_slot, p->row_pos, m->rope_cos, m->rope_sin, m->max_pos, q, kc, vc,
-                                   p->s_max, rows, stream)) != QUIC_OK)
-      return rc;
-    if ((rc = quic_attn_prefill(q, kc, vc, p->seq_start, p->seq_len, p->seq_slot, p->n_seq, p->max_len, rows,
-                                p->s_max, 0.125f /* 64^-0.5, src/model.py:129 */, attn, stream)) != QUIC_OK)
+    QUIC_CUDA(launch_qkv_rope_append(qkv, p->row_slot, p->row_pos, (const half*)m->rope_cos, (const half*)m->rope_sin,
+                                     m->max_pos, q, kc, vc, p->s_max, rows, st, true));
+    if ((rc = attn_prefill_launch(q, kc, vc, p->seq_start, p->seq_len, p->seq_slot, p->n_seq, p->max_len, rows,
+                                  p->s_max, 0.125f /* 64^-0.5, src/model.py:129 */, attn, st, true)) != QUIC_OK)
       return rc;
     if ((rc = linear_rows(attn, L.o, tmp, rows, ws, stream)) != QUIC_OK) return rc;
     // h += o ; xn = norm(h)
-    if ((rc = quic_rmsnorm(tmp, h, L.ln2, m->eps, xn, h, rows, stream)) != QUIC_OK) return rc;
+    QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)L.ln2, m->eps, xn, h, rows, st));
     if ((rc = linear_rows(xn, L.gate_up, gu, rows, ws, stream)) != QUIC_OK) return rc;
-    if ((rc = quic_swiglu_fused(gu, act, rows, stream)) != QUIC_OK) return rc;
+    QUIC_CUDA(launch_swiglu_fused(gu, act, rows, st));
     if ((rc = linear_rows(act, L.down, tmp, rows, ws, stream)) != QUIC_OK) return rc;
     const void* next_ln = (l + 1 < m->n_layers) ? m->layers[l + 1].ln1 : m->final_norm;
-    if ((rc = quic_rmsnorm(tmp, h, next_ln, m->eps, xn, h, rows, stream)) != QUIC_OK) return rc;
+    QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)next_ln, m->eps, xn, h, rows, st));
   }
   // xn holds the finally normalised rows: lm_head + argmax on the last one of every sequence
   gather_last_kernel<<<p->n_seq, 224, 0, st>>>(xn, p->seq_start, p->seq_len, xlast);
