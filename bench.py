@@ -493,22 +493,31 @@ def measure_serving(net, device, n_requests, world, dist, rank):
     engine = Engine(config=EngineConfig(batching="continuous", max_context=2048, decode_burst=8,
                                         prefill_backend="quic"),
                     max_batch_size=64, model_module=module)
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    out = serve(engine, mine)
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - t0
-    tokens = sum(len(v) for v in out.values())
-    if dist is not None:
-        t = torch.tensor([seconds, float(tokens)], device=device, dtype=torch.float64)
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        seconds, tokens = float(tmax[0].item()), int(t[1].item())
+    # First pass: the engine captures one CUDA graph per (rows, context bound, burst) it meets
+    # (a one-time cost of a long-lived server); second pass: the same queue on the warm engine.
+    passes = []
+    for _ in range(2):
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = serve(engine, mine)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        tokens = sum(len(v) for v in out.values())
+        if dist is not None:
+            t = torch.tensor([seconds, float(tokens)], device=device, dtype=torch.float64)
+            tmax = t.clone()
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            seconds, tokens = float(tmax[0].item()), int(t[1].item())
+        passes.append((seconds, tokens))
+    seconds, tokens = passes[1]
     return {"value": tokens / seconds, "unit": "generated tokens/s (prefill included in the time)",
             "requests": n_requests, "generated_tokens": tokens, "prompt_tokens": sum(plens), "seconds": seconds,
+            "first_pass_seconds": passes[0][0], "first_pass_value": passes[0][1] / passes[0][0],
+            "note": "value: second pass over the same queue on the same engine (decode graphs captured); "
+                    "first_pass_*: fresh engine, captures included",
             "slots_per_gpu": 64, "replicas": world}
 
 

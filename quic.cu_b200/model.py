@@ -117,11 +117,13 @@ def _sdpa_backends():
     return sdpa_kernel([SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH])
 
 
-def _ctx_bucket(n: int) -> int:
+def _ctx_bucket(n: int, batch: int = 1) -> int:
     """Context bound a captured graph is valid for: multiples of 128 up to 2048 (so the
-    attention grid tracks the real context closely), powers of two beyond."""
+    attention grid tracks the real context closely), powers of two beyond.  From 16 rows the
+    step is 256: half as many graphs to capture, at most two more empty 64-token tiles per row."""
+    step = 128 if batch < 16 else 256
     if n <= 2048:
-        return max(128, (n + 127) // 128 * 128)
+        return max(step, (n + step - 1) // step * step)
     b = 4096
     while b < n:
         b *= 2
@@ -274,7 +276,7 @@ class QUICForCausalLM:
         longest = max(cache.host_len[s] for s in slots)
         if longest + steps > cache.s_max or longest + steps > self.max_pos:
             raise RuntimeError("decode: context would exceed the KV slot length")
-        ctx = min(_ctx_bucket(longest + steps), cache.s_max)
+        ctx = min(_ctx_bucket(longest + steps, len(slots)), cache.s_max)
         g, rows = self._graph(cache, len(slots), ctx, steps, logits)
         want = cache.rows_tensor(slots)
         if cache._rows_loaded.get(len(slots)) is not want:
@@ -326,7 +328,7 @@ class QUICForCausalLM:
                 raise ValueError("decode: feed needs consecutive slots")
             g, first = self._prepare_decode(cache, slots, steps, None)
             longest = max(host_len[s] for s in slots)  # already advanced by `steps`
-            bound = min(_ctx_bucket(longest), cache.s_max, self.max_pos)
+            bound = min(_ctx_bucket(longest, len(slots)), cache.s_max, self.max_pos)
             host = cache.host_out()
             plan = (g, bound, cache.rows_tensor(slots), cache.tok.data_ptr() + 4 * slots[0],
                     cache.out_tokens.data_ptr(), host.data_ptr(), host.numpy())
