@@ -278,7 +278,10 @@ def run_gpu(args) -> None:
         batch64 = measure_batch64(net, device, world, dist)
     serving = None
     if args.serving_requests > 0:
-        serving = measure_serving(net, device, args.serving_requests, world, dist, rank)
+        try:
+            serving = measure_serving(net, device, args.serving_requests, world, dist, rank)
+        except Exception as exc:  # the headline line must not depend on the extra measurement
+            serving = {"error": f"{type(exc).__name__}: {exc}"}
 
     if rank != 0:
         return
@@ -534,9 +537,9 @@ def main() -> None:
     ap.add_argument("--impl", default="quic_b200", choices=["quic_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-batch64", action="store_true", help="skip the extra batch-64 decode measurement")
-    ap.add_argument("--serving-requests", type=int, default=0,
-                    help="also serve this many synthetic requests with continuous batching (64 slots per GPU); "
-                         "the benchmark configuration uses 4096")
+    ap.add_argument("--serving-requests", type=int, default=256,
+                    help="also serve this many synthetic requests with continuous batching (64 slots per GPU, "
+                         "two passes, a few seconds); the benchmark configuration uses 4096; 0 skips it")
     ap.add_argument("--layers", type=int, default=24,
                     help="decoder layers of the synthetic model; values below 24 exist only to keep "
                          "profiler captures small and do not produce a valid benchmark line")
