@@ -37,6 +37,14 @@ def test_host_only_queries():
     assert lib.quic_attn_scratch_bytes(4, 8) > 4 * 14 * 8 * 64 * 4
     assert lib.quic_decode_scratch_bytes(1, 151936, 4) > 0
     assert lib.quic_w4a16_workspace_bytes(1, 896, 4864) >= 896 * 4
+    # fused prefill arena: grows with the rows, holds at least the gate|up activations
+    small, big = lib.quic_prefill_scratch_bytes(128, 1, 151936), lib.quic_prefill_scratch_bytes(4096, 8, 151936)
+    assert 128 * 9728 * 2 < small < big and big > 4096 * 9728 * 2
+    assert lib.quic_prefill_scratch_bytes(0, 1, 151936) == 0
+    # decode split policy: one warp per 64 tokens on the small-batch chain and on the tensor step up to 2048 tokens
+    assert lib.quic_decode_pick_splits(1, 640) == 10
+    assert lib.quic_decode_pick_splits(64, 768) == 12
+    assert 1 <= lib.quic_decode_pick_splits(64, 8192) <= 64
 
 
 def test_struct_sizes_match_the_header():
