@@ -16,8 +16,8 @@
 namespace quic {
 namespace {
 
-// Read-only load that allocates in L1: the four warps of a CTA walk the same K/V tiles at
-// about the same time, so three of four reads of a tile are L1 hits.  (The cache rows were
+// Read-only load that allocates in L1: the warps of a CTA walk the same K/V tiles at
+// about the same time, so repeated reads of a tile are L1 hits.  (The cache rows were
 // written by an earlier kernel; L1 holds nothing stale at kernel start.)
 __device__ __forceinline__ uint4 ldg_l1_u128(const void* p) {
   uint4 v;
@@ -25,7 +25,7 @@ __device__ __forceinline__ uint4 ldg_l1_u128(const void* p) {
   return v;
 }
 
-constexpr int kPfWarps = 4;
+constexpr int kPfWarps = 2;
 constexpr int kPfRows = 16 * kPfWarps;  // query rows per CTA
 constexpr int kGroupHeads = kHeads / kKvHeads;
 
