@@ -308,7 +308,7 @@ def linear_sweep(device: str = "cuda:0", shapes=None, ms=(1, 4, 16, 64, 256), re
     """The single W4A16 linear-op sweep of the benchmark configuration: the model's four
     (K, N) shapes at M in {1, 4, 16, 64, 256}; int4 values and zero points uniform in 0..15,
     scales |N(0, 0.01)| + 1e-3, activations N(0, 1).  Each point is timed as a CUDA graph of
-    ``reps`` launches (device time, no host overhead).  M < 4 runs the dequant GEMV, M >= 4
+    ``reps`` launches (device time, no host overhead).  M = 1 runs the dequant GEMV, M >= 2
     the tcgen05 GEMM."""
     entry.load_package()
     from quic_cu_b200 import kernels as K
@@ -340,7 +340,7 @@ def linear_sweep(device: str = "cuda:0", shapes=None, ms=(1, 4, 16, 64, 256), re
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / (5 * reps)
             nbytes = w.weight_bytes + m * k * 2 + m * n * 2
-            out.append({"layer": name, "k": k, "n": n, "m": m, "kernel": "tcgen05 gemm" if m >= 4 else "gemv",
+            out.append({"layer": name, "k": k, "n": n, "m": m, "kernel": "tcgen05 gemm" if m >= 2 else "gemv",
                         "us": us, "GB/s": nbytes / us / 1e3, "hbm_frac": nbytes / us / 1e3 / peak,
                         "TFLOP/s": 2.0 * m * n * k / us / 1e6, "algorithmic_bytes": nbytes,
                         "note": "weights stay in L2 between the launches of a graph"})

@@ -198,12 +198,12 @@ extern "C" int quic_w4_dequant(const quic_w4_t* w, void* out, void* stream) {
 }
 
 // Rows from which the tcgen05 GEMM beats the dequant GEMV (measured per layer shape: 5-9 us
-// against 10-19 us at 4 rows).
-static constexpr int kTensorMinRows = 4;
+// against 10-19 us at 4 rows; the GEMV runs 2..8 rows on one 8-row instantiation).
+static constexpr int kTensorMinRows = 2;
 
 extern "C" int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  // 16 KB reserved head, then split-K partials: of the tensor path from 4 rows (it stops
+  // 16 KB reserved head, then split-K partials: of the tensor path from 2 rows (it stops
   // splitting once the output tiles fill the SMs, so large m needs none), of the GEMV below.
   if (m >= kTensorMinRows && n % 128 == 0 && k % 64 == 0) {
     const int64_t tc = 16384 + w4a16_gemm_tc_workspace(m, n, k);

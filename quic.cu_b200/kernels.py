@@ -26,7 +26,7 @@ HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, GROUP, QKV_N = 896, 14, 2, 64, 4864, 1
 ROWS_NATURAL, ROWS_ROPE_PAIRS = 0, 1
 # M >= TENSOR_MIN_ROWS runs the tcgen05 GEMM when True; the dequant GEMV in row chunks otherwise.
 TENSOR_PATH = True
-TENSOR_MIN_ROWS = 4
+TENSOR_MIN_ROWS = 2
 
 
 class W4(C.Structure):
