@@ -155,6 +155,7 @@ cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, f
 int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st,
                   int* splits_out = nullptr);
 int64_t w4a16_gemm_tc_workspace(int m, int n, int k);
+int w4a16_gemm_tc_swiglu(const half* x, const quic_w4_t& w, half* act, int m, cudaStream_t st);
 bool lm_head_tc_supported(int batch, int vocab);
 int lm_head_tc_tiles(int vocab);
 int launch_lm_head_tc(const LmHeadArgs& a, cudaStream_t st);

@@ -249,7 +249,6 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
   half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
   half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
   half* xn = reinterpret_cast<half*>(base + ar.xn);
-  half* gu = reinterpret_cast<half*>(base + ar.gu);
   half* act = reinterpret_cast<half*>(base + ar.act16);
   float* ws = reinterpret_cast<float*>(base + ar.tcws);
   const size_t slot_stride = (size_t)kKvHeads * d->s_max * kHeadDim;
@@ -298,9 +297,8 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     rc = w4a16_gemm_tc(attn_out, L.o, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_rmsnorm_part(part, sp, h, (const half*)L.ln2, m->eps, xn, h, B, st));
-    rc = w4a16_gemm_tc(xn, L.gate_up, gu, B, ws, st);
+    rc = w4a16_gemm_tc_swiglu(xn, L.gate_up, act, B, st);  // SwiGLU in the GEMM's epilogue
     if (rc != QUIC_OK) return rc;
-    QUIC_CUDA(launch_swiglu_fused(gu, act, B, st));
     rc = w4a16_gemm_tc(act, L.down, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
     const half* next_ln = (l + 1 < m->n_layers) ? (const half*)m->layers[l + 1].ln1 : (const half*)m->final_norm;
@@ -370,7 +368,7 @@ extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32
 
 extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_decode_t* d) {
   if (!m) return 0;
-  if (d && d->batch >= g_tensor_min_batch) return 9 * m->n_layers + 3;  // plus split-K finish kernels
+  if (d && d->batch >= g_tensor_min_batch) return 8 * m->n_layers + 3;
   return 5 * m->n_layers + 1;
 }
 

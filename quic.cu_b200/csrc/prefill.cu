@@ -46,7 +46,7 @@ PrefillArena carve_prefill(int rows, int n_seq, int vocab) {
   a.attn = off;
   off += align256((int64_t)rows * kHidden * 2);
   a.gu = off;
-  off += align256((int64_t)rows * 2 * kInter * 2);
+  off += align256((int64_t)(rows < 2 ? rows : 1) * 2 * kInter * 2);  // only the one-row fallback materialises gate|up
   a.act = off;
   off += align256((int64_t)rows * kInter * 2);
   a.xlast = off;
@@ -155,8 +155,17 @@ extern "C" int quic_prefill(const quic_model_t* m, const quic_prefill_t* p, void
     if ((rc = linear_rows(attn, L.o, tmp, rows, ws, stream)) != QUIC_OK) return rc;
     // h += o ; xn = norm(h)
     QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)L.ln2, m->eps, xn, h, rows, st));
-    if ((rc = linear_rows(xn, L.gate_up, gu, rows, ws, stream)) != QUIC_OK) return rc;
-    QUIC_CUDA(launch_swiglu_fused(gu, act, rows, st));
+    if (rows >= 2) {  // gate|up GEMM with SwiGLU in its epilogue: the [rows, 9728] intermediate never exists
+      for (int r0 = 0; r0 < rows; r0 += kPrefillChunk) {
+        const int mrows = rows - r0 < kPrefillChunk ? rows - r0 : kPrefillChunk;
+        if ((rc = w4a16_gemm_tc_swiglu(xn + (size_t)r0 * kHidden, L.gate_up, act + (size_t)r0 * kInter, mrows, st)) !=
+            QUIC_OK)
+          return rc;
+      }
+    } else {
+      if ((rc = linear_rows(xn, L.gate_up, gu, rows, ws, stream)) != QUIC_OK) return rc;
+      QUIC_CUDA(launch_swiglu_fused(gu, act, rows, st));
+    }
     if ((rc = linear_rows(act, L.down, tmp, rows, ws, stream)) != QUIC_OK) return rc;
     const void* next_ln = (l + 1 < m->n_layers) ? m->layers[l + 1].ln1 : m->final_norm;
     QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)next_ln, m->eps, xn, h, rows, st));

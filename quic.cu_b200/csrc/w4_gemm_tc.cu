@@ -59,6 +59,10 @@ struct GemmArgs {
   int m_total;
   int kblocks_per_split;
   int mtl;     // batch-row tiles per CTA (2 from 129 rows up)
+  // SwiGLU fused into the epilogue of the gate|up linear: the CTA's 128 weight rows are 64
+  // gate rows and the 64 up rows of the same columns (two 64-row TMA boxes per stage), and y
+  // is the activation [m_total, N / 2] = silu(gate) * up.
+  int fuse_swiglu;
 };
 
 constexpr int kMaxGroupsPerCta = 40;            // K / 128 of the widest layer (4864) rounded up
@@ -145,9 +149,14 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   }
   // scales and zero points of this CTA's rows for its whole k range
   const int g_first = (kb0 * kStageK) / kGroup, g_last = (kb1 * kStageK - 1) / kGroup;
+  // weight row of tile row r
+  const int half_n = N >> 1;
+  auto tile_row_to_n = [&](int r) {
+    return a.fuse_swiglu ? (r < 64 ? (int)blockIdx.x * 64 + r : half_n + (int)blockIdx.x * 64 + (r - 64)) : n0 + r;
+  };
   if (tid < kTileN) {
     const half* scp = reinterpret_cast<const half*>(a.w.sc);
-    const int n = n0 + tid;
+    const int n = tile_row_to_n(tid);
     for (int g = g_first; g <= g_last && g - g_first < kMaxGroupsPerCta; ++g) {
       sc_s[g - g_first][tid] = scp[(size_t)g * N + n];
       zp_s[g - g_first][tid] = (a.w.zp[(size_t)g * (N >> 1) + (n >> 1)] >> (4 * (n & 1))) & 15;
@@ -173,7 +182,12 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         const uint32_t raw_s = base + it * L::kStage;
         const uint32_t full = smem_u32(&bar_full[it]);
         mbar_expect_tx(full, kRawBytes);
-        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+        if (a.fuse_swiglu) {  // two boxes of 64 rows: gate rows, then the up rows of the same columns
+          tma_load_2d(raw_s, &tm_w, (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
+          tma_load_2d(raw_s + kRawBytes / 2, &tm_w, half_n + (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
+        } else {
+          tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+        }
       }
       pdl_wait();
       GROLE(2);
@@ -194,7 +208,12 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
         const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_aready[stage]);
         mbar_expect_tx(full, kRawBytes);
-        tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+        if (a.fuse_swiglu) {
+          tma_load_2d(raw_s, &tm_w, (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
+          tma_load_2d(raw_s + kRawBytes / 2, &tm_w, half_n + (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
+        } else {
+          tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+        }
         mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL * kSub);
 #pragma unroll
         for (int i = 0; i < MTL * kSub; ++i)
@@ -266,7 +285,9 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       for (int jj = 0; jj < 2 * kSub; ++jj) {
         const int j = 2 * kSub * part + jj;  // k-word 0..15 of the stage: atom j / 8, 16-byte chunk j % 8
         half2 d[4];
-        dequant8(raw_g[j * kTileN + row], zp, s2, d);  // d[p] = (k = p, k = p + 4)
+        // packed word j of tile row `row`: one [16][128] box, or two [16][64] boxes
+        const int raw_i = a.fuse_swiglu ? (row >> 6) * (8 * kSub * 64) + j * 64 + (row & 63) : j * kTileN + row;
+        dequant8(raw_g[raw_i], zp, s2, d);  // d[p] = (k = p, k = p + 4)
         const uint32_t u0 = *reinterpret_cast<uint32_t*>(&d[0]), u1 = *reinterpret_cast<uint32_t*>(&d[1]);
         const uint32_t u2 = *reinterpret_cast<uint32_t*>(&d[2]), u3 = *reinterpret_cast<uint32_t*>(&d[3]);
         uint4 o;
@@ -299,7 +320,50 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status, 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
-    if (ok) {
+    if (a.fuse_swiglu) {
+      // TMEM lanes 0-63 hold the gate rows, 64-127 the up rows of the same 64 columns.  The up
+      // warps park their (fp16-rounded) values in shared memory -- the operand ring is free once
+      // the accumulation is complete -- and the gate warps finish silu(gate) * up.  Every one of
+      // the 16 warps reaches the barrier whether or not its waits succeeded.
+      const int quarter = warp & 3, cgroup = warp >> 2;
+      constexpr int kColsPerGroup = MT >= 32 ? MT / 4 : 8;
+      float* ex = reinterpret_cast<float*>(gen_base);  // [MT * MTL columns][64 rows]
+#pragma unroll 1
+      for (int phase = 0; phase < 2; ++phase) {
+        const bool mine = ok && ((phase == 0) == (quarter >= 2));
+        if (mine) {
+#pragma unroll 1
+          for (int i = 0; i < MTL; ++i) {
+            if (m0 + i * MT >= a.m_total) break;
+#pragma unroll 1
+            for (int c = cgroup * kColsPerGroup; c < min(MT, (cgroup + 1) * kColsPerGroup); c += 8) {
+              const int c0 = i * MT + c;
+              if (m0 + c0 >= a.m_total) break;
+              uint32_t r[8];
+              const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+              asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                           : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                             "=r"(r[7])
+                           : "r"(taddr));
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+              const int row = (quarter & 1) * 32 + lane;  // 0..63 inside the gate (or up) half
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int m = m0 + c0 + j;
+                const float v = __half2float(__float2half_rn(__uint_as_float(r[j])));  // the linear's fp16 output
+                if (phase == 0) {
+                  ex[(c0 + j) * 64 + row] = v;
+                } else if (m < a.m_total) {
+                  const float u = ex[(c0 + j) * 64 + row];
+                  a.y[(size_t)m * half_n + (size_t)blockIdx.x * 64 + row] = __float2half_rn(silu_mul(v, u));
+                }
+              }
+            }
+          }
+        }
+        if (phase == 0) asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+      }
+    } else if (ok) {
       // TMEM lane = tile row; a warp may read lanes 32*(warp % 4)..+31, so the four warps that
       // share a lane quarter split the batch columns between them
       const int quarter = warp & 3, cgroup = warp >> 2;
@@ -387,8 +451,9 @@ int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
   CUtensorMap tm_w, tm_x;
   // packed weights int32 [K/8, N]: box = 8 k-words x 128 rows; x fp16 [m, K]: box = MT rows x 64 k,
   // written with the 128-byte swizzle the UMMA descriptor expects (rows past m read as zero)
+  // (fused SwiGLU: two boxes of 64 rows per stage, gate rows and up rows)
   int rc = make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, a.w.qw, (uint64_t)a.w.k / 8, (uint64_t)a.w.n, 8 * kSub,
-                    kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
+                    a.fuse_swiglu ? kTileN / 2 : kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != QUIC_OK) return rc;
   rc = make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)a.m_total, (uint64_t)a.w.k, MT, kBlockK,
                 CU_TENSOR_MAP_SWIZZLE_128B);
@@ -477,6 +542,33 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
                      (const float*)a.part, (const half*)w.bias, y, m, w.n, splits));
   }
   return QUIC_OK;
+}
+
+// act[m, N/2] = silu(x . Wgate^T) * (x . Wup^T) for the fused gate|up weight (N = 2 x 4864, gate
+// rows first): one GEMM whose epilogue applies SwiGLU, so the [m, N] intermediate never
+// exists.  K is never split here (the activation is not linear in the partial sums).
+int w4a16_gemm_tc_swiglu(const half* x, const quic_w4_t& w, half* act, int m, cudaStream_t st) {
+  QUIC_REQUIRE(w.n % kTileN == 0 && (w.n / 2) % (kTileN / 2) == 0 && w.k % kStageK == 0, QUIC_E_SHAPE,
+               "w4a16 gate_up: N must be a multiple of 128 and K of 128");
+  QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0) && act != nullptr, QUIC_E_ARG,
+               "w4a16 gate_up: x and the packed weights must be 16-byte aligned");
+  QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16 gate_up: K beyond 5120 on the tensor path");
+  int mt, splits, per, mtl;
+  tc_plan(m, w.n, w.k, &mt, &splits, &per, &mtl);
+  GemmArgs a = {};
+  a.w = w;
+  a.y = act;
+  a.m_total = m;
+  a.kblocks_per_split = w.k / kStageK;
+  a.mtl = mtl;
+  a.fuse_swiglu = 1;
+  QUIC_REQUIRE((m + mt - 1) / mt <= 65535, QUIC_E_LIMIT, "w4a16 gate_up: too many rows on the tensor path");
+  switch (mt) {
+    case 16: return run<16>(x, a, 1, st);
+    case 32: return run<32>(x, a, 1, st);
+    case 64: return run<64>(x, a, 1, st);
+    default: return run<128>(x, a, 1, st);
+  }
 }
 
 }  // namespace quic
