@@ -95,9 +95,9 @@ int quic_w4_dequant(const quic_w4_t *w, void *out_f16, void *stream);
 
 /* y[M,N] = x[M,K] · dequant(W)^T + bias, fp16 in/out, fp32 accumulate.
  * Replaces marlin.forward (kernels/cuda/marlin.cu:4769 marlin_gemm, reached
- * through src/quant/marlin.py:190 marlin_linear).  M < 16 runs the dequant
- * GEMV; M >= 16 runs the tcgen05 GEMM when `use_tensor` is non-zero and the
- * GEMV in row chunks otherwise.  `workspace` (>= quic_w4a16_workspace_bytes)
+ * through src/quant/marlin.py:190 marlin_linear).  One row runs the dequant
+ * GEMV; two rows and more run the tcgen05 GEMM when `use_tensor` is non-zero
+ * (N and K multiples of 128) and the GEMV in row chunks otherwise.  `workspace` (>= quic_w4a16_workspace_bytes)
  * holds split-K partials; its first 16 KB (arrival counters of the tensor
  * path) must be zero before the first call and are left zero. */
 int quic_w4a16_linear(const void *x_f16, const quic_w4_t *w, void *y_f16,

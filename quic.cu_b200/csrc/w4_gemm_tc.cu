@@ -1,4 +1,4 @@
-// W4A16 GEMM for batch >= 16 on the 5th-generation tensor cores (tcgen05 + TMEM).
+// W4A16 GEMM (two rows and more) on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
 //   y[m, n] = sum_k x[m, k] * dequant(W)[n, k] (+ bias[n])      fp16 in/out, fp32 accumulate
 //
@@ -9,18 +9,18 @@
 // accumulator of a 128 x MT tile is MT fp32 columns of tensor memory and a thread of the
 // epilogue owns one output column n.
 //
-// Per 64-wide k block a CTA
-//   1. loads 8 packed int32 words per weight row (thread t <-> row t, coalesced over rows),
-//      dequantises them in registers exactly like the GEMV path ((q - zp) * s rounded once
-//      to fp16) and writes the row's 128 bytes into the A stage in the K-major 128-byte
-//      swizzled layout the UMMA shared-memory descriptor expects;
-//   2. copies the x tile (MT rows x 128 bytes) into the B stage in the same layout;
-//   3. makes the writes visible to the async proxy, and one thread issues four
-//      tcgen05.mma (K = 16 each) that accumulate into TMEM, then commits them to the
-//      stage's mbarrier so the stage can be refilled once the tensor core has read it.
-// Three stages keep global loads, dequantisation and MMA overlapped.  Split-K CTAs write
-// fp32 partials that a small kernel sums.  Every mbarrier wait is bounded: on a timeout
-// the kernel records an error code, still frees its tensor memory and returns.
+// Per pipeline stage (128 of K = one quantisation group = two 128-byte swizzle atoms)
+//   1. the TMA warp brings the packed tile (16 int32 words per weight row) and the x tiles
+//      (MT rows x 128 bytes per atom, swizzled by TMA) into shared memory;
+//   2. 16 warps dequantise the packed words exactly like the GEMV path ((q - zp) * s rounded
+//      once to fp16) and write each row's bytes into the A tiles in the K-major 128-byte
+//      swizzled layout the UMMA shared-memory descriptor expects, make the writes visible
+//      to the async proxy and arrive on the stage's barrier;
+//   3. one thread issues the stage's tcgen05.mma (K = 16 each) that accumulate into TMEM and,
+//      where the stage will be refilled, commits them to the stage's "empty" mbarrier.
+// Split-K CTAs write fp32 partials that the consumer kernel (or a small finish kernel) sums;
+// the gate|up form applies SwiGLU in its epilogue.  Every mbarrier wait is bounded: on a
+// timeout the kernel records an error code, still frees its tensor memory and returns.
 #include "tc_common.cuh"
 
 namespace quic {
