@@ -4,18 +4,18 @@
 // Replaces fad_decode_kernel + fad_combine_kernel of the reference
 // (kernels/cuda/flash_attn_decode.cu:12,104).  Same mathematics — fp32 online
 // softmax over the tokens [start_b, end_b) of each row, rows without tokens
-// give zeros (:118-121) — with a different mapping:
-//   * a CTA owns one (split, kv head, batch row); each of its 8 warps walks
-//     tiles of 32 consecutive tokens, ONE TOKEN PER LANE for q·k (no per-token
-//     shuffle chain), all 7 query heads of the group at once;
-//   * K and V tiles are fetched with 16-byte loads issued together, before any
-//     arithmetic, so both are in flight at the same time;
-//   * p·V is done with lanes re-mapped to (token mod 4, 8 dims), probabilities
-//     passing through a per-warp shared-memory tile;
-//   * warps are merged through shared memory, splits through global fp32
-//     partials; the CTA that arrives last at a per-(row, kv head) counter does
-//     the final merge and re-arms the counter, so no second kernel and no
-//     spin-wait is needed.
+// give zeros (:118-121) — with three kernels for three regimes:
+//   * attn_decode_warp_kernel (latency: the decode chain up to 2048 tokens, small problems):
+//     ONE WARP per 64 tokens of a (row, kv head), both products on mma.sync.m16n8k16, no
+//     shared memory; inside the chain its cache tile is requested before the dependency wait;
+//   * attn_decode_mma_kernel (throughput): 4 or 8 warps per CTA walking 32-token tiles with an
+//     online softmax, the same mma.sync fragment mappings (attn_warp.cuh), warps merged
+//     through shared memory;
+//   * attn_decode_kernel (scalar, kept for small stand-alone problems): one token per lane
+//     for q.k, all 7 query heads of the group at once.
+// Splits go through global fp32 partials; they are merged by the consumer (the o_proj kernel
+// of the small-batch chain) or by the CTA that arrives last at a per-(row, kv head) counter,
+// which re-arms the counter, so no second kernel and no spin-wait is needed.
 #include "decode_kernels.cuh"
 #include "attn_warp.cuh"
 

@@ -1,4 +1,4 @@
-// Tied fp16 lm_head for batches above 8 rows on the tcgen05 tensor cores, fused with the
+// Tied fp16 lm_head of the tensor-core decode step (2..128 rows) on tcgen05, fused with the
 // greedy argmax.
 //
 // Replaces cuBLAS lm_head + torch.argmax of the reference (src/model.py:301 ->
@@ -9,9 +9,9 @@
 // layout and the main loop is only: wait for a stage, issue four MMAs, release the stage.
 // The epilogue rounds the logits to fp16 (the reference's logits are an fp16 tensor),
 // optionally stores them, reduces (value, index) over the tile's 128 rows with ties going
-// to the lower index (kernels/cuda/sampler.cu:38-40) and writes one candidate per batch row
-// and tile; the CTA that arrives last at a counter reduces the candidates of all tiles,
-// publishes the tokens and advances the slot state.
+// to the lower index (kernels/cuda/sampler.cu:38-40) and folds the tile's candidate of every
+// batch row into one 64-bit atomic maximum per row; the CTA that arrives last at a counter
+// decodes the maxima, publishes the tokens, advances the slot state and re-arms the maxima.
 #include "tc_common.cuh"
 
 namespace quic {
