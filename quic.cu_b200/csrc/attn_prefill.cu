@@ -3,8 +3,9 @@
 // from the slots that kernel has just filled, and the output is written token-major
 // [rows, 896], which is the layout the o_proj GEMM consumes.
 //
-// Flash-attention-2 style on mma.sync.m16n8k16: a warp owns 16 consecutive query rows of
-// one head and walks the keys 32 at a time up to its causal bound with an online softmax.
+// Flash-attention-2 style on mma.sync.m16n8k16: a CTA owns 16 consecutive query rows of one
+// head; its four warps walk alternate tiles of 32 keys up to the causal bound, each with an
+// online softmax, and their states are merged through shared memory at the end.
 // The fragment mappings are those of attn_warp.cuh (K fragments are the lane's own 32
 // contiguous bytes of a key row, probabilities go from the score fragments straight into the
 // A operand of p.V, V pairs are built with byte permutes); the difference to decode is that
@@ -25,8 +26,14 @@ __device__ __forceinline__ uint4 ldg_l1_u128(const void* p) {
   return v;
 }
 
-constexpr int kPfWarps = 2;
-constexpr int kPfRows = 16 * kPfWarps;  // query rows per CTA
+// Two forms.  kSplitKeys: the 4 warps of a CTA share 16 query rows and take alternate key
+// tiles (the walk over a row's keys is a serial chain per warp -- load, q.K, softmax, p.V per
+// tile -- and four warps cut it to a quarter; their states are merged through shared memory):
+// for launches with few rows, which are bound by that chain (one sequence of 512 tokens: 20 ->
+// 10 us).  Otherwise 2 warps per CTA own 16 query rows each and share their K/V tiles through
+// L1: for launches with many rows, which are bound by cache traffic (16 x 512: 72 us against 85).
+constexpr int kPfSplitWarps = 4;
+constexpr int kPfRowWarps = 2;
 constexpr int kGroupHeads = kHeads / kKvHeads;
 
 struct PrefillAttnArgs {
@@ -42,7 +49,11 @@ struct PrefillAttnArgs {
   float scale;
 };
 
-__global__ void __launch_bounds__(kPfWarps * 32) attn_prefill_kernel(const PrefillAttnArgs a) {
+template <bool kSplitKeys>
+__global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 32)
+    attn_prefill_kernel(const PrefillAttnArgs a) {
+  constexpr int kPfWarps = kSplitKeys ? kPfSplitWarps : kPfRowWarps;
+  constexpr int kPfRows = kSplitKeys ? 16 : 16 * kPfRowWarps;  // query rows per CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int head = blockIdx.y, seq = blockIdx.z;
@@ -50,7 +61,7 @@ __global__ void __launch_bounds__(kPfWarps * 32) attn_prefill_kernel(const Prefi
   pdl_wait();  // queries and cache rows come from the kernels before this one
   const int len = a.seq_len[seq];
   // the longest key ranges first: CTAs of late query rows are launched before the short ones
-  const int r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kPfRows + warp * 16;  // first query position of this warp
+  const int r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kPfRows + (kSplitKeys ? 0 : warp * 16);  // first query row of the warp
   if (r0 >= len) return;
   const int start = a.seq_start[seq];
   const int slot = a.seq_slot[seq];
@@ -82,7 +93,9 @@ __global__ void __launch_bounds__(kPfWarps * 32) attn_prefill_kernel(const Prefi
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
   const int t_stop = min(r0 + 16, len);  // keys 0 .. t_stop - 1 are visible to some row of the warp
-  for (int t0 = 0; t0 < t_stop; t0 += 32) {
+  // Warp w takes the key tiles w, w + 4, ...: the walk over a row's keys is a serial chain per
+  // warp (load, q.K, softmax, p.V per tile), and four warps cut it to a quarter.
+  for (int t0 = kSplitKeys ? 32 * warp : 0; t0 < t_stop; t0 += kSplitKeys ? 32 * kPfWarps : 32) {
     // ---- loads: K rows t0 + 8nb + g, bytes [32c, 32c+32); V rows t0 + 16j + 2c + {0,1,8,9}, dims 8g..8g+7
     uint4 kr[4][2], vr[2][4];
 #pragma unroll
@@ -172,25 +185,75 @@ __global__ void __launch_bounds__(kPfWarps * 32) attn_prefill_kernel(const Prefi
     }
   }
 
-  // ---- C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j; rows g (o[j][0..1]) and g + 8 (o[j][2..3])
+  // ---- (split keys) merge the warps' partial softmax states through shared memory, warp 0 finishes
+  constexpr int kSm = kSplitKeys ? kPfSplitWarps : 1;
+  __shared__ float sm_m[kSm][16], sm_l[kSm][16];
+  __shared__ float sm_o[kSm][32][32 + 1];  // [warp][value index][lane], padded
+  const int sw = kSplitKeys ? warp : 0;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     float l = l_run[r];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    const int row = r0 + g + 8 * r;
+    l_run[r] = l;
+    if (kSplitKeys && c == 0) {
+      sm_m[sw][g + 8 * r] = m_run[r];
+      sm_l[sw][g + 8 * r] = l;
+    }
+  }
+  if (kSplitKeys) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sm_o[sw][4 * j + e][lane] = o[j][e];
+    __syncthreads();
+    if (warp != 0) return;
+  }
+  // C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j; rows g (o[j][0..1]) and g + 8 (o[j][2..3])
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int rr = g + 8 * r;
+    float wgt[kSm], l = 0.f;
+    if (kSplitKeys) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kSm; ++w) mx = fmaxf(mx, sm_m[w][rr]);
+#pragma unroll
+      for (int w = 0; w < kSm; ++w) {
+        wgt[w] = (sm_m[w][rr] == -INFINITY) ? 0.f : __expf(sm_m[w][rr] - mx);
+        l += wgt[w] * sm_l[w][rr];
+      }
+    } else {
+      wgt[0] = 1.f;
+      l = l_run[r];
+    }
+    const int row = r0 + rr;
     if (row >= len) continue;
     const float inv = l > 0.f ? 1.f / l : 0.f;
+    float v[8][2];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float acc = 0.f;
+        if (kSplitKeys) {
+#pragma unroll
+          for (int w = 0; w < kSm; ++w) acc += wgt[w] * sm_o[w][4 * j + 2 * r + e][lane];
+        } else {
+          acc = o[j][2 * r + e];
+        }
+        v[j][e] = acc * inv;
+      }
     half* op = a.out + (size_t)(start + row) * kHidden + head * kHeadDim + 16 * c;
     uint4 lo, hi;
-    lo.x = pack_half2(o[0][2 * r] * inv, o[1][2 * r] * inv);
-    lo.y = pack_half2(o[2][2 * r] * inv, o[3][2 * r] * inv);
-    lo.z = pack_half2(o[4][2 * r] * inv, o[5][2 * r] * inv);
-    lo.w = pack_half2(o[6][2 * r] * inv, o[7][2 * r] * inv);
-    hi.x = pack_half2(o[0][2 * r + 1] * inv, o[1][2 * r + 1] * inv);
-    hi.y = pack_half2(o[2][2 * r + 1] * inv, o[3][2 * r + 1] * inv);
-    hi.z = pack_half2(o[4][2 * r + 1] * inv, o[5][2 * r + 1] * inv);
-    hi.w = pack_half2(o[6][2 * r + 1] * inv, o[7][2 * r + 1] * inv);
+    lo.x = pack_half2(v[0][0], v[1][0]);
+    lo.y = pack_half2(v[2][0], v[3][0]);
+    lo.z = pack_half2(v[4][0], v[5][0]);
+    lo.w = pack_half2(v[6][0], v[7][0]);
+    hi.x = pack_half2(v[0][1], v[1][1]);
+    hi.y = pack_half2(v[2][1], v[3][1]);
+    hi.z = pack_half2(v[4][1], v[5][1]);
+    hi.w = pack_half2(v[6][1], v[7][1]);
     *reinterpret_cast<uint4*>(op) = lo;
     *reinterpret_cast<uint4*>(op + 8) = hi;
   }
@@ -222,8 +285,14 @@ int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, c
   a.rows = rows;
   a.s_max = s_max;
   a.scale = scale > 0.f ? scale : 0.125f;
-  dim3 grid((max_len + kPfRows - 1) / kPfRows, kHeads, n_seq);
-  QUIC_CUDA(launch(attn_prefill_kernel, grid, dim3(kPfWarps * 32), 0, stream, pdl, a));
+  if (n_seq == 1 || rows <= 1024) {  // one sequence or few rows: bound by the per-row key walk
+    dim3 grid((max_len + 15) / 16, kHeads, n_seq);
+    QUIC_CUDA(launch(attn_prefill_kernel<true>, grid, dim3(kPfSplitWarps * 32), 0, stream, pdl, a));
+  } else {
+    constexpr int kRows = 16 * kPfRowWarps;
+    dim3 grid((max_len + kRows - 1) / kRows, kHeads, n_seq);
+    QUIC_CUDA(launch(attn_prefill_kernel<false>, grid, dim3(kPfRowWarps * 32), 0, stream, pdl, a));
+  }
   return QUIC_OK;
 }
 }  // namespace quic

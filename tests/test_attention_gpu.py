@@ -118,7 +118,7 @@ def test_decode_sweep_corners(batch, kv_len):
     assert torch.isfinite(out).all()
 
 
-@pytest.mark.parametrize("lens", [[1], [16], [17, 64], [65, 3, 130], [560], [1024, 300]])
+@pytest.mark.parametrize("lens", [[1], [16], [17, 64], [65, 3, 130], [560], [1024, 300], [1500, 700, 33]])
 def test_prefill_attention_matches_causal_sdpa(lens):
     """quic_attn_prefill against causal torch SDPA per sequence (the reference's default
     prefill attention, kernels/flash_attn_prefill_pytorch.py:10): sequences of ragged
@@ -126,7 +126,7 @@ def test_prefill_attention_matches_causal_sdpa(lens):
     from quic_cu_b200 import kernels as K
 
     g = torch.Generator(device="cuda").manual_seed(sum(lens))
-    rows, n_slots, s_max = sum(lens), 5, 1024
+    rows, n_slots, s_max = sum(lens), 5, 1536  # one sequence or up to 1024 rows: warps split the keys; beyond: rows
     slots = [4, 0, 2][: len(lens)]
     q = torch.randn((HEADS, rows, HEAD_DIM), device="cuda", generator=g).half()
     kc = torch.randn((n_slots, 2, s_max, HEAD_DIM), device="cuda", generator=g).half()
