@@ -405,7 +405,7 @@ def ttft_sweep(device: str = "cuda:0", grid=((1, 128), (1, 512), (4, 128), (4, 5
         gen = torch.Generator().manual_seed(batch * 1000 + ctx)
         prompts = [torch.randint(0, 151936, (ctx,), generator=gen) for _ in range(batch)]
         slots = list(range(batch))
-        cache = net.new_cache(n_slots=batch, s_max=1024)
+        cache = net.new_cache(n_slots=batch, s_max=max(1024, (ctx + gen_tokens + 63) // 64 * 64))
         for _ in range(2):
             net.prefill(cache, slots, prompts)
             net.decode_async(cache, slots, gen_tokens - 1)
@@ -427,6 +427,55 @@ def ttft_sweep(device: str = "cuda:0", grid=((1, 128), (1, 512), (4, 128), (4, 5
                     "note": "W4A16, prefill_backend quic; the reference's H100 figures for this grid: "
                             "TTFT 13.1 / 20.2 / 18.8 / 40.0 / 53.6 / 52.5 ms"})
     return out
+
+
+def engine_batching(net, policy: str, max_batch_size: int = 4, num_requests: int = 8, max_tokens: int = 32,
+                    prompt_len: int = 40) -> dict:
+    """The reference's batching benchmark (benchmarks/collect.py:121-178): ``num_requests`` short
+    prompts through ``Engine.run`` under one admission policy, wall clock around the run.  Prompts
+    are seeded random token ids of the length its chat-templated sentences have."""
+    from types import SimpleNamespace
+
+    from quic_cu_b200.config import EngineConfig
+    from quic_cu_b200.engine import Engine
+
+    module = SimpleNamespace(load=lambda **options: (net, None))
+    engine = Engine(config=EngineConfig(batching=policy, max_context=1024, prefill_backend="quic"),
+                    max_batch_size=max_batch_size, model_module=module)
+    engine.max_tokens = max_tokens
+    gen = torch.Generator().manual_seed(8)
+    for _ in range(num_requests):
+        engine.add_request_ids(torch.randint(0, 151936, (prompt_len,), generator=gen))
+    torch.cuda.reset_peak_memory_stats()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outputs = engine.run()
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    total = sum(len(o) for o in outputs)
+    return {"policy": policy, "max_batch_size": max_batch_size, "num_requests": len(outputs), "total_tokens": total,
+            "elapsed_s": elapsed, "throughput_tps": total / elapsed if elapsed > 0 else 0.0,
+            "peak_vram_mb": torch.cuda.max_memory_allocated() / 2 ** 20}
+
+
+def collect(output_dir: str, device: str = "cuda:0") -> dict:
+    """Writes ``benchmark_results.json`` and ``REPORT.md`` in the reference's schema
+    (benchmarks/collect.py:181-247, benchmarks/report.py): the ``quic_quant`` path on the
+    reference's default grid (batch 1, 4, 16 x context 128, 512, 1024, 2048, 32 generated
+    tokens) and both admission policies of the engine."""
+    from quic_cu_b200 import report
+
+    grid = tuple((b, c) for b in (1, 4, 16) for c in (128, 512, 1024, 2048))
+    rows = ttft_sweep(device, grid)
+    net, _ = build_model(device, 24)
+    batching = {}
+    for policy in ("static", "continuous"):
+        engine_batching(net, policy)  # untimed pass: CUDA graph captures of a fresh engine
+        batching[policy] = engine_batching(net, policy)
+    data = report.collect_results({"quic_quant": rows}, batching)
+    json_path = report.write_results(data, output_dir)
+    report.generate_markdown_report(json_path, os.path.join(output_dir, "REPORT.md"))
+    return data
 
 
 def measure_batch64(net, device, world, dist):
@@ -549,6 +598,8 @@ def main() -> None:
                     help="print the decode-attention sweep (one JSON line per point) and exit")
     ap.add_argument("--ttft-sweep", action="store_true",
                     help="print time-to-first-token and decode rate on the reference's batch x context grid and exit")
+    ap.add_argument("--collect", default="", metavar="DIR",
+                    help="write benchmark_results.json and REPORT.md in the reference collector's schema to DIR")
     ap.add_argument("--attention-point", default="",
                     help="with --attention-sweep: measure the single point 'batch,context' (profiler captures)")
     args = ap.parse_args()
@@ -559,6 +610,9 @@ def main() -> None:
             kw = {"batches": (b,), "contexts": (s_,)}
         for row in attention_sweep(**kw):
             print(json.dumps(row))
+        return
+    if args.collect:
+        print(json.dumps(collect(args.collect)))
         return
     if args.ttft_sweep:
         for row in ttft_sweep():
