@@ -463,6 +463,7 @@ def collect(output_dir: str, device: str = "cuda:0") -> dict:
     (benchmarks/collect.py:181-247, benchmarks/report.py): the ``quic_quant`` path on the
     reference's default grid (batch 1, 4, 16 x context 128, 512, 1024, 2048, 32 generated
     tokens) and both admission policies of the engine."""
+    entry.load_package()
     from quic_cu_b200 import report
 
     grid = tuple((b, c) for b in (1, 4, 16) for c in (128, 512, 1024, 2048))

@@ -11,8 +11,12 @@ __host__ __device__ __forceinline__ int down_group_begin(int ks) {
   return ks <= 3 ? ks * 8 : 24 + (ks - 3) * 7;
 }
 constexpr int kMaxM = 8;  // batch rows per CTA pass
-// Up to this many attention splits are merged by the o_proj kernel itself.
+// The o_proj kernel merges the attention splits itself: this many per pass of loads, up to
+// kMaxConsumerSplitsTotal in all.  kWarpMaxSplits: the single-warp attention kernel covers a
+// context of up to this many 64-token tiles (2048 tokens).
 constexpr int kMaxConsumerSplits = 16;
+constexpr int kMaxConsumerSplitsTotal = 64;
+constexpr int kWarpMaxSplits = 32;
 
 struct RowState {
   const int32_t* rows;  // [batch] slot per row

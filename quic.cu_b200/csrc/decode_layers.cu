@@ -346,31 +346,40 @@ __global__ void __launch_bounds__(224) oproj_kernel(const OProjArgs a) {
         if (a.splits > 0) {
           const int qh = (4 * t) >> 6, d = (4 * t) & 63;
           const size_t row = ((size_t)b * kHeads + qh) * a.splits;
-          float ms[kMaxConsumerSplits], ls[kMaxConsumerSplits];
-          float4 os[kMaxConsumerSplits];
+          // kMaxConsumerSplits splits per pass, every load of a pass in flight together; a
+          // second pass (17..32 splits) folds into the running maximum / sums
+          float mx = -INFINITY, den = 0.f;
+          float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int base = 0; base < a.splits; base += kMaxConsumerSplits) {
+            float ms[kMaxConsumerSplits], ls[kMaxConsumerSplits];
+            float4 os[kMaxConsumerSplits];
 #pragma unroll
-          for (int s = 0; s < kMaxConsumerSplits; ++s) {  // every load in flight together
-            ms[s] = -INFINITY;
-            ls[s] = 0.f;
-            os[s] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (s < a.splits) {
-              ms[s] = __ldcg(a.m_part + row + s);
-              ls[s] = __ldcg(a.l_part + row + s);
-              os[s] = __ldcg(reinterpret_cast<const float4*>(a.o_part + (row + s) * kHeadDim + d));
+            for (int s = 0; s < kMaxConsumerSplits; ++s) {
+              ms[s] = -INFINITY;
+              ls[s] = 0.f;
+              os[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (base + s < a.splits) {
+                ms[s] = __ldcg(a.m_part + row + base + s);
+                ls[s] = __ldcg(a.l_part + row + base + s);
+                os[s] = __ldcg(reinterpret_cast<const float4*>(a.o_part + (row + base + s) * kHeadDim + d));
+              }
             }
-          }
-          float mx = -INFINITY;
+            float mx_new = mx;
 #pragma unroll
-          for (int s = 0; s < kMaxConsumerSplits; ++s) mx = fmaxf(mx, ms[s]);
-          if (mx != -INFINITY) {
-            float den = 0.f;
-            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < kMaxConsumerSplits; ++s) mx_new = fmaxf(mx_new, ms[s]);
+            if (mx_new == -INFINITY) continue;
+            const float keep = (mx == -INFINITY) ? 0.f : __expf(mx - mx_new);
+            den *= keep;
+            num.x *= keep; num.y *= keep; num.z *= keep; num.w *= keep;
+            mx = mx_new;
 #pragma unroll
             for (int s = 0; s < kMaxConsumerSplits; ++s) {
               const float e = (ms[s] == -INFINITY) ? 0.f : __expf(ms[s] - mx);
               den += e * ls[s];
               num.x += e * os[s].x; num.y += e * os[s].y; num.z += e * os[s].z; num.w += e * os[s].w;
             }
+          }
+          if (mx != -INFINITY) {
             // the attention output is an fp16 tensor in the reference
             v.x = __half2float(__float2half_rn(num.x / den));
             v.y = __half2float(__float2half_rn(num.y / den));

@@ -175,9 +175,10 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st,
     aa.chunk = (ctx + splits - 1) / splits;
     aa.scale = 0.125f;  // 64^-0.5, src/model.py:129
     aa.out = attn_out;
-    // 64-token CTAs (latency variant) when the split count says so
-    aa.small = (splits <= kMaxConsumerSplits && (int64_t)splits * 64 >= ctx) ? 1 : 0;
-    const bool consumer_merge = splits > 1 && splits <= kMaxConsumerSplits;
+    // 64-token single-warp CTAs (latency variant) up to 2048 tokens, merged by the o_proj kernel
+    aa.small = (splits <= kWarpMaxSplits && (int64_t)splits * 64 >= ctx) ? 1 : 0;
+    aa.use_mma = 1;  // beyond 2048 tokens: the mma.sync throughput kernel
+    const bool consumer_merge = splits > 1 && splits <= kMaxConsumerSplitsTotal;
     aa.consumer_merge = consumer_merge ? 1 : 0;
     aa.epoch = d->step_counter;
     aa.prefetch = (aa.small && d->step_counter != nullptr) ? 1 : 0;
@@ -355,10 +356,13 @@ extern "C" int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx) {
     if (s > 64) s = 64;
     return s < 1 ? 1 : s;
   }
-  // Short contexts at small batch: one warp per 64 tokens, merged by the o_proj kernel.
+  // Up to 2048 tokens at small batch: one warp per 64 tokens, merged by the o_proj kernel.
   const int small = (ctx + 63) / 64;
-  if (small <= kMaxConsumerSplits && ((int64_t)batch * small * kKvHeads <= 1184 || batch >= g_tensor_min_batch)) return small;
-  return quic_attn_pick_splits(batch, ctx);
+  if (small <= kWarpMaxSplits) return small;
+  // Longer: 4-warp CTAs of the throughput kernel over 128 tokens and more each, and no more
+  // splits than the o_proj kernel merges itself.
+  const int by_len = (ctx + 127) / 128;
+  return by_len < kMaxConsumerSplitsTotal ? by_len : kMaxConsumerSplitsTotal;
 }
 
 extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32_t attn_splits) {

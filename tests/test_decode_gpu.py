@@ -172,6 +172,65 @@ def test_batched_rows_are_independent(tiny_model):
         _assert_greedy_matches([int(first[i])] + rest[i], want[i][0], want[i][1])
 
 
+@pytest.mark.parametrize("prompt_len,steps", [(1100, 5), (2043, 9)])
+def test_single_row_decode_beyond_1024_tokens(tiny_model, prompt_len, steps):
+    """One row at 1025..2048 tokens of context runs the single-warp attention kernel with 17..32
+    splits, which the o_proj kernel merges in two passes of loads; the second case also crosses
+    2048 tokens, where the throughput kernel takes over."""
+    net, ref, _, _ = tiny_model
+    prompt = torch.randint(0, 2048, (prompt_len,), generator=torch.Generator().manual_seed(prompt_len)).tolist()
+    ref_tokens, ref_logits = ref.greedy(prompt, steps)
+    cache = net.new_cache(n_slots=2, s_max=2304)
+    cache.batch_slots = [1]
+    out = net(torch.tensor([prompt]), past_key_values=cache)
+    tokens, kept = [], []
+    for _ in range(steps):
+        kept.append(out.logits[0, -1].clone())
+        nxt = kept[-1].argmax().view(1, 1)
+        tokens.append(int(nxt))
+        out = net(nxt, past_key_values=cache)
+    n = _assert_greedy_matches(tokens, ref_tokens, ref_logits)
+    ok, err = _close(torch.stack(kept)[: n + 1], ref_logits[: n + 1])
+    assert ok, err
+    # the same tokens from one graph of several steps
+    cache2 = net.new_cache(n_slots=2, s_max=2304)
+    first, _ = net.prefill(cache2, [0], [torch.tensor(prompt)])
+    again = [int(first[0])] + net.decode(cache2, [0], steps - 1)[0]
+    assert again == tokens
+
+
+def test_single_row_long_context_matches_the_batched_step(tiny_model):
+    """Beyond 2048 tokens one row runs the throughput attention kernel with up to 64 splits that
+    the o_proj kernel merges in passes of 16; four rows run the tensor-core step, whose splits
+    the last CTA merges.  Same prompt, same fed tokens: the logits of the two must agree."""
+    net, _, _, _ = tiny_model
+    gen = torch.Generator().manual_seed(77)
+    prompt = torch.randint(0, 2048, (4300,), generator=gen)
+    others = [torch.randint(0, 2048, (n,), generator=gen) for n in (40, 700, 3000)]
+    steps = 5
+
+    one = net.new_cache(n_slots=1, s_max=8192)
+    first, _ = net.prefill(one, [0], [prompt])
+    one.batch_slots = [0]
+    fed, single = [int(first[0])], []
+    for _ in range(steps):
+        logits = net(torch.tensor([[fed[-1]]]), past_key_values=one).logits[0, 0].clone()
+        single.append(logits)
+        fed.append(int(logits.argmax()))
+
+    four = net.new_cache(n_slots=4, s_max=8192)
+    firsts, _ = net.prefill(four, [2, 0, 1, 3], [prompt] + others)
+    assert int(firsts[0]) == fed[0]
+    four.batch_slots = [2, 0, 1, 3]
+    nxt = firsts.view(4, 1).clone()
+    for i in range(steps):
+        nxt[0, 0] = fed[i]
+        logits = net(nxt, past_key_values=four).logits[:, 0]
+        ok, err = _close(logits[0], single[i])
+        assert ok, (i, err)
+        nxt = logits.argmax(dim=-1, keepdim=True)
+
+
 def test_golden_hf_quant_logits(tiny_model):
     """Against logits the reference's own model_hf.load produced (tests/golden/make_golden.py)."""
     net, _, _, _ = tiny_model
