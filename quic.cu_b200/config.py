@@ -21,3 +21,6 @@ class EngineConfig:
     # additions (defaults keep reference call sites valid)
     max_context: int = 2048   # tokens per KV slot (prompt + generated)
     decode_burst: int = 8     # greedy steps per graph launch between scheduling points
+    # prefill newly admitted requests on a second CUDA stream while the rows already running
+    # decode their next burst; the new rows join at the following iteration
+    overlap_prefill: bool = True

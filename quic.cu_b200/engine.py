@@ -19,6 +19,13 @@ admission prefills into a free slot, release frees it, and an iteration is a bur
 device->host copy of the burst's tokens.  Tokens produced by a row after it finished are
 discarded exactly as the reference discards them (src/engine.py:180-182).
 
+With ``overlap_prefill`` (default) a request admitted while other rows are running is
+prefilled on a second CUDA stream during those rows' next decode burst and joins the batch at
+the following iteration: slots are disjoint, so the two never touch the same cache rows, and
+the side stream is synchronised before any decode launch that includes the new rows.  The
+outputs are the same (every request is an independent greedy decode); only the iteration at
+which a request starts to decode moves by one.
+
 ``model_module.load(**options)`` must return ``(model, tokenizer)``; the model is driven
 through three calls: ``new_cache(n_slots, s_max)``, ``prefill(cache, slots, prompts)`` and
 ``decode(cache, slots, steps)``.
@@ -70,6 +77,8 @@ class Engine:
         self.max_tokens = 256
         self.registry = registry
         self.burst = max(1, int(config.decode_burst))
+        self.overlap_prefill = bool(getattr(config, "overlap_prefill", True))
+        self._prefill_stream = None
         self.cache = self.model.new_cache(max_batch_size, config.max_context)
         self.free_slots: list[int] = list(range(max_batch_size))
         self._request_id_generator = itertools.count(1)
@@ -132,14 +141,41 @@ class Engine:
                         self._update_sequence_with_token(seq, int(token))
 
     @torch.inference_mode()
-    def _prefill_sequences(self, sequences: list[SequenceState]) -> None:
+    def _prefill_begin(self, sequences: list[SequenceState], stream=None):
+        """Assigns slots and enqueues the prefill (on ``stream`` when given); nothing is read
+        back yet.  Returns what ``_prefill_end`` needs."""
         for seq in sequences:
             seq.slot = self.free_slots.pop(0)
-        first, _ = self.model.prefill(self.cache, [s.slot for s in sequences],
-                                      [s.prompt_tokens.view(-1) for s in sequences])
+        slots = [s.slot for s in sequences]
+        prompts = [s.prompt_tokens.view(-1) for s in sequences]
+        if stream is None:
+            first, _ = self.model.prefill(self.cache, slots, prompts)
+        else:
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                first, _ = self.model.prefill(self.cache, slots, prompts)
+        return sequences, first, stream
+
+    @torch.inference_mode()
+    def _prefill_end(self, pending) -> None:
+        sequences, first, stream = pending
+        if stream is not None:
+            stream.synchronize()  # the slots are complete before any later decode launch
         first = first.tolist() if hasattr(first, "tolist") else list(first)
         for seq, token in zip(sequences, first):
             self._update_sequence_with_token(seq, int(token))
+
+    def _prefill_sequences(self, sequences: list[SequenceState]) -> None:
+        self._prefill_end(self._prefill_begin(sequences))
+
+    def _side_stream(self):
+        """Second CUDA stream for overlapped prefills (None for a model that is not on a GPU)."""
+        device = getattr(self.model, "device", None)
+        if device is None or getattr(device, "type", "cpu") != "cuda":
+            return None
+        if self._prefill_stream is None:
+            self._prefill_stream = torch.cuda.Stream(device=device)
+        return self._prefill_stream
 
     def _finish(self, seq: SequenceState):
         if self.tokenizer is not None:
@@ -162,12 +198,22 @@ class Engine:
                         seq.slot = None
                     if released:
                         self.running = [s for s in self.running if s.request_id not in released]
+                pending = None
                 if decision.admit:
                     with Span("prefill", self.registry):
                         admitted = [self.waiting.popleft() for _ in decision.admit]
-                        self._prefill_sequences(admitted)
-                        self.running.extend(admitted)
-                if not self.running:
+                        if self.overlap_prefill and any(not seq.is_finished for seq in self.running):
+                            # the rows already running decode their burst while the admitted
+                            # prompts prefill into their (disjoint) slots; they join afterwards
+                            pending = self._prefill_begin(admitted, self._side_stream())
+                        else:
+                            self._prefill_sequences(admitted)
+                            self.running.extend(admitted)
+                if not self.running and pending is None:
                     break
                 self.step()
+                if pending is not None:
+                    with Span("prefill", self.registry):
+                        self._prefill_end(pending)
+                        self.running.extend(pending[0])
         return [outputs[request_id] for request_id in sorted(outputs)]

@@ -21,8 +21,9 @@ def test_empty_run_returns_empty_list():  # reference tests/test_engine.py:12
 
 @pytest.mark.parametrize("batching", ["static", "continuous"])
 @pytest.mark.parametrize("burst", [1, 3, 8])
-def test_outputs_equal_independent_greedy_generation(batching, burst):
-    engine, module = _engine(batching, max_batch=3, burst=burst)
+@pytest.mark.parametrize("overlap", [True, False])
+def test_outputs_equal_independent_greedy_generation(batching, burst, overlap):
+    engine, module = _engine(batching, max_batch=3, burst=burst, overlap_prefill=overlap)
     engine.max_tokens = 16
     prompts = [[5, 6, 7], [1], [9, 9, 9, 9], [2, 3], [11] * 10, [4, 5], [8]]
     limits = [16, 3, 16, 1, 9, 16, 2]
@@ -88,3 +89,24 @@ def test_continuous_refills_vacant_slots_while_others_run():
     second_prefill = [i for i, c in enumerate(calls) if c[0] == "prefill"][1]
     assert calls[second_prefill][1] == [0]
     assert any(c[0] == "decode" and len(c[1]) == 2 for c in calls[second_prefill:])
+
+
+def test_overlapped_admission_prefills_before_the_running_rows_decode():
+    """With overlap_prefill a request admitted while another is running is prefilled first (on
+    the GPU: on a second stream), the running row decodes alone, and the new row joins the next
+    burst; without it the new row decodes in the same iteration."""
+    def order(overlap):
+        engine, module = _engine("continuous", max_batch=2, burst=2, overlap_prefill=overlap)
+        engine.add_request_ids([1], max_tokens=2)
+        engine.add_request_ids([2], max_tokens=12)
+        engine.add_request_ids([3], max_tokens=4)
+        out = engine.run()
+        calls = module.model.calls
+        second = [i for i, c in enumerate(calls) if c[0] == "prefill"][1]
+        return out, [(c[0], len(c[1])) for c in calls[second:second + 3]]
+
+    out_a, seq_a = order(True)
+    out_b, seq_b = order(False)
+    assert out_a == out_b
+    assert seq_a == [("prefill", 1), ("decode", 1), ("decode", 2)]
+    assert seq_b == [("prefill", 1), ("decode", 2), ("decode", 2)]

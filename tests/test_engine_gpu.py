@@ -44,6 +44,34 @@ def test_engine_multirequest_generation(tiny_model, batching, prefill_backend): 
     net.prefill_backend = "pytorch"  # the fixture is shared
 
 
+@pytest.mark.parametrize("overlap", [True, False])
+def test_overlapped_prefill_is_repeatable_and_follows_the_oracle(tiny_model, overlap):
+    """More requests than slots, so most admissions happen while other rows decode: with
+    overlap_prefill they are prefilled on a second stream during the running rows' burst.  Every
+    output follows the oracle, and a second run of the same queue on the same engine returns
+    the same tokens (a race between the two streams would show as a difference)."""
+    net, ref, _, _ = tiny_model
+    module = SimpleNamespace(load=lambda **options: (net, None))
+    engine = Engine(config=EngineConfig(batching="continuous", max_context=256, decode_burst=4,
+                                        prefill_backend="quic", overlap_prefill=overlap),
+                    max_batch_size=3, model_module=module)
+    gen = torch.Generator().manual_seed(11)
+    lens = [23, 150, 7, 64, 1, 99, 31, 12, 180, 5, 47, 3]
+    limits = [9, 14, 30, 5, 22, 11, 1, 17, 8, 26, 13, 6]
+    prompts = [torch.randint(0, 2048, (n,), generator=gen).tolist() for n in lens]
+    runs = []
+    for _ in range(2):
+        for p, lim in zip(prompts, limits):
+            engine.add_request_ids(p, max_tokens=lim)
+        runs.append(engine.run())
+    assert runs[0] == runs[1]
+    for out, p, lim in zip(runs[0], prompts, limits):
+        ref_tokens, ref_logits = ref.greedy(p, lim)
+        assert len(out) == lim
+        _prefix_ok(out, ref_tokens, ref_logits)
+    net.prefill_backend = "pytorch"  # the fixture is shared
+
+
 def test_load_from_checkpoint_directory(tmp_path, tiny_model):
     """model.load(path) reads config.json + model.safetensors like src/model.py:306-365."""
     from quic_cu_b200 import model as qmodel
