@@ -633,7 +633,7 @@ cudaError_t launch_down_m(const DownArgs& a, cudaStream_t s, bool pdl) {
   return launch(down_kernel<M>, grid, dim3(256), 0, s, pdl, a);
 }
 
-inline int pick_m(int batch) { return batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8; }
+inline int pick_m(int batch) { return batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 3 ? 3 : batch <= 4 ? 4 : 8; }
 
 }  // namespace
 
@@ -641,6 +641,7 @@ inline int pick_m(int batch) { return batch <= 1 ? 1 : batch <= 2 ? 2 : batch <=
   switch (pick_m(batch)) {                       \
     case 1: return fn<1>(__VA_ARGS__);           \
     case 2: return fn<2>(__VA_ARGS__);           \
+    case 3: return fn<3>(__VA_ARGS__);           \
     case 4: return fn<4>(__VA_ARGS__);           \
     default: return fn<8>(__VA_ARGS__);          \
   }
