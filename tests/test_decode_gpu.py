@@ -231,6 +231,39 @@ def test_single_row_long_context_matches_the_batched_step(tiny_model):
         nxt = logits.argmax(dim=-1, keepdim=True)
 
 
+def test_three_ragged_rows_long_context_match_the_batched_step(tiny_model):
+    """Three rows of 4300 / 40 / 2500 tokens on the GEMV chain (3-row kernels, throughput
+    attention kernel, splits without tokens for the short rows, o_proj merging 64 splits)
+    against the same rows inside a 4-row tensor-core step, fed the same tokens."""
+    net, _, _, _ = tiny_model
+    gen = torch.Generator().manual_seed(78)
+    prompts = [torch.randint(0, 2048, (n,), generator=gen) for n in (4300, 40, 2500, 900)]
+    steps = 4
+
+    three = net.new_cache(n_slots=4, s_max=8192)
+    firsts, _ = net.prefill(three, [3, 1, 0], prompts[:3])
+    three.batch_slots = [3, 1, 0]
+    nxt = firsts.view(3, 1).clone()
+    fed, chain = [nxt.clone()], []
+    for _ in range(steps):
+        logits = net(nxt, past_key_values=three).logits[:, 0].clone()
+        chain.append(logits)
+        nxt = logits.argmax(dim=-1, keepdim=True)
+        fed.append(nxt.clone())
+
+    four = net.new_cache(n_slots=4, s_max=8192)
+    firsts4, _ = net.prefill(four, [0, 1, 2, 3], prompts)
+    assert firsts4[:3].tolist() == firsts.tolist()
+    four.batch_slots = [0, 1, 2, 3]
+    nxt4 = firsts4.view(4, 1).clone()
+    for i in range(steps):
+        nxt4[:3] = fed[i]
+        logits = net(nxt4, past_key_values=four).logits[:, 0]
+        ok, err = _close(logits[:3], chain[i])
+        assert ok, (i, err)
+        nxt4 = logits.argmax(dim=-1, keepdim=True)
+
+
 def test_golden_hf_quant_logits(tiny_model):
     """Against logits the reference's own model_hf.load produced (tests/golden/make_golden.py)."""
     net, _, _, _ = tiny_model
