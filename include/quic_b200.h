@@ -38,6 +38,7 @@ extern "C" {
 #define QUIC_E_SHAPE (-2)   /* shape not supported by the kernels */
 #define QUIC_E_CUDA (-3)    /* a CUDA runtime call failed */
 #define QUIC_E_LIMIT (-4)   /* size beyond a documented fixed maximum */
+#define QUIC_E_TIMEOUT (-5) /* a bounded wait inside a kernel gave up; results invalid */
 
 const char *quic_last_error(void);
 /* Library ABI version; bumped when a struct below changes. */
@@ -349,6 +350,61 @@ int quic_graph_run_host(void *graph, void *stream, const int32_t *host_in,
                         int32_t *dev_in, int32_t n_in, const int32_t *dev_out,
                         int32_t *host_out, int32_t n_out);
 int quic_graph_destroy(void *graph);
+
+/* ------------------------------------------------------------------------
+ * The decode token loop as one persistent kernel (1..quic_persist_max_rows()
+ * batch rows, contexts up to 16 x 256 tokens).  Opt-in: on B200 it measures
+ * slower than quic_decode_step's kernel chain (587 vs 352 us per token).
+ *
+ * Replaces the same reference code as quic_decode_step, for `steps` consecutive
+ * greedy tokens in ONE launch: Engine.step + QUICForCausalLM.forward with
+ * seq_len == 1 (src/engine.py:78-107, src/model.py:211-224, 272-303).  148
+ * resident CTAs walk layers and tokens; a layer phase hands its result to the
+ * next through 8-byte {payload, tag} words in `sync`, and the weights stream
+ * from a per-CTA copy of the W4 matrices ("W4S", built once by
+ * quic_persist_pack from the W4T matrices of quic_model_t) into a
+ * shared-memory ring.  Arithmetic and rounding points are those of
+ * quic_decode_step.  The kernel is launched cooperatively: it needs a GPU with
+ * at least 148 SMs on which all its CTAs can be resident, and it occupies the
+ * whole GPU until the burst ends (work on other streams waits).
+ *
+ *  - `wstream`: quic_persist_stream_bytes(n_layers) bytes, 256-byte aligned,
+ *    filled by quic_persist_pack (replaces, like quic_w4_prepack, the repack of
+ *    src/quant/marlin.py:105-125).
+ *  - `sync`: quic_persist_sync_bytes() bytes, 256-byte aligned, zeroed once by
+ *    the caller; one area serves every launch on a stream, launches that can
+ *    overlap on the GPU need an area each.
+ *  - quic_decode_t: `scratch` is not used; `attn_splits` 0 lets the library
+ *    choose from `ctx_hint` (an upper bound of pos + steps over the rows);
+ *    `logits` only with steps == 1.
+ *  - Every wait inside the kernel is bounded.  If one gives up the kernel ends
+ *    early, the tokens of that launch are invalid and the status word of `sync`
+ *    is non-zero: quic_decode_persist_status() returns and clears it (it
+ *    synchronises the stream), quic_decode_persist_run_host() checks it itself
+ *    and returns QUIC_E_TIMEOUT.  No reference counterpart (its kernels have no
+ *    bounded waits, kernels/cuda/marlin.cu:1467-1476).
+ * ---------------------------------------------------------------------- */
+int32_t quic_persist_max_rows(void);
+int64_t quic_persist_stream_bytes(int32_t n_layers);
+int64_t quic_persist_sync_bytes(void);
+/* Attention splits per (row, kv head) for contexts up to `ctx`; more than 16
+ * means the context is too long for this kernel (use quic_decode_step). */
+int32_t quic_persist_pick_splits(int32_t batch, int32_t ctx);
+int quic_persist_pack(const quic_model_t *m, void *wstream_out, void *stream);
+int quic_decode_persist(const quic_model_t *m, const quic_decode_t *d,
+                        const void *wstream, void *sync, int32_t steps,
+                        void *stream);
+int quic_decode_persist_status(void *sync, void *stream, int32_t *status_out);
+/* The host-driven form (compare quic_graph_run_host; src/engine.py:82-84,
+ * 98-104): n_in int32 host -> device, the launch, n_out int32 and the status
+ * word device -> host (host_status: one page-locked int32), stream
+ * synchronised. */
+int quic_decode_persist_run_host(const quic_model_t *m, const quic_decode_t *d,
+                                 const void *wstream, void *sync, int32_t steps,
+                                 void *stream, const int32_t *host_in,
+                                 int32_t *dev_in, int32_t n_in,
+                                 const int32_t *dev_out, int32_t *host_out,
+                                 int32_t n_out, int32_t *host_status);
 
 #ifdef __cplusplus
 }

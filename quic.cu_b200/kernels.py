@@ -154,6 +154,15 @@ SIGNATURES = {
     "quic_graph_launch": (C.c_int, [_P, _P]),
     "quic_graph_run_host": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P, _P, C.c_int32]),
     "quic_graph_destroy": (C.c_int, [_P]),
+    "quic_persist_max_rows": (_I32, []),
+    "quic_persist_stream_bytes": (_I64, [_I32]),
+    "quic_persist_sync_bytes": (_I64, []),
+    "quic_persist_pick_splits": (_I32, [_I32, _I32]),
+    "quic_persist_pack": (C.c_int, [C.POINTER(Model), _P, _P]),
+    "quic_decode_persist": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _P, _P, _I32, _P]),
+    "quic_decode_persist_status": (C.c_int, [_P, _P, C.POINTER(_I32)]),
+    "quic_decode_persist_run_host": (C.c_int, [C.POINTER(Model), C.POINTER(Decode), _P, _P, _I32, _P, _P, _P, _I32,
+                                               _P, _P, _I32, _P]),
 }
 
 

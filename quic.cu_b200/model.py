@@ -29,6 +29,10 @@ from . import kernels as K
 from .checkpoint import LAYER_LINEARS, detect_group_size, packed_prefixes
 
 DTYPE = torch.float16
+# QUIC_PERSIST=1 (or model.use_persist = True) decodes batches of up to quic_persist_max_rows()
+# rows in the persistent kernel: one launch per burst of tokens.  Off by default: measured at
+# 587 us per token against 352 us for the kernel chain (24 layers, one row).
+PERSIST = os.environ.get("QUIC_PERSIST", "0") == "1"
 HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, QKV_N = K.HIDDEN, K.HEADS, K.KV_HEADS, K.HEAD_DIM, K.INTER, K.QKV_N
 
 
@@ -86,6 +90,15 @@ class SlotCache:
             need = K.lib().quic_decode_scratch_bytes(batch, self.vocab, splits)
             t = torch.zeros(need, dtype=torch.uint8, device=self.device)
             self._scratch[key] = t
+        return t
+
+    def persist_sync(self) -> torch.Tensor:
+        """Exchange area of the persistent decode kernel (zeroed once; its tags only grow)."""
+        t = self.__dict__.get("_persist_sync")
+        if t is None:
+            t = torch.zeros(K.lib().quic_persist_sync_bytes(), dtype=torch.uint8, device=self.device)
+            self._persist_sync = t
+            self._persist_status = torch.zeros(1, dtype=torch.int32).pin_memory()
         return t
 
     def host_out(self) -> torch.Tensor:
@@ -154,6 +167,8 @@ class QUICForCausalLM:
         self._c_model = None
         self.default_slots = 8
         self.default_context = 4096
+        self.use_persist = PERSIST
+        self._wstream: torch.Tensor | None = None
 
     # ---- weights -------------------------------------------------------------
     def load_state(self, weights: dict) -> None:
@@ -233,7 +248,16 @@ class QUICForCausalLM:
         return self.forward(*args, **kwargs)
 
     # ---- decode ----------------------------------------------------------------
-    def _decode_struct(self, cache: SlotCache, batch: int, ctx: int, logits: torch.Tensor | None):
+    def _decode_struct(self, cache: SlotCache, batch: int, ctx: int, logits: torch.Tensor | None,
+                       persist: bool = False):
+        if persist:  # no scratch arena; the library picks the splits from ctx
+            rows = cache._row_bufs.get(batch)
+            if rows is None:
+                rows = cache._row_bufs[batch] = torch.zeros(batch, dtype=torch.int32, device=self.device)
+            d = K.Decode(K.ptr(cache.kv), cache.n_slots, cache.s_max, K.ptr(cache.tok), K.ptr(cache.pos),
+                         K.ptr(rows), batch, K.ptr(cache.out_tokens), cache.ring, K.ptr(cache.step_counter),
+                         K.ptr(logits), None, 0, ctx)
+            return d, rows
         splits = K.lib().quic_decode_pick_splits(batch, ctx)
         # captured graphs keep this buffer's address: it lives as long as the cache
         rows = cache._row_bufs.get(batch)
@@ -259,16 +283,40 @@ class QUICForCausalLM:
             cache._graphs[key] = g
         return g, rows
 
+    # ---- persistent decode kernel ------------------------------------------------------
+    def persist_stream(self) -> torch.Tensor:
+        """The per-CTA weight stream of the persistent kernel, packed on first use from the
+        W4T matrices (a second copy of the layer weights, ~10 MB per layer)."""
+        if self._wstream is None:
+            need = K.lib().quic_persist_stream_bytes(self.n_layers)
+            if need <= 0:
+                raise RuntimeError("persistent decode: unsupported layer count")
+            t = torch.empty(need, dtype=torch.uint8, device=self.device)
+            K.check(K.lib().quic_persist_pack(C.byref(self._c_model), K.ptr(t), K.stream_ptr()), "persist_pack")
+            self._wstream = t
+        return self._wstream
+
+    def persist_ok(self, batch: int, ctx: int) -> bool:
+        """Whether ``batch`` rows with contexts up to ``ctx`` tokens run in the persistent kernel."""
+        lib = K.lib()
+        return (self.use_persist and batch <= lib.quic_persist_max_rows() and self.vocab >= 296
+                and lib.quic_persist_stream_bytes(self.n_layers) > 0
+                and lib.quic_persist_pick_splits(batch, ctx) <= 16)
+
     def launches_per_step(self, cache: SlotCache | None = None, batch: int = 1, ctx: int = 1024) -> int:
-        """Kernels one decode step launches for ``batch`` rows at a context bound of ``ctx``."""
+        """Kernels one decode step launches for ``batch`` rows at a context bound of ``ctx``
+        (the persistent kernel is one launch per burst, counted as one per step here)."""
+        if self.persist_ok(batch, ctx):
+            return 1
         if cache is None:
             return 5 * self.n_layers + 1
         d, _ = self._decode_struct(cache, batch, ctx, None)
         return int(K.lib().quic_decode_launch_count(C.byref(self._c_model), C.byref(d)))
 
     def _prepare_decode(self, cache: SlotCache, slots: list[int], steps: int, logits):
-        """Checks the request, loads the row->slot map and returns (graph handle, ring index
-        of the first generated token row) after advancing the host mirrors."""
+        """Checks the request, loads the row->slot map and returns (handle, ring index of the
+        first generated token row) after advancing the host mirrors.  ``handle`` is a captured
+        graph (int) or, for the persistent kernel, the quic_decode_t of the launch."""
         if not slots:
             raise RuntimeError("decode: empty batch")
         if steps < 1 or steps > cache.ring:
@@ -277,7 +325,10 @@ class QUICForCausalLM:
         if longest + steps > cache.s_max or longest + steps > self.max_pos:
             raise RuntimeError("decode: context would exceed the KV slot length")
         ctx = min(_ctx_bucket(longest + steps, len(slots)), cache.s_max)
-        g, rows = self._graph(cache, len(slots), ctx, steps, logits)
+        if self.persist_ok(len(slots), ctx):
+            g, rows = self._decode_struct(cache, len(slots), ctx, logits, persist=True)
+        else:
+            g, rows = self._graph(cache, len(slots), ctx, steps, logits)
         want = cache.rows_tensor(slots)
         if cache._rows_loaded.get(len(slots)) is not want:
             rows.copy_(want)
@@ -293,8 +344,23 @@ class QUICForCausalLM:
         """Enqueues ``steps`` greedy decode steps for the rows ``slots`` (no host sync).
         Returns the ring index of the first generated token row in ``cache.out_tokens``."""
         g, first = self._prepare_decode(cache, slots, steps, logits)
-        K.check(K.lib().quic_graph_launch(g, K.stream_ptr()), "graph_launch")
+        self._launch(cache, g, steps)
         return first
+
+    def _launch(self, cache: SlotCache, handle, steps: int) -> None:
+        if isinstance(handle, K.Decode):
+            K.check(K.lib().quic_decode_persist(C.byref(self._c_model), C.byref(handle), K.ptr(self.persist_stream()),
+                                                K.ptr(cache.persist_sync()), steps, K.stream_ptr()), "decode_persist")
+        else:
+            K.check(K.lib().quic_graph_launch(handle, K.stream_ptr()), "graph_launch")
+
+    def persist_status(self, cache: SlotCache) -> int:
+        """Status word of the persistent kernel (0 = every wait was met); reading clears it
+        and synchronises the stream."""
+        out = C.c_int32(0)
+        K.check(K.lib().quic_decode_persist_status(K.ptr(cache.persist_sync()), K.stream_ptr(), C.byref(out)),
+                "decode_persist_status")
+        return int(out.value)
 
     def decode(self, cache: SlotCache, slots: list[int], steps: int,
                feed: torch.Tensor | None = None) -> list[list[int]]:
@@ -338,16 +404,23 @@ class QUICForCausalLM:
             if first + steps > cache.ring:  # the block of rows wraps around the ring
                 if n_in:
                     cache.tok[slots[0]: slots[0] + n_in].copy_(feed, non_blocking=True)
-                K.check(K.lib().quic_graph_launch(g, K.stream_ptr()), "graph_launch")
+                self._launch(cache, g, steps)
                 idx = (torch.arange(steps, device=self.device) + first) % cache.ring
                 toks = cache.out_tokens.index_select(0, idx).index_select(1, cache.rows_tensor(slots).long())
                 return toks.t().cpu().tolist()
         n = cache.n_slots
         offset = 4 * first * n
-        rc = K.lib().quic_graph_run_host(g, K.stream_ptr(), feed.data_ptr() if n_in else None, plan[3], n_in,
-                                         plan[4] + offset, plan[5] + offset, steps * n)
+        if isinstance(g, K.Decode):
+            sync = cache.persist_sync()
+            rc = K.lib().quic_decode_persist_run_host(
+                C.byref(self._c_model), C.byref(g), K.ptr(self.persist_stream()), K.ptr(sync), steps, K.stream_ptr(),
+                feed.data_ptr() if n_in else None, plan[3], n_in, plan[4] + offset, plan[5] + offset, steps * n,
+                cache._persist_status.data_ptr())
+        else:
+            rc = K.lib().quic_graph_run_host(g, K.stream_ptr(), feed.data_ptr() if n_in else None, plan[3], n_in,
+                                             plan[4] + offset, plan[5] + offset, steps * n)
         if rc != 0:
-            K.check(rc, "graph_run_host")
+            K.check(rc, "decode run_host")
         host_np = plan[6]
         if steps == 1 and len(slots) == 1:
             return [[int(host_np[first, slots[0]])]]
