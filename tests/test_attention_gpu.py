@@ -98,10 +98,11 @@ def test_all_masked_row_gives_zeros_and_oracle_agrees():
         assert torch.allclose(out[:, :, 0].cpu().float(), want.float(), atol=2e-3)
 
 
-@pytest.mark.parametrize("batch,kv_len", [(4, 32768), (256, 1024), (64, 8192)])
+@pytest.mark.parametrize("batch,kv_len", [(4, 32768), (256, 1024), (64, 8192), (64, 32768), (256, 8192)])
 def test_decode_sweep_corners(batch, kv_len):
-    """Corners of the benchmark's attention sweep (maximum context, maximum batch): against
-    SDPA on the rows that fit in memory, and split-count invariance on all rows."""
+    """Corners of the benchmark's attention sweep (maximum context, maximum batch, and the two
+    largest problems, which are the ones that run at the memory roofline: 2.1 GB of K and V
+    each): against SDPA on the first rows, and split-count invariance on all rows."""
     from quic_cu_b200 import kernels as K
 
     g = torch.Generator(device="cuda").manual_seed(batch + kv_len)
