@@ -43,6 +43,14 @@ CONFIG = {
 }
 
 
+def profile_shares() -> dict:
+    """Figures taken from committed ncu summaries (not measured by this run): the time share of
+    each layer kernel among the layer kernels and the DRAM traffic of one lm_head launch."""
+    path = os.path.join(ROOT, "profiles", "decode_step_kernel_shares.json")
+    with open(path) as handle:
+        return json.load(handle)
+
+
 def peaks() -> tuple[float, str]:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -242,8 +250,11 @@ def run_gpu(args) -> None:
            "note": "per 256-token step: 256 public decode calls, each with a 4-byte token id H2D from "
                    "pinned memory and a 4-byte sampled id D2H"}
 
-    # ---- roofline of the dominant kernel (tied lm_head + argmax: 58% of the bytes of a token)
+    # ---- rooflines.  By time the step is its 120 layer kernels (87 %), by bytes the lm_head
+    # (58 %): `roofline` names the group that dominates by time, `roofline_kernels` lists every
+    # kernel type, `roofline_step` is the whole token.
     peak, peak_kind = peaks()
+    prof = profile_shares()
     x = torch.randn(1, 896, device=device, dtype=torch.float16)
     for _ in range(3):
         K.lm_head_argmax(x, net.embed, net.final_norm, net.eps)
@@ -257,17 +268,36 @@ def run_gpu(args) -> None:
     torch.cuda.synchronize()
     lm_us = k0.elapsed_time(k1) * 1e3 / reps
     lm_bytes = 151936 * 896 * 2 + 896 * 4
-    achieved = lm_bytes / (lm_us * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": "lm_head_kernel<1> (tied fp16 lm_head GEMV + final RMSNorm + argmax)",
-                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"of {peak_kind}", "us_per_launch": lm_us, "algorithmic_bytes": lm_bytes,
-                "traffic": LM_HEAD_TRAFFIC_BYTES,
-                "timing": f"{reps} back-to-back launches between CUDA events on the launching stream; the "
-                          "272 MB table exceeds L2"}
     mean_ctx = PROMPT_LEN + GEN_TOKENS / 2
     step_bytes = net.weight_bytes() + 12288 * (mean_ctx + 1)
     us_per_token = elapsed_ms * 1e3 / tokens
     step_gbs = step_bytes / (us_per_token * 1e-6) / 1e9
+    layers_us = max(us_per_token - lm_us, 1e-3)           # all 5 x 24 layer kernels of a token
+    layer_bytes = step_bytes - lm_bytes                     # W4 weights of 24 layers + K/V read and written
+    per_layer = {"qkv_kernel<1>": 536256 + 2304 + 1792 + 512, "attn_decode_warp_kernel": 512 * (mean_ctx + 1),
+                 "oproj_kernel<1>": 417088, "gateup_kernel<1>": 4528384 + 1792, "down_kernel<1>": 2264192}
+    kernels = []
+    for name, share in prof["layer_kernel_share"].items():
+        us = layers_us / net.n_layers * share
+        kernels.append({"kernel": name, "launches_per_token": net.n_layers, "algorithmic_bytes": per_layer[name],
+                        "us_per_launch": us, "achieved": per_layer[name] / us / 1e3, "unit": "GB/s",
+                        "frac": per_layer[name] / us / 1e3 / peak, "share_of_step": us * net.n_layers / us_per_token,
+                        "timing": "(token time - live lm_head time) / layers x the kernel's share of the layer "
+                                  "kernels' time in the committed ncu launch list"})
+    kernels.append({"kernel": "lm_head_kernel<1>", "launches_per_token": 1, "algorithmic_bytes": lm_bytes,
+                    "us_per_launch": lm_us, "achieved": lm_bytes / lm_us / 1e3, "unit": "GB/s",
+                    "frac": lm_bytes / lm_us / 1e3 / peak, "share_of_step": lm_us / us_per_token,
+                    "traffic": prof["dram_traffic_bytes_per_launch"]["lm_head_kernel<1>"],
+                    "traffic_source": "ncu capture summarised under profiles/ (not measured by this run)",
+                    "timing": f"{reps} back-to-back launches between CUDA events on the launching stream; the "
+                              "272 MB table exceeds L2"})
+    roofline = {"bound": "hbm", "kernel": "the 120 layer kernels of a token (qkv, attention, o_proj, gate_up, down "
+                                          "x 24: dominant by time)",
+                "achieved": layer_bytes / layers_us / 1e3, "peak": peak, "unit": "GB/s",
+                "frac": layer_bytes / layers_us / 1e3 / peak, "peak_kind": f"of {peak_kind}",
+                "share_of_step": layers_us / us_per_token, "us_per_token": layers_us,
+                "algorithmic_bytes": layer_bytes, "traffic": None,
+                "timing": "token time (CUDA events over the timed region) minus the lm_head kernel's live time"}
     roofline_step = {"bound": "hbm", "scope": "whole decode step (121 kernels)", "achieved": step_gbs,
                      "peak": peak, "unit": "GB/s", "frac": step_gbs / peak, "us_per_token": us_per_token,
                      "algorithmic_bytes": step_bytes}
@@ -289,9 +319,10 @@ def run_gpu(args) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate",
-        "data": "synthetic", "config": dict(CONFIG, parallelism=f"{world} independent replica(s)"),
+        "data": "synthetic", "config": CONFIG, "parallelism": f"{world} independent replica(s), no collective",
         "clocks": clocks, "e2e": e2e, "gpu_launches": world * args.steps * GEN_TOKENS * net.launches_per_step(cache, 1, PROMPT_LEN + GEN_TOKENS),
-        "roofline": roofline, "roofline_step": roofline_step, "batch64": batch64, "serving": serving,
+        "roofline": roofline, "roofline_kernels": kernels, "roofline_step": roofline_step, "batch64": batch64,
+        "serving": serving,
     }
     if args.layers != 24:
         line["invalid"] = "reduced layer count: profiling run, not a benchmark"
@@ -525,23 +556,30 @@ def measure_batch64(net, device, world, dist):
 
 
 def measure_serving(net, device, n_requests, world, dist, rank):
-    """Continuous batching with 64 KV slots per GPU: prompt lengths uniform in 64..1024, output
-    lengths uniform in 128..512 (forced through max_tokens; random weights never emit EOS), all
-    requests queued at t = 0 (arrivals at saturation), greedy, prefill attention by the
-    library's own kernel (prefill_backend "quic").  The queue is dealt round-robin to the
-    replicas; wall-clock on every rank, max over ranks."""
+    """Continuous batching with 64 KV slots per GPU (benchmark configuration 4): prompt lengths
+    uniform in 64..1024, output lengths uniform in 128..512 (forced through max_tokens; random
+    weights never emit EOS), all requests queued at t = 0 (arrivals at saturation), greedy,
+    prefill attention by the library's own kernel.  ``n_requests`` is the size of the WHOLE
+    queue: the replicas pull chunks of 16 requests from one shared FIFO kept in the process
+    group's store (quic_cu_b200.replicas.serve_pulled), so the work is fixed as N grows.
+    Wall clock on every rank from the common start to the moment the last chunk is done, max
+    over ranks."""
     from types import SimpleNamespace
+
+    import torch.distributed as tdist
 
     from quic_cu_b200.config import EngineConfig
     from quic_cu_b200.engine import Engine
-    from quic_cu_b200.replicas import Request, serve, shard
+    from quic_cu_b200.replicas import Request, StoreQueue, chunks_of, group_store, serve_pulled
 
     gen = torch.Generator().manual_seed(4)
     plens = torch.randint(64, 1025, (n_requests,), generator=gen).tolist()
     olens = torch.randint(128, 513, (n_requests,), generator=gen).tolist()
     reqs = [Request(i, tuple(torch.randint(0, 151936, (plens[i],), generator=gen).tolist()), olens[i])
             for i in range(n_requests)]
-    mine = shard(reqs, rank, world)
+    chunk = 16
+    n_chunks = len(chunks_of(reqs, chunk))
+    store = group_store(dist) if dist is not None else tdist.HashStore()
     module = SimpleNamespace(load=lambda **options: (net, None))
     engine = Engine(config=EngineConfig(batching="continuous", max_context=2048, decode_burst=8,
                                         prefill_backend="quic"),
@@ -549,34 +587,37 @@ def measure_serving(net, device, n_requests, world, dist, rank):
     # First pass: the engine captures one CUDA graph per (rows, context bound, burst) it meets
     # (a one-time cost of a long-lived server); second pass: the same queue on the warm engine.
     passes = []
-    for _ in range(2):
+    for p in range(2):
+        queue = StoreQueue(store, n_chunks, rank, prefix=f"serving{p}", stale_s=60.0)
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        out = serve(engine, mine)
+        kept0, cpu0, t0 = engine.generated, time.process_time(), time.perf_counter()
+        stats = serve_pulled(engine, reqs, queue, chunk=chunk)
         torch.cuda.synchronize()
         seconds = time.perf_counter() - t0
-        tokens = sum(len(v) for v in out.values())
+        mine = [seconds, float(engine.generated - kept0), stats["busy_s"], time.process_time() - cpu0,
+                float(stats["requests"])]
         if dist is not None:
-            t = torch.tensor([seconds, float(tokens)], device=device, dtype=torch.float64)
-            tmax = t.clone()
-            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-            dist.all_reduce(t, op=dist.ReduceOp.SUM)
-            seconds, tokens = float(tmax[0].item()), int(t[1].item())
-        passes.append((seconds, tokens))
-    seconds, tokens = passes[1]
+            everyone = [None] * world
+            dist.all_gather_object(everyone, mine)
+        else:
+            everyone = [mine]
+        passes.append(everyone)
+    warm = passes[1]
+    seconds = max(r[0] for r in warm)
+    tokens = int(sum(r[1] for r in warm))
+    cold_seconds = max(r[0] for r in passes[0])
     return {"value": tokens / seconds, "unit": "generated tokens/s (prefill included in the time)",
             "requests": n_requests, "generated_tokens": tokens, "prompt_tokens": sum(plens), "seconds": seconds,
-            "first_pass_seconds": passes[0][0], "first_pass_value": passes[0][1] / passes[0][0],
+            "first_pass_seconds": cold_seconds, "first_pass_value": int(sum(r[1] for r in passes[0])) / cold_seconds,
+            "per_replica": [{"requests": int(r[4]), "generated_tokens": int(r[1]), "seconds": r[0],
+                             "engine_busy_s": r[2], "host_cpu_share": r[3] / r[0] if r[0] > 0 else None} for r in warm],
+            "queue": "pull-based: chunks of 16 requests claimed from a FIFO in the process group's store; "
+                     "the queue size is fixed as N grows (strong scaling)",
             "note": "value: second pass over the same queue on the same engine (decode graphs captured); "
                     "first_pass_*: fresh engine, captures included",
             "slots_per_gpu": 64, "replicas": world}
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one lm_head_kernel<1> launch at vocab 151936,
-# from the ncu capture summarised in profiles/lm_head_kernel_batch1_vocab151936.md.
-LM_HEAD_TRAFFIC_BYTES = 276_400_000
 
 
 def main() -> None:
@@ -587,9 +628,10 @@ def main() -> None:
     ap.add_argument("--impl", default="quic_b200", choices=["quic_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-batch64", action="store_true", help="skip the extra batch-64 decode measurement")
-    ap.add_argument("--serving-requests", type=int, default=256,
-                    help="also serve this many synthetic requests with continuous batching (64 slots per GPU, "
-                         "two passes, a few seconds); the benchmark configuration uses 4096; 0 skips it")
+    ap.add_argument("--serving-requests", type=int, default=4096,
+                    help="also serve a queue of this many synthetic requests with continuous batching (64 slots "
+                         "per GPU, pulled by all replicas from one FIFO, two passes: about 35 s each on one GPU); "
+                         "4096 is the benchmark configuration; 0 skips it")
     ap.add_argument("--layers", type=int, default=24,
                     help="decoder layers of the synthetic model; values below 24 exist only to keep "
                          "profiler captures small and do not produce a valid benchmark line")

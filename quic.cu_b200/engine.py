@@ -86,6 +86,13 @@ class Engine:
         self.eos_token_id = getattr(self.tokenizer, "eos_token_id", None)
         self.decode_steps = 0      # device decode iterations issued
         self.generated = 0         # tokens kept
+        # Optional pull-based feed (request-sharded replicas): ``request_source(room)`` is asked
+        # for up to ``room`` more requests, as (token ids, max_tokens, tag) triples, whenever
+        # fewer than a batch are waiting; it returns [] when it has nothing (now).  ``on_finish``
+        # is called with (tag, output) when a request that carries a tag is released.
+        self.request_source = None
+        self.on_finish = None
+        self._tags: dict[int, object] = {}
 
     # ---- requests ------------------------------------------------------------------
     def add_request(self, prompt: str) -> int:
@@ -97,8 +104,9 @@ class Engine:
             return_tensors="pt", return_dict=True)
         return self.add_request_ids(encoding["input_ids"])
 
-    def add_request_ids(self, input_ids, max_tokens: int | None = None) -> int:
-        """Token-id request: ``input_ids`` is a list or a [1, T] / [T] tensor."""
+    def add_request_ids(self, input_ids, max_tokens: int | None = None, tag=None) -> int:
+        """Token-id request: ``input_ids`` is a list or a [1, T] / [T] tensor.  ``tag`` travels
+        with the request and is handed to ``on_finish`` with its output."""
         ids = torch.as_tensor(input_ids, dtype=torch.long).reshape(1, -1).cpu()
         if ids.shape[1] < 1:
             raise ValueError("empty prompt")
@@ -107,7 +115,9 @@ class Engine:
             raise ValueError(f"prompt ({ids.shape[1]}) + max_tokens ({limit}) + burst does not fit a "
                              f"KV slot of {self.config.max_context} tokens")
         request_id = next(self._request_id_generator)
-        self.waiting.append(SequenceState(prompt_tokens=ids, request_id=request_id, max_tokens=limit))
+        seq = SequenceState(prompt_tokens=ids, request_id=request_id, max_tokens=limit)
+        self._tags[request_id] = tag
+        self.waiting.append(seq)
         return request_id
 
     # ---- one iteration ---------------------------------------------------------------
@@ -190,10 +200,16 @@ class Engine:
         with Span("request run", self.registry):
             while True:
                 with Span("scheduling", self.registry):
+                    if self.request_source is not None and len(self.waiting) < self.max_batch_size:
+                        for ids, limit, tag in self.request_source(self.max_batch_size - len(self.waiting)):
+                            self.add_request_ids(ids, max_tokens=limit, tag=tag)
                     decision = self.batching_policy.decide(self.running, self.waiting, self.max_batch_size)
                     released = {seq.request_id for seq in decision.release}
                     for seq in decision.release:
                         outputs[seq.request_id] = self._finish(seq)
+                        tag = self._tags.pop(seq.request_id, None)
+                        if self.on_finish is not None and tag is not None:
+                            self.on_finish(tag, outputs[seq.request_id])
                         self.free_slots.append(seq.slot)
                         seq.slot = None
                     if released:

@@ -17,7 +17,8 @@ entry.load_package()
 
 from quic_cu_b200.config import EngineConfig
 from quic_cu_b200.engine import Engine
-from quic_cu_b200.replicas import Request, dispatch, merge, serve, serve_sharded, shard
+from quic_cu_b200.replicas import (Request, StoreQueue, chunks_of, dispatch, group_store, merge, serve,
+                                   serve_pulled, serve_sharded, shard)
 from tests.fake_model import FakeModule, expected_generation
 
 
@@ -90,3 +91,45 @@ def test_two_gloo_ranks_shard_and_gather(tmp_path):
     out_path = str(tmp_path / "out.pt")
     mp.spawn(_worker, args=(2, port, out_path), nprocs=2, join=True)
     assert torch.load(out_path) == _expected(_requests(9))
+
+
+def _pull_worker(rank, world, port, out_path, leave):
+    """Rank 0 serves until the whole FIFO is done and collects; rank 1 either serves normally or
+    leaves with its first chunk claimed and unfinished (between two iterations of its loop:
+    no kernel, no collective in flight -- there are none on this path anyway)."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    reqs = _requests(23)
+    chunk = 4
+    queue = StoreQueue(group_store(dist), len(chunks_of(reqs, chunk)), rank, prefix="t", stale_s=0.4)
+    dist.barrier()  # both queues exist (first heartbeat written) before anybody pulls
+    if rank == 1 and leave:
+        stats = serve_pulled(_engine(), reqs, queue, chunk=chunk, leave_after_chunks=1)
+        assert stats["chunks"] == 1
+        return  # gone: no goodbye, no destroy_process_group
+    stats = serve_pulled(_engine(), reqs, queue, chunk=chunk)
+    if rank == 0:
+        assert queue.finished()
+        merged = queue.collect()
+        torch.save(([merged[k] for k in sorted(merged)], stats), out_path)
+    if not leave:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("leave", [False, True])
+def test_two_gloo_ranks_pull_chunks_and_a_leaver_is_replaced(tmp_path, leave):
+    """World size 2 on the CPU: both replicas pull chunks from the queue in the group's store
+    and every request is served exactly once; when rank 1 leaves with a claimed chunk, rank 0
+    claims it again once the heartbeat is stale and the outputs are still complete."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out_path = str(tmp_path / "out.pt")
+    mp.spawn(_pull_worker, args=(2, port, out_path, leave), nprocs=2, join=True)
+    outputs, stats = torch.load(out_path)
+    assert outputs == _expected(_requests(23))
+    if leave:
+        assert stats["chunks"] >= 5 and stats["requests"] >= 20  # rank 0 also served the orphan
