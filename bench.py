@@ -185,6 +185,10 @@ def run_gpu(args) -> None:
     entry.load_package()
     from quic_cu_b200 import kernels as K
 
+    if world > 1:
+        # N replicas share the host: the small CPU tensor ops of the serving loop must not each
+        # spin up (and then spin-wait in) an OpenMP team of every core
+        torch.set_num_threads(max(1, (os.cpu_count() or 8) // (2 * world)))
     net, state = build_model(device, args.layers)
     cache = net.new_cache(n_slots=1, s_max=1024)
     gen_ids = torch.Generator().manual_seed(rank)  # every replica serves its own request
