@@ -564,7 +564,7 @@ def measure_serving(net, device, n_requests, world, dist, rank):
     uniform in 64..1024, output lengths uniform in 128..512 (forced through max_tokens; random
     weights never emit EOS), all requests queued at t = 0 (arrivals at saturation), greedy,
     prefill attention by the library's own kernel.  ``n_requests`` is the size of the WHOLE
-    queue: the replicas pull chunks of 16 requests from one shared FIFO kept in the process
+    queue: the replicas pull chunks of 8 requests from one shared FIFO kept in the process
     group's store (quic_cu_b200.replicas.serve_pulled), so the work is fixed as N grows.
     Wall clock on every rank from the common start to the moment the last chunk is done, max
     over ranks."""
@@ -581,7 +581,7 @@ def measure_serving(net, device, n_requests, world, dist, rank):
     olens = torch.randint(128, 513, (n_requests,), generator=gen).tolist()
     reqs = [Request(i, tuple(torch.randint(0, 151936, (plens[i],), generator=gen).tolist()), olens[i])
             for i in range(n_requests)]
-    chunk = 16
+    chunk = 8
     n_chunks = len(chunks_of(reqs, chunk))
     store = group_store(dist) if dist is not None else tdist.HashStore()
     module = SimpleNamespace(load=lambda **options: (net, None))
@@ -617,7 +617,7 @@ def measure_serving(net, device, n_requests, world, dist, rank):
             "first_pass_seconds": cold_seconds, "first_pass_value": int(sum(r[1] for r in passes[0])) / cold_seconds,
             "per_replica": [{"requests": int(r[4]), "generated_tokens": int(r[1]), "seconds": r[0],
                              "engine_busy_s": r[2], "host_cpu_share": r[3] / r[0] if r[0] > 0 else None} for r in warm],
-            "queue": "pull-based: chunks of 16 requests claimed from a FIFO in the process group's store; "
+            "queue": "pull-based: chunks of 8 requests claimed from a FIFO in the process group's store; "
                      "the queue size is fixed as N grows (strong scaling)",
             "note": "value: second pass over the same queue on the same engine (decode graphs captured); "
                     "first_pass_*: fresh engine, captures included",

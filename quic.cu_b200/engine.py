@@ -86,9 +86,10 @@ class Engine:
         self.eos_token_id = getattr(self.tokenizer, "eos_token_id", None)
         self.decode_steps = 0      # device decode iterations issued
         self.generated = 0         # tokens kept
-        # Optional pull-based feed (request-sharded replicas): ``request_source(room)`` is asked
-        # for up to ``room`` more requests, as (token ids, max_tokens, tag) triples, whenever
-        # fewer than a batch are waiting; it returns [] when it has nothing (now).  ``on_finish``
+        # Optional pull-based feed (request-sharded replicas): before every scheduling decision
+        # ``request_source(room)`` is asked for up to ``room`` more requests (the slots that
+        # are free or about to be), as (token ids, max_tokens, tag) triples; it returns []
+        # when it has nothing (now).  ``on_finish``
         # is called with (tag, output) when a request that carries a tag is released.
         self.request_source = None
         self.on_finish = None
@@ -200,9 +201,15 @@ class Engine:
         with Span("request run", self.registry):
             while True:
                 with Span("scheduling", self.registry):
-                    if self.request_source is not None and len(self.waiting) < self.max_batch_size:
-                        for ids, limit, tag in self.request_source(self.max_batch_size - len(self.waiting)):
-                            self.add_request_ids(ids, max_tokens=limit, tag=tag)
+                    if self.request_source is not None:
+                        # ask only for what can be admitted now (slots that are free or about to
+                        # be released): requests a replica hoards are requests another replica
+                        # could be serving
+                        done = sum(1 for seq in self.running if seq.is_finished)
+                        room = len(self.free_slots) + done - len(self.waiting)
+                        if room > 0:
+                            for ids, limit, tag in self.request_source(room):
+                                self.add_request_ids(ids, max_tokens=limit, tag=tag)
                     decision = self.batching_policy.decide(self.running, self.waiting, self.max_batch_size)
                     released = {seq.request_id for seq in decision.release}
                     for seq in decision.release:
