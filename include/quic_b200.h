@@ -232,6 +232,17 @@ int quic_attn_decode_noalloc(const void *q_f16, const void *k_f16, const void *v
                              const int32_t *end, int32_t s_max, float scale,
                              void *out_f16, int32_t b, int32_t splits, void *stream);
 int64_t quic_attn_decode_noalloc_max_bytes(void);
+/* Same operation, same arguments, for up to quic_attn_decode_cta_max_tokens()
+ * (4096) cached tokens, with neither scratch nor counters: one CTA of eight
+ * warps covers 512 tokens of a (row, KV head) and the CTAs of a (row, KV head)
+ * are a thread-block cluster whose partial results meet in the shared memory
+ * of its first CTA.  This is the attention of the decode step at 2..16 rows.
+ * Longer caches are refused with QUIC_E_LIMIT. */
+int quic_attn_decode_cta(const void *q_f16, const void *k_f16, const void *v_f16,
+                         int64_t stride_b, int64_t stride_h, const int32_t *start,
+                         const int32_t *end, int32_t s_max, float scale,
+                         void *out_f16, int32_t b, void *stream);
+int32_t quic_attn_decode_cta_max_tokens(void);
 int32_t quic_attn_pick_splits(int32_t b, int32_t s_max);
 int64_t quic_attn_scratch_bytes(int32_t b, int32_t splits);
 
@@ -318,12 +329,17 @@ typedef struct {
 int64_t quic_prefill_scratch_bytes(int32_t rows, int32_t n_seq, int32_t vocab);
 int quic_prefill(const quic_model_t *m, const quic_prefill_t *p, void *stream);
 
-/* Batches of at least this many rows run the decode step on the tensor-core
- * kernels (tcgen05 GEMM, tensor lm_head); smaller ones on the fused GEMV chain.
- * Default 4 (measured crossover on B200); accepted range 2..9.  Set it before graphs are captured.  No
- * reference counterpart (Marlin picks its tile shapes per call,
- * kernels/cuda/marlin.cu:3795-3805). */
+/* Which of the three forms of the decode step a batch takes.  Batches of at
+ * least quic_set_tensor_min_batch rows (default 17, range 2..17) run every
+ * linear on the tcgen05 GEMM and the tensor lm_head; below that, batches of at
+ * least quic_set_mma_chain_min_batch rows (default 3, range 2..17) run the
+ * five-kernel layer chain with the rows on the M side of mma.sync, whose cost
+ * hardly grows with the row count; smaller batches (one row, and two by
+ * default) run the GEMV chain.  The defaults are the crossovers measured on
+ * B200.  Set them before graphs are captured.  No reference counterpart
+ * (Marlin picks its tile shapes per call, kernels/cuda/marlin.cu:3795-3805). */
 void quic_set_tensor_min_batch(int32_t batch);
+void quic_set_mma_chain_min_batch(int32_t batch);
 /* Attention split count the decode step uses for `batch` rows whose contexts are
  * at most `ctx` tokens (pass the result as attn_splits and to the scratch size). */
 int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx);

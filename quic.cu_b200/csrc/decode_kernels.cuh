@@ -100,6 +100,12 @@ struct AttnArgs {
   float* l_part;
 };
 
+// Scratch-free attention (attn_decode_cta.cu): CTAs of 512 tokens, a.splits of them (a cluster)
+// per (row, KV head).
+constexpr int kAttnCtaMaxSplits = 8;
+int attn_cta_splits(int ctx);
+cudaError_t launch_attn_cta(const AttnArgs& a, int batch, cudaStream_t stream, bool pdl);
+
 struct LmHeadArgs {
   const half* embed;  // [vocab][896]
   const half* ln;
@@ -133,6 +139,19 @@ cudaError_t launch_down(const DownArgs& a, cudaStream_t s, bool pdl);
 cudaError_t launch_attn(const AttnArgs& a, int batch, cudaStream_t s, bool pdl);
 cudaError_t launch_lm_head(const LmHeadArgs& a, int grid, cudaStream_t s, bool pdl);
 int lm_head_grid(int vocab);
+
+// the layer kernels for 2..16 rows (decode_layers_mma.cu)
+constexpr int kMmaChainMaxRows = 16;
+cudaError_t launch_qkv_mma(const quic_w4_t& w, const half* ln, const half* embed, const half* x_in,
+                           const float* ssq_in, half* x_copy, const RowState& rs, float eps, bool first_layer,
+                           int vocab, const half* cos_t, const half* sin_t, int max_pos, half* qbuf, half* kcache,
+                           half* vcache, int s_max, cudaStream_t st, bool pdl);
+cudaError_t launch_oproj_mma(const quic_w4_t& w, const half* attn, const half* xres_in, half* xres_out, float* ssq_out,
+                             int batch, cudaStream_t st);
+cudaError_t launch_gateup_mma(const quic_w4_t& w, const half* ln, const half* xres, const float* ssq_in, half* act,
+                              int batch, float eps, cudaStream_t st);
+cudaError_t launch_down_mma(const quic_w4_t& w, const half* act, const half* xres_in, half* xres_out, float* ssq_out,
+                            float* partial, int32_t* counters, int batch, cudaStream_t st);
 
 // pieces of the batched (batch > 8) decode step
 cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,

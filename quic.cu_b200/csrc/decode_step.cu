@@ -106,13 +106,19 @@ int check(const quic_model_t* m, const quic_decode_t* d) {
 }
 
 int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head);
+int enqueue_step_rows16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head);
 
-// Smallest batch that takes the tensor-core step (quic_set_tensor_min_batch); 2..9.
-int g_tensor_min_batch = 4;  // measured us per step, chain / tensor: 3 rows 683 / 810, 4 rows 877 / 810
+// Smallest batch that takes the tensor-core (tcgen05) step (quic_set_tensor_min_batch): 2..17,
+// and smallest batch that takes the mma.sync chain (quic_set_mma_chain_min_batch): 2..17.
+// Below both, the rows run the GEMV chain (FMA; its cost grows with every row, measured 352,
+// 491 and 683 us per step at 1, 2 and 3 rows against 565 and 580 us of the mma.sync chain).
+int g_tensor_min_batch = kMmaChainMaxRows + 1;
+int g_mma_chain_min_batch = 3;
 
 int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
   const int B = d->batch;
   if (B >= g_tensor_min_batch) return enqueue_step_batched(m, d, st, chain_head);
+  if (B >= g_mma_chain_min_batch) return enqueue_step_rows16(m, d, st, chain_head);
   const int splits = pick_splits(d);
   const Arena ar = carve(B, m->vocab, splits);
   char* base = static_cast<char*>(d->scratch);
@@ -238,7 +244,106 @@ int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st,
   return QUIC_OK;
 }
 
-// Batch > 8: every linear is the tcgen05 GEMM; norms, RoPE/KV append and SwiGLU are
+// 2..16 rows: five launches per layer as for one row, every linear on mma.sync with the rows on
+// the M side; each kernel writes a finished fp16 tensor (decode_layers_mma.cu).
+int enqueue_step_rows16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
+  const int B = d->batch;
+  const int splits = pick_splits(d);
+  const Arena ar = carve(B, m->vocab, splits);
+  char* base = static_cast<char*>(d->scratch);
+  half* xa = reinterpret_cast<half*>(base + ar.xres);  // residual stream entering a layer
+  half* xb = xa + (size_t)B * kHidden;                  // after the attention block
+  half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
+  half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
+  half* act = reinterpret_cast<half*>(base + ar.act16);
+  half* xn = reinterpret_cast<half*>(base + ar.xn);
+  // per-tile sums of squares of the two residual streams ([B][32] fp32 each), the down
+  // kernel's K-split planes and its arrival counters (in the arena's zeroed head)
+  float* ssq_a = reinterpret_cast<float*>(base + ar.act);
+  float* ssq_b = ssq_a + kMmaChainMaxRows * 32;
+  float* partial = reinterpret_cast<float*>(base + ar.partial);
+  int32_t* down_counters = reinterpret_cast<int32_t*>(base + ar.lm_counter + 128);
+  const size_t slot_stride = (size_t)kKvHeads * d->s_max * kHeadDim;
+  const size_t kv_plane = (size_t)d->n_slots * slot_stride;
+  int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
+  if (ctx > d->s_max) ctx = d->s_max;
+  RowState rs;
+  rs.rows = d->rows;
+  rs.tok = d->tok;
+  rs.pos = d->pos;
+  rs.batch = B;
+  const half* embed = (const half*)m->embed;
+
+  for (int l = 0; l < m->n_layers; ++l) {
+    const quic_layer_t& L = m->layers[l];
+    half* kc = static_cast<half*>(d->kv) + (size_t)(2 * l) * kv_plane;
+    half* vc = kc + kv_plane;
+    // (the head of a sequence starts only after everything enqueued before it has completed)
+    QUIC_CUDA(launch_qkv_mma(L.qkv, (const half*)L.ln1, embed, xa, ssq_a, xa, rs, m->eps, l == 0, m->vocab,
+                             (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos, qbuf, kc, vc, d->s_max,
+                             st, !(chain_head && l == 0)));
+    AttnArgs aa = {};
+    aa.q = qbuf;
+    aa.k = kc;
+    aa.v = vc;
+    aa.stride_b = (int64_t)slot_stride;
+    aa.stride_h = (int64_t)d->s_max * kHeadDim;
+    aa.rows = d->rows;
+    aa.pos = d->pos;
+    aa.s_cap = ctx;
+    aa.splits = splits;
+    aa.chunk = (ctx + splits - 1) / splits;
+    aa.scale = 0.125f;
+    aa.out = attn_out;
+    aa.small = (splits <= 32 && (int64_t)splits * 64 >= ctx) ? 1 : 0;
+    aa.use_mma = 1;
+    aa.consumer_merge = 0;  // the splits are merged by the last CTA to arrive
+    aa.epoch = d->step_counter;
+    aa.prefetch = (aa.small && d->step_counter != nullptr) ? 1 : 0;
+    if (attn_cta_splits(ctx) <= kAttnCtaMaxSplits) {
+      // up to 4096 tokens: CTAs of 512 tokens, merged through (distributed) shared memory
+      aa.splits = attn_cta_splits(ctx);
+      aa.chunk = 512;
+      aa.prefetch = d->step_counter != nullptr ? 1 : 0;
+      QUIC_CUDA(launch_attn_cta(aa, B, st, true));
+    } else {
+      if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
+      QUIC_CUDA(launch_attn(aa, B, st, true));
+    }
+    QUIC_CUDA(launch_oproj_mma(L.o, attn_out, xa, xb, ssq_b, B, st));
+    QUIC_CUDA(launch_gateup_mma(L.gate_up, (const half*)L.ln2, xb, ssq_b, act, B, m->eps, st));
+    QUIC_CUDA(launch_down_mma(L.down, act, xb, xa, ssq_a, partial, down_counters, B, st));
+  }
+  LmHeadArgs la = {};
+  la.embed = embed;
+  la.batch = B;
+  la.vocab = m->vocab;
+  la.eps = m->eps;
+  la.logits = (half*)d->logits;
+  la.best_val = reinterpret_cast<float*>(base + ar.best_val);
+  la.best_idx = reinterpret_cast<int32_t*>(base + ar.best_idx);
+  la.counter = reinterpret_cast<int32_t*>(base + ar.lm_counter);
+  la.keys = reinterpret_cast<unsigned long long*>(base + ar.lm_counter + 256);
+  la.rows = d->rows;
+  la.tok = d->tok;
+  la.pos = d->pos;
+  la.out_tokens = d->out_tokens;
+  la.n_slots = d->n_slots;
+  la.ring = d->ring > 0 ? d->ring : 1;
+  la.step_counter = d->step_counter;
+  if (B > 4 && lm_head_tc_supported(B, m->vocab)) {
+    QUIC_CUDA(launch_rmsnorm(xa, nullptr, (const half*)m->final_norm, m->eps, xn, nullptr, B, st));
+    la.x_normed = xn;
+    return launch_lm_head_tc(la, st);
+  }
+  // up to four rows: the GEMV form, final norm fused, one launch
+  la.ln = (const half*)m->final_norm;
+  la.xres_in = xa;
+  QUIC_CUDA(launch_lm_head(la, lm_head_grid(m->vocab), st, true));
+  return QUIC_OK;
+}
+
+// Batch > 16: every linear is the tcgen05 GEMM; norms, RoPE/KV append and SwiGLU are
 // separate small kernels (at these sizes each kernel does microseconds of real work, so
 // the launch chain is no longer what bounds the step).
 int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
@@ -340,7 +445,11 @@ struct Graph {
 using namespace quic;
 
 extern "C" void quic_set_tensor_min_batch(int32_t batch) {
-  g_tensor_min_batch = batch < 2 ? 2 : (batch > kMaxM + 1 ? kMaxM + 1 : batch);
+  g_tensor_min_batch = batch < 2 ? 2 : (batch > kMmaChainMaxRows + 1 ? kMmaChainMaxRows + 1 : batch);
+}
+
+extern "C" void quic_set_mma_chain_min_batch(int32_t batch) {
+  g_mma_chain_min_batch = batch < 2 ? 2 : (batch > kMmaChainMaxRows + 1 ? kMmaChainMaxRows + 1 : batch);
 }
 
 extern "C" int32_t quic_decode_pick_splits(int32_t batch, int32_t ctx) {
@@ -373,6 +482,7 @@ extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32
 extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_decode_t* d) {
   if (!m) return 0;
   if (d && d->batch >= g_tensor_min_batch) return 8 * m->n_layers + 3;
+  if (d && d->batch >= g_mma_chain_min_batch) return 5 * m->n_layers + ((d->batch > 4 && lm_head_tc_supported(d->batch, m->vocab)) ? 2 : 1);
   return 5 * m->n_layers + 1;
 }
 

@@ -141,9 +141,12 @@ SIGNATURES = {
     "quic_attn_decode": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _I32, _F, _P, _I32, _I32, _P, _P]),
     "quic_attn_decode_noalloc": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _I32, _F, _P, _I32, _I32, _P]),
     "quic_attn_decode_noalloc_max_bytes": (_I64, []),
+    "quic_attn_decode_cta": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _I32, _F, _P, _I32, _P]),
+    "quic_attn_decode_cta_max_tokens": (_I32, []),
     "quic_attn_pick_splits": (_I32, [_I32, _I32]),
     "quic_attn_scratch_bytes": (_I64, [_I32, _I32]),
     "quic_set_tensor_min_batch": (None, [_I32]),
+    "quic_set_mma_chain_min_batch": (None, [_I32]),
     "quic_decode_pick_splits": (_I32, [_I32, _I32]),
     "quic_decode_scratch_bytes": (_I64, [_I32, _I32, _I32]),
     "quic_decode_launch_count": (_I32, [C.POINTER(Model), C.POINTER(Decode)]),
@@ -475,7 +478,7 @@ def lm_head_argmax(x: torch.Tensor, embed: torch.Tensor, norm_weight: torch.Tens
 
 def _flash_attn_decode_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                softmax_scale: float = -1.0, pad_lens: torch.Tensor | None = None,
-                               splits: int = 0) -> torch.Tensor:
+                               splits: int = 0, cta_merge: bool = False) -> torch.Tensor:
     """flash_attn_decode.forward(Q fp16 [B,nh,1,64], K, V fp16 [B,n_kv,S,64], softmax_scale,
     pad_lens int32 [B] or None) -> fp16 [B,nh,1,64] (flash_attn_decode.cu:133-198)."""
     _need_cuda(q, k, v, pad_lens)
@@ -495,6 +498,12 @@ def _flash_attn_decode_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     out = torch.empty(b, nh, 1, HEAD_DIM, dtype=torch.float16, device=q.device)
     if s == 0:
         return out.zero_()
+    scale = float(softmax_scale) if softmax_scale and softmax_scale > 0 else HEAD_DIM ** -0.5
+    if cta_merge:  # CTAs of 512 tokens merged through (distributed) shared memory: no scratch
+        check(lib().quic_attn_decode_cta(ptr(q), ptr(k), ptr(v), KV_HEADS * s * HEAD_DIM, s * HEAD_DIM,
+                                         ptr(pad_lens), None, s, scale, ptr(out), b, stream_ptr()),
+              "attn_decode_cta")
+        return out
     if splits <= 0:
         splits = lib().quic_attn_pick_splits(b, s)
     scratch = None
@@ -505,7 +514,6 @@ def _flash_attn_decode_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         if scratch is None or scratch.numel() < need:
             scratch = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=q.device)
             _attn_scratch[key] = scratch
-    scale = float(softmax_scale) if softmax_scale and softmax_scale > 0 else HEAD_DIM ** -0.5
     check(lib().quic_attn_decode(ptr(q), ptr(k), ptr(v), KV_HEADS * s * HEAD_DIM, s * HEAD_DIM,
                                  ptr(pad_lens), None, s, scale, ptr(out), b, splits, ptr(scratch),
                                  stream_ptr()), "attn_decode")

@@ -143,3 +143,34 @@ def test_prefill_attention_matches_causal_sdpa(lens):
             is_causal=True, scale=SCALE, enable_gqa=True)[0]  # [14, n, 64]
         got = out[a:a + n].view(n, HEADS, HEAD_DIM).transpose(0, 1).float()
         assert torch.allclose(got, want, atol=ATOL), (n, (got - want).abs().max().item())
+
+
+@pytest.mark.parametrize("batch,kv_len", [(1, 1), (2, 63), (1, 512), (3, 513), (2, 1000), (16, 777), (4, 2048),
+                                          (2, 3585), (5, 4096)])
+def test_decode_cta_merge_variant(batch, kv_len):
+    """The scratch-free form (CTAs of 512 tokens; beyond 512 tokens a cluster of CTAs merged
+    through the first CTA's shared memory) against the oracle: ragged left pads, one row fully
+    padded, lengths on both sides of a CTA and of a warp boundary, the longest cache it takes."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(batch * 104729 + kv_len)
+    q = torch.randn((batch, HEADS, 1, HEAD_DIM), device="cuda", generator=g).half()
+    k = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    v = torch.randn((batch, 2, kv_len, HEAD_DIM), device="cuda", generator=g).half()
+    pads = torch.randint(0, kv_len // 2 + 1, (batch,), device="cuda", generator=g).int()
+    if batch > 2:
+        pads[1] = kv_len
+    want = quic_ref.attn_decode(q[:, :, 0].cpu(), k.cpu(), v.cpu(), SCALE, start=pads.cpu())
+    for _ in range(2):
+        out = K.flash_attn_decode().forward(q, k, v, SCALE, pads, cta_merge=True)
+        assert torch.isfinite(out).all()
+        assert torch.allclose(out[:, :, 0].float().cpu(), want.float(), atol=ATOL)
+
+
+def test_decode_cta_merge_refuses_longer_caches():
+    from quic_cu_b200 import kernels as K
+
+    q = torch.zeros((1, HEADS, 1, HEAD_DIM), device="cuda").half()
+    k = torch.zeros((1, 2, 4097, HEAD_DIM), device="cuda").half()
+    with pytest.raises(RuntimeError, match="4096"):
+        K.flash_attn_decode().forward(q, k, k, SCALE, None, cta_merge=True)

@@ -41,10 +41,10 @@ def test_tensor_gemm_matches_gemv_and_oracle(name):
     assert K.lib().quic_w4a16_tensor_status() == 0
 
 
-@pytest.mark.parametrize("batch", [4, 9, 12, 40])
+@pytest.mark.parametrize("batch", [2, 4, 9, 12, 16, 17, 40])
 def test_batched_decode_step_matches_oracle(tiny_model, batch):
-    """From 4 rows the decode step runs on the tensor-core kernels; every row must still give
-    what the oracle gives for that request alone."""
+    """2..16 rows run the layer chain on mma.sync (rows on the M side), 17 and more the tcgen05
+    step; every row must still give what the oracle gives for that request alone."""
     from quic_cu_b200 import kernels as K
 
     net, ref, _, _ = tiny_model
@@ -61,33 +61,42 @@ def test_batched_decode_step_matches_oracle(tiny_model, batch):
     assert K.lib().quic_w4a16_tensor_status() == 0
 
 
-@pytest.mark.parametrize("batch", [3, 5, 8])
-def test_gemv_chain_and_tensor_step_agree_with_oracle(tiny_model, batch):
-    """The same rows through the fused GEMV chain (forced up to 8 rows per step) and through
-    the tensor-core step (forced from 2 rows): both must match the oracle row by row."""
+@pytest.mark.parametrize("batch", [2, 3, 4, 5, 8, 11, 16])
+def test_the_three_decode_steps_agree_with_oracle(tiny_model, batch):
+    """The same rows through the five-kernel layer chain on mma.sync (forced from 2 rows), through
+    the GEMV chain (where it takes the batch: up to 4 rows) and through the tcgen05 step (forced
+    from 2 rows): each must match the oracle row by row."""
     from quic_cu_b200 import kernels as K
 
     net, ref, _, _ = tiny_model
     gen = torch.Generator().manual_seed(100 + batch)
     prompts = [torch.randint(0, 2048, (int(n),), generator=gen) for n in torch.randint(1, 30, (batch,), generator=gen)]
     want = [ref.greedy(p.tolist(), 5) for p in prompts]
+    paths = [(17, 2), (2, 17)] + ([(17, 17)] if batch <= 4 else [])  # (tensor from, mma.sync chain from)
     try:
-        for threshold in (9, 2):
-            K.lib().quic_set_tensor_min_batch(threshold)
-            cache = net.new_cache(n_slots=8, s_max=128)  # new cache: graphs are captured per threshold
+        for tensor_from, mma_from in paths:
+            K.lib().quic_set_tensor_min_batch(tensor_from)
+            K.lib().quic_set_mma_chain_min_batch(mma_from)
+            cache = net.new_cache(n_slots=16, s_max=128)  # new cache: graphs are captured per setting
             slots = list(range(batch))
             first, _ = net.prefill(cache, slots, prompts)
             rest = net.decode(cache, slots, 4)
             for i in range(batch):
                 _near_tie_ok([int(first[i])] + rest[i], want[i][0], want[i][1])
     finally:
-        K.lib().quic_set_tensor_min_batch(4)
+        K.lib().quic_set_tensor_min_batch(17)
+        K.lib().quic_set_mma_chain_min_batch(3)
     assert K.lib().quic_w4a16_tensor_status() == 0
 
 
-def test_batched_forward_logits_match_oracle(tiny_model):
-    """Tensor lm_head: logits of a 12-row decode step against the oracle's per-row logits."""
+@pytest.mark.parametrize("threshold", [17, 2])
+def test_batched_forward_logits_match_oracle(tiny_model, threshold):
+    """Logits of a 12-row decode step (tensor lm_head; layers on the mma.sync chain or, forced,
+    on the tcgen05 step) against the oracle's per-row logits."""
+    from quic_cu_b200 import kernels as K
+
     net, ref, _, _ = tiny_model
+    K.lib().quic_set_tensor_min_batch(threshold)
     gen = torch.Generator().manual_seed(77)
     prompts = [torch.randint(0, 2048, (int(n),), generator=gen).tolist() for n in range(3, 15)]
     width = max(len(p) for p in prompts)
@@ -105,4 +114,7 @@ def test_batched_forward_logits_match_oracle(tiny_model):
         if int(nxt[i]) != ref_tokens[0]:
             continue  # near tie on the first token: the second step saw another input
         got = step.logits[i, 0].float().cpu()
-        assert torch.allclose(got, ref_logits[1].float(), rtol=2e-2, atol=5e-2), (got - ref_logits[1].float()).abs().max()
+        try:
+            assert torch.allclose(got, ref_logits[1].float(), rtol=2e-2, atol=5e-2), (got - ref_logits[1].float()).abs().max()
+        finally:
+            K.lib().quic_set_tensor_min_batch(17)
