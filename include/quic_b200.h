@@ -107,9 +107,19 @@ int quic_w4a16_linear(const void *x_f16, const quic_w4_t *w, void *y_f16,
 int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k);
 /* Error word of the tensor path: 0, or a non-zero code if a bounded wait inside
  * the tcgen05 kernel gave up since the last call (results are then invalid).
- * Synchronises the device; for tests and debugging.  No reference counterpart
- * (Marlin's lock spins are unbounded, kernels/cuda/marlin.cu:1467-1476). */
+ * The word is taken (exchanged with zero on the device).  Synchronises the
+ * device; quic_graph_run_host reads the same word together with the tokens,
+ * without a synchronisation of its own, and returns QUIC_E_TIMEOUT when it is
+ * set.  No reference counterpart (Marlin's lock spins are unbounded,
+ * kernels/cuda/marlin.cu:1467-1476). */
 int quic_w4a16_tensor_status(void);
+/* Test hook for those bounded waits: the GEMM launches that follow probe at
+ * most `spin_limit` times per wait (0: the default, 1 << 22) and never request
+ * the packed weight tile of k block `skip_kblock` (128 k each; -1: none), so
+ * the waits for it run out, every role of the CTA leaves its loop, the status
+ * word is set and the kernel returns with its tensor memory released.  Call
+ * with (0, -1) to restore normal operation. */
+void quic_w4a16_tensor_test_hook(uint32_t spin_limit, int32_t skip_kblock);
 
 /* ------------------------------------------------------------------------
  * Stand-alone operators with the reference's per-op signatures.
@@ -139,28 +149,32 @@ int quic_rope(const void *x_f16, const void *cos_f16, const void *sin_f16,
  * head, rotation pairs adjacent); row r belongs to KV slot slots[r] at position
  * positions[r].  Writes the rotated queries head-major, q_out fp16
  * [14, rows, 64], and the rotated keys / plain values into the layer's cache
- * planes [n_slots, 2, s_max, 64] at (slot, head, position).  Replaces
+ * planes [n_slots, 2, s_max, 64] at (slot, head, position); a row whose slot
+ * is outside 0..n_slots-1 or whose position is outside 0..s_max-1 appends
+ * nothing (its query is still written).  Replaces
  * _heads + rope.forward x2 + DynamicCache.update of the reference's attention
  * (src/model.py:138-160). */
 int quic_qkv_rope_append(const void *qkv_f16, const int32_t *slots,
                          const int32_t *positions, const void *cos_f16,
                          const void *sin_f16, int32_t max_pos, void *q_out_f16,
                          void *kcache_f16, void *vcache_f16, int32_t s_max,
-                         int32_t rows, void *stream);
+                         int32_t n_slots, int32_t rows, void *stream);
 
 /* Causal prefill attention of n_seq sequences in one launch (GQA 14:2,
  * head_dim 64).  q_f16 [14, rows, 64] as written by quic_qkv_rope_append;
  * sequence i owns rows seq_start[i] .. seq_start[i] + seq_len[i] - 1, its keys
  * and values are positions 0 .. seq_len[i] - 1 of KV slot seq_slot[i] in the
  * layer's cache planes [n_slots, 2, s_max, 64] (no padding is stored, so no pad
- * mask exists); out_f16 [rows, 896] token-major.  Replaces the reference's
+ * mask exists); out_f16 [rows, 896] token-major; the rows of a sequence whose
+ * slot is outside 0..n_slots-1 are left unwritten.  Replaces the reference's
  * prefill attention (kernels/flash_attn_prefill_pytorch.py:10 = torch SDPA with
  * a causal + left-pad mask; kernels/cuda/flash_attn_prefill.cu:87). */
 int quic_attn_prefill(const void *q_f16, const void *kcache_f16,
                       const void *vcache_f16, const int32_t *seq_start,
                       const int32_t *seq_len, const int32_t *seq_slot,
                       int32_t n_seq, int32_t max_len, int32_t rows,
-                      int32_t s_max, float scale, void *out_f16, void *stream);
+                      int32_t s_max, int32_t n_slots, float scale,
+                      void *out_f16, void *stream);
 
 /* y = silu(gate) * up, rows of 4864.  Replaces swiglu.forward
  * (kernels/cuda/swiglu.cu:37). */

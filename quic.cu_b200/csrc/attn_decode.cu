@@ -33,18 +33,6 @@ namespace {
 
 constexpr int kGroupHeads = kHeads / kKvHeads;  // 7
 
-// Debug build (-DQUIC_TRACE): SM-clock stamps of the first CTAs of the last launch of the
-// latency kernel, read back with quic_trace_read_attn().  Compiled out otherwise.
-#ifdef QUIC_TRACE
-__device__ long long g_trace_attn[8][8];
-#define ATTN_STAMP(idx)                                                          \
-  do {                                                                            \
-    if (threadIdx.x == 0 && blockIdx.x < 8 && blockIdx.y == 0 && blockIdx.z == 0) \
-      g_trace_attn[blockIdx.x][idx] = clock64();                                  \
-  } while (0)
-#else
-#define ATTN_STAMP(idx)
-#endif
 constexpr int kWarps = 8;
 constexpr int kTile = 32;
 
@@ -184,7 +172,6 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
   if (a.pos != nullptr) slot = a.rows[b];
   pdl_trigger_early();
   pdl_wait();
-  QUIC_TLOG_BEGIN(2);
 
   const half* kbase = a.k + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
   const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
@@ -358,7 +345,6 @@ __global__ void __launch_bounds__(kWarps * 32) attn_decode_kernel(const AttnArgs
       }
     }
   }
-  QUIC_TLOG_END();
   if (a.splits == 1 || a.consumer_merge) return;
 
   merge_splits_last_cta(a, b, kvh, split, &last_flag);
@@ -391,7 +377,6 @@ __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) 
   const half* vbase = a.v + (size_t)slot * a.stride_b + (size_t)kvh * a.stride_h;
   const int last_tok = a.s_cap - 1;
   const int t0 = split * kWarpChunk;
-  ATTN_STAMP(0);
   pdl_trigger_early();
 
   WarpTile tile;
@@ -402,8 +387,6 @@ __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) 
     warp_tile_request(tile, kbase, vbase, t0, last_tok, g, c);
   }
   pdl_wait();
-  QUIC_TLOG_BEGIN(2);
-  ATTN_STAMP(1);
 
   int t_begin = 0, t_end = a.s_cap;
   int fresh = -1;  // row appended by the preceding kernel of the chain
@@ -423,11 +406,9 @@ __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) 
   if (t_begin < 0) t_begin = 0;
   const int c_begin = max(t_begin, t0);
   const int c_end = min(t_end, t0 + kWarpChunk);
-  ATTN_STAMP(2);
 
   float m, l, o[8][4];
   warp_tile_attend(tile, qa0, qa2, t0, c_begin, c_end, a.scale, c, m, l, o);
-  ATTN_STAMP(5);
 
   // ---- C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j of head g
   if (g < kGroupHeads) {
@@ -459,8 +440,6 @@ __global__ void __launch_bounds__(32) attn_decode_warp_kernel(const AttnArgs a) 
       }
     }
   }
-  ATTN_STAMP(7);
-  QUIC_TLOG_END();
   if (a.splits == 1 || a.consumer_merge) return;
   if (a.splits <= 32) {
     merge_splits_warp(a, b, kvh);
@@ -504,7 +483,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32) attn_decode_mma_kernel(const A
   if (a.pos != nullptr) slot = a.rows[b];
   pdl_trigger_early();
   pdl_wait();
-  QUIC_TLOG_BEGIN(2);
 
   int t_begin = 0, t_end = a.s_cap;
   if (a.pos != nullptr) {
@@ -665,7 +643,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32) attn_decode_mma_kernel(const A
       }
     }
   }
-  QUIC_TLOG_END();
   if (a.splits == 1 || a.consumer_merge) return;
   merge_splits_last_cta(a, b, kvh, split, &last_flag);
 }
@@ -814,11 +791,3 @@ extern "C" int quic_attn_decode_noalloc(const void* q, const void* k, const void
                           scratch, stream);
 }
 
-#ifdef QUIC_TRACE
-QUIC_TRACE_SETTER(attn)
-#endif
-#ifdef QUIC_TRACE
-extern "C" int quic_trace_read_attn(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, quic::g_trace_attn, sizeof(long long) * 8 * 8);
-}
-#endif

@@ -46,6 +46,7 @@ struct PrefillAttnArgs {
   half* out;            // [rows][896]
   int32_t rows;
   int32_t s_max;
+  int32_t n_slots;
   float scale;
 };
 
@@ -65,6 +66,7 @@ __global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 3
   if (r0 >= len) return;
   const int start = a.seq_start[seq];
   const int slot = a.seq_slot[seq];
+  if (slot < 0 || slot >= a.n_slots) return;  // no such slot: the sequence's rows stay unwritten
   const int kvh = head / kGroupHeads;
   const half* kbase = a.kcache + ((size_t)slot * kKvHeads + kvh) * a.s_max * kHeadDim;
   const half* vbase = a.vcache + ((size_t)slot * kKvHeads + kvh) * a.s_max * kHeadDim;
@@ -265,10 +267,11 @@ __global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 3
 namespace quic {
 int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
                         const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len, int32_t rows,
-                        int32_t s_max, float scale, void* out, cudaStream_t stream, bool pdl) {
+                        int32_t s_max, int32_t n_slots, float scale, void* out, cudaStream_t stream, bool pdl) {
   QUIC_REQUIRE(q && kcache && vcache && seq_start && seq_len && seq_slot && out, QUIC_E_ARG,
                "attn_prefill: null tensor");
-  QUIC_REQUIRE(n_seq >= 0 && n_seq <= 65535 && rows >= 0 && max_len >= 0 && s_max >= 1 && max_len <= s_max,
+  QUIC_REQUIRE(n_seq >= 0 && n_seq <= 65535 && rows >= 0 && max_len >= 0 && s_max >= 1 && max_len <= s_max &&
+                   n_slots >= 1,
                QUIC_E_SHAPE, "attn_prefill: bad sequence count or lengths");
   QUIC_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)kcache % 16 == 0) && ((uintptr_t)vcache % 16 == 0) &&
                    ((uintptr_t)out % 16 == 0),
@@ -284,6 +287,7 @@ int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, c
   a.out = (half*)out;
   a.rows = rows;
   a.s_max = s_max;
+  a.n_slots = n_slots;
   a.scale = scale > 0.f ? scale : 0.125f;
   if (n_seq == 1 || rows <= 1024) {  // one sequence or few rows: bound by the per-row key walk
     dim3 grid((max_len + 15) / 16, kHeads, n_seq);
@@ -299,7 +303,8 @@ int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, c
 
 extern "C" int quic_attn_prefill(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
                                  const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len,
-                                 int32_t rows, int32_t s_max, float scale, void* out, void* stream) {
+                                 int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,
+                                 void* stream) {
   return quic::attn_prefill_launch(q, kcache, vcache, seq_start, seq_len, seq_slot, n_seq, max_len, rows, s_max,
-                                   scale, out, (cudaStream_t)stream, false);
+                                   n_slots, scale, out, (cudaStream_t)stream, false);
 }

@@ -76,49 +76,6 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-// ---- debug timeline (-DQUIC_TRACE) ---------------------------------------------
-// Thread 0 of CTA 0 of every launch logs (kernel id, globaltimer when its wait
-// returned, globaltimer at its end); read back with quic_trace_log().
-#ifdef QUIC_TRACE
-struct TraceRow { unsigned long long id, t_wait, t_end; };
-// one pointer pair per translation unit, installed by QUIC_TRACE_SETTER(name)
-static __device__ TraceRow* g_tlog;
-static __device__ unsigned* g_tlog_n_ptr;
-#define QUIC_TRACE_SETTER(name)                                                      \
-  extern "C" int quic_trace_set_##name(void* rows, void* counter) {                  \
-    cudaMemcpyToSymbol(quic::g_tlog, &rows, sizeof(void*));                          \
-    return (int)cudaMemcpyToSymbol(quic::g_tlog_n_ptr, &counter, sizeof(void*));     \
-  }
-__device__ __forceinline__ unsigned long long gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ int tlog_begin(int id) {
-  if (threadIdx.x || blockIdx.x || blockIdx.y || blockIdx.z) return -1;
-  if (g_tlog == nullptr) return -1;
-  const int i = atomicAdd(g_tlog_n_ptr, 1u) & 8191;
-  g_tlog[i].id = id;
-  g_tlog[i].t_wait = gtimer();
-  return i;
-}
-__device__ __forceinline__ void tlog_end(int i) {
-  if (i >= 0) g_tlog[i].t_end = gtimer();
-}
-#define QUIC_TLOG_BEGIN(id) const int tlog_i__ = tlog_begin(id)
-#define QUIC_TLOG_END() tlog_end(tlog_i__)
-struct TlogScope {
-  int i;
-  __device__ explicit TlogScope(int id) : i(tlog_begin(id)) {}
-  __device__ ~TlogScope() { tlog_end(i); }
-};
-#define QUIC_TLOG_SCOPE(id) TlogScope tlog_scope__(id)
-#else
-#define QUIC_TLOG_SCOPE(id)
-#define QUIC_TLOG_BEGIN(id)
-#define QUIC_TLOG_END()
-#endif
-
 // ---- small device utilities -------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -159,20 +159,20 @@ cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int3
 // Fused consumers of split-K partial sums [splits][batch][N] (fp32).
 cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
                                  const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,
-                                 half* kcache, half* vcache, int s_max, int batch, cudaStream_t st);
+                                 half* kcache, half* vcache, int s_max, int n_slots, int batch, cudaStream_t st);
 cudaError_t launch_rmsnorm_part(const float* part, int splits, const half* residual, const half* w, float eps,
                                 half* y, half* sum_out, int rows, cudaStream_t st);
 cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t* pos, const half* cos_t,
                             const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
-                            int batch, cudaStream_t st);
+                            int n_slots, int batch, cudaStream_t st);
 cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream_t st);
 // prefill pieces, chainable with programmatic dependent launch
 cudaError_t launch_qkv_rope_append(const half* qkv, const int32_t* slots, const int32_t* positions, const half* cos_t,
                                    const half* sin_t, int max_pos, half* q_out, half* kcache, half* vcache, int s_max,
-                                   int rows, cudaStream_t st, bool pdl);
+                                   int n_slots, int rows, cudaStream_t st, bool pdl);
 int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
                         const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len, int32_t rows,
-                        int32_t s_max, float scale, void* out, cudaStream_t stream, bool pdl);
+                        int32_t s_max, int32_t n_slots, float scale, void* out, cudaStream_t stream, bool pdl);
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st);
 int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st,
@@ -182,6 +182,11 @@ int w4a16_gemm_tc_swiglu(const half* x, const quic_w4_t& w, half* act, int m, cu
 bool lm_head_tc_supported(int batch, int vocab);
 int lm_head_tc_tiles(int vocab);
 int launch_lm_head_tc(const LmHeadArgs& a, cudaStream_t st);
-int lm_head_tc_status();
+// Error words of the tcgen05 kernels ([0] GEMM, [1] lm_head; w4_gemm_tc.cu): device address,
+// an asynchronous copy to page-locked memory, and the value seen by that copy (taken, i.e.
+// exchanged with zero, when it is not 0).
+int* tc_status_words();
+int tc_status_poll_async(cudaStream_t st);
+int tc_status_polled(cudaStream_t st);
 
 }  // namespace quic

@@ -24,19 +24,6 @@ namespace {
 
 constexpr int kQuarter = kHidden / 4;  // 224 threads cover a 896-wide row, 4 each
 
-// Debug build (-DQUIC_TRACE): SM-clock stamps of the first CTAs of the last launch
-// of each kernel, read back with quic_trace_read().  Compiled out otherwise.
-#ifdef QUIC_TRACE
-__device__ long long g_trace[4][8][8];
-#define QUIC_STAMP(kernel, idx)                                                   \
-  do {                                                                            \
-    if (threadIdx.x == 0 && blockIdx.x < 8 && blockIdx.y == 0 && blockIdx.z == 0) \
-      g_trace[kernel][blockIdx.x][idx] = clock64();                               \
-  } while (0)
-#else
-#define QUIC_STAMP(kernel, idx)
-#endif
-
 struct Half4 {
   half2 a, b;
 };
@@ -228,7 +215,6 @@ __global__ void __launch_bounds__(224) qkv_kernel(const QkvArgs a) {
   dequant_group(gr, n, gf);
   pdl_trigger_early();
   pdl_wait();
-  QUIC_TLOG_BEGIN(1);
 
   const half* src[M];
   int pos[M];
@@ -310,7 +296,6 @@ __global__ void __launch_bounds__(224) qkv_kernel(const QkvArgs a) {
       base[(((size_t)sl * kKvHeads + kvh) * a.s_max + p) * kHeadDim + dim] = o16;
     }
   }
-  QUIC_TLOG_END();
 }
 
 // ---------------------------------------------------------------------------
@@ -334,7 +319,6 @@ __global__ void __launch_bounds__(224) oproj_kernel(const OProjArgs a) {
   dequant_group(gr, n, gf);
   pdl_trigger_early();
   pdl_wait();
-  QUIC_TLOG_BEGIN(3);
 
   {
     const int t = threadIdx.x;  // 224 threads x 4 elements
@@ -427,7 +411,6 @@ __global__ void __launch_bounds__(224) oproj_kernel(const OProjArgs a) {
     const float o = __half2float(__float2half_rn(v));
     a.xres_out[(size_t)b * kHidden + n] = __float2half_rn(resid[i] + o);
   }
-  QUIC_TLOG_END();
 }
 
 // ---------------------------------------------------------------------------
@@ -458,7 +441,6 @@ __global__ void __launch_bounds__(256, M == 1 ? 2 : 1) gateup_kernel(const GateU
   const int n = tile * 32 + lane;
   const int row0 = blockIdx.y * M;
 
-  QUIC_STAMP(2, 0);
   GroupRegs gg, gu;
   load_group(gg, a.w, g, n);
   load_group(gu, a.w, g, n + kInter);
@@ -469,18 +451,14 @@ __global__ void __launch_bounds__(256, M == 1 ? 2 : 1) gateup_kernel(const GateU
     dequant_group(gg, n, fg);
     dequant_group(gu, n + kInter, fu);
   }
-  QUIC_STAMP(2, 1);
   pdl_trigger_early();
   pdl_wait();
-  QUIC_TLOG_BEGIN(4);
-  QUIC_STAMP(2, 2);
 
   const half* src[M];
 #pragma unroll
   for (int m = 0; m < M; ++m)
     src[m] = (row0 + m < a.batch) ? a.xres + (size_t)(row0 + m) * kHidden : nullptr;
   residual_norm_to_smem<M>(xs, red, src, nullptr, 0, a.batch, row0, lnw, a.eps, nullptr);
-  QUIC_STAMP(2, 3);
 
   float ag[M], au[M];
 #pragma unroll
@@ -498,9 +476,7 @@ __global__ void __launch_bounds__(256, M == 1 ? 2 : 1) gateup_kernel(const GateU
     red[((warp * M + m) * 2 + 0) * 32 + lane] = ag[m];
     red[((warp * M + m) * 2 + 1) * 32 + lane] = au[m];
   }
-  QUIC_STAMP(2, 4);
   __syncthreads();
-  QUIC_STAMP(2, 5);
 
   // Warps 0 and 1 finish the (at most two) tiles this CTA touches.
   if (warp < 2) {
@@ -531,8 +507,6 @@ __global__ void __launch_bounds__(256, M == 1 ? 2 : 1) gateup_kernel(const GateU
       }
     }
   }
-  QUIC_STAMP(2, 6);
-  QUIC_TLOG_END();
 }
 
 // ---------------------------------------------------------------------------
@@ -559,7 +533,6 @@ __global__ void __launch_bounds__(256) down_kernel(const DownArgs a) {
   }
   pdl_trigger_early();
   pdl_wait();
-  QUIC_TLOG_BEGIN(5);
 
   // Activation slice: add the two gate/up partial planes, round to fp16 (the
   // reference's linear outputs are fp16), SwiGLU, round again.
@@ -609,7 +582,6 @@ __global__ void __launch_bounds__(256) down_kernel(const DownArgs a) {
     for (int g = 0; g < 8; ++g) v += red[(g * M + m) * 32 + lane];
     a.partial[((size_t)ks * a.batch + b) * kHidden + n] = v;
   }
-  QUIC_TLOG_END();
 }
 
 template <int M>
@@ -661,12 +633,4 @@ cudaError_t launch_down(const DownArgs& a, cudaStream_t s, bool pdl) {
 
 }  // namespace quic
 
-#ifdef QUIC_TRACE
-extern "C" int quic_trace_read(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, quic::g_trace, sizeof(long long) * 4 * 8 * 8);
-}
-#endif
 
-#ifdef QUIC_TRACE
-QUIC_TRACE_SETTER(layers)
-#endif

@@ -6,6 +6,7 @@
 // reference (src/engine.py:78-107, src/model.py:272-303).  Token ids, positions
 // and the row -> slot map live in device memory, so a captured graph is valid
 // for any position and consecutive steps need no host round trip.
+#include <cstdio>
 #include <new>
 
 #include "decode_kernels.cuh"
@@ -376,7 +377,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     int rc = w4a16_gemm_tc(xn, L.qkv, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_qkv_post_part(part, sp, (const half*)L.qkv.bias, d->rows, d->pos, (const half*)m->rope_cos,
-                                   (const half*)m->rope_sin, m->max_pos, qbuf, kc, vc, d->s_max, B, st));
+                                   (const half*)m->rope_sin, m->max_pos, qbuf, kc, vc, d->s_max, d->n_slots, B, st));
     AttnArgs aa = {};
     aa.q = qbuf;
     aa.k = kc;
@@ -546,7 +547,18 @@ extern "C" int quic_graph_run_host(void* graph, void* stream, const int32_t* hos
   QUIC_CUDA(cudaGraphLaunch(g->exec, st));
   if (n_out > 0)
     QUIC_CUDA(cudaMemcpyAsync(host_out, dev_out, sizeof(int32_t) * n_out, cudaMemcpyDeviceToHost, st));
+  // the error words of the tensor-core kernels ride along with the tokens
+  int rc = tc_status_poll_async(st);
+  if (rc != QUIC_OK) return rc;
   QUIC_CUDA(cudaStreamSynchronize(st));
+  const int word = tc_status_polled(st);
+  if (word != 0) {
+    static char msg[160];
+    snprintf(msg, sizeof(msg),
+             "decode: a bounded wait of a tensor-core kernel gave up (status 0x%x); the tokens of this call are invalid",
+             word);
+    return fail(QUIC_E_TIMEOUT, msg);
+  }
   return QUIC_OK;
 }
 

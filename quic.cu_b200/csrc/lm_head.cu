@@ -63,7 +63,6 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_kernel(const LmHeadArgs a
   }
   pdl_trigger_early();
   pdl_wait();
-  QUIC_TLOG_BEGIN(6);
 
   // ---- activation: (x + partial sums) -> RMSNorm -> xs (natural order) ----
   {
@@ -246,7 +245,6 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_kernel(const LmHeadArgs a
     }
   }
 
-  QUIC_TLOG_END();
   // Last CTA (over the whole grid) reduces the candidates of every row.
   __threadfence();
   __syncthreads();
@@ -355,6 +353,3 @@ extern "C" int quic_lm_head_argmax(const void* x, const void* norm_w, float eps,
   return QUIC_OK;
 }
 
-#ifdef QUIC_TRACE
-QUIC_TRACE_SETTER(lm)
-#endif

@@ -75,7 +75,6 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   const uint32_t idesc = umma_idesc_f16(MT);
   pdl_launch_dependents();
   pdl_wait();  // the normalised activations come from the previous kernel
-  QUIC_TLOG_SCOPE(12);
 
   if (warp == 4) {
     if (lane == 0) {
@@ -196,8 +195,6 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   }
 }
 
-__device__ int g_lm_tc_status;
-
 template <int MT>
 int run(const LmHeadArgs& a, cudaStream_t st) {
   CUtensorMap tm_e, tm_x;
@@ -207,8 +204,9 @@ int run(const LmHeadArgs& a, cudaStream_t st) {
   rc = make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x_normed, (uint64_t)a.batch, kHidden, MT, kBlockK,
                 CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != QUIC_OK) return rc;
-  int* status = nullptr;
-  QUIC_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_lm_tc_status));
+  int* status = tc_status_words();  // word 1 is this kernel's
+  QUIC_REQUIRE(status != nullptr, QUIC_E_CUDA, "lm_head: no address for the tensor path's error words");
+  status += 1;
   const size_t smem = LmSmem<MT>::kTotal;
   QUIC_CUDA(cudaFuncSetAttribute(lm_head_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   QUIC_CUDA(launch(lm_head_tc_kernel<MT>, dim3(a.vocab / kTileN), dim3(kLmThreads), smem, st, true, tm_e, tm_x, a,
@@ -233,16 +231,5 @@ int launch_lm_head_tc(const LmHeadArgs& a, cudaStream_t st) {
   return run<128>(a, st);
 }
 
-int lm_head_tc_status() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_lm_tc_status, sizeof(int)) != cudaSuccess) return -1;
-  int zero = 0;
-  cudaMemcpyToSymbol(g_lm_tc_status, &zero, sizeof(int));
-  return v;
-}
-
 }  // namespace quic
 
-#ifdef QUIC_TRACE
-QUIC_TRACE_SETTER(lmtc)
-#endif

@@ -40,7 +40,6 @@ __global__ void __launch_bounds__(224) rmsnorm_kernel(const half* __restrict__ x
   const uint2 wv = *reinterpret_cast<const uint2*>(w + c);  // weights: not produced by the chain
   pdl_launch_dependents();
   pdl_wait();
-  QUIC_TLOG_SCOPE(8);
   uint2 r = make_uint2(0, 0);
   if (res != nullptr) r = *reinterpret_cast<const uint2*>(res + (size_t)row * kHidden + c);
   float2 a, b;
@@ -232,7 +231,6 @@ __global__ void embed_rows_kernel(const half* __restrict__ embed, const int32_t*
   const int b = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
-  QUIC_TLOG_SCOPE(11);
   if (b >= batch) return;
   int t = tok[rows[b]];
   t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
@@ -248,17 +246,17 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
                                 const int32_t* __restrict__ pos, const half* __restrict__ cos_t,
                                 const half* __restrict__ sin_t, int max_pos, half* __restrict__ qbuf,
                                 half* __restrict__ kcache, half* __restrict__ vcache, int s_max, int batch,
-                                const int32_t* __restrict__ row_pos, int q_head_major) {
+                                const int32_t* __restrict__ row_pos, int q_head_major, int n_slots) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
-  QUIC_TLOG_SCOPE(9);
   if (idx >= batch * (kQkvN / 2)) return;
   const int b = idx / (kQkvN / 2), c2 = idx % (kQkvN / 2);
   const int head = c2 >> 5, pair = c2 & 31;  // stored columns (2*pair, 2*pair+1) = dims (pair, pair+32)
   const int slot = rows[b];
+  const bool slot_ok = slot >= 0 && slot < n_slots;  // a row with a slot outside the cache appends nothing
   // decode: the row's position is its slot's; prefill: every row (token) brings its own
-  const int p = row_pos != nullptr ? row_pos[b] : pos[slot];
+  const int p = row_pos != nullptr ? row_pos[b] : (slot_ok ? pos[slot] : 0);
   float2 v;
   if (part != nullptr) {  // fp16(sum of the split-K partials) + bias, as the GEMM epilogue would do
     float2 p[16];
@@ -280,7 +278,7 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
   }
   float lo = v.x, hi = v.y;
   if (head < kHeads + kKvHeads) {
-    const int pp = p < max_pos ? p : max_pos - 1;
+    const int pp = p < max_pos ? (p < 0 ? 0 : p) : max_pos - 1;
     const float c = __half2float(cos_t[(size_t)pp * 32 + pair]), s = __half2float(sin_t[(size_t)pp * 32 + pair]);
     lo = v.x * c - v.y * s;
     hi = v.x * s + v.y * c;
@@ -289,7 +287,7 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
   if (head < kHeads) {
     dst = q_head_major ? qbuf + ((size_t)head * batch + b) * kHeadDim : qbuf + ((size_t)b * kHeads + head) * kHeadDim;
   } else {
-    if (p >= s_max || p < 0) return;
+    if (p >= s_max || p < 0 || !slot_ok) return;
     const int kvh = (head - kHeads) & 1;
     half* base = (head < kHeads + kKvHeads) ? kcache : vcache;
     dst = base + (((size_t)slot * kKvHeads + kvh) * s_max + p) * kHeadDim;
@@ -306,7 +304,6 @@ __global__ void swiglu_fused_kernel(const half* __restrict__ gu, const float* __
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
-  QUIC_TLOG_SCOPE(10);
   if (idx >= (size_t)batch * (kInter / 2)) return;
   const int b = idx / (kInter / 2), i2 = idx % (kInter / 2);
   float2 g, u;
@@ -347,27 +344,27 @@ cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int3
 }
 cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t* pos, const half* cos_t,
                             const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
-                            int batch, cudaStream_t st) {
+                            int n_slots, int batch, cudaStream_t st) {
   const int total = batch * (kQkvN / 2);
   return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, qkv, (const float*)nullptr, 0,
                 (const half*)nullptr, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch,
-                (const int32_t*)nullptr, 0);
+                (const int32_t*)nullptr, 0, n_slots);
 }
 cudaError_t launch_qkv_rope_append(const half* qkv, const int32_t* slots, const int32_t* positions, const half* cos_t,
                                    const half* sin_t, int max_pos, half* q_out, half* kcache, half* vcache, int s_max,
-                                   int rows, cudaStream_t st, bool pdl) {
+                                   int n_slots, int rows, cudaStream_t st, bool pdl) {
   const int total = rows * (kQkvN / 2);
   return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, pdl, qkv, (const float*)nullptr, 0,
                 (const half*)nullptr, slots, (const int32_t*)nullptr, cos_t, sin_t, max_pos, q_out, kcache, vcache,
-                s_max, rows, positions, 1);
+                s_max, rows, positions, 1, n_slots);
 }
 cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
                                  const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,
-                                 half* kcache, half* vcache, int s_max, int batch, cudaStream_t st) {
+                                 half* kcache, half* vcache, int s_max, int n_slots, int batch, cudaStream_t st) {
   const int total = batch * (kQkvN / 2);
   return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, true, (const half*)nullptr, part,
                 splits, bias, rows, pos, cos_t, sin_t, max_pos, qbuf, kcache, vcache, s_max, batch,
-                (const int32_t*)nullptr, 0);
+                (const int32_t*)nullptr, 0, n_slots);
 }
 cudaError_t launch_rmsnorm_part(const float* part, int splits, const half* residual, const half* w, float eps,
                                 half* y, half* sum_out, int rows, cudaStream_t st) {
@@ -442,15 +439,16 @@ extern "C" int quic_swiglu(const void* gate, const void* up, void* y, int32_t ro
 
 extern "C" int quic_qkv_rope_append(const void* qkv, const int32_t* slots, const int32_t* positions,
                                     const void* cos_t, const void* sin_t, int32_t max_pos, void* q_out,
-                                    void* kcache, void* vcache, int32_t s_max, int32_t rows, void* stream) {
+                                    void* kcache, void* vcache, int32_t s_max, int32_t n_slots, int32_t rows,
+                                    void* stream) {
   QUIC_REQUIRE(qkv && slots && positions && cos_t && sin_t && q_out && kcache && vcache, QUIC_E_ARG,
                "qkv_rope_append: null tensor");
-  QUIC_REQUIRE(rows >= 0 && rows <= (1 << 20) && s_max >= 1 && max_pos >= 1, QUIC_E_SHAPE,
-               "qkv_rope_append: bad row count or cache length");
+  QUIC_REQUIRE(rows >= 0 && rows <= (1 << 20) && s_max >= 1 && max_pos >= 1 && n_slots >= 1, QUIC_E_SHAPE,
+               "qkv_rope_append: bad row count or cache geometry");
   if (rows == 0) return QUIC_OK;
   QUIC_CUDA(launch_qkv_rope_append((const half*)qkv, slots, positions, (const half*)cos_t, (const half*)sin_t,
-                                   (int)max_pos, (half*)q_out, (half*)kcache, (half*)vcache, (int)s_max, (int)rows,
-                                   (cudaStream_t)stream, false));
+                                   (int)max_pos, (half*)q_out, (half*)kcache, (half*)vcache, (int)s_max, (int)n_slots,
+                                   (int)rows, (cudaStream_t)stream, false));
   return QUIC_OK;
 }
 
@@ -496,6 +494,3 @@ extern "C" int quic_gemm_f16(const void* x, const void* w, const void* bias, voi
 }
 
 
-#ifdef QUIC_TRACE
-QUIC_TRACE_SETTER(ops)
-#endif

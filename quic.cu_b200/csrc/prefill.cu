@@ -148,9 +148,9 @@ extern "C" int quic_prefill(const quic_model_t* m, const quic_prefill_t* p, void
     half* vc = kc + kv_plane;
     if ((rc = linear_rows(xn, L.qkv, qkv, rows, ws, stream)) != QUIC_OK) return rc;
     QUIC_CUDA(launch_qkv_rope_append(qkv, p->row_slot, p->row_pos, (const half*)m->rope_cos, (const half*)m->rope_sin,
-                                     m->max_pos, q, kc, vc, p->s_max, rows, st, true));
+                                     m->max_pos, q, kc, vc, p->s_max, p->n_slots, rows, st, true));
     if ((rc = attn_prefill_launch(q, kc, vc, p->seq_start, p->seq_len, p->seq_slot, p->n_seq, p->max_len, rows,
-                                  p->s_max, 0.125f /* 64^-0.5, src/model.py:129 */, attn, st, true)) != QUIC_OK)
+                                  p->s_max, p->n_slots, 0.125f /* 64^-0.5, src/model.py:129 */, attn, st, true)) != QUIC_OK)
       return rc;
     if ((rc = linear_rows(attn, L.o, tmp, rows, ws, stream)) != QUIC_OK) return rc;
     // h += o ; xn = norm(h)

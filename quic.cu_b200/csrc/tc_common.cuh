@@ -8,7 +8,7 @@
 namespace quic {
 
 constexpr int kTileN = 128;   // rows of the weight-side tile (UMMA M)
-constexpr int kBlockK = 64;   // k per pipeline stage: 64 fp16 = one 128-byte swizzle row
+constexpr int kBlockK = 64;   // k per swizzle atom: 64 fp16 = one 128-byte swizzle row (a GEMM stage holds two)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -17,9 +17,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-// Bounded wait for the phase with the given parity; false on timeout.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Bounded wait for the phase with the given parity; false on timeout (after `limit` probes).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -35,8 +35,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 // The same wait for roles that are many warps wide and not on the critical path of the MMA
 // issue: sleeps between probes so the probes do not crowd the issuing thread's instructions
 // out of the shared-memory pipeline.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, uint32_t sleep_ns) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, uint32_t sleep_ns,
+                                                  uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

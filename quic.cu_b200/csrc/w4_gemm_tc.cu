@@ -28,28 +28,14 @@ namespace {
 
 constexpr int kCounterInts = 4096;  // arrival counters at the head of the split-K workspace
 
-__device__ int g_tc_status;
-#ifdef QUIC_TRACE
-__device__ long long g_gemm_trace[2][20][6];
-#define GSTAMP(it, i) do { if (tid == 0 && blockIdx.x < 2 && blockIdx.y == 0 && (it) < 20) g_gemm_trace[blockIdx.x][it][i] = clock64(); } while (0)
-// role stamps of CTA (0,0,0) of the last launch of each weight shape
-__device__ long long g_gemm_roles[4][8];
-__device__ long long g_gemm_mma[4][16][3];
-#define GMMA(it, i)                                                                      \
-  do {                                                                                   \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 16)               \
-      g_gemm_mma[a.w.n == 1152 ? 0 : (a.w.n == 9728 ? 2 : (a.w.k == 896 ? 1 : 3))][it][i] = clock64(); \
-  } while (0)
-#define GROLE(i)                                                                         \
-  do {                                                                                   \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)                            \
-      g_gemm_roles[a.w.n == 1152 ? 0 : (a.w.n == 9728 ? 2 : (a.w.k == 896 ? 1 : 3))][i] = clock64(); \
-  } while (0)
-#else
-#define GSTAMP(it, i)
-#define GROLE(i)
-#define GMMA(it, i)
-#endif  // 0 = ok; otherwise (code << 16) | block of the first failure
+// Error words of the tensor path: [0] the GEMM, [1] the tensor lm_head.  0 = ok; otherwise
+// (code << 16) | block of the first bounded wait that gave up.
+__device__ int g_tc_status[2];
+
+// What a test may change for the launches that follow (quic_w4a16_tensor_test_hook): the probe
+// limit of the bounded waits and one k block whose packed weight tile the producer never requests.
+uint32_t g_spin_limit = kSpinLimit;
+int g_skip_kblock = -1;
 
 struct GemmArgs {
   quic_w4_t w;
@@ -59,6 +45,8 @@ struct GemmArgs {
   int m_total;
   int kblocks_per_split;
   int mtl;     // batch-row tiles per CTA (2 from 129 rows up)
+  uint32_t spin_limit;  // probes of a bounded wait
+  int skip_kblock;      // test hook: the weight tile of this k block is never requested (-1: none)
   // SwiGLU fused into the epilogue of the gate|up linear: the CTA's 128 weight rows are 64
   // gate rows and the 64 up rows of the same columns (two 64-row TMA boxes per stage), and y
   // is the activation [m_total, N / 2] = silu(gate) * up.
@@ -124,7 +112,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   const int kb0 = split * a.kblocks_per_split;
   const int kb1 = min(kb_total, kb0 + a.kblocks_per_split);
   const int nkb = kb1 - kb0;
-  if (tid == 0) GROLE(0);
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -172,7 +159,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   // requests the packed weight tiles of the first ring pass, THEN waits for the predecessor
   // and requests the x tiles; the other roles wait before they touch global memory.
   pdl_launch_dependents();
-  if (tid == 0) GROLE(1);
 
   if (warp == kConsumers / 32) {
     // ---------------- TMA producer ----------------
@@ -181,6 +167,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       for (int it = 0; it < first; ++it) {
         const uint32_t raw_s = base + it * L::kStage;
         const uint32_t full = smem_u32(&bar_full[it]);
+        if (kb0 + it == a.skip_kblock) continue;  // test hook: the consumers' wait for this tile runs out
         mbar_expect_tx(full, kRawBytes);
         if (a.fuse_swiglu) {  // two boxes of 64 rows: gate rows, then the up rows of the same columns
           tma_load_2d(raw_s, &tm_w, (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
@@ -190,7 +177,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         }
       }
       pdl_wait();
-      GROLE(2);
       for (int it = 0; it < first; ++it) {
         const uint32_t xfull = smem_u32(&bar_aready[it]);
         mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL * kSub);
@@ -201,18 +187,20 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       }
       // (ring position and phase are carried along: the depth is a run-time value)
       for (int it = first, stage = 0, pass = 1; it < nkb; ++it) {
-        if (!mbar_wait(smem_u32(&bar_empty[stage]), (pass - 1) & 1)) {
+        if (!mbar_wait(smem_u32(&bar_empty[stage]), (pass - 1) & 1, a.spin_limit)) {
           fail_s = 2;
           break;
         }
         const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
         const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_aready[stage]);
-        mbar_expect_tx(full, kRawBytes);
-        if (a.fuse_swiglu) {
-          tma_load_2d(raw_s, &tm_w, (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
-          tma_load_2d(raw_s + kRawBytes / 2, &tm_w, half_n + (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
-        } else {
-          tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+        if (kb0 + it != a.skip_kblock) {  // (test hook: see the first pass)
+          mbar_expect_tx(full, kRawBytes);
+          if (a.fuse_swiglu) {
+            tma_load_2d(raw_s, &tm_w, (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
+            tma_load_2d(raw_s + kRawBytes / 2, &tm_w, half_n + (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
+          } else {
+            tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+          }
         }
         mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL * kSub);
 #pragma unroll
@@ -232,15 +220,12 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       // of these costs the issuing thread a round trip, and at these sizes the loop is bound
       // by that, not by the tensor pipe.
       for (int it = 0, stage = 0, pass = 0; it < nkb; ++it) {
-        if (!mbar_wait(smem_u32(&bar_aready[stage]), pass & 1)) {
+        if (!mbar_wait(smem_u32(&bar_aready[stage]), pass & 1, a.spin_limit)) {
           fail_s = 3;
           break;
         }
         if (it == 0) tc_fence_after();
-        if (it == 0) GROLE(3);
-        GMMA(it, 0);
         const uint32_t b_s = base + stage * L::kStage + kRawBytes, a_s = b_s + L::kB;
-#ifndef QUIC_TC_NO_MMA  // timing experiments only
 #pragma unroll
         for (int i = 0; i < MTL; ++i) {
           if (i > 0 && m0 + i * MT >= a.m_total) break;  // tile of rows beyond the end
@@ -252,17 +237,13 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
                        umma_desc_sw128(b_s + (i * kSub + sub) * L::kBTile + k * 32), idesc,
                        (it > 0 || sub > 0 || k > 0) ? 1u : 0u);
         }
-#endif
-        GMMA(it, 1);
         if (it + kStages < nkb) umma_commit(smem_u32(&bar_empty[stage]));
         if (it == nkb - 1) umma_commit(smem_u32(&bar_done));
-        GMMA(it, 2);
         if (++stage == kStages) {
           stage = 0;
           ++pass;
         }
       }
-      GROLE(4);
     }
   } else {
     // ---------------- consumers: dequantise ----------------
@@ -270,7 +251,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     for (int it = 0, stage = 0, pass = 0; it < nkb; ++it) {
       // "full" of this phase also means the MMAs of the stage's previous use are complete
       // (the TMA warp refilled it only after "empty"), so the A tile may be overwritten.
-      if (!mbar_wait(smem_u32(&bar_full[stage]), pass & 1)) {
+      if (!mbar_wait(smem_u32(&bar_full[stage]), pass & 1, a.spin_limit)) {
         fail_s = 1;
         break;
       }
@@ -280,7 +261,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       const int g = ((kb0 + it) * kStageK) / kGroup - g_first;
       const half2 s2 = __half2half2(sc_s[g][row]);
       const half2 zp = zp_to_half2(zp_s[g][row]);
-#ifndef QUIC_TC_NO_DEQUANT  // timing experiments only
 #pragma unroll
       for (int jj = 0; jj < 2 * kSub; ++jj) {
         const int j = 2 * kSub * part + jj;  // k-word 0..15 of the stage: atom j / 8, 16-byte chunk j % 8
@@ -297,7 +277,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         o.w = __byte_perm(u2, u3, 0x7632);  // (k6, k7)
         *reinterpret_cast<uint4*>(a_g + (j >> 3) * L::kASub + sw128_offset(row, j & 7)) = o;
       }
-#endif
       fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_aready[stage]));
@@ -308,18 +287,15 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     }
   }
   __syncwarp();
-  if (tid == 0) GROLE(5);
 
   // wait for the whole accumulation, then read the accumulator out of tensor memory
   if (warp < kConsumers / 32) {
     pdl_wait();  // the output / partial buffers may still be read by earlier kernels of the chain
-    QUIC_TLOG_SCOPE(7);
     bool ok = !fail_s && nkb > 0;
-    if (ok) ok = mbar_wait_relaxed(smem_u32(&bar_done), 0, 64);
-    if (tid == 0) GROLE(6);
+    if (ok) ok = mbar_wait_relaxed(smem_u32(&bar_done), 0, 64, a.spin_limit);
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
-    if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status, 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
+    if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status[0], 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
     if (a.fuse_swiglu) {
       // TMEM lanes 0-63 hold the gate rows, 64-127 the up rows of the same 64 columns.  The up
       // warps park their (fp16-rounded) values in shared memory -- the operand ring is free once
@@ -403,7 +379,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       }
     }
   }
-  if (tid == 0) GROLE(7);
   tc_fence_before();
   __syncthreads();
   if (warp == 0)
@@ -447,7 +422,10 @@ __global__ void tc_splitk_finish_kernel(const float* __restrict__ part, const ha
 }
 
 template <int MT>
-int run(const half* x, const GemmArgs& a, int splits, cudaStream_t st) {
+int run(const half* x, const GemmArgs& args, int splits, cudaStream_t st) {
+  GemmArgs a = args;
+  a.spin_limit = g_spin_limit;
+  a.skip_kblock = g_skip_kblock;
   CUtensorMap tm_w, tm_x;
   // packed weights int32 [K/8, N]: box = 8 k-words x 128 rows; x fp16 [m, K]: box = MT rows x 64 k,
   // written with the 128-byte swizzle the UMMA descriptor expects (rows past m read as zero)
@@ -573,30 +551,70 @@ int w4a16_gemm_tc_swiglu(const half* x, const quic_w4_t& w, half* act, int m, cu
 
 }  // namespace quic
 
-// Error word of the tensor path: 0, or (code << 16 | block) of the first bounded wait that
-// gave up since the last call.  Synchronises the device; meant for tests and debugging.
-extern "C" int quic_w4a16_tensor_status(void) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, quic::g_tc_status, sizeof(int)) != cudaSuccess) return -1;
-  int zero = 0;
-  cudaMemcpyToSymbol(quic::g_tc_status, &zero, sizeof(int));
-  const int lm = quic::lm_head_tc_status();
-  if (v == 0) v = lm;
+namespace quic {
+namespace {
+__global__ void tc_status_take_kernel(int* out) {
+  out[0] = atomicExch(&g_tc_status[0], 0);
+  out[1] = atomicExch(&g_tc_status[1], 0);
+}
+struct StatusHost {
+  int* words[16] = {};   // device address of g_tc_status per device
+  int* pinned = nullptr;  // two page-locked ints the status travels through
+};
+StatusHost g_status_host;
+}  // namespace
+
+// Device address of the error words (index 1 is the tensor lm_head's).  Looks the symbol up on
+// first use per device: call it once outside any stream capture.
+int* tc_status_words() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  if (g_status_host.words[dev] == nullptr)
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&g_status_host.words[dev]), g_tc_status) != cudaSuccess)
+      return nullptr;
+  return g_status_host.words[dev];
+}
+
+// Enqueues a copy of the error words to page-locked host memory on `st`; tc_status_polled()
+// reads them once the stream has been synchronised.  Costs no synchronisation of its own.
+int tc_status_poll_async(cudaStream_t st) {
+  int* words = tc_status_words();
+  if (words == nullptr) return QUIC_OK;
+  if (g_status_host.pinned == nullptr)
+    QUIC_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&g_status_host.pinned), 2 * sizeof(int), cudaHostAllocDefault));
+  QUIC_CUDA(cudaMemcpyAsync(g_status_host.pinned, words, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+  return QUIC_OK;
+}
+// After the stream of tc_status_poll_async is idle: 0, or the first non-zero word, which is then
+// taken (exchanged with zero on the device, so a word set meanwhile is not lost).
+int tc_status_polled(cudaStream_t st) {
+  if (g_status_host.pinned == nullptr) return 0;
+  const int v = g_status_host.pinned[0] ? g_status_host.pinned[0] : g_status_host.pinned[1];
+  if (v == 0) return 0;
+  tc_status_take_kernel<<<1, 1, 0, st>>>(g_status_host.pinned);  // page-locked memory is device-accessible (UVA)
+  cudaStreamSynchronize(st);
   return v;
 }
+}  // namespace quic
 
-#ifdef QUIC_TRACE
-extern "C" int quic_gemm_trace_read(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, quic::g_gemm_trace, sizeof(long long) * 2 * 20 * 6);
+// Error word of the tensor path: 0, or (code << 16 | block) of the first bounded wait that gave
+// up since the last call (code 1: a weight tile never landed, 2: a ring stage never drained,
+// 3: operands or the accumulation never completed; bit 15 marks the tensor lm_head).  The word
+// is exchanged with zero on the device.  Synchronises the device.
+extern "C" int quic_w4a16_tensor_status(void) {
+  if (quic::tc_status_words() == nullptr) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (quic::tc_status_poll_async(nullptr) != QUIC_OK) return -1;
+  if (cudaStreamSynchronize(nullptr) != cudaSuccess) return -1;
+  return quic::tc_status_polled(nullptr);
 }
-#endif
 
-#ifdef QUIC_TRACE
-QUIC_TRACE_SETTER(gemm)
-extern "C" int quic_trace_read_gemm_mma(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, quic::g_gemm_mma, sizeof(long long) * 4 * 16 * 3);
+// Test hook for the bounded waits of the tcgen05 GEMM: launches that follow probe at most
+// `spin_limit` times per wait (0 restores the default) and never request the packed weight
+// tile of k block `skip_kblock` (128 k per block; -1: none), so the waits for it run out, the
+// CTA's roles leave their loops, the error word is set and the kernel returns with its tensor
+// memory released.  Nothing faults and nothing waits without a bound.
+extern "C" void quic_w4a16_tensor_test_hook(uint32_t spin_limit, int32_t skip_kblock) {
+  quic::g_spin_limit = spin_limit ? spin_limit : quic::kSpinLimit;
+  quic::g_skip_kblock = skip_kblock;
 }
-extern "C" int quic_trace_read_gemm_roles(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, quic::g_gemm_roles, sizeof(long long) * 4 * 8);
-}
-#endif

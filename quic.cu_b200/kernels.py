@@ -127,11 +127,12 @@ SIGNATURES = {
     "quic_w4a16_linear": (C.c_int, [_P, C.POINTER(W4), _P, _I32, _I32, _P, _P]),
     "quic_w4a16_workspace_bytes": (_I64, [_I32, _I32, _I32]),
     "quic_w4a16_tensor_status": (C.c_int, []),
+    "quic_w4a16_tensor_test_hook": (None, [C.c_uint32, _I32]),
     "quic_rmsnorm": (C.c_int, [_P, _P, _P, _F, _P, _P, _I32, _P]),
     "quic_rope_table_init": (C.c_int, [_P, _I32, _P, _P, _P]),
     "quic_rope": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P]),
-    "quic_qkv_rope_append": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _I32, _I32, _P]),
-    "quic_attn_prefill": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, C.c_float, _P, _P]),
+    "quic_qkv_rope_append": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _I32, _I32, _I32, _P]),
+    "quic_attn_prefill": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, C.c_float, _P, _P]),
     "quic_swiglu": (C.c_int, [_P, _P, _P, _I32, _P]),
     "quic_swiglu_fused": (C.c_int, [_P, _P, _I32, _P]),
     "quic_argmax": (C.c_int, [_P, _I32, _I32, _P, _P]),
@@ -385,8 +386,8 @@ def qkv_rope_append(qkv: torch.Tensor, slots: torch.Tensor, positions: torch.Ten
         raise RuntimeError("qkv_rope_append: cache planes must be contiguous [n_slots, 2, s_max, 64]")
     q = torch.empty(HEADS, rows, HEAD_DIM, dtype=torch.float16, device=qkv.device)
     check(lib().quic_qkv_rope_append(ptr(qkv.contiguous()), ptr(slots), ptr(positions), ptr(cos), ptr(sin),
-                                     cos.shape[0], ptr(q), ptr(kcache), ptr(vcache), kcache.shape[2], rows,
-                                     stream_ptr()), "qkv_rope_append")
+                                     cos.shape[0], ptr(q), ptr(kcache), ptr(vcache), kcache.shape[2],
+                                     kcache.shape[0], rows, stream_ptr()), "qkv_rope_append")
     return q
 
 
@@ -404,7 +405,8 @@ def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, se
     rows, n_seq = q.shape[1], seq_len.numel()
     out = torch.empty(rows, HEADS * HEAD_DIM, dtype=torch.float16, device=q.device)
     check(lib().quic_attn_prefill(ptr(q), ptr(kcache), ptr(vcache), ptr(seq_start), ptr(seq_len), ptr(seq_slot),
-                                  n_seq, int(max_len), rows, kcache.shape[2], float(scale), ptr(out), stream_ptr()),
+                                  n_seq, int(max_len), rows, kcache.shape[2], kcache.shape[0], float(scale), ptr(out),
+                                  stream_ptr()),
           "attn_prefill")
     return out
 

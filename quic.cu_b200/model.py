@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import ctypes as C
 import json
+import numbers
 import os
 from dataclasses import dataclass
 
@@ -69,6 +70,16 @@ class SlotCache:
         self._plans: dict[tuple, tuple] = {}       # decode(): per (rows, steps) launch plan
         self._rows_loaded: dict[int, torch.Tensor] = {}  # row->slot map now on the device, per batch size
         self.host_steps = 0                        # host mirror of step_counter
+
+    def check_slots(self, slots, count: int, what: str) -> None:
+        """Every kernel indexes the KV planes and the per-slot state by slot: a slot outside
+        the cache or one used twice in a batch is refused here, before any launch."""
+        if len(slots) != count:
+            raise ValueError(f"{what}: {len(slots)} slots for {count} rows")
+        if any((not isinstance(s, numbers.Integral)) or s < 0 or s >= self.n_slots for s in slots):
+            raise ValueError(f"{what}: slots must be integers in 0..{self.n_slots - 1}, got {list(slots)[:8]}")
+        if len(set(slots)) != len(slots):
+            raise ValueError(f"{what}: a slot appears twice in the batch")
 
     def get_seq_length(self, layer_idx: int = 0) -> int:
         return max((self.host_len[s] for s in self.batch_slots), default=0)
@@ -319,6 +330,7 @@ class QUICForCausalLM:
         graph (int) or, for the persistent kernel, the quic_decode_t of the launch."""
         if not slots:
             raise RuntimeError("decode: empty batch")
+        cache.check_slots(slots, len(slots), "decode")
         if steps < 1 or steps > cache.ring:
             raise RuntimeError(f"decode: steps must be in 1..{cache.ring}")
         longest = max(cache.host_len[s] for s in slots)
@@ -435,6 +447,7 @@ class QUICForCausalLM:
         W4A16 kernels at M = total prompt tokens; attention is torch SDPA per sequence, as the
         reference's default prefill backend (kernels/flash_attn_prefill_pytorch.py:10)."""
         dev = self.device
+        cache.check_slots(slots, len(prompts), "prefill")
         lens = [int(p.numel()) for p in prompts]
         if any(n < 1 for n in lens):
             raise RuntimeError("prefill: empty prompt")
@@ -540,6 +553,7 @@ class QUICForCausalLM:
             cache.batch_slots = list(range(batch))
         if len(cache.batch_slots) != batch:
             raise ValueError(f"cache holds {len(cache.batch_slots)} rows, input has {batch}")
+        cache.check_slots(cache.batch_slots, batch, "forward")
         past_len = cache.get_seq_length()
         kv_len = past_len + seq_len
         input_ids = input_ids.to(self.device)

@@ -281,3 +281,24 @@ def test_golden_hf_quant_logits(tiny_model):
     ok, err = _close(got, torch.from_numpy(g["logits"]))
     assert ok, err
     assert got.argmax(-1).tolist() == tokens
+
+
+def test_slots_are_checked_before_any_launch(tiny_model):
+    """Slots outside the cache, repeated slots and a slot count that does not match the rows
+    are refused on the host by prefill(), decode() and forward()."""
+    net = tiny_model[0]
+    cache = net.new_cache(n_slots=2, s_max=64)
+    p = torch.tensor([5, 6, 7])
+    for bad in ([2], [-1], [0, 0], [0, 1, 1]):
+        with pytest.raises(ValueError):
+            net.prefill(cache, bad, [p] * len(bad))
+    with pytest.raises(ValueError):
+        net.prefill(cache, [0, 1], [p])
+    net.prefill(cache, [1], [p])
+    for bad in ([2], [1, 1], [-3]):
+        with pytest.raises(ValueError):
+            net.decode(cache, bad, 1)
+    small = net.new_cache(n_slots=2, s_max=64)
+    with pytest.raises(ValueError):  # three rows, two slots
+        net(torch.tensor([[1, 2], [3, 4], [5, 6]]), past_key_values=small)
+    assert net.decode(cache, [1], 2)[0]  # the cache is still usable

@@ -147,6 +147,38 @@ def test_qkv_rope_append_matches_split_rope_and_cache_update(K):
     assert torch.count_nonzero(kc[1]) == 0 and torch.count_nonzero(vc[2]) == 0
 
 
+def test_rows_with_slots_outside_the_cache_append_nothing(K):
+    """A row whose slot is not one of the cache's (or whose position is negative) still gets
+    its query written, but nothing is appended for it and the rows of a sequence in such a slot
+    are skipped by the prefill attention; the valid rows are unaffected."""
+    torch.manual_seed(4)
+    exponent = torch.arange(0, 64, 2, dtype=torch.float32) / 64
+    cos, sin = K.rope().init_table((1.0 / (1e6 ** exponent)).cuda(), 4096)
+    n_slots, rows = 3, 6
+    qkv = torch.randn(rows, 1152, device="cuda", dtype=torch.float16)
+    slot_of = torch.tensor([1, 1, 3, -1, 1000, 2], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([0, 1, 0, 0, 0, -1], dtype=torch.int32, device="cuda")
+    # the planes sit inside a larger zeroed block, so a stray write would land where it is seen
+    block = torch.zeros(n_slots + 4, 2, 16, 64, device="cuda", dtype=torch.float16)
+    vblock = torch.zeros_like(block)
+    kc, vc = block[:n_slots], vblock[:n_slots]
+    q = K.qkv_rope_append(qkv, slot_of, pos, cos, sin, kc, vc)
+    good = torch.zeros_like(kc)
+    q_ref = K.qkv_rope_append(qkv[:2].contiguous(), slot_of[:2].contiguous(), pos[:2].contiguous(), cos, sin, good,
+                              torch.zeros_like(vc))
+    assert torch.equal(q[:, :2], q_ref) and torch.isfinite(q).all()
+    assert torch.equal(kc, good)
+    assert torch.count_nonzero(block[n_slots:]) == 0 and torch.count_nonzero(vblock[n_slots:]) == 0
+    assert torch.count_nonzero(kc[0]) == 0 and torch.count_nonzero(kc[2]) == 0
+
+    dev = dict(device="cuda", dtype=torch.int32)
+    out = K.attn_prefill(q[:, :4].contiguous(), kc, vc, torch.tensor([0, 2], **dev), torch.tensor([2, 2], **dev),
+                         torch.tensor([1, 7], **dev), 2)
+    want = K.attn_prefill(q[:, :2].contiguous(), kc, vc, torch.tensor([0], **dev), torch.tensor([2], **dev),
+                          torch.tensor([1], **dev), 2)
+    assert torch.equal(out[:2], want)
+
+
 def test_errors_are_runtime_errors(K):
     with pytest.raises(RuntimeError):
         K.rmsnorm().forward(torch.zeros(2, 896, dtype=torch.float16), torch.ones(896, dtype=torch.float16), 1e-6)

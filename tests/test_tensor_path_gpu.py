@@ -118,3 +118,52 @@ def test_batched_forward_logits_match_oracle(tiny_model, threshold):
             assert torch.allclose(got, ref_logits[1].float(), rtol=2e-2, atol=5e-2), (got - ref_logits[1].float()).abs().max()
         finally:
             K.lib().quic_set_tensor_min_batch(17)
+
+
+def test_a_gemm_wait_that_runs_out_is_reported_and_the_next_call_works(tiny_model):
+    """The bounded waits of the tcgen05 GEMM: with the probe limit lowered and one packed weight
+    tile never requested (the library's test hook), the consumer warps' wait for that tile runs
+    out, the MMA warp's and the epilogue's waits follow, every role leaves its loop, the CTA
+    releases its tensor memory and returns; the status word names the wait.  Nothing faults.
+    Then, with the hook cleared: the same call is correct, and a decode burst whose graph was
+    captured under the hook raises from decode() and a fresh one works."""
+    from quic_cu_b200 import kernels as K
+
+    net, ref, _, _ = tiny_model
+    lib = K.lib()
+    L = net.layers[0]
+    x = torch.randn(64, 896, device="cuda", dtype=torch.float16, generator=torch.Generator(device="cuda").manual_seed(1))
+    want = K.w4a16_linear(L["qkv"], x, use_tensor=1).clone()
+    assert lib.quic_w4a16_tensor_status() == 0
+    try:
+        lib.quic_w4a16_tensor_test_hook(20000, 0)
+        K.w4a16_linear(L["qkv"], x, use_tensor=1)
+        code = lib.quic_w4a16_tensor_status()
+        assert code != 0 and (code >> 16) in (1, 2, 3), hex(code)
+        assert lib.quic_w4a16_tensor_status() == 0          # the word was taken
+        lib.quic_w4a16_tensor_test_hook(0, -1)
+        assert torch.equal(K.w4a16_linear(L["qkv"], x, use_tensor=1), want)
+        assert lib.quic_w4a16_tensor_status() == 0
+
+        # decode(): the graph of a 20-row burst captured under the hook carries it
+        gen = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, 2048, (6,), generator=gen) for _ in range(20)]
+        slots = list(range(20))
+        cache = net.new_cache(n_slots=20, s_max=64)
+        net.prefill(cache, slots, prompts)
+        lib.quic_w4a16_tensor_test_hook(20000, 0)
+        try:
+            with pytest.raises(RuntimeError, match="bounded wait"):
+                net.decode(cache, slots, 2)
+        finally:
+            lib.quic_w4a16_tensor_test_hook(0, -1)
+        assert lib.quic_w4a16_tensor_status() == 0          # decode() took the word
+        cache = net.new_cache(n_slots=20, s_max=64)
+        first, _ = net.prefill(cache, slots, prompts)
+        rest = net.decode(cache, slots, 3)
+        for i in (0, 7, 19):
+            ref_tokens, ref_logits = ref.greedy(prompts[i].tolist(), 4)
+            _near_tie_ok([int(first[i])] + rest[i], ref_tokens, ref_logits)
+    finally:
+        lib.quic_w4a16_tensor_test_hook(0, -1)
+    assert lib.quic_w4a16_tensor_status() == 0
