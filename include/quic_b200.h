@@ -71,6 +71,10 @@ typedef struct {
   const void *bias;  /* fp16 [N] in output-row order of this layout, or NULL */
   int32_t n;
   int32_t k;
+  /* Dense form of the same linear (the un-quantised model): fp16 [N, K], K
+   * contiguous, rows in the order the packed layout gives its columns; then qw,
+   * sc and zp are NULL.  NULL for a packed weight. */
+  const void *w16;
 } quic_w4_t;
 
 /* Row orders accepted by quic_w4_prepack. */

@@ -102,6 +102,25 @@ def synthetic_checkpoint(n_layers: int = 24, vocab: int = 151936, seed: int = 0)
     return state
 
 
+def synthetic_dense_checkpoint(n_layers: int = 24, vocab: int = 151936, seed: int = 0) -> dict:
+    """State dict of the same architecture with UN-QUANTISED fp16 linears (``.weight`` [N, K]
+    ~ N(0, 0.02)), the form of the reference's FP16 checkpoints (src/model.py:332-356 without
+    packed tensors).  Deterministic in (n_layers, vocab, seed)."""
+    gen = torch.Generator().manual_seed(seed)
+    state: dict[str, torch.Tensor] = {}
+    state["model.embed_tokens.weight"] = (torch.randn(vocab, HIDDEN, generator=gen) * 0.02).to(torch.float16)
+    state["model.norm.weight"] = torch.ones(HIDDEN, dtype=torch.float16)
+    for i in range(n_layers):
+        base = f"model.layers.{i}"
+        state[f"{base}.input_layernorm.weight"] = torch.ones(HIDDEN, dtype=torch.float16)
+        state[f"{base}.post_attention_layernorm.weight"] = torch.ones(HIDDEN, dtype=torch.float16)
+        for name, n, k, has_bias in LAYER_LINEARS:
+            state[f"{base}.{name}.weight"] = (torch.randn(n, k, generator=gen) * 0.02).to(torch.float16)
+            if has_bias:
+                state[f"{base}.{name}.bias"] = (torch.randn(n, generator=gen) * 0.02).to(torch.float16)
+    return state
+
+
 def qwen_config_dict(n_layers: int = 24, vocab: int = 151936, group: int = GROUP,
                      max_position_embeddings: int = 32768) -> dict:
     """``config.json`` contents of the architecture (Qwen2.5-0.5B values)."""

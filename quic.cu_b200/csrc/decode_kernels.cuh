@@ -153,6 +153,21 @@ cudaError_t launch_gateup_mma(const quic_w4_t& w, const half* ln, const half* xr
 cudaError_t launch_down_mma(const quic_w4_t& w, const half* act, const half* xres_in, half* xres_out, float* ssq_out,
                             float* partial, int32_t* counters, int batch, cudaStream_t st);
 
+// Dense fp16 weights (quic_w4_t.w16): the layer chain for 1..kF16ChainMaxRows rows
+// (decode_layers_f16.cu) and the tcgen05 GEMM for more rows and for prefill (gemm_f16_tc.cu).
+constexpr int kF16ChainMaxRows = 4;
+cudaError_t launch_qkv_f16(const quic_w4_t& w, const half* ln, const half* embed, const half* x_in, half* x_copy,
+                           const RowState& rs, float eps, bool first_layer, int vocab, const half* cos_t,
+                           const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
+                           int n_slots, cudaStream_t st, bool pdl);
+cudaError_t launch_residual_f16(const quic_w4_t& w, const half* x, const half* xres_in, half* xres_out, int batch,
+                                cudaStream_t st);
+cudaError_t launch_gateup_f16(const quic_w4_t& w, const half* ln, const half* xres, half* act, int batch, float eps,
+                              cudaStream_t st);
+bool gemm_f16_tc_supported(int m, int n, int k);
+int gemm_f16_tc(const half* x, const half* w, const half* bias, half* y, int m, int n, int k, cudaStream_t st,
+                bool pdl);
+
 // pieces of the batched (batch > 8) decode step
 cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,
                               int batch, cudaStream_t st, bool pdl);

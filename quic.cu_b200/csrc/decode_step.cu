@@ -100,8 +100,11 @@ int check(const quic_model_t* m, const quic_decode_t* d) {
                      L.gate_up.n == 2 * kInter && L.gate_up.k == kHidden && L.down.n == kHidden &&
                      L.down.k == kInter,
                  QUIC_E_SHAPE, "decode_step: layer shapes are not Qwen2.5-0.5B's");
-    QUIC_REQUIRE(L.qkv.qw && L.o.qw && L.gate_up.qw && L.down.qw && L.ln1 && L.ln2, QUIC_E_ARG,
-                 "decode_step: missing layer tensor");
+    const bool packed = L.qkv.qw && L.o.qw && L.gate_up.qw && L.down.qw;
+    const bool dense = L.qkv.w16 && L.o.w16 && L.gate_up.w16 && L.down.w16;
+    QUIC_REQUIRE((packed || dense) && L.ln1 && L.ln2, QUIC_E_ARG, "decode_step: missing layer tensor");
+    QUIC_REQUIRE(dense == (m->layers[0].qkv.w16 != nullptr), QUIC_E_ARG,
+                 "decode_step: packed and dense layers cannot be mixed");
   }
   return QUIC_OK;
 }
@@ -116,8 +119,13 @@ int enqueue_step_rows16(const quic_model_t* m, const quic_decode_t* d, cudaStrea
 int g_tensor_min_batch = kMmaChainMaxRows + 1;
 int g_mma_chain_min_batch = 3;
 
+int enqueue_step_f16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head);
+int enqueue_step_batched_f16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head);
+
 int enqueue_step(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
   const int B = d->batch;
+  if (m->layers[0].qkv.w16 != nullptr)  // dense fp16 weights
+    return B <= kF16ChainMaxRows ? enqueue_step_f16(m, d, st, chain_head) : enqueue_step_batched_f16(m, d, st, chain_head);
   if (B >= g_tensor_min_batch) return enqueue_step_batched(m, d, st, chain_head);
   if (B >= g_mma_chain_min_batch) return enqueue_step_rows16(m, d, st, chain_head);
   const int splits = pick_splits(d);
@@ -435,6 +443,152 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
   return QUIC_OK;
 }
 
+// Attention of a decode step with finished fp16 output: the scratch-free CTA form up to 4096
+// tokens, the split form merged by the last CTA to arrive beyond.
+int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int ctx, half* qbuf, half* kc, half* vc,
+                      half* attn_out, cudaStream_t st) {
+  const int B = d->batch;
+  char* base = static_cast<char*>(d->scratch);
+  const size_t slot_stride = (size_t)kKvHeads * d->s_max * kHeadDim;
+  AttnArgs aa = {};
+  aa.q = qbuf;
+  aa.k = kc;
+  aa.v = vc;
+  aa.stride_b = (int64_t)slot_stride;
+  aa.stride_h = (int64_t)d->s_max * kHeadDim;
+  aa.rows = d->rows;
+  aa.pos = d->pos;
+  aa.s_cap = ctx;
+  aa.scale = 0.125f;  // 64^-0.5, src/model.py:129
+  aa.out = attn_out;
+  aa.use_mma = 1;
+  aa.consumer_merge = 0;
+  aa.epoch = d->step_counter;
+  if (attn_cta_splits(ctx) <= kAttnCtaMaxSplits) {
+    aa.splits = attn_cta_splits(ctx);
+    aa.chunk = 512;
+    aa.prefetch = d->step_counter != nullptr ? 1 : 0;
+    QUIC_CUDA(launch_attn_cta(aa, B, st, true));
+    return QUIC_OK;
+  }
+  aa.splits = splits;
+  aa.chunk = (ctx + splits - 1) / splits;
+  aa.small = (splits <= 32 && (int64_t)splits * 64 >= ctx) ? 1 : 0;
+  aa.prefetch = (aa.small && d->step_counter != nullptr) ? 1 : 0;
+  if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
+  QUIC_CUDA(launch_attn(aa, B, st, true));
+  return QUIC_OK;
+}
+
+LmHeadArgs lm_head_args(const quic_model_t* m, const quic_decode_t* d, const Arena& ar) {
+  char* base = static_cast<char*>(d->scratch);
+  LmHeadArgs la = {};
+  la.embed = (const half*)m->embed;
+  la.batch = d->batch;
+  la.vocab = m->vocab;
+  la.eps = m->eps;
+  la.logits = (half*)d->logits;
+  la.best_val = reinterpret_cast<float*>(base + ar.best_val);
+  la.best_idx = reinterpret_cast<int32_t*>(base + ar.best_idx);
+  la.counter = reinterpret_cast<int32_t*>(base + ar.lm_counter);
+  la.keys = reinterpret_cast<unsigned long long*>(base + ar.lm_counter + 256);
+  la.rows = d->rows;
+  la.tok = d->tok;
+  la.pos = d->pos;
+  la.out_tokens = d->out_tokens;
+  la.n_slots = d->n_slots;
+  la.ring = d->ring > 0 ? d->ring : 1;
+  la.step_counter = d->step_counter;
+  return la;
+}
+
+// Dense fp16 weights, 1..4 rows: five kernels per layer (decode_layers_f16.cu) and the GEMV
+// lm_head with the final norm fused.
+int enqueue_step_f16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
+  const int B = d->batch;
+  const int splits = pick_splits(d);
+  const Arena ar = carve(B, m->vocab, splits);
+  char* base = static_cast<char*>(d->scratch);
+  half* xa = reinterpret_cast<half*>(base + ar.xres);  // residual stream entering a layer
+  half* xb = xa + (size_t)B * kHidden;                  // after the attention block
+  half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
+  half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
+  half* act = reinterpret_cast<half*>(base + ar.act);
+  const size_t kv_plane = (size_t)d->n_slots * kKvHeads * d->s_max * kHeadDim;
+  int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
+  if (ctx > d->s_max) ctx = d->s_max;
+  RowState rs;
+  rs.rows = d->rows;
+  rs.tok = d->tok;
+  rs.pos = d->pos;
+  rs.batch = B;
+  for (int l = 0; l < m->n_layers; ++l) {
+    const quic_layer_t& L = m->layers[l];
+    half* kc = static_cast<half*>(d->kv) + (size_t)(2 * l) * kv_plane;
+    half* vc = kc + kv_plane;
+    QUIC_CUDA(launch_qkv_f16(L.qkv, (const half*)L.ln1, (const half*)m->embed, xa, xa, rs, m->eps, l == 0, m->vocab,
+                             (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos, qbuf, kc, vc, d->s_max,
+                             d->n_slots, st, !(chain_head && l == 0)));
+    int rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_residual_f16(L.o, attn_out, xa, xb, B, st));
+    QUIC_CUDA(launch_gateup_f16(L.gate_up, (const half*)L.ln2, xb, act, B, m->eps, st));
+    QUIC_CUDA(launch_residual_f16(L.down, act, xb, xa, B, st));
+  }
+  LmHeadArgs la = lm_head_args(m, d, ar);
+  la.ln = (const half*)m->final_norm;
+  la.xres_in = xa;
+  QUIC_CUDA(launch_lm_head(la, lm_head_grid(m->vocab), st, true));
+  return QUIC_OK;
+}
+
+// Dense fp16 weights, more rows: every linear on the tcgen05 fp16 GEMM; norms, RoPE / KV append
+// and SwiGLU are the small kernels of the batched W4A16 step.
+int enqueue_step_batched_f16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
+  const int B = d->batch;
+  const int splits = pick_splits(d);
+  const Arena ar = carve(B, m->vocab, splits);
+  char* base = static_cast<char*>(d->scratch);
+  half* h = reinterpret_cast<half*>(base + ar.xres);
+  half* qbuf = reinterpret_cast<half*>(base + ar.qbuf);
+  half* attn_out = reinterpret_cast<half*>(base + ar.attn_out);
+  half* xn = reinterpret_cast<half*>(base + ar.xn);
+  half* qkv = reinterpret_cast<half*>(base + ar.qkv);  // [B][1152]; also holds a [B][896] linear output
+  half* gu = reinterpret_cast<half*>(base + ar.gu);
+  half* act = reinterpret_cast<half*>(base + ar.act16);
+  const size_t kv_plane = (size_t)d->n_slots * kKvHeads * d->s_max * kHeadDim;
+  int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
+  if (ctx > d->s_max) ctx = d->s_max;
+  QUIC_CUDA(launch_embed_rows((const half*)m->embed, d->rows, d->tok, m->vocab, h, B, st, !chain_head));
+  QUIC_CUDA(launch_rmsnorm(h, nullptr, (const half*)m->layers[0].ln1, m->eps, xn, nullptr, B, st));
+  for (int l = 0; l < m->n_layers; ++l) {
+    const quic_layer_t& L = m->layers[l];
+    half* kc = static_cast<half*>(d->kv) + (size_t)(2 * l) * kv_plane;
+    half* vc = kc + kv_plane;
+    int rc = gemm_f16_tc(xn, (const half*)L.qkv.w16, (const half*)L.qkv.bias, qkv, B, kQkvN, kHidden, st, true);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_qkv_post(qkv, d->rows, d->pos, (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos,
+                              qbuf, kc, vc, d->s_max, d->n_slots, B, st));
+    rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st);
+    if (rc != QUIC_OK) return rc;
+    rc = gemm_f16_tc(attn_out, (const half*)L.o.w16, nullptr, qkv, B, kHidden, kHidden, st, true);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_rmsnorm(qkv, h, (const half*)L.ln2, m->eps, xn, h, B, st));
+    rc = gemm_f16_tc(xn, (const half*)L.gate_up.w16, nullptr, gu, B, 2 * kInter, kHidden, st, true);
+    if (rc != QUIC_OK) return rc;
+    QUIC_CUDA(launch_swiglu_fused(gu, act, B, st));
+    rc = gemm_f16_tc(act, (const half*)L.down.w16, nullptr, qkv, B, kHidden, kInter, st, true);
+    if (rc != QUIC_OK) return rc;
+    const half* next_ln = (l + 1 < m->n_layers) ? (const half*)m->layers[l + 1].ln1 : (const half*)m->final_norm;
+    QUIC_CUDA(launch_rmsnorm(qkv, h, next_ln, m->eps, xn, h, B, st));
+  }
+  LmHeadArgs la = lm_head_args(m, d, ar);
+  la.x_normed = xn;
+  if (lm_head_tc_supported(B, m->vocab)) return launch_lm_head_tc(la, st);
+  QUIC_CUDA(launch_lm_head(la, lm_head_grid(m->vocab), st, false));
+  return QUIC_OK;
+}
+
 struct Graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
@@ -482,6 +636,10 @@ extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32
 
 extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_decode_t* d) {
   if (!m) return 0;
+  if (m->layers && m->layers[0].qkv.w16 != nullptr) {
+    if (d && d->batch > kF16ChainMaxRows) return 9 * m->n_layers + 3;
+    return 5 * m->n_layers + 1;
+  }
   if (d && d->batch >= g_tensor_min_batch) return 8 * m->n_layers + 3;
   if (d && d->batch >= g_mma_chain_min_batch) return 5 * m->n_layers + ((d->batch > 4 && lm_head_tc_supported(d->batch, m->vocab)) ? 2 : 1);
   return 5 * m->n_layers + 1;

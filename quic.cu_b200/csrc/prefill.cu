@@ -9,6 +9,7 @@ namespace quic {
 namespace {
 
 constexpr int kPrefillChunk = 8192;  // rows per linear call (bounds the split-K workspace)
+constexpr int kGuChunk = 1024;      // rows of gate|up output held at once by the dense fp16 path
 
 inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
@@ -46,7 +47,8 @@ PrefillArena carve_prefill(int rows, int n_seq, int vocab) {
   a.attn = off;
   off += align256((int64_t)rows * kHidden * 2);
   a.gu = off;
-  off += align256((int64_t)(rows < 2 ? rows : 1) * 2 * kInter * 2);  // only the one-row fallback materialises gate|up
+  // gate|up is materialised by the one-row fallback and, kGuChunk rows at a time, by the dense fp16 path
+  off += align256((int64_t)(rows < kGuChunk ? rows : kGuChunk) * 2 * kInter * 2);
   a.act = off;
   off += align256((int64_t)rows * kInter * 2);
   a.xlast = off;
@@ -155,7 +157,13 @@ extern "C" int quic_prefill(const quic_model_t* m, const quic_prefill_t* p, void
     if ((rc = linear_rows(attn, L.o, tmp, rows, ws, stream)) != QUIC_OK) return rc;
     // h += o ; xn = norm(h)
     QUIC_CUDA(launch_rmsnorm(tmp, h, (const half*)L.ln2, m->eps, xn, h, rows, st));
-    if (rows >= 2) {  // gate|up GEMM with SwiGLU in its epilogue: the [rows, 9728] intermediate never exists
+    if (L.gate_up.w16 != nullptr) {  // dense fp16 weights: GEMM, then SwiGLU, a chunk of rows at a time
+      for (int r0 = 0; r0 < rows; r0 += kGuChunk) {
+        const int mrows = rows - r0 < kGuChunk ? rows - r0 : kGuChunk;
+        if ((rc = linear_rows(xn + (size_t)r0 * kHidden, L.gate_up, gu, mrows, ws, stream)) != QUIC_OK) return rc;
+        QUIC_CUDA(launch_swiglu_fused(gu, act + (size_t)r0 * kInter, mrows, st));
+      }
+    } else if (rows >= 2) {  // gate|up GEMM with SwiGLU in its epilogue: the [rows, 9728] intermediate never exists
       for (int r0 = 0; r0 < rows; r0 += kPrefillChunk) {
         const int mrows = rows - r0 < kPrefillChunk ? rows - r0 : kPrefillChunk;
         if ((rc = w4a16_gemm_tc_swiglu(xn + (size_t)r0 * kHidden, L.gate_up, act + (size_t)r0 * kInter, mrows, st)) !=

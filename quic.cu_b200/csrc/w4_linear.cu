@@ -216,7 +216,16 @@ extern "C" int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k) {
 
 extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int32_t m,
                                  int32_t use_tensor, void* workspace, void* stream) {
-  QUIC_REQUIRE(x && w && y && w->qw && w->sc && w->zp, QUIC_E_ARG, "w4a16_linear: null tensor");
+  QUIC_REQUIRE(x && w && y, QUIC_E_ARG, "w4a16_linear: null tensor");
+  if (w->w16 != nullptr) {  // dense fp16 weight [N, K]: a row or two on the GEMV, more on the tcgen05 GEMM
+    QUIC_REQUIRE(w->n > 0 && w->k > 0 && w->k % 8 == 0 && m >= 0, QUIC_E_SHAPE, "linear: bad dense shape");
+    if (m == 0) return QUIC_OK;
+    if (m >= 2 && use_tensor && gemm_f16_tc_supported(m, w->n, w->k))
+      return gemm_f16_tc((const half*)x, (const half*)w->w16, (const half*)w->bias, (half*)y, m, w->n, w->k,
+                         (cudaStream_t)stream, true);
+    return quic_gemm_f16(x, w->w16, w->bias, y, m, w->n, w->k, stream);
+  }
+  QUIC_REQUIRE(w->qw && w->sc && w->zp, QUIC_E_ARG, "w4a16_linear: null tensor");
   QUIC_REQUIRE(w->n > 0 && w->k > 0 && w->n % 32 == 0 && w->k % kGroup == 0, QUIC_E_SHAPE,
                "w4a16_linear: N must be a multiple of 32 and K of 128");
   QUIC_REQUIRE(m >= 0, QUIC_E_SHAPE, "w4a16_linear: negative M");

@@ -39,6 +39,7 @@ class W4(C.Structure):
         ("bias", C.c_void_p),
         ("n", C.c_int32),
         ("k", C.c_int32),
+        ("w16", C.c_void_p),
     ]
 
 
@@ -253,7 +254,7 @@ class W4Weight:
                                     ptr(self.zp), stream_ptr()), "w4_prepack")
 
     def struct(self) -> W4:
-        return W4(ptr(self.qw), ptr(self.sc), ptr(self.zp), ptr(self.bias), self.size_n, self.size_k)
+        return W4(ptr(self.qw), ptr(self.sc), ptr(self.zp), ptr(self.bias), self.size_n, self.size_k, None)
 
     def dequant(self) -> torch.Tensor:
         out = torch.empty(self.size_n, self.size_k, dtype=torch.float16, device=self.qw.device)
@@ -276,12 +277,50 @@ class W4Weight:
         return self.qw.numel() * 4 + self.sc.numel() * 2 + self.zp.numel()
 
 
+class F16Weight:
+    """One (possibly fused) DENSE fp16 matrix [N, K] of the un-quantised model, in the form the
+    kernels read through quic_w4_t.w16: K contiguous, rows in the order W4Weight gives its
+    columns.  The second execution path of the reference (src/model.py:35-41: a linear
+    without a packed weight runs kernels/cuda/gemm.cu:36)."""
+
+    def __init__(self, n: int, k: int, device, bias: torch.Tensor | None = None):
+        if n % 8 or k % 8:
+            raise RuntimeError("F16Weight: N and K must be multiples of 8")
+        self.size_n, self.size_k = n, k
+        self.w = torch.empty(n, k, dtype=torch.float16, device=device)
+        self.bias = bias
+
+    def put(self, weight: torch.Tensor, row_offset: int = 0, row_order: int = ROWS_NATURAL) -> None:
+        """Places one checkpoint layer [N_layer, K] at rows [row_offset, row_offset + N_layer)."""
+        w = weight.to(self.w.device, torch.float16)
+        n, k = w.shape
+        if k != self.size_k or row_offset + n > self.size_n:
+            raise RuntimeError("F16Weight.put: checkpoint tensor shape does not match")
+        if row_order == ROWS_ROPE_PAIRS:  # (0,32,1,33,...) inside every head of 64 rows
+            w = w.view(-1, 2, 32, k).transpose(1, 2).reshape(n, k)
+        self.w[row_offset:row_offset + n] = w
+
+    def struct(self) -> W4:
+        return W4(None, None, None, ptr(self.bias), self.size_n, self.size_k, ptr(self.w))
+
+    def dequant(self) -> torch.Tensor:
+        return self.w
+
+    def workspace(self, m: int):
+        return None
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.w.numel() * 2
+
+
 _linear_workspace: dict = {}
 MAX_LINEAR_ROWS = 8192  # rows per launch; longer inputs are processed in chunks to bound scratch memory
 
 
-def w4a16_linear(w: W4Weight, x: torch.Tensor, use_tensor: bool | None = None) -> torch.Tensor:
-    """y = x · dequant(W)^T + bias.  Replaces marlin_linear (src/quant/marlin.py:190)."""
+def w4a16_linear(w, x: torch.Tensor, use_tensor: bool | None = None) -> torch.Tensor:
+    """y = x · dequant(W)^T + bias.  Replaces marlin_linear (src/quant/marlin.py:190); with an
+    F16Weight the dense linear of the un-quantised model (_linear, src/model.py:35-41)."""
     _need_cuda(x)
     _need_half(x)
     x2 = x.contiguous().reshape(-1, w.size_k)

@@ -155,7 +155,8 @@ def _ctx_bucket(n: int, batch: int = 1) -> int:
 
 
 class QUICForCausalLM:
-    """The model: W4A16 weights in device layout + the C structs the kernels read."""
+    """The model: W4A16 (or, for an un-quantised checkpoint, dense fp16) weights in device
+    layout + the C structs the kernels read."""
 
     def __init__(self, config: dict, device="cuda"):
         self.config = config
@@ -179,6 +180,7 @@ class QUICForCausalLM:
         self.default_slots = 8
         self.default_context = 4096
         self.use_persist = PERSIST
+        self.dense = False  # True: un-quantised fp16 weights (F16Weight), the dense kernels
         self._wstream: torch.Tensor | None = None
 
     # ---- weights -------------------------------------------------------------
@@ -191,14 +193,19 @@ class QUICForCausalLM:
         self.final_norm = weights["model.norm.weight"].to(dev, DTYPE).contiguous()
         if self.embed.shape != (self.vocab, HIDDEN):
             raise RuntimeError("weight mismatch: embed_tokens shape")
+        self.dense = not prefixes  # no packed tensor at all: the un-quantised fp16 model
         for i in range(self.n_layers):
             base = f"model.layers.{i}"
             for name, _, _, _ in LAYER_LINEARS:
-                if f"{base}.{name}" not in prefixes:
-                    raise RuntimeError(f"no W4A16 kernel for layers: ['{base}.{name}'] (unpacked weights)")
+                if not self.dense and f"{base}.{name}" not in prefixes:
+                    raise RuntimeError(f"packed and dense layers cannot be mixed: '{base}.{name}' has no packed weight")
 
             def get(name, key):
                 return weights[f"{base}.{name}.{key}"]
+
+            if self.dense:
+                self.layers.append(self._dense_layer(base, get, weights, dev))
+                continue
 
             bias = torch.empty(QKV_N, dtype=DTYPE, device=dev)
             qkv = K.W4Weight(QKV_N, HIDDEN, dev, bias=bias)
@@ -231,6 +238,26 @@ class QUICForCausalLM:
         self.rope_cos, self.rope_sin = K.rope().init_table(inv_freq, self.max_pos)
         self._build_structs()
         torch.cuda.synchronize(dev)
+
+    def _dense_layer(self, base: str, get, weights: dict, dev) -> dict:
+        """The four fused matrices of a layer from un-quantised ``.weight`` tensors ([N, K])."""
+        bias = torch.empty(QKV_N, dtype=DTYPE, device=dev)
+        qkv = K.F16Weight(QKV_N, HIDDEN, dev, bias=bias)
+        off = 0
+        for name, n in (("self_attn.q_proj", 896), ("self_attn.k_proj", 128), ("self_attn.v_proj", 128)):
+            qkv.put(get(name, "weight"), row_offset=off, row_order=K.ROWS_ROPE_PAIRS)
+            bias[off:off + n] = get(name, "bias").to(dev, DTYPE).view(-1, 2, 32).transpose(1, 2).reshape(-1)
+            off += n
+        o = K.F16Weight(HIDDEN, HIDDEN, dev)
+        o.put(get("self_attn.o_proj", "weight"))
+        gu = K.F16Weight(2 * INTER, HIDDEN, dev)
+        gu.put(get("mlp.gate_proj", "weight"), row_offset=0)
+        gu.put(get("mlp.up_proj", "weight"), row_offset=INTER)
+        down = K.F16Weight(HIDDEN, INTER, dev)
+        down.put(get("mlp.down_proj", "weight"))
+        return {"qkv": qkv, "o": o, "gate_up": gu, "down": down,
+                "ln1": weights[f"{base}.input_layernorm.weight"].to(dev, DTYPE).contiguous(),
+                "ln2": weights[f"{base}.post_attention_layernorm.weight"].to(dev, DTYPE).contiguous()}
 
     def _build_structs(self) -> None:
         arr = (K.Layer * self.n_layers)()
@@ -310,7 +337,7 @@ class QUICForCausalLM:
     def persist_ok(self, batch: int, ctx: int) -> bool:
         """Whether ``batch`` rows with contexts up to ``ctx`` tokens run in the persistent kernel."""
         lib = K.lib()
-        return (self.use_persist and batch <= lib.quic_persist_max_rows() and self.vocab >= 296
+        return (self.use_persist and not self.dense and batch <= lib.quic_persist_max_rows() and self.vocab >= 296
                 and lib.quic_persist_stream_bytes(self.n_layers) > 0
                 and lib.quic_persist_pick_splits(batch, ctx) <= 16)
 
@@ -613,11 +640,10 @@ def load(path: str, prefill_backend: str = "pytorch", use_marlin: bool = False, 
     with open(os.path.join(path, "config.json")) as handle:
         config = json.load(handle)
     weights = load_file(os.path.join(path, "model.safetensors"))
-    if not packed_prefixes(weights):
-        raise RuntimeError("quic_b200 runs the quantised (quic_quant) path only: no packed tensors found")
-    group = detect_group_size(config)
-    if group != K.GROUP:
-        raise RuntimeError(f"quic_b200 kernels are built for group size {K.GROUP}, checkpoint has {group}")
+    if packed_prefixes(weights):  # (an un-quantised checkpoint runs the dense fp16 kernels)
+        group = detect_group_size(config)
+        if group != K.GROUP:
+            raise RuntimeError(f"quic_b200 kernels are built for group size {K.GROUP}, checkpoint has {group}")
     model = from_state_dict(weights, config)
     if prefill_backend is not None:
         model.prefill_backend = prefill_backend

@@ -48,8 +48,8 @@ def test_host_only_queries():
 
 
 def test_struct_sizes_match_the_header():
-    assert ctypes.sizeof(K.W4) == 40
-    assert ctypes.sizeof(K.Layer) == 4 * 40 + 16
+    assert ctypes.sizeof(K.W4) == 48  # four pointers, two ints, the dense-weight pointer
+    assert ctypes.sizeof(K.Layer) == 4 * 48 + 16
     assert ctypes.sizeof(K.Model) == 56
     assert ctypes.sizeof(K.Decode) == 96
     assert ctypes.sizeof(K.Prefill) == 120
