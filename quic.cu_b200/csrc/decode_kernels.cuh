@@ -155,7 +155,7 @@ cudaError_t launch_down_mma(const quic_w4_t& w, const half* act, const half* xre
 
 // Dense fp16 weights (quic_w4_t.w16): the layer chain for 1..kF16ChainMaxRows rows
 // (decode_layers_f16.cu) and the tcgen05 GEMM for more rows and for prefill (gemm_f16_tc.cu).
-constexpr int kF16ChainMaxRows = 4;
+constexpr int kF16ChainMaxRows = 2;  // measured: 493 / 593 us per step at 1 / 2 rows, ~890 us on the GEMM step from 3
 cudaError_t launch_qkv_f16(const quic_w4_t& w, const half* ln, const half* embed, const half* x_in, half* x_copy,
                            const RowState& rs, float eps, bool first_layer, int vocab, const half* cos_t,
                            const half* sin_t, int max_pos, half* qbuf, half* kcache, half* vcache, int s_max,
@@ -165,8 +165,9 @@ cudaError_t launch_residual_f16(const quic_w4_t& w, const half* x, const half* x
 cudaError_t launch_gateup_f16(const quic_w4_t& w, const half* ln, const half* xres, half* act, int batch, float eps,
                               cudaStream_t st);
 bool gemm_f16_tc_supported(int m, int n, int k);
-int gemm_f16_tc(const half* x, const half* w, const half* bias, half* y, int m, int n, int k, cudaStream_t st,
-                bool pdl);
+int64_t gemm_f16_tc_workspace(int m, int n, int k);
+int gemm_f16_tc(const half* x, const half* w, const half* bias, half* y, int m, int n, int k, float* ws,
+                cudaStream_t st, bool pdl);
 
 // pieces of the batched (batch > 8) decode step
 cudaError_t launch_embed_rows(const half* embed, const int32_t* rows, const int32_t* tok, int vocab, half* x,

@@ -1,4 +1,4 @@
-// The four linears of a decoder layer with DENSE fp16 weights for 1..4 batch rows: the
+// The four linears of a decoder layer with DENSE fp16 weights for one or two batch rows: the
 // un-quantised model through the same fused decode step (the reference's second execution
 // path: src/model.py:35-41 falls to kernels/cuda/gemm.cu:36 when a linear carries no packed
 // weight).  Same fusion as the W4A16 chain -- RMSNorm in front, bias / RoPE / KV append,
@@ -6,12 +6,13 @@
 // contiguous (the checkpoint's own layout; q|k|v and gate|up fused along N, the q and k rows
 // of a head in rotation-pair order).
 //
-// Shape of every kernel: ONE WARP per output column (two weight rows for gate|up), lanes
-// striding K in 16-byte pieces, the M activation rows in shared memory, fp32 accumulation.
-// The weights are four times the int4 ones (29.8 MB per layer), so these kernels are bound
-// by streaming them: before griddepcontrol.wait a CTA asks L2 for its weight rows
-// (prefetch.global.L2), which overlaps the previous kernel of the chain; after the wait the
-// rows stream from L2.  No split-K and no partial planes: a column is finished by its warp.
+// Shape of every kernel: a warp per output column (two weight rows for gate|up; four warps per
+// column, a quarter of K each, for down), lanes striding K in 16-byte pieces, the M activation
+// rows in shared memory, fp32 accumulation with mixed-precision FMAs.  The weights are four
+// times the int4 ones (29.8 MB per layer), so these kernels are bound by streaming them: every
+// lane requests ALL its weight pieces (at most five) before griddepcontrol.wait, so the whole
+// matrix is in flight while the previous kernel of the chain still runs, and after the wait
+// only the activations are fetched.  No cross-CTA reduction: a column is finished by its CTA.
 //
 // Rounding points as in the W4A16 chain (decode_layers.cu): a linear's output is an fp16
 // tensor, so is the residual stream, the normalised activation and the SwiGLU output.
@@ -23,48 +24,51 @@ namespace {
 constexpr int kF16Warps = 8;
 constexpr int kF16Threads = kF16Warps * 32;
 
-__device__ __forceinline__ void prefetch_row(const half* row, int bytes, int lane) {
-  for (int off = lane * 128; off < bytes; off += 32 * 128) prefetch_l2(reinterpret_cast<const char*>(row) + off);
-}
-
-// dot of 8 fp16 weights with 8 fp16 activations, fp32 accumulate
-__device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
+// acc += dot of 8 fp16 weights with 8 fp16 activations: mixed-precision FMA (fp16 operands, fp32
+// accumulator, no conversions), two accumulators so that consecutive FMAs are independent.
+__device__ __forceinline__ void dot8(const uint4& w, const uint4& x, float (&acc)[2]) {
   const half2* wh = reinterpret_cast<const half2*>(&w);
   const half2* xh = reinterpret_cast<const half2*>(&x);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 a = __half22float2(wh[i]), b = __half22float2(xh[i]);
-    acc = fmaf(a.x, b.x, acc);
-    acc = fmaf(a.y, b.y, acc);
+    acc[0] = fma_h(acc[0], __low2half(wh[i]), __low2half(xh[i]));
+    acc[1] = fma_h(acc[1], __high2half(wh[i]), __high2half(xh[i]));
   }
-  return acc;
 }
 
-// acc[m] = W[row] . xs[m] over K (multiple of 8); all lanes hold the sums on return.
-template <int M>
-__device__ __forceinline__ void warp_gemv(const half* wrow, const half* xs, int k, int lane, float (&acc)[M]) {
-  const int nvec = k >> 3;
+// The lane's pieces (16 bytes each, lane + 32 u) of `nvec` pieces of a weight row, all requested
+// at once: ceil(nvec / 32) <= kMaxPieces loads in flight per lane.
+constexpr int kMaxPieces = 5;
+struct RowRegs {
+  uint4 w[kMaxPieces];
+};
+__device__ __forceinline__ void load_row(RowRegs& r, const half* wrow, int nvec, int lane) {
   const uint4* wp = reinterpret_cast<const uint4*>(wrow);
 #pragma unroll
-  for (int m = 0; m < M; ++m) acc[m] = 0.f;
-  int i = lane;
-  for (; i + 96 < nvec; i += 128) {  // four pieces in flight
-    uint4 w[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) w[u] = ldg_nc_u128(wp + i + 32 * u);
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int m = 0; m < M; ++m)
-        acc[m] = dot8(w[u], *reinterpret_cast<const uint4*>(xs + (size_t)m * k + 8 * (i + 32 * u)), acc[m]);
+  for (int u = 0; u < kMaxPieces; ++u) {
+    const int i = lane + 32 * u;
+    r.w[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < nvec) r.w[u] = ldg_nc_u128(wp + i);
   }
-  for (; i < nvec; i += 32) {
-    const uint4 w = ldg_nc_u128(wp + i);
+}
+// acc[m] = sum over the lane's pieces of W . xs[m] (xs: the M rows, `stride` halves apart, at the
+// row's first k); the warp total is on every lane on return.
+template <int M>
+__device__ __forceinline__ void row_dot(const RowRegs& r, const half* xs, int stride, int nvec, int lane,
+                                        float (&acc)[M]) {
+  float a2[M][2];
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[m] = dot8(w, *reinterpret_cast<const uint4*>(xs + (size_t)m * k + 8 * i), acc[m]);
+  for (int m = 0; m < M; ++m) a2[m][0] = a2[m][1] = 0.f;
+#pragma unroll
+  for (int u = 0; u < kMaxPieces; ++u) {
+    const int i = lane + 32 * u;
+    if (i < nvec) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) dot8(r.w[u], *reinterpret_cast<const uint4*>(xs + (size_t)m * stride + 8 * i), a2[m]);
+    }
   }
 #pragma unroll
-  for (int m = 0; m < M; ++m) acc[m] = warp_sum(acc[m]);
+  for (int m = 0; m < M; ++m) acc[m] = warp_sum(a2[m][0] + a2[m][1]);
 }
 
 // M rows of 896 halves -> xs, RMS-normalised when ln != nullptr (fp32 statistics, fp16 result,
@@ -158,7 +162,8 @@ __global__ void __launch_bounds__(kF16Threads) qkv_f16_kernel(const QkvF16Args a
   const int row0 = blockIdx.y * M;
   const half* wrow = a.w + (size_t)n * kHidden;
   pdl_trigger_early();
-  prefetch_row(wrow, kHidden * 2, lane);
+  RowRegs wr;
+  load_row(wr, wrow, kHidden / 8, lane);  // weights: not written by the chain, requested before the wait
   const float bias = a.bias != nullptr ? __half2float(a.bias[n]) : 0.f;
   int slot[M];
 #pragma unroll
@@ -185,7 +190,7 @@ __global__ void __launch_bounds__(kF16Threads) qkv_f16_kernel(const QkvF16Args a
   stage_hidden<M>(xs, red, src, a.ln, a.eps, (a.first_layer && blockIdx.x == 0) ? a.x_copy : nullptr, row0);
 
   float acc[M];
-  warp_gemv<M>(wrow, xs, kHidden, lane, acc);
+  row_dot<M>(wr, xs, kHidden, kHidden / 8, lane, acc);
   pdl_trigger_late();
   if (lane == 0) {
 #pragma unroll
@@ -240,20 +245,27 @@ struct ResidualF16Args {
   int32_t batch, k;
 };
 
-template <int M>
-__global__ void __launch_bounds__(kF16Threads) residual_f16_kernel(const ResidualF16Args a) {
+// KW warps share a column, each owning a contiguous 1/KW of K (KW = 1 for o_proj, 4 for down, so
+// that a lane holds at most kMaxPieces pieces and every weight byte of the kernel is requested
+// at once); 8 columns per CTA, the KW partial sums of a column meet in shared memory.
+template <int M, int KW>
+__global__ void __launch_bounds__(kF16Threads * KW) residual_f16_kernel(const ResidualF16Args a) {
   extern __shared__ __align__(16) unsigned char smem_dyn[];
   half* xs = reinterpret_cast<half*>(smem_dyn);  // [M][K]
+  __shared__ float part[KW][kF16Warps][M];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * kF16Warps + warp;
+  const int cw = warp % kF16Warps, kq = warp / kF16Warps;  // column of the CTA, quarter of K
+  const int n = blockIdx.x * kF16Warps + cw;
   const int row0 = blockIdx.y * M;
-  const half* wrow = a.w + (size_t)n * a.k;
+  const int kpart = a.k / KW;  // multiple of 8
+  const half* wrow = a.w + (size_t)n * a.k + (size_t)kq * kpart;
   pdl_trigger_early();
-  prefetch_row(wrow, a.k * 2, lane);
+  RowRegs wr;
+  load_row(wr, wrow, kpart / 8, lane);
   pdl_wait();
 
   const int nvec = a.k >> 3;
-  for (int p = threadIdx.x; p < M * nvec; p += kF16Threads) {
+  for (int p = threadIdx.x; p < M * nvec; p += kF16Threads * KW) {
     const int m = p / nvec, c = p - m * nvec;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (row0 + m < a.batch) v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(row0 + m) * a.k) + c);
@@ -261,8 +273,23 @@ __global__ void __launch_bounds__(kF16Threads) residual_f16_kernel(const Residua
   }
   __syncthreads();
   float acc[M];
-  warp_gemv<M>(wrow, xs, a.k, lane, acc);
+  row_dot<M>(wr, xs + (size_t)kq * kpart, a.k, kpart / 8, lane, acc);
   pdl_trigger_late();
+  if (KW > 1) {
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) part[kq][cw][m] = acc[m];
+    }
+    __syncthreads();
+    if (kq != 0) return;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float v = 0.f;
+#pragma unroll
+      for (int q = 0; q < KW; ++q) v += part[q][cw][m];
+      acc[m] = v;
+    }
+  }
   if (lane < M && row0 + lane < a.batch) {
     float v = 0.f;
 #pragma unroll
@@ -296,8 +323,9 @@ __global__ void __launch_bounds__(kF16Threads) gateup_f16_kernel(const GateUpF16
   const half* grow = a.w + (size_t)c * kHidden;
   const half* urow = a.w + (size_t)(kInter + c) * kHidden;
   pdl_trigger_early();
-  prefetch_row(grow, kHidden * 2, lane);
-  prefetch_row(urow, kHidden * 2, lane);
+  RowRegs gr, ur;
+  load_row(gr, grow, kHidden / 8, lane);
+  load_row(ur, urow, kHidden / 8, lane);
   pdl_wait();
 
   const half* src[M];
@@ -305,8 +333,8 @@ __global__ void __launch_bounds__(kF16Threads) gateup_f16_kernel(const GateUpF16
   for (int m = 0; m < M; ++m) src[m] = row0 + m < a.batch ? a.xres + (size_t)(row0 + m) * kHidden : nullptr;
   stage_hidden<M>(xs, red, src, a.ln, a.eps, nullptr, row0);
   float g[M], u[M];
-  warp_gemv<M>(grow, xs, kHidden, lane, g);
-  warp_gemv<M>(urow, xs, kHidden, lane, u);
+  row_dot<M>(gr, xs, kHidden, kHidden / 8, lane, g);
+  row_dot<M>(ur, xs, kHidden, kHidden / 8, lane, u);
   pdl_trigger_late();
   if (lane < M && row0 + lane < a.batch) {
     float gv = 0.f, uv = 0.f;
@@ -321,13 +349,10 @@ __global__ void __launch_bounds__(kF16Threads) gateup_f16_kernel(const GateUpF16
 
 template <int M>
 cudaError_t launch_residual(const ResidualF16Args& a, cudaStream_t st) {
-  const size_t smem = (size_t)M * a.k * sizeof(half);
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(residual_f16_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-  }
-  return launch(residual_f16_kernel<M>, dim3(kHidden / kF16Warps, (a.batch + M - 1) / M), dim3(kF16Threads), smem, st,
-                true, a);
+  const size_t smem = (size_t)M * a.k * sizeof(half);  // at most 2 x 4864 x 2 = 19,456 bytes
+  const dim3 grid(kHidden / kF16Warps, (a.batch + M - 1) / M);
+  if (a.k == kInter) return launch(residual_f16_kernel<M, 4>, grid, dim3(kF16Threads * 4), smem, st, true, a);
+  return launch(residual_f16_kernel<M, 1>, grid, dim3(kF16Threads), smem, st, true, a);
 }
 
 }  // namespace
@@ -335,8 +360,7 @@ cudaError_t launch_residual(const ResidualF16Args& a, cudaStream_t st) {
 #define QUIC_F16_DISPATCH_M(batch, fn, ...)    \
   do {                                         \
     if ((batch) <= 1) return fn<1>(__VA_ARGS__); \
-    if ((batch) <= 2) return fn<2>(__VA_ARGS__); \
-    return fn<4>(__VA_ARGS__);                 \
+    return fn<2>(__VA_ARGS__);                 \
   } while (0)
 
 namespace {

@@ -31,7 +31,14 @@ int64_t tc_workspace_bytes(int batch) {
   const int64_t d = w4a16_gemm_tc_workspace(batch, kHidden, kInter);
   w = w > o ? w : o;
   w = w > g ? w : g;
-  return w > d ? w : d;
+  w = w > d ? w : d;
+  // the dense fp16 GEMM's split-K planes (same arena slot)
+  const int shapes[4][2] = {{kQkvN, kHidden}, {kHidden, kHidden}, {2 * kInter, kHidden}, {kHidden, kInter}};
+  for (const auto& s : shapes) {
+    const int64_t f = gemm_f16_tc_workspace(batch, s[0], s[1]);
+    w = w > f ? w : f;
+  }
+  return w;
 }
 
 // The regions that must start zeroed (arrival counters) come first.
@@ -502,7 +509,7 @@ LmHeadArgs lm_head_args(const quic_model_t* m, const quic_decode_t* d, const Are
   return la;
 }
 
-// Dense fp16 weights, 1..4 rows: five kernels per layer (decode_layers_f16.cu) and the GEMV
+// Dense fp16 weights, one or two rows: five kernels per layer (decode_layers_f16.cu) and the GEMV
 // lm_head with the final norm fused.
 int enqueue_step_f16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
   const int B = d->batch;
@@ -556,6 +563,7 @@ int enqueue_step_batched_f16(const quic_model_t* m, const quic_decode_t* d, cuda
   half* qkv = reinterpret_cast<half*>(base + ar.qkv);  // [B][1152]; also holds a [B][896] linear output
   half* gu = reinterpret_cast<half*>(base + ar.gu);
   half* act = reinterpret_cast<half*>(base + ar.act16);
+  float* ws = reinterpret_cast<float*>(base + ar.tcws);  // split-K partials of the small GEMMs
   const size_t kv_plane = (size_t)d->n_slots * kKvHeads * d->s_max * kHeadDim;
   int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
   if (ctx > d->s_max) ctx = d->s_max;
@@ -565,19 +573,19 @@ int enqueue_step_batched_f16(const quic_model_t* m, const quic_decode_t* d, cuda
     const quic_layer_t& L = m->layers[l];
     half* kc = static_cast<half*>(d->kv) + (size_t)(2 * l) * kv_plane;
     half* vc = kc + kv_plane;
-    int rc = gemm_f16_tc(xn, (const half*)L.qkv.w16, (const half*)L.qkv.bias, qkv, B, kQkvN, kHidden, st, true);
+    int rc = gemm_f16_tc(xn, (const half*)L.qkv.w16, (const half*)L.qkv.bias, qkv, B, kQkvN, kHidden, ws, st, true);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_qkv_post(qkv, d->rows, d->pos, (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos,
                               qbuf, kc, vc, d->s_max, d->n_slots, B, st));
     rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st);
     if (rc != QUIC_OK) return rc;
-    rc = gemm_f16_tc(attn_out, (const half*)L.o.w16, nullptr, qkv, B, kHidden, kHidden, st, true);
+    rc = gemm_f16_tc(attn_out, (const half*)L.o.w16, nullptr, qkv, B, kHidden, kHidden, ws, st, true);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_rmsnorm(qkv, h, (const half*)L.ln2, m->eps, xn, h, B, st));
-    rc = gemm_f16_tc(xn, (const half*)L.gate_up.w16, nullptr, gu, B, 2 * kInter, kHidden, st, true);
+    rc = gemm_f16_tc(xn, (const half*)L.gate_up.w16, nullptr, gu, B, 2 * kInter, kHidden, ws, st, true);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_swiglu_fused(gu, act, B, st));
-    rc = gemm_f16_tc(act, (const half*)L.down.w16, nullptr, qkv, B, kHidden, kInter, st, true);
+    rc = gemm_f16_tc(act, (const half*)L.down.w16, nullptr, qkv, B, kHidden, kInter, ws, st, true);
     if (rc != QUIC_OK) return rc;
     const half* next_ln = (l + 1 < m->n_layers) ? (const half*)m->layers[l + 1].ln1 : (const half*)m->final_norm;
     QUIC_CUDA(launch_rmsnorm(qkv, h, next_ln, m->eps, xn, h, B, st));

@@ -33,7 +33,9 @@ struct DenseSmem {
 struct DenseArgs {
   const half* bias;  // [N] or nullptr
   half* y;           // [M, N]
+  float* part;       // split K: [splits][M][N] fp32 partial sums (then y and bias belong to the finish kernel)
   int m_total, n, k;
+  int kb_per_split;  // 64-wide k blocks per CTA along grid.z
 };
 
 template <int MT>
@@ -50,7 +52,8 @@ __global__ void __launch_bounds__(kDenseThreads) gemm_f16_tc_kernel(const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kTileN;
   const int m0 = blockIdx.y * MT;
-  const int nkb = a.k / kBlockK;
+  const int kb0 = blockIdx.z * a.kb_per_split;
+  const int nkb = min(a.k / kBlockK - kb0, a.kb_per_split);
   using L = DenseSmem<MT>;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr uint32_t kCols = MT < 32 ? 32 : MT;
@@ -87,11 +90,11 @@ __global__ void __launch_bounds__(kDenseThreads) gemm_f16_tc_kernel(const __grid
       for (int it = 0; it < first; ++it) {
         const uint32_t full = smem_u32(&bar_full[it]);
         mbar_expect_tx(full, L::kA + (uint32_t)MT * 128u);
-        tma_load_2d(base + it * L::kStage, &tm_w, it * kBlockK, n0, full);
+        tma_load_2d(base + it * L::kStage, &tm_w, (kb0 + it) * kBlockK, n0, full);
       }
       pdl_wait();
       for (int it = 0; it < first; ++it)
-        tma_load_2d(base + it * L::kStage + L::kA, &tm_x, it * kBlockK, m0, smem_u32(&bar_full[it]));
+        tma_load_2d(base + it * L::kStage + L::kA, &tm_x, (kb0 + it) * kBlockK, m0, smem_u32(&bar_full[it]));
       for (int it = first; it < nkb; ++it) {
         const int stage = it % kDenseStages;
         if (!mbar_wait(smem_u32(&bar_empty[stage]), ((it / kDenseStages) - 1) & 1)) {
@@ -101,8 +104,8 @@ __global__ void __launch_bounds__(kDenseThreads) gemm_f16_tc_kernel(const __grid
         const uint32_t a_s = base + stage * L::kStage, b_s = a_s + L::kA;
         const uint32_t full = smem_u32(&bar_full[stage]);
         mbar_expect_tx(full, L::kA + (uint32_t)MT * 128u);
-        tma_load_2d(a_s, &tm_w, it * kBlockK, n0, full);
-        tma_load_2d(b_s, &tm_x, it * kBlockK, m0, full);
+        tma_load_2d(a_s, &tm_w, (kb0 + it) * kBlockK, n0, full);
+        tma_load_2d(b_s, &tm_x, (kb0 + it) * kBlockK, m0, full);
       }
     }
   } else if (tid == 0) {
@@ -147,6 +150,10 @@ __global__ void __launch_bounds__(kDenseThreads) gemm_f16_tc_kernel(const __grid
         for (int j = 0; j < 8; ++j) {
           const int m = m0 + c0 + j;
           if (m >= a.m_total) continue;
+          if (a.part != nullptr) {
+            a.part[((size_t)blockIdx.z * a.m_total + m) * a.n + col] = __uint_as_float(r[j]);
+            continue;
+          }
           float o = __half2float(__float2half_rn(__uint_as_float(r[j])));
           if (a.bias != nullptr) o += bias;
           a.y[(size_t)m * a.n + col] = __float2half_rn(o);
@@ -160,8 +167,44 @@ __global__ void __launch_bounds__(kDenseThreads) gemm_f16_tc_kernel(const __grid
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kCols) : "memory");
 }
 
+// y = fp16(sum of the split-K partials, in split order) (+ bias): four consecutive outputs per thread.
+__global__ void gemm_f16_finish_kernel(const float* __restrict__ part, const half* __restrict__ bias,
+                                       half* __restrict__ y, int m_total, int n, int splits) {
+  const size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const size_t total = (size_t)m_total * n;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (idx >= total) return;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < splits; ++s) {
+    const float4 p = __ldcg(reinterpret_cast<const float4*>(part + (size_t)s * total + idx));
+    v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+  }
+  float o[4] = {v.x, v.y, v.z, v.w};
+  const int col = (int)(idx % (size_t)n);
+  half h[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float f = __half2float(__float2half_rn(o[j]));
+    if (bias != nullptr) f += __half2float(bias[col + j]);
+    h[j] = __float2half_rn(f);
+  }
+  *reinterpret_cast<uint2*>(y + idx) = *reinterpret_cast<const uint2*>(h);
+}
+
+// K splits for a problem whose tiles would leave most SMs idle: at most 16, at least two k
+// blocks each, while the CTAs at most fill the SMs once.
+int dense_splits(int m, int n, int k, int mt) {
+  const int ctas = (n / kTileN) * ((m + mt - 1) / mt);
+  const int nkb = k / kBlockK;
+  int splits = 1;
+  while (splits < 16 && ctas * splits * 2 <= 148 && nkb / (splits * 2) >= 2) splits *= 2;
+  return splits;
+}
+int dense_mt(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+
 template <int MT>
-int run(const half* x, const half* w, const DenseArgs& a, cudaStream_t st, bool pdl) {
+int run(const half* x, const half* w, const DenseArgs& a, int splits, cudaStream_t st, bool pdl) {
   CUtensorMap tm_w, tm_x;
   int rc = make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w, (uint64_t)a.n, (uint64_t)a.k, kTileN, kBlockK,
                     CU_TENSOR_MAP_SWIZZLE_128B);
@@ -173,7 +216,7 @@ int run(const half* x, const half* w, const DenseArgs& a, cudaStream_t st, bool 
   QUIC_REQUIRE(status != nullptr, QUIC_E_CUDA, "gemm_f16: no address for the tensor path's error words");
   const size_t smem = DenseSmem<MT>::kTotal;
   QUIC_CUDA(cudaFuncSetAttribute(gemm_f16_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(a.n / kTileN, (a.m_total + MT - 1) / MT);
+  dim3 grid(a.n / kTileN, (a.m_total + MT - 1) / MT, splits);
   QUIC_CUDA(launch(gemm_f16_tc_kernel<MT>, grid, dim3(kDenseThreads), smem, st, pdl, tm_w, tm_x, a, status));
   return QUIC_OK;
 }
@@ -184,23 +227,45 @@ bool gemm_f16_tc_supported(int m, int n, int k) {
   return m >= 1 && n >= kTileN && n % kTileN == 0 && k >= kBlockK && k % kBlockK == 0 && (m + 127) / 128 <= 65535;
 }
 
+// Bytes of split-K workspace gemm_f16_tc may use for this shape (0: it never splits it).
+int64_t gemm_f16_tc_workspace(int m, int n, int k) {
+  if (!gemm_f16_tc_supported(m, n, k)) return 0;
+  const int splits = dense_splits(m, n, k, dense_mt(m));
+  return splits > 1 ? (int64_t)splits * m * n * 4 : 0;
+}
+
 // x fp16 [m, k] (row-major, 16-byte aligned), w fp16 [n, k], bias fp16 [n] or nullptr -> y fp16 [m, n].
-int gemm_f16_tc(const half* x, const half* w, const half* bias, half* y, int m, int n, int k, cudaStream_t st,
-                bool pdl) {
+// `ws` (gemm_f16_tc_workspace bytes, may be null): lets small problems split K over more CTAs.
+int gemm_f16_tc(const half* x, const half* w, const half* bias, half* y, int m, int n, int k, float* ws,
+                cudaStream_t st, bool pdl) {
   QUIC_REQUIRE(gemm_f16_tc_supported(m, n, k), QUIC_E_SHAPE,
                "gemm_f16: the tensor path needs N a multiple of 128 and K a multiple of 64");
   QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), QUIC_E_ARG,
                "gemm_f16: x and w must be 16-byte aligned");
+  const int mt = dense_mt(m);
+  int splits = ws != nullptr ? dense_splits(m, n, k, mt) : 1;
+  const int nkb = k / kBlockK;
   DenseArgs a = {};
   a.bias = bias;
   a.y = y;
   a.m_total = m;
   a.n = n;
   a.k = k;
-  if (m <= 16) return run<16>(x, w, a, st, pdl);
-  if (m <= 32) return run<32>(x, w, a, st, pdl);
-  if (m <= 64) return run<64>(x, w, a, st, pdl);
-  return run<128>(x, w, a, st, pdl);
+  a.kb_per_split = (nkb + splits - 1) / splits;
+  splits = (nkb + a.kb_per_split - 1) / a.kb_per_split;
+  a.part = splits > 1 ? ws : nullptr;
+  int rc;
+  switch (mt) {
+    case 16: rc = run<16>(x, w, a, splits, st, pdl); break;
+    case 32: rc = run<32>(x, w, a, splits, st, pdl); break;
+    case 64: rc = run<64>(x, w, a, splits, st, pdl); break;
+    default: rc = run<128>(x, w, a, splits, st, pdl); break;
+  }
+  if (rc != QUIC_OK || splits == 1) return rc;
+  const size_t total = (size_t)m * n;
+  QUIC_CUDA(launch(gemm_f16_finish_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, st, true,
+                   (const float*)ws, bias, y, m, n, splits));
+  return QUIC_OK;
 }
 
 }  // namespace quic

@@ -201,8 +201,16 @@ extern "C" int quic_w4_dequant(const quic_w4_t* w, void* out, void* stream) {
 // against 10-19 us at 4 rows; the GEMV runs 2..8 rows on one 8-row instantiation).
 static constexpr int kTensorMinRows = 2;
 
+static int64_t packed_workspace_bytes(int32_t m, int32_t n, int32_t k);
+
 extern "C" int64_t quic_w4a16_workspace_bytes(int32_t m, int32_t n, int32_t k) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
+  // the same block serves a packed or a dense weight of this shape
+  const int64_t packed = packed_workspace_bytes(m, n, k), dense = gemm_f16_tc_workspace(m, n, k);
+  return packed > dense ? packed : dense;
+}
+
+static int64_t packed_workspace_bytes(int32_t m, int32_t n, int32_t k) {
   // 16 KB reserved head, then split-K partials: of the tensor path from 2 rows (it stops
   // splitting once the output tiles fill the SMs, so large m needs none), of the GEMV below.
   if (m >= kTensorMinRows && n % 128 == 0 && k % 64 == 0) {
@@ -222,7 +230,7 @@ extern "C" int quic_w4a16_linear(const void* x, const quic_w4_t* w, void* y, int
     if (m == 0) return QUIC_OK;
     if (m >= 2 && use_tensor && gemm_f16_tc_supported(m, w->n, w->k))
       return gemm_f16_tc((const half*)x, (const half*)w->w16, (const half*)w->bias, (half*)y, m, w->n, w->k,
-                         (cudaStream_t)stream, true);
+                         (float*)workspace, (cudaStream_t)stream, true);
     return quic_gemm_f16(x, w->w16, w->bias, y, m, w->n, w->k, stream);
   }
   QUIC_REQUIRE(w->qw && w->sc && w->zp, QUIC_E_ARG, "w4a16_linear: null tensor");

@@ -1,6 +1,6 @@
 """The un-quantised fp16 model through the same fused step (the reference's second execution
 path: a linear without a packed weight runs kernels/cuda/gemm.cu:36, src/model.py:35-41):
-the dense GEMV chain (1..4 rows), the tcgen05 fp16 GEMM (more rows, prefill) and loading an
+the dense GEMV chain (one or two rows), the tcgen05 fp16 GEMM (more rows, prefill) and loading an
 unpacked checkpoint, against torch, the same-rounding oracle and HF fp16 (the recipe of the
 reference's tests/test_parity.py:29-30,73-77: mean |dlogit| < 0.05, argmax equal)."""
 
@@ -57,7 +57,7 @@ def test_dense_linear_matches_torch(m, n, k):
 
 @pytest.mark.parametrize("rows", [1, 2, 3, 4, 6, 20])
 def test_dense_decode_matches_oracle(dense_model, rows):
-    """Prefill + greedy bursts: the chain of decode_layers_f16.cu up to 4 rows, the GEMM step
+    """Prefill + greedy bursts: the chain of decode_layers_f16.cu up to 2 rows, the GEMM step
     beyond; tokens against the oracle row by row (up to a near-tie)."""
     net, ref, _, _ = dense_model
     gen = torch.Generator().manual_seed(rows)

@@ -117,3 +117,81 @@ def test_left_padded_batch_prefill_matches_unpadded(tiny_model):
     mask2 = torch.cat([mask, torch.ones(2, 1, dtype=mask.dtype)], dim=1)
     step = net(nxt, past_key_values=out.past_key_values, attention_mask=mask2)
     assert step.logits.shape == (2, 1, 2048) and torch.isfinite(step.logits).all()
+
+
+def _write_stub_tokenizer(path, vocab):
+    """WordLevel tokenizer ("t<i>" <-> i, <unk> = 0, <eos> = 1) with a chat template, in the
+    files AutoTokenizer reads (tokenizer.json + tokenizer_config.json)."""
+    import json
+    import os
+
+    from tokenizers import Tokenizer, models, pre_tokenizers
+
+    words = {f"t{i}": i for i in range(2, vocab)}
+    words["<unk>"], words["<eos>"] = 0, 1
+    tok = Tokenizer(models.WordLevel(words, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok.save(os.path.join(path, "tokenizer.json"))
+    template = ("{% for m in messages %}t5 {{ m['content'] }} t6{% endfor %}"
+                "{% if add_generation_prompt %} t7{% endif %}")
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as handle:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "<unk>", "eos_token": "<eos>",
+                   "chat_template": template}, handle)
+
+
+@pytest.mark.parametrize("spelling", ["top_level", "config_groups"])
+def test_checkpoint_dir_with_tokenizer_runs_text_requests(tmp_path, tiny_model, spelling):
+    """The on-disk form the reference ingests (src/model.py:332-363, src/quant/checkpoint.py:5-20,
+    src/engine.py:59-75): a compressed-tensors style directory whose safetensors carry
+    ``.weight_shape`` beside the packed tensors, whose quantization_config spells the group
+    size at the top level or under config_groups, and whose tokenizer files hold a chat
+    template.  Engine(model_path=...) loads it, add_request(str) applies the template, run()
+    returns decoded strings; the tokens must be the oracle's."""
+    from safetensors import safe_open
+
+    from quic_cu_b200.checkpoint import write_checkpoint_dir
+    from quic_cu_b200.config import EngineConfig
+    from quic_cu_b200.engine import Engine
+
+    _, ref, state, config = tiny_model
+    config = {k: v for k, v in config.items() if k != "quantization_config"}
+    if spelling == "top_level":
+        config["quantization_config"] = {"quant_method": "compressed-tensors", "group_size": 128, "bits": 4}
+    else:
+        config["quantization_config"] = {"quant_method": "compressed-tensors", "config_groups": {
+            "group_0": {"targets": ["Linear"], "weights": {"num_bits": 4, "group_size": 128, "symmetric": False}}}}
+    write_checkpoint_dir(str(tmp_path), state, config)
+    _write_stub_tokenizer(str(tmp_path), 2048)
+    with safe_open(str(tmp_path / "model.safetensors"), "pt") as handle:
+        shapes = [k for k in handle.keys() if k.endswith(".weight_shape")]
+        assert len(shapes) == 2 * 7
+        assert handle.get_tensor("model.layers.0.mlp.down_proj.weight_shape").tolist() == [896, 4864]
+
+    engine = Engine(max_batch_size=4, config=EngineConfig(model_path=str(tmp_path), max_context=256,
+                                                         batching="continuous", prefill_backend="quic"))
+    assert engine.tokenizer is not None and engine.eos_token_id == 1
+    engine.max_tokens = 12
+    texts = ["t10 t11 t12", "t900 t3", "t77 t78 t79 t80 t81 t82"]
+    for text in texts:
+        engine.add_request(text)
+    outputs = engine.run()
+    assert len(outputs) == 3 and all(isinstance(o, str) for o in outputs)
+    for text, out in zip(texts, outputs):
+        ids = [5] + [int(w[1:]) for w in text.split()] + [6, 7]        # the template, by hand
+        want_tokens, want_logits = ref.greedy(ids, 12)
+        if 1 in want_tokens:                                            # generation stops at <eos>
+            want_tokens = want_tokens[: want_tokens.index(1) + 1]
+        got = [1 if w == "<eos>" else int(w[1:]) for w in out.split()]
+        kept = [t for t in want_tokens if t not in (0, 1)]              # special tokens are skipped on decode
+        n = min(len(got), len(kept))
+        assert n >= 1
+        for i in range(n):
+            if got[i] != kept[i]:
+                top = torch.topk(want_logits[i].float(), 2)
+                assert (top.values[0] - top.values[1]).item() < 2e-2, (text, i, got[i], kept[i])
+                break
+
+    bad = dict(config, quantization_config={"quant_method": "compressed-tensors", "group_size": 32})
+    write_checkpoint_dir(str(tmp_path), state, bad)
+    with pytest.raises(RuntimeError, match="group size"):
+        Engine(max_batch_size=2, config=EngineConfig(model_path=str(tmp_path), max_context=64))
