@@ -166,8 +166,10 @@ int quic_qkv_rope_append(const void *qkv_f16, const int32_t *slots,
 
 /* Causal prefill attention of n_seq sequences in one launch (GQA 14:2,
  * head_dim 64).  q_f16 [14, rows, 64] as written by quic_qkv_rope_append;
- * sequence i owns rows seq_start[i] .. seq_start[i] + seq_len[i] - 1, its keys
- * and values are positions 0 .. seq_len[i] - 1 of KV slot seq_slot[i] in the
+ * sequence i owns rows seq_start[i] .. seq_start[i] + seq_len[i] - 1; with
+ * seq_off (NULL = zeros) its rows are positions seq_off[i] .. of the sequence (a
+ * later chunk of a prompt), and its keys and values are positions
+ * 0 .. seq_off[i] + seq_len[i] - 1 of KV slot seq_slot[i] in the
  * layer's cache planes [n_slots, 2, s_max, 64] (no padding is stored, so no pad
  * mask exists); out_f16 [rows, 896] token-major; the rows of a sequence whose
  * slot is outside 0..n_slots-1 are left unwritten.  Replaces the reference's
@@ -176,7 +178,8 @@ int quic_qkv_rope_append(const void *qkv_f16, const int32_t *slots,
 int quic_attn_prefill(const void *q_f16, const void *kcache_f16,
                       const void *vcache_f16, const int32_t *seq_start,
                       const int32_t *seq_len, const int32_t *seq_slot,
-                      int32_t n_seq, int32_t max_len, int32_t rows,
+                      const int32_t *seq_off, int32_t n_seq, int32_t max_len,
+                      int32_t rows,
                       int32_t s_max, int32_t n_slots, float scale,
                       void *out_f16, void *stream);
 
@@ -343,6 +346,11 @@ typedef struct {
   int64_t *first_tokens; /* [n_seq] out */
   void *logits;          /* optional fp16 [n_seq, vocab] of the last positions */
   void *scratch;         /* quic_prefill_scratch_bytes() bytes, zeroed once by the caller */
+  /* Chunked prefill: tokens of the sequence already in its slot, [n_seq] or
+   * NULL (none).  The rows of the call are then the NEXT tokens of the prompt:
+   * row_pos continues from seq_off, attention sees the cached tokens too, and
+   * pos[slot] becomes seq_off + seq_len. */
+  const int32_t *seq_off;
 } quic_prefill_t;
 int64_t quic_prefill_scratch_bytes(int32_t rows, int32_t n_seq, int32_t vocab);
 int quic_prefill(const quic_model_t *m, const quic_prefill_t *p, void *stream);

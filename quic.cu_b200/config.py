@@ -15,12 +15,15 @@ class EngineConfig:
     model_path: str | None = None
     tokenizer_path: str | None = None
     use_machete: bool = False  # accepted for compatibility; the Hopper-only backend is not built
-    # "pytorch": torch SDPA per sequence (the reference's default); "quic": the library's causal
-    # prefill kernel, all admitted sequences in one launch (the reference's name for its own kernel)
-    prefill_backend: Literal["pytorch", "quic"] = "pytorch"
+    # kept for the reference's call sites ("pytorch" = torch SDPA, "quic" = its own kernel there);
+    # here every value runs the library's causal prefill kernel, all admitted sequences in one launch
+    prefill_backend: Literal["pytorch", "quic"] = "quic"
     # additions (defaults keep reference call sites valid)
     max_context: int = 2048   # tokens per KV slot (prompt + generated)
     decode_burst: int = 8     # greedy steps per graph launch between scheduling points
     # prefill newly admitted requests on a second CUDA stream while the rows already running
     # decode their next burst; the new rows join at the following iteration
     overlap_prefill: bool = True
+    # chunked prefill: at most this many prompt tokens per sequence per iteration (None: the whole
+    # prompt at once); the rows already running decode a burst between two chunks
+    prefill_chunk: int | None = None

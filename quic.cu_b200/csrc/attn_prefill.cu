@@ -43,6 +43,7 @@ struct PrefillAttnArgs {
   const int32_t* seq_start;  // [n_seq] first row of the sequence in q / out
   const int32_t* seq_len;    // [n_seq]
   const int32_t* seq_slot;   // [n_seq]
+  const int32_t* seq_off;    // [n_seq] tokens of the sequence already in its slot (a later chunk of a prompt), or nullptr
   half* out;            // [rows][896]
   int32_t rows;
   int32_t s_max;
@@ -65,17 +66,19 @@ __global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 3
   const int r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kPfRows + (kSplitKeys ? 0 : warp * 16);  // first query row of the warp
   if (r0 >= len) return;
   const int start = a.seq_start[seq];
+  const int off = a.seq_off != nullptr ? max(a.seq_off[seq], 0) : 0;  // query row r sits at position off + r
+  const int kv_len = off + len;
   const int slot = a.seq_slot[seq];
   if (slot < 0 || slot >= a.n_slots) return;  // no such slot: the sequence's rows stay unwritten
   const int kvh = head / kGroupHeads;
   const half* kbase = a.kcache + ((size_t)slot * kKvHeads + kvh) * a.s_max * kHeadDim;
   const half* vbase = a.vcache + ((size_t)slot * kKvHeads + kvh) * a.s_max * kHeadDim;
-  const int last_tok = len - 1;
+  const int last_tok = kv_len - 1, last_row = len - 1;
 
   // Q fragments of rows r0 + g (a0, a2) and r0 + g + 8 (a1, a3): dims 16c + 4ks + {0,1} | {2,3}
   uint32_t qa[4][4];
   {
-    const int ra = min(r0 + g, last_tok), rb = min(r0 + g + 8, last_tok);  // rows past the end mirror the last
+    const int ra = min(r0 + g, last_row), rb = min(r0 + g + 8, last_row);  // rows past the end mirror the last
     const half* qa_p = a.q + ((size_t)head * a.rows + start + ra) * kHeadDim + 16 * c;
     const half* qb_p = a.q + ((size_t)head * a.rows + start + rb) * kHeadDim + 16 * c;
 #pragma unroll
@@ -88,13 +91,13 @@ __global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 3
       qa[ks][3] = ub.y;
     }
   }
-  const int pos_a = r0 + g, pos_b = r0 + g + 8;  // causal bounds of the lane's two rows
+  const int pos_a = off + r0 + g, pos_b = off + r0 + g + 8;  // causal bounds of the lane's two rows
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-  const int t_stop = min(r0 + 16, len);  // keys 0 .. t_stop - 1 are visible to some row of the warp
+  const int t_stop = min(off + r0 + 16, kv_len);  // keys 0 .. t_stop - 1 are visible to some row of the warp
   // Warp w takes the key tiles w, w + 4, ...: the walk over a row's keys is a serial chain per
   // warp (load, q.K, softmax, p.V per tile), and four warps cut it to a quarter.
   for (int t0 = kSplitKeys ? 32 * warp : 0; t0 < t_stop; t0 += kSplitKeys ? 32 * kPfWarps : 32) {
@@ -132,8 +135,8 @@ __global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 3
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int t = t0 + 8 * nb + 2 * c + e;
-        d[nb][e] = (t <= pos_a && t < len) ? d[nb][e] * a.scale : -INFINITY;
-        d[nb][2 + e] = (t <= pos_b && t < len) ? d[nb][2 + e] * a.scale : -INFINITY;
+        d[nb][e] = (t <= pos_a && t < kv_len) ? d[nb][e] * a.scale : -INFINITY;
+        d[nb][2 + e] = (t <= pos_b && t < kv_len) ? d[nb][2 + e] * a.scale : -INFINITY;
         mt[0] = fmaxf(mt[0], d[nb][e]);
         mt[1] = fmaxf(mt[1], d[nb][2 + e]);
       }
@@ -266,8 +269,9 @@ __global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 3
 
 namespace quic {
 int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
-                        const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len, int32_t rows,
-                        int32_t s_max, int32_t n_slots, float scale, void* out, cudaStream_t stream, bool pdl) {
+                        const int32_t* seq_len, const int32_t* seq_slot, const int32_t* seq_off, int32_t n_seq,
+                        int32_t max_len, int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,
+                        cudaStream_t stream, bool pdl) {
   QUIC_REQUIRE(q && kcache && vcache && seq_start && seq_len && seq_slot && out, QUIC_E_ARG,
                "attn_prefill: null tensor");
   QUIC_REQUIRE(n_seq >= 0 && n_seq <= 65535 && rows >= 0 && max_len >= 0 && s_max >= 1 && max_len <= s_max &&
@@ -284,6 +288,7 @@ int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, c
   a.seq_start = seq_start;
   a.seq_len = seq_len;
   a.seq_slot = seq_slot;
+  a.seq_off = seq_off;
   a.out = (half*)out;
   a.rows = rows;
   a.s_max = s_max;
@@ -302,9 +307,9 @@ int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, c
 }  // namespace quic
 
 extern "C" int quic_attn_prefill(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
-                                 const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len,
-                                 int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,
-                                 void* stream) {
-  return quic::attn_prefill_launch(q, kcache, vcache, seq_start, seq_len, seq_slot, n_seq, max_len, rows, s_max,
-                                   n_slots, scale, out, (cudaStream_t)stream, false);
+                                 const int32_t* seq_len, const int32_t* seq_slot, const int32_t* seq_off,
+                                 int32_t n_seq, int32_t max_len, int32_t rows, int32_t s_max, int32_t n_slots,
+                                 float scale, void* out, void* stream) {
+  return quic::attn_prefill_launch(q, kcache, vcache, seq_start, seq_len, seq_slot, seq_off, n_seq, max_len, rows,
+                                   s_max, n_slots, scale, out, (cudaStream_t)stream, false);
 }

@@ -187,8 +187,9 @@ cudaError_t launch_qkv_rope_append(const half* qkv, const int32_t* slots, const 
                                    const half* sin_t, int max_pos, half* q_out, half* kcache, half* vcache, int s_max,
                                    int n_slots, int rows, cudaStream_t st, bool pdl);
 int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
-                        const int32_t* seq_len, const int32_t* seq_slot, int32_t n_seq, int32_t max_len, int32_t rows,
-                        int32_t s_max, int32_t n_slots, float scale, void* out, cudaStream_t stream, bool pdl);
+                        const int32_t* seq_len, const int32_t* seq_slot, const int32_t* seq_off, int32_t n_seq,
+                        int32_t max_len, int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,
+                        cudaStream_t stream, bool pdl);
 cudaError_t launch_rmsnorm(const half* x, const half* residual, const half* w, float eps, half* y, half* sum_out,
                            int rows, cudaStream_t st);
 int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* workspace, cudaStream_t st,

@@ -82,14 +82,14 @@ __global__ void __launch_bounds__(224) gather_last_kernel(const half* __restrict
 
 // tok[slot] = first generated token, pos[slot] = prompt length.
 __global__ void set_slot_state_kernel(const int64_t* __restrict__ first, const int32_t* __restrict__ seq_len,
-                                      const int32_t* __restrict__ seq_slot, int n_seq, int n_slots,
-                                      int32_t* __restrict__ tok, int32_t* __restrict__ pos) {
+                                      const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_off,
+                                      int n_seq, int n_slots, int32_t* __restrict__ tok, int32_t* __restrict__ pos) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_seq) return;
   const int slot = seq_slot[i];
   if (slot < 0 || slot >= n_slots) return;
   tok[slot] = (int32_t)first[i];
-  pos[slot] = seq_len[i];
+  pos[slot] = seq_len[i] + (seq_off != nullptr ? seq_off[i] : 0);
 }
 
 // One W4A16 linear over all rows, in chunks that bound the split-K workspace.
@@ -151,8 +151,8 @@ extern "C" int quic_prefill(const quic_model_t* m, const quic_prefill_t* p, void
     if ((rc = linear_rows(xn, L.qkv, qkv, rows, ws, stream)) != QUIC_OK) return rc;
     QUIC_CUDA(launch_qkv_rope_append(qkv, p->row_slot, p->row_pos, (const half*)m->rope_cos, (const half*)m->rope_sin,
                                      m->max_pos, q, kc, vc, p->s_max, p->n_slots, rows, st, true));
-    if ((rc = attn_prefill_launch(q, kc, vc, p->seq_start, p->seq_len, p->seq_slot, p->n_seq, p->max_len, rows,
-                                  p->s_max, p->n_slots, 0.125f /* 64^-0.5, src/model.py:129 */, attn, st, true)) != QUIC_OK)
+    if ((rc = attn_prefill_launch(q, kc, vc, p->seq_start, p->seq_len, p->seq_slot, p->seq_off, p->n_seq, p->max_len,
+                                  rows, p->s_max, p->n_slots, 0.125f /* 64^-0.5, src/model.py:129 */, attn, st, true)) != QUIC_OK)
       return rc;
     if ((rc = linear_rows(attn, L.o, tmp, rows, ws, stream)) != QUIC_OK) return rc;
     // h += o ; xn = norm(h)
@@ -184,8 +184,8 @@ extern "C" int quic_prefill(const quic_model_t* m, const quic_prefill_t* p, void
   if ((rc = quic_lm_head_argmax(xlast, nullptr, m->eps, m->embed, m->vocab, p->n_seq, p->logits, p->first_tokens,
                                 base + ar.lm, stream)) != QUIC_OK)
     return rc;
-  set_slot_state_kernel<<<(p->n_seq + 127) / 128, 128, 0, st>>>(p->first_tokens, p->seq_len, p->seq_slot, p->n_seq,
-                                                               p->n_slots, p->tok, p->pos);
+  set_slot_state_kernel<<<(p->n_seq + 127) / 128, 128, 0, st>>>(p->first_tokens, p->seq_len, p->seq_slot, p->seq_off,
+                                                               p->n_seq, p->n_slots, p->tok, p->pos);
   QUIC_CUDA(cudaGetLastError());
   return QUIC_OK;
 }

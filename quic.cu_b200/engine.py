@@ -94,6 +94,10 @@ class Engine:
         self.request_source = None
         self.on_finish = None
         self._tags: dict[int, object] = {}
+        # chunked prefill: sequences whose prompt is only partly in their slot, and how much is
+        self.prefill_chunk = getattr(config, "prefill_chunk", None)
+        self.prefilling: list[SequenceState] = []
+        self._prefilled: dict[int, int] = {}
 
     # ---- requests ------------------------------------------------------------------
     def add_request(self, prompt: str) -> int:
@@ -153,31 +157,50 @@ class Engine:
 
     @torch.inference_mode()
     def _prefill_begin(self, sequences: list[SequenceState], stream=None):
-        """Assigns slots and enqueues the prefill (on ``stream`` when given); nothing is read
-        back yet.  Returns what ``_prefill_end`` needs."""
+        """Assigns slots to new sequences and enqueues the prefill of every sequence's next
+        chunk (the whole prompt without ``prefill_chunk``), on ``stream`` when given; nothing is
+        read back yet.  Returns what ``_prefill_end`` needs."""
         for seq in sequences:
-            seq.slot = self.free_slots.pop(0)
+            if seq.slot is None:
+                seq.slot = self.free_slots.pop(0)
         slots = [s.slot for s in sequences]
-        prompts = [s.prompt_tokens.view(-1) for s in sequences]
+        offs = [self._prefilled.get(s.request_id, 0) for s in sequences]
+        prompts, done = [], []
+        for seq, off in zip(sequences, offs):
+            ids = seq.prompt_tokens.view(-1)
+            end = ids.numel() if not self.prefill_chunk else min(ids.numel(), off + int(self.prefill_chunk))
+            prompts.append(ids[off:end])
+            done.append(end)
+        kwargs = {"offsets": offs} if any(offs) else {}
         if stream is None:
-            first, _ = self.model.prefill(self.cache, slots, prompts)
+            first, _ = self.model.prefill(self.cache, slots, prompts, **kwargs)
         else:
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
-                first, _ = self.model.prefill(self.cache, slots, prompts)
-        return sequences, first, stream
+                first, _ = self.model.prefill(self.cache, slots, prompts, **kwargs)
+        return sequences, first, stream, done
 
     @torch.inference_mode()
-    def _prefill_end(self, pending) -> None:
-        sequences, first, stream = pending
+    def _prefill_end(self, pending) -> list[SequenceState]:
+        """Reads the first tokens back.  Sequences whose whole prompt is now cached get theirs
+        and are returned (they join the running rows); the others stay in ``prefilling``."""
+        sequences, first, stream, done = pending
         if stream is not None:
             stream.synchronize()  # the slots are complete before any later decode launch
         first = first.tolist() if hasattr(first, "tolist") else list(first)
-        for seq, token in zip(sequences, first):
-            self._update_sequence_with_token(seq, int(token))
+        complete, self.prefilling = [], []
+        for seq, token, end in zip(sequences, first, done):
+            if end >= seq.prompt_tokens.numel():
+                self._prefilled.pop(seq.request_id, None)
+                self._update_sequence_with_token(seq, int(token))
+                complete.append(seq)
+            else:  # (the token predicted after a partial prompt is not used)
+                self._prefilled[seq.request_id] = end
+                self.prefilling.append(seq)
+        return complete
 
-    def _prefill_sequences(self, sequences: list[SequenceState]) -> None:
-        self._prefill_end(self._prefill_begin(sequences))
+    def _prefill_sequences(self, sequences: list[SequenceState]) -> list[SequenceState]:
+        return self._prefill_end(self._prefill_begin(sequences))
 
     def _side_stream(self):
         """Second CUDA stream for overlapped prefills (None for a model that is not on a GPU)."""
@@ -210,7 +233,9 @@ class Engine:
                         if room > 0:
                             for ids, limit, tag in self.request_source(room):
                                 self.add_request_ids(ids, max_tokens=limit, tag=tag)
-                    decision = self.batching_policy.decide(self.running, self.waiting, self.max_batch_size)
+                    # (sequences still prefilling hold a slot: they count as running for admission)
+                    decision = self.batching_policy.decide(self.running + self.prefilling, self.waiting,
+                                                           self.max_batch_size)
                     released = {seq.request_id for seq in decision.release}
                     for seq in decision.release:
                         outputs[seq.request_id] = self._finish(seq)
@@ -222,21 +247,20 @@ class Engine:
                     if released:
                         self.running = [s for s in self.running if s.request_id not in released]
                 pending = None
-                if decision.admit:
+                if decision.admit or self.prefilling:
                     with Span("prefill", self.registry):
-                        admitted = [self.waiting.popleft() for _ in decision.admit]
+                        admitted = self.prefilling + [self.waiting.popleft() for _ in decision.admit]
                         if self.overlap_prefill and any(not seq.is_finished for seq in self.running):
                             # the rows already running decode their burst while the admitted
-                            # prompts prefill into their (disjoint) slots; they join afterwards
+                            # prompts (or their next chunks) prefill into their (disjoint) slots;
+                            # they join afterwards
                             pending = self._prefill_begin(admitted, self._side_stream())
                         else:
-                            self._prefill_sequences(admitted)
-                            self.running.extend(admitted)
-                if not self.running and pending is None:
+                            self.running.extend(self._prefill_sequences(admitted))
+                if not self.running and pending is None and not self.prefilling:
                     break
                 self.step()
                 if pending is not None:
                     with Span("prefill", self.registry):
-                        self._prefill_end(pending)
-                        self.running.extend(pending[0])
+                        self.running.extend(self._prefill_end(pending))
         return [outputs[request_id] for request_id in sorted(outputs)]

@@ -114,6 +114,7 @@ class Prefill(C.Structure):
         ("first_tokens", C.c_void_p),
         ("logits", C.c_void_p),
         ("scratch", C.c_void_p),
+        ("seq_off", C.c_void_p),
     ]
 
 
@@ -133,7 +134,7 @@ SIGNATURES = {
     "quic_rope_table_init": (C.c_int, [_P, _I32, _P, _P, _P]),
     "quic_rope": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P]),
     "quic_qkv_rope_append": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _I32, _I32, _I32, _P]),
-    "quic_attn_prefill": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, C.c_float, _P, _P]),
+    "quic_attn_prefill": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, C.c_float, _P, _P]),
     "quic_swiglu": (C.c_int, [_P, _P, _P, _I32, _P]),
     "quic_swiglu_fused": (C.c_int, [_P, _P, _I32, _P]),
     "quic_argmax": (C.c_int, [_P, _I32, _I32, _P, _P]),
@@ -431,7 +432,8 @@ def qkv_rope_append(qkv: torch.Tensor, slots: torch.Tensor, positions: torch.Ten
 
 
 def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, seq_start: torch.Tensor,
-                 seq_len: torch.Tensor, seq_slot: torch.Tensor, max_len: int, scale: float = -1.0) -> torch.Tensor:
+                 seq_len: torch.Tensor, seq_slot: torch.Tensor, max_len: int, scale: float = -1.0,
+                 seq_off: torch.Tensor | None = None) -> torch.Tensor:
     """Causal prefill attention of several sequences in one launch.  ``q`` fp16 [14, rows, 64]
     (from qkv_rope_append); ``seq_start`` / ``seq_len`` / ``seq_slot`` int32 [n_seq] on the
     device; keys and values are read from the slots.  Returns fp16 [rows, 896]."""
@@ -443,10 +445,56 @@ def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, se
         raise RuntimeError("attn_prefill: sequence tables must be int32")
     rows, n_seq = q.shape[1], seq_len.numel()
     out = torch.empty(rows, HEADS * HEAD_DIM, dtype=torch.float16, device=q.device)
+    if seq_off is not None and (seq_off.dtype != torch.int32 or seq_off.numel() != n_seq or not seq_off.is_cuda):
+        raise RuntimeError("attn_prefill: seq_off must be a CUDA int32 tensor with one entry per sequence")
     check(lib().quic_attn_prefill(ptr(q), ptr(kcache), ptr(vcache), ptr(seq_start), ptr(seq_len), ptr(seq_slot),
-                                  n_seq, int(max_len), rows, kcache.shape[2], kcache.shape[0], float(scale), ptr(out),
+                                  ptr(seq_off), n_seq, int(max_len), rows, kcache.shape[2], kcache.shape[0], float(scale), ptr(out),
                                   stream_ptr()),
           "attn_prefill")
+    return out
+
+
+def _flash_attn_prefill_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = True,
+                                softmax_scale: float = -1.0, pad_lens: torch.Tensor | None = None) -> torch.Tensor:
+    """flash_attn_prefill.forward(Q fp16 [B,14,N,64], K, V fp16 [B,14 or 2,N,64], is_causal,
+    softmax_scale, pad_lens int32 [B] or None) -> fp16 [B,14,N,64]: the reference's prefill
+    attention call (kernels/cuda/flash_attn_prefill.cu:520, kernels/flash_attn_prefill_pytorch.py:10)
+    on left-padded batches.  The rows are repacked without their padding, run through
+    ``attn_prefill`` in one launch and scattered back; rows inside the padding come back as zeros
+    (the reference lets them attend to themselves; nothing reads them)."""
+    _need_cuda(q, k, v, pad_lens)
+    _need_half(q, k, v)
+    if not is_causal:
+        raise RuntimeError("flash_attn_prefill: only the causal form is built")
+    b, nh, n, d = q.shape
+    if nh != HEADS or d != HEAD_DIM or k.shape != v.shape or k.shape[0] != b or k.shape[2] != n or \
+            k.shape[1] not in (HEADS, KV_HEADS):
+        raise RuntimeError("flash_attn_prefill: expected Q [B,14,N,64] and K, V [B,14|2,N,64]")
+    if k.shape[1] == HEADS:  # repeat_kv layout: query head h reads kv head h // 7
+        k, v = k[:, :: HEADS // KV_HEADS], v[:, :: HEADS // KV_HEADS]
+    pads = [0] * b if pad_lens is None else [int(p) for p in pad_lens.tolist()]
+    lens = [n - p for p in pads]
+    if any(l < 0 for l in lens):
+        raise RuntimeError("flash_attn_prefill: a pad length exceeds the sequence length")
+    dev = q.device
+    pos = torch.arange(n, device=dev)
+    pad_t = torch.tensor(pads, device=dev)
+    keep = pos[None, :] >= pad_t[:, None]                                    # [B, N] real tokens
+    src = torch.clamp(pos[None, :] + pad_t[:, None], max=n - 1)              # token t of the sequence sits at pad + t
+    idx = src[:, None, :, None].expand(b, KV_HEADS, n, d)
+    kc, vc = k.gather(2, idx).contiguous(), v.gather(2, idx).contiguous()    # [B, 2, N, 64], sequences at position 0
+    q_rows = q.permute(1, 0, 2, 3)[:, keep].contiguous()                     # [14, rows, 64]
+    starts, total = [], 0
+    for l in lens:
+        starts.append(total)
+        total += l
+    live = [i for i, l in enumerate(lens) if l > 0]
+    out = torch.zeros(b, nh, n, d, dtype=torch.float16, device=dev)
+    if not live:
+        return out
+    table = torch.tensor([[starts[i] for i in live], [lens[i] for i in live], live], dtype=torch.int32, device=dev)
+    rows = attn_prefill(q_rows, kc, vc, table[0], table[1], table[2], max(lens), float(softmax_scale))
+    out.permute(0, 2, 1, 3)[keep] = rows.view(total, nh, d)
     return out
 
 
@@ -595,6 +643,13 @@ def gemm():
 def flash_attn_decode():
     lib()
     return SimpleNamespace(forward=_flash_attn_decode_forward)
+
+
+@functools.cache
+def flash_attn_prefill():
+    """Same getter as the reference's (kernels/__init__.py:76-85)."""
+    lib()
+    return SimpleNamespace(forward=_flash_attn_prefill_forward)
 
 
 @functools.cache

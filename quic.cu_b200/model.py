@@ -24,7 +24,6 @@ import os
 from dataclasses import dataclass
 
 import torch
-import torch.nn.functional as F
 
 from . import kernels as K
 from .checkpoint import LAYER_LINEARS, detect_group_size, packed_prefixes
@@ -132,15 +131,6 @@ class SlotCache:
             pass
 
 
-def _sdpa_backends():
-    """Prefill attention is torch SDPA, as in the reference.  The cuDNN backend builds an
-    execution plan for every new sequence length (~0.1 s each), which a serving loop with
-    ragged prompts pays on almost every admission; the flash / memory-efficient kernels do not."""
-    from torch.nn.attention import SDPBackend, sdpa_kernel
-
-    return sdpa_kernel([SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH])
-
-
 def _ctx_bucket(n: int, batch: int = 1) -> int:
     """Context bound a captured graph is valid for: multiples of 128 up to 2048 (so the
     attention grid tracks the real context closely), powers of two beyond.  From 16 rows the
@@ -170,7 +160,9 @@ class QUICForCausalLM:
         if (config["hidden_size"], config["intermediate_size"], config["num_attention_heads"],
                 config["num_key_value_heads"]) != (HIDDEN, INTER, HEADS, KV_HEADS):
             raise RuntimeError("quic_b200 kernels are built for the Qwen2.5-0.5B layer shapes only")
-        self.prefill_backend = "pytorch"
+        # kept for the reference's load(prefill_backend=...) signature; every value runs the
+        # library's own prefill attention kernel
+        self.prefill_backend = "quic"
         self.prefill_all_logits = False
         self.layers: list[dict] = []
         self.embed: torch.Tensor | None = None
@@ -468,32 +460,40 @@ class QUICForCausalLM:
     # ---- prefill -----------------------------------------------------------------
     @torch.inference_mode()
     def prefill(self, cache: SlotCache, slots: list[int], prompts: list[torch.Tensor],
-                all_logits: bool = False):
+                all_logits: bool = False, offsets: list[int] | None = None):
         """Runs the prompts (1-D int64 tensors) through the model, fills their KV slots and
-        returns (first greedy token per prompt [n] int64, logits).  Linear layers run the
-        W4A16 kernels at M = total prompt tokens; attention is torch SDPA per sequence, as the
-        reference's default prefill backend (kernels/flash_attn_prefill_pytorch.py:10)."""
+        returns (first greedy token per prompt [n] int64, logits).  Linear layers run at
+        M = total prompt tokens; attention is the library's causal prefill kernel, every
+        sequence in one launch (the reference: src/model.py:164-199, prefill attention
+        kernels/flash_attn_prefill_pytorch.py:10 / kernels/cuda/flash_attn_prefill.cu:87).
+
+        ``offsets[i]`` > 0 makes ``prompts[i]`` the NEXT chunk of a prompt whose first
+        offsets[i] tokens are already in slot slots[i] (chunked prefill): positions continue
+        from there and attention sees the cached tokens as well."""
         dev = self.device
         cache.check_slots(slots, len(prompts), "prefill")
         lens = [int(p.numel()) for p in prompts]
+        offs = [0] * len(lens) if offsets is None else [int(o) for o in offsets]
+        if len(offs) != len(lens) or any(o < 0 for o in offs):
+            raise ValueError("prefill: one non-negative offset per prompt")
+        if any(o > 0 and cache.host_len[s] != o for s, o in zip(slots, offs)):
+            raise ValueError("prefill: an offset must equal the tokens already cached in the slot")
         if any(n < 1 for n in lens):
             raise RuntimeError("prefill: empty prompt")
-        if any(n > cache.s_max or n > self.max_pos for n in lens):
+        if any(o + n > cache.s_max or o + n > self.max_pos for n, o in zip(lens, offs)):
             raise RuntimeError("prefill: prompt longer than the KV slot")
         bounds = [0]
         for n in lens:
             bounds.append(bounds[-1] + n)
-        if self.prefill_backend != "pytorch" and not all_logits:
-            return self._prefill_fused(cache, slots, prompts, lens, bounds)
+        if not all_logits:
+            return self._prefill_fused(cache, slots, prompts, lens, bounds, offs)
         ids = torch.cat([p.reshape(-1) for p in prompts]).to(dev, torch.long)
         # per token: its KV slot and its position (one small host -> device copy each)
-        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev, non_blocking=True)
+        pos = torch.cat([torch.arange(o, o + n, dtype=torch.int32) for n, o in zip(lens, offs)]).to(dev, non_blocking=True)
         slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32),
                                           torch.tensor(lens)).to(dev, non_blocking=True)
-        T = ids.numel()
-        if self.prefill_backend != "pytorch":
-            table = torch.tensor([bounds[:-1], lens, slots], dtype=torch.int32).to(dev, non_blocking=True)
-            seq_start, seq_len, seq_slot = table[0], table[1], table[2]
+        table = torch.tensor([bounds[:-1], lens, slots, offs], dtype=torch.int32).to(dev, non_blocking=True)
+        seq_start, seq_len, seq_slot, seq_off = table[0], table[1], table[2], table[3]
         h = self.embed[ids]
         rms, lin = K.rmsnorm().forward, K.w4a16_linear
         xn = rms(h, self.layers[0]["ln1"], self.eps)
@@ -501,17 +501,8 @@ class QUICForCausalLM:
             qkv = lin(L["qkv"], xn)
             # heads split, RoPE applied and K/V written into their slots by one kernel
             q = K.qkv_rope_append(qkv, slot_of, pos, self.rope_cos, self.rope_sin, cache.kv[li, 0], cache.kv[li, 1])
-            if self.prefill_backend == "pytorch":  # the reference's default: torch SDPA per sequence
-                attn = torch.empty(T, HEADS * HEAD_DIM, dtype=DTYPE, device=dev)
-                with _sdpa_backends():
-                    for i, s in enumerate(slots):
-                        a, b = bounds[i], bounds[i + 1]
-                        k, v = cache.kv[li, 0, s, :, : b - a], cache.kv[li, 1, s, :, : b - a]
-                        o = F.scaled_dot_product_attention(q[None, :, a:b], k[None], v[None],
-                                                           is_causal=True, scale=HEAD_DIM ** -0.5, enable_gqa=True)
-                        attn[a:b] = o[0].transpose(0, 1).reshape(b - a, -1)
-            else:  # "quic": every sequence in one launch of the causal prefill kernel
-                attn = K.attn_prefill(q, cache.kv[li, 0], cache.kv[li, 1], seq_start, seq_len, seq_slot, max(lens))
+            attn = K.attn_prefill(q, cache.kv[li, 0], cache.kv[li, 1], seq_start, seq_len, seq_slot, max(lens),
+                                  seq_off=seq_off)
             o = lin(L["o"], attn)
             xn, h = rms(o, L["ln2"], self.eps, residual=h)
             gu = lin(L["gate_up"], xn)
@@ -520,30 +511,27 @@ class QUICForCausalLM:
             nxt = self.layers[li + 1]["ln1"] if li + 1 < self.n_layers else self.final_norm
             xn, h = rms(d, nxt, self.eps, residual=h)
         last = torch.tensor([b - 1 for b in bounds[1:]], device=dev)
-        if all_logits:
-            logits = K.gemm().forward(xn, self.embed)
-            first = K.sampler().forward(logits[last].unsqueeze(1)).view(-1)
-        else:  # xn is already normalised: fused lm_head + argmax on the last positions
-            first, logits = K.lm_head_argmax(xn[last], self.embed, want_logits=True)
+        logits = K.gemm().forward(xn, self.embed)
+        first = K.sampler().forward(logits[last].unsqueeze(1)).view(-1)
         st = torch.tensor(slots, device=dev, dtype=torch.long)
         cache.tok[st] = first.to(torch.int32)
-        cache.pos[st] = torch.tensor(lens, device=dev, dtype=torch.int32)
-        for s, n in zip(slots, lens):
-            cache.host_len[s] = n
+        cache.pos[st] = torch.tensor([o + n for n, o in zip(lens, offs)], device=dev, dtype=torch.int32)
+        for s, n, o in zip(slots, lens, offs):
+            cache.host_len[s] = o + n
         return first, logits
 
     def _prefill_fused(self, cache: SlotCache, slots: list[int], prompts: list[torch.Tensor], lens: list[int],
-                       bounds: list[int]):
-        """prefill_backend "quic": the whole prefill as ONE library call (quic_prefill): the
-        host builds one int32 table (token ids, slot and position per row, start / length /
-        slot per sequence), copies it once, and reads nothing back."""
+                       bounds: list[int], offs: list[int]):
+        """The whole prefill as ONE library call (quic_prefill): the host builds one int32 table
+        (token ids, slot and position per row; start / length / slot / tokens already cached
+        per sequence), copies it once, and reads nothing back."""
         dev = self.device
         rows, n_seq = bounds[-1], len(lens)
-        table = torch.empty(3 * rows + 3 * n_seq, dtype=torch.int32)
+        table = torch.empty(3 * rows + 4 * n_seq, dtype=torch.int32)
         table[:rows] = torch.cat([p.reshape(-1) for p in prompts])
         table[rows:2 * rows] = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32), torch.tensor(lens))
-        table[2 * rows:3 * rows] = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
-        table[3 * rows:] = torch.tensor([bounds[:-1], lens, slots], dtype=torch.int32).reshape(-1)
+        table[2 * rows:3 * rows] = torch.cat([torch.arange(o, o + n, dtype=torch.int32) for n, o in zip(lens, offs)])
+        table[3 * rows:] = torch.tensor([bounds[:-1], lens, slots, offs], dtype=torch.int32).reshape(-1)
         t = table.to(dev, non_blocking=True)
         need = K.lib().quic_prefill_scratch_bytes(rows, n_seq, self.vocab)
         scratch = cache.__dict__.get("_prefill_scratch")
@@ -555,10 +543,11 @@ class QUICForCausalLM:
         base = t.data_ptr()
         p = K.Prefill(base, base + 4 * rows, base + 8 * rows, base + 12 * rows, base + 12 * rows + 4 * n_seq,
                       base + 12 * rows + 8 * n_seq, rows, n_seq, max(lens), K.ptr(cache.kv), cache.n_slots,
-                      cache.s_max, K.ptr(cache.tok), K.ptr(cache.pos), K.ptr(first), K.ptr(logits), K.ptr(scratch))
+                      cache.s_max, K.ptr(cache.tok), K.ptr(cache.pos), K.ptr(first), K.ptr(logits), K.ptr(scratch),
+                      base + 12 * rows + 12 * n_seq if any(offs) else None)
         K.check(K.lib().quic_prefill(C.byref(self._c_model), C.byref(p), K.stream_ptr()), "prefill")
-        for s_, n in zip(slots, lens):
-            cache.host_len[s_] = n
+        for s_, n, o in zip(slots, lens, offs):
+            cache.host_len[s_] = o + n
         return first, logits
 
     # ---- reference-shaped forward ------------------------------------------------------
@@ -597,7 +586,18 @@ class QUICForCausalLM:
             return CausalLMOutput(logits=logits.view(batch, 1, self.vocab),
                                   past_key_values=cache if use_cache else None)
         if past_len != 0:
-            raise RuntimeError("forward: multi-token input on a non-empty cache is not supported")
+            # the next chunk of every row's prompt (the reference's forward accepts a multi-token
+            # input on a filled cache, src/model.py:280-291): no new padding can appear here
+            if any(cache.host_len[s] == 0 for s in cache.batch_slots):
+                raise RuntimeError("forward: a multi-token input continues rows that are already cached")
+            if attention_mask is not None and not bool(attention_mask[:, -seq_len:].bool().all()):
+                raise ValueError("forward: the tokens of a continuation cannot be padding")
+            offs = [cache.host_len[s] for s in cache.batch_slots]
+            want_all = self.prefill_all_logits
+            _, logits = self.prefill(cache, cache.batch_slots, [input_ids[b] for b in range(batch)],
+                                     all_logits=want_all, offsets=offs)
+            logits = logits.view(batch, seq_len, self.vocab) if want_all else logits.view(batch, 1, self.vocab)
+            return CausalLMOutput(logits=logits, past_key_values=cache if use_cache else None)
         if attention_mask is not None:
             if tuple(attention_mask.shape) != (batch, kv_len):
                 raise ValueError(f"attention_mask {tuple(attention_mask.shape)} does not match "

@@ -30,13 +30,16 @@ class FakeSlotModel:
     def new_cache(self, n_slots, s_max):
         return SimpleNamespace(n_slots=n_slots, s_max=s_max, last=[0] * n_slots, length=[0] * n_slots)
 
-    def prefill(self, cache, slots, prompts):
-        self.calls.append(("prefill", list(slots)))
+    def prefill(self, cache, slots, prompts, offsets=None):
+        """``offsets``: tokens of each prompt already cached (chunked prefill)."""
+        offsets = [0] * len(slots) if offsets is None else list(offsets)
+        self.calls.append(("prefill", list(slots), [len(p) for p in prompts], offsets))
         first = []
-        for slot, prompt in zip(slots, prompts):
+        for slot, prompt, off in zip(slots, prompts, offsets):
             ids = [int(t) for t in prompt]
-            tok = next_token(ids[-1], len(ids))
-            cache.last[slot], cache.length[slot] = tok, len(ids)
+            assert off == 0 or cache.length[slot] == off, "a chunk continues what the slot holds"
+            tok = next_token(ids[-1], off + len(ids))
+            cache.last[slot], cache.length[slot] = tok, off + len(ids)
             first.append(tok)
         return first, None
 

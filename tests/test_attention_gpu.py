@@ -174,3 +174,60 @@ def test_decode_cta_merge_refuses_longer_caches():
     k = torch.zeros((1, 2, 4097, HEAD_DIM), device="cuda").half()
     with pytest.raises(RuntimeError, match="4096"):
         K.flash_attn_decode().forward(q, k, k, SCALE, None, cta_merge=True)
+
+
+def test_prefill_attention_of_a_later_chunk_sees_the_cached_tokens():
+    """quic_attn_prefill with seq_off: the rows of a call are tokens off .. off + len - 1 of their
+    sequence, keys and values 0 .. off + len - 1 come from the slot; against causal SDPA over
+    the whole sequence.  Offsets on both sides of the 16-row and 32-key tile edges, one
+    sequence without an offset, one whose slot index is not its row."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    offs, lens, slots = [37, 0, 16, 511], [50, 21, 1, 33], [2, 0, 3, 1]
+    s_max = 600
+    kc = torch.zeros(4, 2, s_max, 64, device="cuda", dtype=torch.float16)
+    vc = torch.zeros_like(kc)
+    rows = sum(lens)
+    q = torch.randn(HEADS, rows, 64, device="cuda", generator=g).half()
+    starts, want = [], torch.empty(rows, HEADS * 64)
+    a = 0
+    for off, n, slot in zip(offs, lens, slots):
+        starts.append(a)
+        kc[slot, :, : off + n] = torch.randn(2, off + n, 64, device="cuda", generator=g).half()
+        vc[slot, :, : off + n] = torch.randn(2, off + n, 64, device="cuda", generator=g).half()
+        keys = kc[slot, :, : off + n].repeat_interleave(7, dim=0).float()
+        vals = vc[slot, :, : off + n].repeat_interleave(7, dim=0).float()
+        qs = q[:, a:a + n].float()                                           # [14, n, 64]
+        causal = torch.arange(off + n, device="cuda")[None, :] <= (off + torch.arange(n, device="cuda"))[:, None]
+        o = F.scaled_dot_product_attention(qs[None], keys[None], vals[None], attn_mask=causal[None, None], scale=SCALE)
+        want[a:a + n] = o[0].transpose(0, 1).reshape(n, -1).cpu()
+        a += n
+    dev = dict(device="cuda", dtype=torch.int32)
+    out = K.attn_prefill(q, kc, vc, torch.tensor(starts, **dev), torch.tensor(lens, **dev), torch.tensor(slots, **dev),
+                         max(lens), seq_off=torch.tensor(offs, **dev))
+    assert torch.allclose(out.float().cpu(), want, atol=ATOL), (out.float().cpu() - want).abs().max()
+
+
+@pytest.mark.parametrize("kv_repeated", [True, False])
+def test_flash_attn_prefill_getter_matches_the_reference_recipe(kv_repeated):
+    """flash_attn_prefill().forward on a left-padded batch, the reference's call shape
+    (src/model.py:176-183), against its PyTorch backend's mask recipe
+    (kernels/flash_attn_prefill_pytorch.py:21-32) on the rows that are real tokens."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    b, n = 3, 70
+    q = torch.randn(b, HEADS, n, 64, device="cuda", generator=g).half()
+    k = torch.randn(b, 2, n, 64, device="cuda", generator=g).half()
+    v = torch.randn(b, 2, n, 64, device="cuda", generator=g).half()
+    pads = torch.tensor([0, 13, 69], device="cuda", dtype=torch.int32)
+    kr, vr = k.repeat_interleave(7, dim=1), v.repeat_interleave(7, dim=1)
+    out = K.flash_attn_prefill().forward(q, kr if kv_repeated else k, vr if kv_repeated else v, True, SCALE, pads)
+    pos = torch.arange(n, device="cuda")
+    mask = ((pos[None, :] <= pos[:, None])[None, None] & (pos[None, :] >= pads[:, None])[:, None, None, :]) | \
+        torch.eye(n, dtype=torch.bool, device="cuda")
+    want = F.scaled_dot_product_attention(q.float(), kr.float(), vr.float(), attn_mask=mask, scale=SCALE)
+    real = (pos[None, :] >= pads[:, None])[:, None, :, None].expand_as(out)
+    assert torch.allclose(out.float()[real], want[real], atol=ATOL)
+    assert torch.count_nonzero(out[~real]) == 0

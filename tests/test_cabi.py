@@ -52,7 +52,7 @@ def test_struct_sizes_match_the_header():
     assert ctypes.sizeof(K.Layer) == 4 * 48 + 16
     assert ctypes.sizeof(K.Model) == 56
     assert ctypes.sizeof(K.Decode) == 96
-    assert ctypes.sizeof(K.Prefill) == 120
+    assert ctypes.sizeof(K.Prefill) == 128
 
 
 def test_argument_errors_are_reported_without_a_gpu():

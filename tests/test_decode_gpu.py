@@ -302,3 +302,42 @@ def test_slots_are_checked_before_any_launch(tiny_model):
     with pytest.raises(ValueError):  # three rows, two slots
         net(torch.tensor([[1, 2], [3, 4], [5, 6]]), past_key_values=small)
     assert net.decode(cache, [1], 2)[0]  # the cache is still usable
+
+
+@pytest.mark.parametrize("all_logits", [False, True])
+def test_chunked_prefill_equals_whole_prompt_prefill(tiny_model, all_logits):
+    """A prompt prefilled in chunks (prefill(..., offsets=...): 17 + 40 + 3 tokens and, in the
+    same calls, a second sequence in one piece) must leave the slot and the following decode
+    exactly as the whole prompt does, in the fused library call and in the per-op path."""
+    net = tiny_model[0]
+    gen = torch.Generator().manual_seed(21)
+    long_p, short_p = torch.randint(0, 2048, (60,), generator=gen), torch.randint(0, 2048, (9,), generator=gen)
+    whole = net.new_cache(n_slots=4, s_max=128)
+    first_w, _ = net.prefill(whole, [2, 0], [long_p, short_p], all_logits=all_logits)
+    tokens_w = net.decode(whole, [2, 0], 8)
+
+    cache = net.new_cache(n_slots=4, s_max=128)
+    net.prefill(cache, [2, 0], [long_p[:17], short_p], all_logits=all_logits)
+    net.prefill(cache, [2], [long_p[17:57]], all_logits=all_logits, offsets=[17])
+    first_c, _ = net.prefill(cache, [2], [long_p[57:]], all_logits=all_logits, offsets=[57])
+    assert cache.host_len[2] == 60 and int(cache.pos[2]) == 60
+    assert int(first_c[0]) == int(first_w[0])
+    assert torch.equal(cache.kv[:, :, 2, :, :60], whole.kv[:, :, 2, :, :60])
+    assert net.decode(cache, [2, 0], 8) == tokens_w
+    with pytest.raises(ValueError):
+        net.prefill(cache, [2], [long_p[:4]], offsets=[5])  # does not continue what the slot holds
+
+
+def test_forward_accepts_a_multi_token_input_on_a_filled_cache(tiny_model):
+    """The reference's forward takes seq_len > 1 with past_key_values (src/model.py:280-291):
+    here that is the next chunk of every row's prompt."""
+    net, ref, _, _ = tiny_model
+    prompt = [11, 7, 1999, 42, 0, 512, 77, 1023, 5, 6, 900]
+    ref_tokens, ref_logits = ref.greedy(prompt, 1)
+    cache = net.new_cache(n_slots=2, s_max=64)
+    cache.batch_slots = [1]
+    net(torch.tensor([prompt[:4]]), past_key_values=cache)
+    out = net(torch.tensor([prompt[4:]]), past_key_values=cache)
+    assert out.logits.shape == (1, 1, 2048) and cache.get_seq_length() == len(prompt)
+    got = out.logits[0, 0].float().cpu()
+    assert torch.allclose(got, ref_logits[0].float(), rtol=2e-2, atol=5e-2), (got - ref_logits[0].float()).abs().max()

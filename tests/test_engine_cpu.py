@@ -63,9 +63,9 @@ def test_eos_is_appended_and_ends_the_request():  # src/engine.py:180-184
 
 def test_load_options_follow_the_reference_engine():  # src/engine.py:40-51
     engine, module = _engine("continuous", model_path="/m", tokenizer_path="/t")
-    assert module.options == {"path": "/m", "tokenizer_path": "/t", "prefill_backend": "pytorch"}
+    assert module.options == {"path": "/m", "tokenizer_path": "/t", "prefill_backend": "quic"}
     engine2, module2 = _engine("static")
-    assert module2.options == {"prefill_backend": "pytorch"}
+    assert module2.options == {"prefill_backend": "quic"}
 
 
 def test_request_that_cannot_fit_a_slot_is_rejected():
@@ -110,3 +110,28 @@ def test_overlapped_admission_prefills_before_the_running_rows_decode():
     assert out_a == out_b
     assert seq_a == [("prefill", 1), ("decode", 1), ("decode", 2)]
     assert seq_b == [("prefill", 1), ("decode", 2), ("decode", 2)]
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_chunked_prefill_gives_the_same_outputs_and_interleaves_with_decode(overlap):
+    """With prefill_chunk = 4 a 10-token prompt enters its slot in three calls (4, 4, 2 tokens,
+    each continuing at the tokens already cached), the rows that are running decode a burst
+    between the chunks, and every output equals independent greedy generation."""
+    module = FakeModule()
+    engine = Engine(max_batch_size=2, model_module=module,
+                    config=EngineConfig(batching="continuous", decode_burst=2, overlap_prefill=overlap,
+                                        max_context=64, prefill_chunk=4))
+    engine.max_tokens = 9
+    engine.eos_token_id = None
+    prompts = [[3, 4], list(range(20, 30)), [5, 6, 7]]
+    for p in prompts:
+        engine.add_request_ids(p)
+    outputs = engine.run()
+    assert outputs == [expected_generation(p, 9, eos=None) for p in prompts]
+    calls = module.model.calls
+    long_chunks = [(n, o) for c in calls if c[0] == "prefill"
+                   for slot, n, o in zip(c[1], c[2], c[3]) if (n, o) in ((4, 0), (4, 4), (2, 8))]
+    assert long_chunks == [(4, 0), (4, 4), (2, 8)]
+    first = next(i for i, c in enumerate(calls) if c[0] == "prefill" and 4 in c[3])   # second chunk
+    last = next(i for i, c in enumerate(calls) if c[0] == "prefill" and 8 in c[3])    # third chunk
+    assert any(c[0] == "decode" for c in calls[first:last])  # the short request decodes in between

@@ -195,3 +195,28 @@ def test_checkpoint_dir_with_tokenizer_runs_text_requests(tmp_path, tiny_model, 
     write_checkpoint_dir(str(tmp_path), state, bad)
     with pytest.raises(RuntimeError, match="group size"):
         Engine(max_batch_size=2, config=EngineConfig(model_path=str(tmp_path), max_context=64))
+
+
+def test_engine_with_chunked_prefill_matches_unchunked(tiny_model):
+    """prefill_chunk = 16: long prompts enter their slots a chunk per iteration while the
+    running rows decode; the outputs are those of the unchunked engine."""
+    from quic_cu_b200.config import EngineConfig
+    from quic_cu_b200.engine import Engine
+    from tests.fake_model import FakeModule
+
+    net = tiny_model[0]
+    gen = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, 2048, (int(n),), generator=gen).tolist() for n in (5, 70, 33, 16, 49, 2)]
+
+    def serve(chunk):
+        module = FakeModule()
+        module.model = net
+        engine = Engine(max_batch_size=3, model_module=module,
+                        config=EngineConfig(batching="continuous", max_context=256, decode_burst=4,
+                                            prefill_chunk=chunk))
+        engine.max_tokens = 10
+        for p in prompts:
+            engine.add_request_ids(p)
+        return engine.run()
+
+    assert serve(16) == serve(None)
