@@ -183,6 +183,12 @@ int quic_attn_prefill(const void *q_f16, const void *kcache_f16,
                       int32_t s_max, int32_t n_slots, float scale,
                       void *out_f16, void *stream);
 
+/* Prompts of 128 tokens and more run quic_attn_prefill on tcgen05 with
+ * TMA-staged tiles; shorter ones, and every call after
+ * quic_set_prefill_tensor_attention(0), on the mma.sync kernels (for A/B timing
+ * and tests). */
+void quic_set_prefill_tensor_attention(int enabled);
+
 /* y = silu(gate) * up, rows of 4864.  Replaces swiglu.forward
  * (kernels/cuda/swiglu.cu:37). */
 int quic_swiglu(const void *gate_f16, const void *up_f16, void *y_f16,

@@ -268,6 +268,9 @@ __global__ void __launch_bounds__((kSplitKeys ? kPfSplitWarps : kPfRowWarps) * 3
 }  // namespace quic
 
 namespace quic {
+// Prompts of 128 tokens and more take the tcgen05 kernel (quic_set_prefill_tensor_attention).
+bool g_prefill_tc = true;
+
 int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
                         const int32_t* seq_len, const int32_t* seq_slot, const int32_t* seq_off, int32_t n_seq,
                         int32_t max_len, int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,
@@ -281,6 +284,9 @@ int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, c
                    ((uintptr_t)out % 16 == 0),
                QUIC_E_ARG, "attn_prefill: tensors must be 16-byte aligned");
   if (n_seq == 0 || rows == 0 || max_len == 0) return QUIC_OK;
+  if (g_prefill_tc && attn_prefill_tc_supported(n_seq, max_len, rows, s_max, n_slots))
+    return attn_prefill_tc_launch(q, kcache, vcache, seq_start, seq_len, seq_slot, seq_off, n_seq, max_len, rows,
+                                  s_max, n_slots, scale, out, stream, pdl);
   PrefillAttnArgs a = {};
   a.q = (const half*)q;
   a.kcache = (const half*)kcache;
@@ -313,3 +319,5 @@ extern "C" int quic_attn_prefill(const void* q, const void* kcache, const void* 
   return quic::attn_prefill_launch(q, kcache, vcache, seq_start, seq_len, seq_slot, seq_off, n_seq, max_len, rows,
                                    s_max, n_slots, scale, out, (cudaStream_t)stream, false);
 }
+
+extern "C" void quic_set_prefill_tensor_attention(int enabled) { quic::g_prefill_tc = enabled != 0; }

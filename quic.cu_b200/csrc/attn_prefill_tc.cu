@@ -1,0 +1,333 @@
+// Causal prefill attention on tcgen05 with TMA-staged tiles (GQA 14:2, head_dim 64): the
+// throughput form of attn_prefill.cu for prompts of 128 tokens and more.
+//
+// Replaces the reference's prefill attention (kernels/flash_attn_prefill_pytorch.py:10 = torch
+// SDPA with a causal + left-pad mask; kernels/cuda/flash_attn_prefill.cu:87, wgmma + TMA on
+// Hopper).  Same mathematics as attn_prefill.cu: fp32 online softmax over the keys
+// 0 .. position of each query row, probabilities rounded to fp16 before they multiply V.
+//
+// One CTA owns 128 query rows of one (sequence, query head) and walks the key tiles of 64
+// tokens its rows may see.  Per tile:
+//   S = Q K^T      tcgen05.mma, A = Q tile (128 x 64, loaded once), B = K tile (64 x 64), both
+//                  K-major in the 128-byte swizzle TMA writes; S (128 x 64 fp32) in tensor memory;
+//   softmax        four warps, one query row per thread (TMEM lane = row): tcgen05.ld the row's
+//                  scores, mask, running maximum and sum, P = exp2(..) rounded to fp16 and
+//                  stored as the swizzled A operand of the second product;
+//   O_tile = P V   tcgen05.mma, B = V^T.  V sits token-major in the cache, so the same four
+//                  warps transpose the 64 x 64 tile in shared memory while the first product
+//                  runs; O_tile (128 x 64 fp32) in tensor memory;
+//   O = alpha O + O_tile in registers (64 per thread), alpha = exp2(m_old - m_new).
+// K and V tiles arrive through a two-stage TMA ring (plain cp.async.bulk.tensor, no cluster
+// multicast; the tensor maps cover this GPU's own cache planes and query buffer).  The next
+// tile's first product is issued before the softmax warps pick up O_tile, and two CTAs share
+// an SM, so tensor pipe, softmax and TMA of different tiles overlap.
+//
+// Roles: warps 0-3 softmax / transpose / epilogue, warp 4 TMA producer, warp 5 MMA issuer.
+// Every wait is bounded; a wait that runs out sets word 0 of the tensor path's error words
+// and the CTA leaves with its tensor memory released.
+#include "tc_common.cuh"
+
+namespace quic {
+namespace {
+
+constexpr int kQRows = 128;   // query rows per CTA (UMMA M)
+constexpr int kKeys = 64;     // keys per tile (UMMA N of the first product, K of the second)
+constexpr int kAttThreads = 192;
+constexpr uint32_t kQBytes = kQRows * 128;   // 128 rows x 64 halves
+constexpr uint32_t kTileBytes = kKeys * 128;  // 64 rows x 64 halves
+constexpr uint32_t kSmemQ = 0, kSmemK = kQBytes, kSmemVraw = kSmemK + 2 * kTileBytes, kSmemVt = kSmemVraw + 2 * kTileBytes,
+                   kSmemP = kSmemVt + kTileBytes, kSmemTotal = kSmemP + kQBytes + 1024;
+
+struct PrefillTcArgs {
+  const int32_t* seq_start;
+  const int32_t* seq_len;
+  const int32_t* seq_slot;
+  const int32_t* seq_off;  // or nullptr
+  half* out;               // [rows][896]
+  int32_t rows, s_max, n_slots;
+  float scale_log2;        // softmax scale x log2(e)
+};
+
+__device__ __forceinline__ uint32_t pack2(float x, float y) {
+  const half2 h = __floats2half2_rn(x, y);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q,
+                                                                         const __grid_constant__ CUtensorMap tm_k,
+                                                                         const __grid_constant__ CUtensorMap tm_v,
+                                                                         const PrefillTcArgs a, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bar_q, bar_full[2], bar_empty[2], bar_s, bar_p, bar_o;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int fail_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int len = a.seq_len[seq];  // (the sequence tables are not written by the kernels before this one)
+  const int r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kQRows;  // the longest key ranges are launched first
+  if (r0 >= len) return;
+  const int start = a.seq_start[seq];
+  const int off = a.seq_off != nullptr ? max(a.seq_off[seq], 0) : 0;
+  const int kv_len = off + len;
+  const int slot = a.seq_slot[seq];
+  if (slot < 0 || slot >= a.n_slots) return;
+  const int kvh = head / (kHeads / kKvHeads);
+  const int kv_row0 = (slot * kKvHeads + kvh) * a.s_max;  // first row of the (slot, kv head) in the cache plane
+  const int n_tiles = (min(kv_len, off + r0 + kQRows) + kKeys - 1) / kKeys;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&bar_q), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 4);
+    }
+    mbar_init(smem_u32(&bar_s), 1);
+    mbar_init(smem_u32(&bar_p), 4);
+    mbar_init(smem_u32(&bar_o), 1);
+    fail_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"(128u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 64u;  // S: columns 0..63, O_tile: 64..127
+  const uint32_t idesc = umma_idesc_f16(kKeys);  // M = 128, N = 64 for both products
+  pdl_launch_dependents();
+  pdl_wait();  // queries and cache rows come from the kernels before this one
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&bar_q), kQBytes);
+      tma_load_2d(base + kSmemQ, &tm_q, 0, head * a.rows + start + r0, smem_u32(&bar_q));
+      for (int i = 0; i < n_tiles; ++i) {
+        const int st = i & 1;
+        if (i >= 2 && !mbar_wait(smem_u32(&bar_empty[st]), ((i >> 1) - 1) & 1)) {
+          fail_s = 2;
+          break;
+        }
+        const uint32_t full = smem_u32(&bar_full[st]);
+        mbar_expect_tx(full, 2 * kTileBytes);
+        tma_load_2d(base + kSmemK + st * kTileBytes, &tm_k, 0, kv_row0 + i * kKeys, full);
+        tma_load_2d(base + kSmemVraw + st * kTileBytes, &tm_v, 0, kv_row0 + i * kKeys, full);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = mbar_wait(smem_u32(&bar_q), 0) && mbar_wait(smem_u32(&bar_full[0]), 0);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem_s, umma_desc_sw128(base + kSmemQ + k * 32), umma_desc_sw128(base + kSmemK + k * 32), idesc,
+                   k > 0 ? 1u : 0u);
+        umma_commit(smem_u32(&bar_s));
+      }
+      for (int i = 0; ok && i < n_tiles; ++i) {
+        // P(i) and V^T(i) are in shared memory, S(i) and O_tile(i - 1) have been read
+        if (!mbar_wait(smem_u32(&bar_p), i & 1)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem_o, umma_desc_sw128(base + kSmemP + k * 32), umma_desc_sw128(base + kSmemVt + k * 32), idesc,
+                   k > 0 ? 1u : 0u);
+        umma_commit(smem_u32(&bar_o));
+        if (i + 1 < n_tiles) {  // the next tile's scores while the softmax warps pick up O_tile(i)
+          const int st = (i + 1) & 1;
+          if (!mbar_wait(smem_u32(&bar_full[st]), ((i + 1) >> 1) & 1)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16(tmem_s, umma_desc_sw128(base + kSmemQ + k * 32),
+                     umma_desc_sw128(base + kSmemK + st * kTileBytes + k * 32), idesc, k > 0 ? 1u : 0u);
+          umma_commit(smem_u32(&bar_s));
+        }
+      }
+      if (!ok) fail_s = 3;
+    }
+  } else {
+    // ---------------- softmax, V transpose, epilogue: thread = query row ----------------
+    const int row = tid;                       // 0..127, TMEM lane
+    const int pos = off + r0 + row;            // position of the row in its sequence
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[64];
+#pragma unroll
+    for (int d = 0; d < 64; ++d) o[d] = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int st = i & 1, t0 = i * kKeys;
+      // ---- V(i) -> V^T as the swizzled B operand: thread (dim d, half of the tokens)
+      if (!mbar_wait_relaxed(smem_u32(&bar_full[st]), (i >> 1) & 1, 20)) {
+        ok = false;
+        break;
+      }
+      {
+        const half* vraw = reinterpret_cast<const half*>(gen + kSmemVraw + st * kTileBytes);  // [64 tokens][64 dims]
+        const int d = tid & 63, hf = tid >> 6;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int t = 32 * hf + 8 * c + 2 * j;
+            const half2 h = __halves2half2(vraw[t * 64 + d], vraw[(t + 1) * 64 + d]);
+            w[j] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(gen + kSmemVt + sw128_offset(d, 4 * hf + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      // ---- scores of the row
+      if (!mbar_wait_relaxed(smem_u32(&bar_s), i & 1, 20)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      __syncwarp();  // every lane of the warp has finished its share of the transpose
+      if (lane == 0) mbar_arrive_cta(smem_u32(&bar_empty[st]));  // K(i) has been multiplied, V(i) transposed
+      const int t_hi = min(pos, kv_len - 1) - t0;  // columns 0 .. t_hi of the tile are visible to the row
+      float mt = -INFINITY;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float s[16];
+        tmem_ld16(tmem_s + lane_addr + 16 * q4, s);
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (16 * q4 + j <= t_hi) mt = fmaxf(mt, s[j] * a.scale_log2);
+      }
+      const float m_new = fmaxf(m_run, mt);
+      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+      float l_add = 0.f;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float s[16];
+        tmem_ld16(tmem_s + lane_addr + 16 * q4, s);
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c0 = 16 * q4 + 2 * j;
+          const float p0 = (c0 <= t_hi) ? exp2f(s[2 * j] * a.scale_log2 - m_new) : 0.f;
+          const float p1 = (c0 + 1 <= t_hi) ? exp2f(s[2 * j + 1] * a.scale_log2 - m_new) : 0.f;
+          const half2 ph = __floats2half2_rn(p0, p1);
+          l_add += __low2float(ph) + __high2float(ph);  // the sum uses the rounded probabilities that multiply V
+          w[j] = *reinterpret_cast<const uint32_t*>(&ph);
+        }
+        *reinterpret_cast<uint4*>(gen + kSmemP + sw128_offset(row, 2 * q4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(gen + kSmemP + sw128_offset(row, 2 * q4 + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      l_run = l_run * alpha + l_add;
+      m_run = m_new;
+      fence_proxy_async();  // P and V^T (generic-proxy stores) -> visible to the tensor core
+      tc_fence_before();    // the loads of S precede the next product into the same columns
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cta(smem_u32(&bar_p));
+      // ---- O = alpha O + P V
+      if (!mbar_wait_relaxed(smem_u32(&bar_o), i & 1, 20)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float v[16];
+        tmem_ld16(tmem_o + lane_addr + 16 * q4, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[16 * q4 + j] = fmaf(o[16 * q4 + j], alpha, v[j]);
+      }
+      tc_fence_before();
+    }
+    ok = ok && !fail_s;
+    if (!ok && lane == 0) atomicCAS(status, 0, ((fail_s ? fail_s : 1) << 16) | 0x2000 | ((int)blockIdx.x & 0x1fff));
+    if (ok && r0 + row < len) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      half* op = a.out + (size_t)(start + r0 + row) * kHidden + head * kHeadDim;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 u;
+        u.x = pack2(o[8 * c + 0] * inv, o[8 * c + 1] * inv);
+        u.y = pack2(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
+        u.z = pack2(o[8 * c + 4] * inv, o[8 * c + 5] * inv);
+        u.w = pack2(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
+        reinterpret_cast<uint4*>(op)[c] = u;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(128u) : "memory");
+}
+
+}  // namespace
+
+// Whether the tcgen05 form takes this call (otherwise attn_prefill.cu's mma.sync kernels do).
+bool attn_prefill_tc_supported(int n_seq, int max_len, int rows, int s_max, int n_slots) {
+  return max_len >= kQRows && (int64_t)n_slots * kKvHeads * s_max < (1ll << 31) && (int64_t)kHeads * rows < (1ll << 31);
+}
+
+int attn_prefill_tc_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
+                           const int32_t* seq_len, const int32_t* seq_slot, const int32_t* seq_off, int32_t n_seq,
+                           int32_t max_len, int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,
+                           cudaStream_t stream, bool pdl) {
+  CUtensorMap tm_q, tm_k, tm_v;
+  int rc = make_map(&tm_q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q, (uint64_t)kHeads * rows, kHeadDim, kQRows, kHeadDim,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != QUIC_OK) return rc;
+  const uint64_t kv_rows = (uint64_t)n_slots * kKvHeads * s_max;
+  rc = make_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, kcache, kv_rows, kHeadDim, kKeys, kHeadDim,
+                CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != QUIC_OK) return rc;
+  rc = make_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, vcache, kv_rows, kHeadDim, kKeys, kHeadDim,
+                CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != QUIC_OK) return rc;
+  int* status = tc_status_words();
+  QUIC_REQUIRE(status != nullptr, QUIC_E_CUDA, "attn_prefill: no address for the tensor path's error words");
+  PrefillTcArgs a = {};
+  a.seq_start = seq_start;
+  a.seq_len = seq_len;
+  a.seq_slot = seq_slot;
+  a.seq_off = seq_off;
+  a.out = (half*)out;
+  a.rows = rows;
+  a.s_max = s_max;
+  a.n_slots = n_slots;
+  a.scale_log2 = (scale > 0.f ? scale : 0.125f) * 1.4426950408889634f;
+  QUIC_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal));
+  dim3 grid((max_len + kQRows - 1) / kQRows, kHeads, n_seq);
+  QUIC_CUDA(launch(attn_prefill_tc_kernel, grid, dim3(kAttThreads), kSmemTotal, stream, pdl, tm_q, tm_k, tm_v, a, status));
+  return QUIC_OK;
+}
+
+}  // namespace quic

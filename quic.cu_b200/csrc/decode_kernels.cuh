@@ -186,6 +186,12 @@ cudaError_t launch_swiglu_fused(const half* gu, half* act, int batch, cudaStream
 cudaError_t launch_qkv_rope_append(const half* qkv, const int32_t* slots, const int32_t* positions, const half* cos_t,
                                    const half* sin_t, int max_pos, half* q_out, half* kcache, half* vcache, int s_max,
                                    int n_slots, int rows, cudaStream_t st, bool pdl);
+// tcgen05 + TMA form for prompts of 128 tokens and more (attn_prefill_tc.cu)
+bool attn_prefill_tc_supported(int n_seq, int max_len, int rows, int s_max, int n_slots);
+int attn_prefill_tc_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
+                           const int32_t* seq_len, const int32_t* seq_slot, const int32_t* seq_off, int32_t n_seq,
+                           int32_t max_len, int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,
+                           cudaStream_t stream, bool pdl);
 int attn_prefill_launch(const void* q, const void* kcache, const void* vcache, const int32_t* seq_start,
                         const int32_t* seq_len, const int32_t* seq_slot, const int32_t* seq_off, int32_t n_seq,
                         int32_t max_len, int32_t rows, int32_t s_max, int32_t n_slots, float scale, void* out,

@@ -149,6 +149,7 @@ SIGNATURES = {
     "quic_attn_pick_splits": (_I32, [_I32, _I32]),
     "quic_attn_scratch_bytes": (_I64, [_I32, _I32]),
     "quic_set_tensor_min_batch": (None, [_I32]),
+    "quic_set_prefill_tensor_attention": (None, [C.c_int]),
     "quic_set_mma_chain_min_batch": (None, [_I32]),
     "quic_decode_pick_splits": (_I32, [_I32, _I32]),
     "quic_decode_scratch_bytes": (_I64, [_I32, _I32, _I32]),

@@ -231,3 +231,43 @@ def test_flash_attn_prefill_getter_matches_the_reference_recipe(kv_repeated):
     real = (pos[None, :] >= pads[:, None])[:, None, :, None].expand_as(out)
     assert torch.allclose(out.float()[real], want[real], atol=ATOL)
     assert torch.count_nonzero(out[~real]) == 0
+
+
+@pytest.mark.parametrize("lens,offs", [([128], None), ([300, 129], None), ([2048], None), ([640, 1, 200], None),
+                                       ([256, 130], [100, 513]), ([129], [1407])])
+def test_prefill_attention_tensor_and_mma_kernels_agree_with_sdpa(lens, offs):
+    """Prompts of 128 tokens and more run on tcgen05 (128-row query tiles, 64-key tiles through
+    TMA, S and O in tensor memory); the mma.sync kernels are kept for shorter ones and as the
+    comparison here.  Both against causal SDPA over each whole sequence: ragged lengths, rows
+    that end inside a tile, later chunks of a prompt (offsets on both sides of tile edges)."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(sum(lens) + 7)
+    offs = offs or [0] * len(lens)
+    rows, n_slots, s_max = sum(lens), 4, 2048
+    slots = [3, 0, 2][: len(lens)]
+    q = torch.randn((HEADS, rows, HEAD_DIM), device="cuda", generator=g).half()
+    kc = torch.randn((n_slots, 2, s_max, HEAD_DIM), device="cuda", generator=g).half()
+    vc = torch.randn((n_slots, 2, s_max, HEAD_DIM), device="cuda", generator=g).half()
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    dev = dict(device="cuda", dtype=torch.int32)
+    args = (q, kc, vc, torch.tensor(starts, **dev), torch.tensor(lens, **dev), torch.tensor(slots, **dev), max(lens), SCALE)
+    off_t = torch.tensor(offs, **dev) if any(offs) else None
+    out = K.attn_prefill(*args, seq_off=off_t)
+    assert K.lib().quic_w4a16_tensor_status() == 0
+    try:
+        K.lib().quic_set_prefill_tensor_attention(0)
+        other = K.attn_prefill(*args, seq_off=off_t)
+    finally:
+        K.lib().quic_set_prefill_tensor_attention(1)
+    assert torch.isfinite(out).all()
+    for a, n, s, o in zip(starts, lens, slots, offs):
+        keys = kc[s, :, : o + n].repeat_interleave(7, dim=0).float()
+        vals = vc[s, :, : o + n].repeat_interleave(7, dim=0).float()
+        causal = torch.arange(o + n, device="cuda")[None, :] <= (o + torch.arange(n, device="cuda"))[:, None]
+        want = F.scaled_dot_product_attention(q[None, :, a:a + n].float(), keys[None], vals[None],
+                                              attn_mask=causal[None, None], scale=SCALE)[0]
+        got = out[a:a + n].view(n, HEADS, HEAD_DIM).transpose(0, 1).float()
+        assert torch.allclose(got, want, atol=ATOL), (n, o, (got - want).abs().max().item())
+        ref = other[a:a + n].view(n, HEADS, HEAD_DIM).transpose(0, 1).float()
+        assert torch.allclose(got, ref, atol=4e-3), (n, o, (got - ref).abs().max().item())
