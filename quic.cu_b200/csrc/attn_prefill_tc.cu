@@ -4,7 +4,7 @@
 // Replaces the reference's prefill attention (kernels/flash_attn_prefill_pytorch.py:10 = torch
 // SDPA with a causal + left-pad mask; kernels/cuda/flash_attn_prefill.cu:87, wgmma + TMA on
 // Hopper).  Same mathematics as attn_prefill.cu: fp32 online softmax over the keys
-// 0 .. position of each query row, probabilities rounded to fp16 before they multiply V.
+// 0 .. position of each query row; the probabilities multiply V as fp16 and are summed in fp32.
 //
 // One CTA owns 128 query rows of one (sequence, query head) and walks the key tiles of 64
 // tokens its rows may see.  Per tile:
@@ -18,9 +18,10 @@
 //                  runs; O_tile (128 x 64 fp32) in tensor memory;
 //   O = alpha O + O_tile in registers (64 per thread), alpha = exp2(m_old - m_new).
 // K and V tiles arrive through a two-stage TMA ring (plain cp.async.bulk.tensor, no cluster
-// multicast; the tensor maps cover this GPU's own cache planes and query buffer).  The next
-// tile's first product is issued before the softmax warps pick up O_tile, and two CTAs share
-// an SM, so tensor pipe, softmax and TMA of different tiles overlap.
+// multicast; the tensor maps cover this GPU's own cache planes and query buffer).  P, V^T and
+// O_tile are double-buffered: the second product of tile i runs while the softmax warps work on
+// tile i + 1 (whose scores were issued right behind it) and is folded into O one tile late, so
+// no role waits for the tensor pipe in the steady state; two CTAs share an SM.
 //
 // Roles: warps 0-3 softmax / transpose / epilogue, warp 4 TMA producer, warp 5 MMA issuer.
 // Every wait is bounded; a wait that runs out sets word 0 of the tensor path's error words
@@ -35,8 +36,11 @@ constexpr int kKeys = 64;     // keys per tile (UMMA N of the first product, K o
 constexpr int kAttThreads = 192;
 constexpr uint32_t kQBytes = kQRows * 128;   // 128 rows x 64 halves
 constexpr uint32_t kTileBytes = kKeys * 128;  // 64 rows x 64 halves
+// Q | K x2 (ring) | V as loaded x2 (ring) | V^T x2 | P x2 (the second product of tile i may still
+// run while tile i + 1 goes through the softmax)
 constexpr uint32_t kSmemQ = 0, kSmemK = kQBytes, kSmemVraw = kSmemK + 2 * kTileBytes, kSmemVt = kSmemVraw + 2 * kTileBytes,
-                   kSmemP = kSmemVt + kTileBytes, kSmemTotal = kSmemP + kQBytes + 1024;
+                   kSmemP = kSmemVt + 2 * kTileBytes, kSmemTotal = kSmemP + 2 * kQBytes + 1024;
+constexpr uint32_t kTmemCols = 256;  // S: 0..63, O_tile of even / odd tiles: 64..127 / 128..191
 
 struct PrefillTcArgs {
   const int32_t* seq_start;
@@ -55,17 +59,27 @@ __device__ __forceinline__ uint32_t pack2(float x, float y) {
 __device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// 16 consecutive fp32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
+// 64 consecutive fp32 columns of this thread's TMEM lane: four loads in flight, one wait
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
+          "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
+          "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]),
+          "=r"(r[16 * q + 14]), "=r"(r[16 * q + 15])
+        : "r"(taddr + 16u * q));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 2^x, one MUFU instruction (x = -inf gives 0)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -73,7 +87,7 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
                                                                          const __grid_constant__ CUtensorMap tm_v,
                                                                          const PrefillTcArgs a, int* status) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bar_q, bar_full[2], bar_empty[2], bar_s, bar_p, bar_o;
+  __shared__ __align__(8) uint64_t bar_q, bar_full[2], bar_empty[2], bar_s, bar_p, bar_o[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
 
@@ -102,20 +116,21 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
     }
     mbar_init(smem_u32(&bar_s), 1);
     mbar_init(smem_u32(&bar_p), 4);
-    mbar_init(smem_u32(&bar_o), 1);
+    mbar_init(smem_u32(&bar_o[0]), 1);
+    mbar_init(smem_u32(&bar_o[1]), 1);
     fail_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
-                 "r"(128u)
+                 "r"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 64u;  // S: columns 0..63, O_tile: 64..127
+  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 64u;  // O_tile(i) at tmem_o + 64 (i & 1)
   const uint32_t idesc = umma_idesc_f16(kKeys);  // M = 128, N = 64 for both products
   pdl_launch_dependents();
   pdl_wait();  // queries and cache rows come from the kernels before this one
@@ -150,17 +165,18 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
         umma_commit(smem_u32(&bar_s));
       }
       for (int i = 0; ok && i < n_tiles; ++i) {
-        // P(i) and V^T(i) are in shared memory, S(i) and O_tile(i - 1) have been read
+        // P(i) and V^T(i) are in shared memory, S(i) and O_tile(i - 2) have been read
         if (!mbar_wait(smem_u32(&bar_p), i & 1)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        const int buf = i & 1;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_f16(tmem_o, umma_desc_sw128(base + kSmemP + k * 32), umma_desc_sw128(base + kSmemVt + k * 32), idesc,
-                   k > 0 ? 1u : 0u);
-        umma_commit(smem_u32(&bar_o));
+          umma_f16(tmem_o + 64u * buf, umma_desc_sw128(base + kSmemP + buf * kQBytes + k * 32),
+                   umma_desc_sw128(base + kSmemVt + buf * kTileBytes + k * 32), idesc, k > 0 ? 1u : 0u);
+        umma_commit(smem_u32(&bar_o[buf]));
         if (i + 1 < n_tiles) {  // the next tile's scores while the softmax warps pick up O_tile(i)
           const int st = (i + 1) & 1;
           if (!mbar_wait(smem_u32(&bar_full[st]), ((i + 1) >> 1) & 1)) {
@@ -187,10 +203,11 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
 #pragma unroll
     for (int d = 0; d < 64; ++d) o[d] = 0.f;
     bool ok = true;
+    float alpha_prev = 0.f;  // rescale that goes with O_tile(i - 1), picked up one tile later
     for (int i = 0; i < n_tiles; ++i) {
       const int st = i & 1, t0 = i * kKeys;
       // ---- V(i) -> V^T as the swizzled B operand: thread (dim d, half of the tokens)
-      if (!mbar_wait_relaxed(smem_u32(&bar_full[st]), (i >> 1) & 1, 20)) {
+      if (!mbar_wait(smem_u32(&bar_full[st]), (i >> 1) & 1)) {
         ok = false;
         break;
       }
@@ -206,11 +223,12 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
             const half2 h = __halves2half2(vraw[t * 64 + d], vraw[(t + 1) * 64 + d]);
             w[j] = *reinterpret_cast<const uint32_t*>(&h);
           }
-          *reinterpret_cast<uint4*>(gen + kSmemVt + sw128_offset(d, 4 * hf + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(gen + kSmemVt + st * kTileBytes + sw128_offset(d, 4 * hf + c)) =
+              make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       // ---- scores of the row
-      if (!mbar_wait_relaxed(smem_u32(&bar_s), i & 1, 20)) {
+      if (!mbar_wait(smem_u32(&bar_s), i & 1)) {
         ok = false;
         break;
       }
@@ -218,55 +236,73 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
       __syncwarp();  // every lane of the warp has finished its share of the transpose
       if (lane == 0) mbar_arrive_cta(smem_u32(&bar_empty[st]));  // K(i) has been multiplied, V(i) transposed
       const int t_hi = min(pos, kv_len - 1) - t0;  // columns 0 .. t_hi of the tile are visible to the row
-      float mt = -INFINITY;
+      // a tile wholly below the diagonal of all 128 rows needs no mask (CTA-uniform)
+      const bool unmasked = t0 + kKeys - 1 <= min(off + r0, kv_len - 1);
+      float s[64];
+      tmem_ld64(tmem_s + lane_addr, s);
+      tc_fence_before();  // the loads of S precede the next product into the same columns
+      if (!unmasked) {
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        float s[16];
-        tmem_ld16(tmem_s + lane_addr + 16 * q4, s);
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (16 * q4 + j <= t_hi) mt = fmaxf(mt, s[j] * a.scale_log2);
+        for (int j = 0; j < 64; ++j)
+          if (j > t_hi) s[j] = -INFINITY;
       }
-      const float m_new = fmaxf(m_run, mt);
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
-      float l_add = 0.f;
+      float mx[8];  // eight independent chains instead of one of 64 dependent maxima
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        float s[16];
-        tmem_ld16(tmem_s + lane_addr + 16 * q4, s);
-        uint32_t w[8];
+      for (int j = 0; j < 8; ++j) mx[j] = s[j];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int c0 = 16 * q4 + 2 * j;
-          const float p0 = (c0 <= t_hi) ? exp2f(s[2 * j] * a.scale_log2 - m_new) : 0.f;
-          const float p1 = (c0 + 1 <= t_hi) ? exp2f(s[2 * j + 1] * a.scale_log2 - m_new) : 0.f;
-          const half2 ph = __floats2half2_rn(p0, p1);
-          l_add += __low2float(ph) + __high2float(ph);  // the sum uses the rounded probabilities that multiply V
-          w[j] = *reinterpret_cast<const uint32_t*>(&ph);
+      for (int j = 8; j < 64; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
+      const float mt = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      const float m_new = fmaxf(m_run, mt * a.scale_log2);  // (the scale is positive)
+      const float alpha = ex2(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+      // m_new is finite from the first tile on: every row sees key 0
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float p0 = ex2(fmaf(s[8 * c + 2 * j], a.scale_log2, -m_new));  // 2^-inf = 0 for masked keys
+          const float p1 = ex2(fmaf(s[8 * c + 2 * j + 1], a.scale_log2, -m_new));
+          l4[j] += p0 + p1;
+          w[j] = pack2(p0, p1);
         }
-        *reinterpret_cast<uint4*>(gen + kSmemP + sw128_offset(row, 2 * q4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(gen + kSmemP + sw128_offset(row, 2 * q4 + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
+        *reinterpret_cast<uint4*>(gen + kSmemP + st * kQBytes + sw128_offset(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l_run = l_run * alpha + l_add;
+      l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
       m_run = m_new;
       fence_proxy_async();  // P and V^T (generic-proxy stores) -> visible to the tensor core
-      tc_fence_before();    // the loads of S precede the next product into the same columns
       __syncwarp();
       if (lane == 0) mbar_arrive_cta(smem_u32(&bar_p));
-      // ---- O = alpha O + P V
-      if (!mbar_wait_relaxed(smem_u32(&bar_o), i & 1, 20)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
+      // ---- O = alpha O + P V of the PREVIOUS tile: its product ran while this tile's softmax did
+      if (i > 0) {
+        if (!mbar_wait(smem_u32(&bar_o[(i - 1) & 1]), ((i - 1) >> 1) & 1)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        {
+          float v[64];
+          tmem_ld64(tmem_o + 64u * ((i - 1) & 1) + lane_addr, v);
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        float v[16];
-        tmem_ld16(tmem_o + lane_addr + 16 * q4, v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) o[16 * q4 + j] = fmaf(o[16 * q4 + j], alpha, v[j]);
+          for (int j = 0; j < 64; ++j) o[j] = fmaf(o[j], alpha_prev, v[j]);
+        }
+        tc_fence_before();
       }
-      tc_fence_before();
+      alpha_prev = alpha;
+    }
+    if (ok) {  // the last tile's product
+      const int i = n_tiles - 1;
+      ok = mbar_wait(smem_u32(&bar_o[i & 1]), (i >> 1) & 1);
+      if (ok) {
+        tc_fence_after();
+        {
+          float v[64];
+          tmem_ld64(tmem_o + 64u * (i & 1) + lane_addr, v);
+#pragma unroll
+          for (int j = 0; j < 64; ++j) o[j] = fmaf(o[j], alpha_prev, v[j]);
+        }
+        tc_fence_before();
+      }
     }
     ok = ok && !fail_s;
     if (!ok && lane == 0) atomicCAS(status, 0, ((fail_s ? fail_s : 1) << 16) | 0x2000 | ((int)blockIdx.x & 0x1fff));
@@ -287,7 +323,7 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
   tc_fence_before();
   __syncthreads();
   if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(128u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(kTmemCols) : "memory");
 }
 
 }  // namespace
