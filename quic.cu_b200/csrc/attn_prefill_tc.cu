@@ -14,8 +14,9 @@
 //                  scores, mask, running maximum and sum, P = exp2(..) rounded to fp16 and
 //                  stored as the swizzled A operand of the second product;
 //   O_tile = P V   tcgen05.mma, B = V^T.  V sits token-major in the cache, so the same four
-//                  warps transpose the 64 x 64 tile in shared memory while the first product
-//                  runs; O_tile (128 x 64 fp32) in tensor memory;
+//                  warps transpose the 64 x 64 tile in shared memory (ldmatrix.trans / stmatrix,
+//                  four instructions each per warp) while the first product runs; O_tile
+//                  (128 x 64 fp32) in tensor memory;
 //   O = alpha O + O_tile in registers (64 per thread), alpha = exp2(m_old - m_new).
 // K and V tiles arrive through a two-stage TMA ring (plain cp.async.bulk.tensor, no cluster
 // multicast; the tensor maps cover this GPU's own cache planes and query buffer).  P, V^T and
@@ -212,19 +213,24 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
         break;
       }
       {
-        const half* vraw = reinterpret_cast<const half*>(gen + kSmemVraw + st * kTileBytes);  // [64 tokens][64 dims]
-        const int d = tid & 63, hf = tid >> 6;
+        // 8 x 8 blocks through ldmatrix.trans / stmatrix: block (tb, db) = tokens 8 tb.., dims 8 db..
+        // of the tile as loaded ([64 tokens][64 dims], 128-byte rows, swizzled: the eight rows of a
+        // block sit in eight different bank groups) becomes the 16-byte chunk tb
+        // of rows 8 db .. 8 db + 7 of V^T.  Warp w moves the blocks with db = 2 w, 2 w + 1: four
+        // instructions of four blocks each (lanes 8 m .. 8 m + 7 address the rows of block m).
+        const uint32_t vraw = base + kSmemVraw + st * kTileBytes, vt = base + kSmemVt + st * kTileBytes;
+        const int m = lane >> 3, r = lane & 7;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int t = 32 * hf + 8 * c + 2 * j;
-            const half2 h = __halves2half2(vraw[t * 64 + d], vraw[(t + 1) * 64 + d]);
-            w[j] = *reinterpret_cast<const uint32_t*>(&h);
-          }
-          *reinterpret_cast<uint4*>(gen + kSmemVt + st * kTileBytes + sw128_offset(d, 4 * hf + c)) =
-              make_uint4(w[0], w[1], w[2], w[3]);
+        for (int it = 0; it < 4; ++it) {
+          const int tb = 2 * it + (m >> 1), db = 2 * warp + (m & 1);
+          uint32_t x0, x1, x2, x3;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
+                       : "r"(vraw + sw128_offset(8 * tb + r, db)));
+          asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(
+                           vt + sw128_offset(8 * db + r, tb)),
+                       "r"(x0), "r"(x1), "r"(x2), "r"(x3)
+                       : "memory");
         }
       }
       // ---- scores of the row
@@ -346,7 +352,7 @@ int attn_prefill_tc_launch(const void* q, const void* kcache, const void* vcache
                 CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != QUIC_OK) return rc;
   rc = make_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, vcache, kv_rows, kHeadDim, kKeys, kHeadDim,
-                CU_TENSOR_MAP_SWIZZLE_NONE);
+                CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != QUIC_OK) return rc;
   int* status = tc_status_words();
   QUIC_REQUIRE(status != nullptr, QUIC_E_CUDA, "attn_prefill: no address for the tensor path's error words");
