@@ -362,6 +362,9 @@ int enqueue_step_rows16(const quic_model_t* m, const quic_decode_t* d, cudaStrea
 // Batch > 16: every linear is the tcgen05 GEMM; norms, RoPE/KV append and SwiGLU are
 // separate small kernels (at these sizes each kernel does microseconds of real work, so
 // the launch chain is no longer what bounds the step).
+int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int ctx, half* qbuf, half* kc, half* vc,
+                      half* attn_out, cudaStream_t st);
+
 int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head) {
   const int B = d->batch;
   const int splits = pick_splits(d);
@@ -393,29 +396,8 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_qkv_post_part(part, sp, (const half*)L.qkv.bias, d->rows, d->pos, (const half*)m->rope_cos,
                                    (const half*)m->rope_sin, m->max_pos, qbuf, kc, vc, d->s_max, d->n_slots, B, st));
-    AttnArgs aa = {};
-    aa.q = qbuf;
-    aa.k = kc;
-    aa.v = vc;
-    aa.stride_b = (int64_t)slot_stride;
-    aa.stride_h = (int64_t)d->s_max * kHeadDim;
-    aa.rows = d->rows;
-    aa.pos = d->pos;
-    aa.s_cap = ctx;
-    aa.splits = splits;
-    aa.chunk = (ctx + splits - 1) / splits;
-    aa.scale = 0.125f;
-    aa.out = attn_out;
-    // One warp per 64 tokens with the cache tile requested ahead of the dependency wait while
-    // that needs at most 32 splits; 4-warp CTAs walking longer ranges beyond.  Either way the
-    // splits are merged by the last CTA to arrive.
-    aa.small = (splits <= 32 && (int64_t)splits * 64 >= ctx) ? 1 : 0;
-    aa.use_mma = 1;
-    aa.consumer_merge = 0;
-    aa.epoch = d->step_counter;
-    aa.prefetch = (aa.small && d->step_counter != nullptr) ? 1 : 0;
-    if (splits > 1) attn_carve_scratch(base + ar.attn, B, splits, &aa);
-    QUIC_CUDA(launch_attn(aa, B, st, true));
+    rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st);
+    if (rc != QUIC_OK) return rc;
     rc = w4a16_gemm_tc(attn_out, L.o, nullptr, B, ws, st, &sp);
     if (rc != QUIC_OK) return rc;
     QUIC_CUDA(launch_rmsnorm_part(part, sp, h, (const half*)L.ln2, m->eps, xn, h, B, st));
@@ -451,7 +433,7 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
 }
 
 // Attention of a decode step with finished fp16 output: the scratch-free CTA form up to 4096
-// tokens, the split form merged by the last CTA to arrive beyond.
+// tokens and 32 rows, the split form merged by the last CTA to arrive beyond.
 int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int ctx, half* qbuf, half* kc, half* vc,
                       half* attn_out, cudaStream_t st) {
   const int B = d->batch;
@@ -471,7 +453,9 @@ int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int c
   aa.use_mma = 1;
   aa.consumer_merge = 0;
   aa.epoch = d->step_counter;
-  if (attn_cta_splits(ctx) <= kAttnCtaMaxSplits) {
+  // (measured at 512 tokens: 9 and 7 % off the step at 17 and 32 rows, 3 % slower at 64, where its
+  // 128 CTAs of 512 tokens each leave less room per SM than 1024 single-warp CTAs)
+  if (attn_cta_splits(ctx) <= kAttnCtaMaxSplits && B <= 32) {
     aa.splits = attn_cta_splits(ctx);
     aa.chunk = 512;
     aa.prefetch = d->step_counter != nullptr ? 1 : 0;
