@@ -310,6 +310,14 @@ def run_gpu(args) -> None:
     batch64 = None
     if not args.skip_batch64:
         batch64 = measure_batch64(net, device, world, dist)
+    extras = {}
+    if world == 1 and not args.skip_extras and args.layers == 24:
+        for name, fn in (("rows_sweep", lambda: measure_rows_sweep(net, device)),
+                         ("prefill", lambda: measure_prefill(net, device))):
+            try:
+                extras[name] = fn()
+            except Exception as exc:  # the headline line must not depend on the extra measurements
+                extras[name] = {"error": f"{type(exc).__name__}: {exc}"}
     serving = None
     if args.serving_requests > 0:
         try:
@@ -328,8 +336,17 @@ def run_gpu(args) -> None:
         "roofline": roofline, "roofline_kernels": kernels, "roofline_step": roofline_step, "batch64": batch64,
         "serving": serving,
     }
+    line.update(extras)
     if args.layers != 24:
         line["invalid"] = "reduced layer count: profiling run, not a benchmark"
+    if world == 1 and not args.skip_extras and args.layers == 24:
+        del net, cache
+        net = cache = None
+        torch.cuda.empty_cache()
+        try:
+            line["dense_fp16"] = measure_dense(device)
+        except Exception as exc:
+            line["dense_fp16"] = {"error": f"{type(exc).__name__}: {exc}"}
     if world == 1 and not args.no_cpu_baseline and args.layers == 24:
         del net, cache
         base, _ = cpu_baseline(state, threads=os.cpu_count(), gen=16, repeats=1, warmup=0)
@@ -559,6 +576,114 @@ def measure_batch64(net, device, world, dist):
             "algorithmic_bytes_per_step": step_bytes}
 
 
+def _time_decode(net, device, rows: int, ctx: int = PROMPT_LEN, steps: int = 64, burst: int = 32, reps: int = 3) -> float:
+    """us per decode step with ``rows`` rows in flight at ``ctx`` cached tokens (random K/V stand
+    in for the prefilled tokens), state resident, CUDA events."""
+    cache = net.new_cache(n_slots=max(rows, 1), s_max=1024)
+    slots = list(range(rows))
+    gen = torch.Generator(device=device).manual_seed(1)
+    cache.kv.normal_(0, 1, generator=gen)
+    cache.tok.copy_(torch.randint(0, 151936, (cache.n_slots,), generator=gen, device=device, dtype=torch.int32))
+
+    def run():
+        cache.pos.fill_(ctx)
+        for s_ in slots:
+            cache.host_len[s_] = ctx
+        for _ in range(steps // burst):
+            net.decode_async(cache, slots, burst)
+
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    cache.release_graphs()
+    return e0.elapsed_time(e1) * 1e3 / (reps * steps)
+
+
+def measure_rows_sweep(net, device) -> dict:
+    """Decode step time against the number of rows: one row on the GEMV chain, two on its
+    two-row form, 3..16 on the mma.sync chain, more on the tcgen05 step."""
+    out = {}
+    for rows in (1, 2, 3, 4, 8, 16, 32):
+        us = _time_decode(net, device, rows)
+        out[str(rows)] = {"us_per_step": us, "tokens_per_s": rows / (us * 1e-6)}
+    one = out["1"]["us_per_step"]
+    for v in out.values():
+        v["vs_one_row"] = v["us_per_step"] / one
+    return {"context": PROMPT_LEN, "rows": out}
+
+
+def measure_prefill(net, device) -> dict:
+    """Time to first token of 16 prompts of 2048 tokens through the public prefill call (ids on
+    the host, first tokens read back), and the prefill attention kernel alone at 1 x 2048 and
+    16 x 2048 on tcgen05 and on the mma.sync kernels it replaces."""
+    from quic_cu_b200 import kernels as K
+
+    n_seq, n = 16, 2048
+    gen = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 151936, (n,), generator=gen) for _ in range(n_seq)]
+    cache = net.new_cache(n_slots=n_seq, s_max=n + 64)
+    for _ in range(2):
+        net.prefill(cache, list(range(n_seq)), prompts)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    reps = 3
+    for _ in range(reps):
+        first, _ = net.prefill(cache, list(range(n_seq)), prompts)
+        first.cpu()
+    ttft_ms = (time.perf_counter() - t0) / reps * 1e3
+    del cache
+    dev = dict(device=device, dtype=torch.int32)
+    kernels = []
+    for seqs in (1, 16):
+        rows = seqs * n
+        q = torch.randn((14, rows, 64), device=device).half()
+        kc = torch.randn((seqs, 2, n, 64), device=device).half()
+        vc = torch.randn_like(kc)
+        starts = torch.tensor([i * n for i in range(seqs)], **dev)
+        lens, slots = torch.tensor([n] * seqs, **dev), torch.arange(seqs, **dev)
+        flops = seqs * 14 * n * (n + 1) / 2 * 64 * 4
+        for mode, name in ((1, "tcgen05 + TMA"), (0, "mma.sync")):
+            K.lib().quic_set_prefill_tensor_attention(mode)
+            for _ in range(3):
+                K.attn_prefill(q, kc, vc, starts, lens, slots, n, 0.125)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                K.attn_prefill(q, kc, vc, starts, lens, slots, n, 0.125)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 100
+            kernels.append({"sequences": seqs, "tokens": n, "kernel": name, "us": us, "tflops": flops / us / 1e6})
+        K.lib().quic_set_prefill_tensor_attention(1)
+    return {"ttft_ms": ttft_ms, "prompts": n_seq, "prompt_tokens": n, "attention": kernels,
+            "note": "W4A16 linears on the tcgen05 GEMM at M = 32768, attention on tcgen05; causal flops counted"}
+
+
+def measure_dense(device) -> dict:
+    """The un-quantised fp16 model through the same step: one-row decode (GEMV chain over
+    988 MB of weights per token) and 64 rows (tcgen05 fp16 GEMM)."""
+    from quic_cu_b200 import model as qmodel
+    from quic_cu_b200.checkpoint import qwen_config_dict, synthetic_dense_checkpoint
+
+    cfg = qwen_config_dict(24, 151936)
+    cfg.pop("quantization_config", None)
+    net = qmodel.from_state_dict(synthetic_dense_checkpoint(n_layers=24, vocab=151936, seed=0), cfg, device=device)
+    peak, kind = peaks()
+    out = {}
+    for rows in (1, 64):
+        us = _time_decode(net, device, rows)
+        step_bytes = net.weight_bytes() + rows * 12288 * (PROMPT_LEN + 33)
+        out[str(rows)] = {"us_per_step": us, "tokens_per_s": rows / (us * 1e-6),
+                          "hbm_frac": step_bytes / (us * 1e-6) / 1e9 / peak, "algorithmic_bytes_per_step": step_bytes}
+    return {"dtype": "fp16 weights x fp16 activations, fp32 accumulate", "peak_kind": f"of {kind}", "rows": out}
+
+
 def measure_serving(net, device, n_requests, world, dist, rank):
     """Continuous batching with 64 KV slots per GPU (benchmark configuration 4): prompt lengths
     uniform in 64..1024, output lengths uniform in 128..512 (forced through max_tokens; random
@@ -632,6 +757,8 @@ def main() -> None:
     ap.add_argument("--impl", default="quic_b200", choices=["quic_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-batch64", action="store_true", help="skip the extra batch-64 decode measurement")
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="skip the rows sweep, the prefill and the dense fp16 measurements (N = 1 only)")
     ap.add_argument("--serving-requests", type=int, default=4096,
                     help="also serve a queue of this many synthetic requests with continuous batching (64 slots "
                          "per GPU, pulled by all replicas from one FIFO, two passes: about 35 s each on one GPU); "
