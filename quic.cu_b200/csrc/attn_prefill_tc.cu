@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
                                                                          const __grid_constant__ CUtensorMap tm_v,
                                                                          const PrefillTcArgs a, int* status) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bar_q, bar_full[2], bar_empty[2], bar_s[2], bar_p, bar_o[2];
+  __shared__ __align__(8) uint64_t bar_q, bar_full[2], bar_empty[2], bar_s[2], bar_p[2], bar_o[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
   __shared__ float pmax_s[2][2][kQRows];  // [tile parity][key half][row]: a warp's row maxima for its partner
@@ -143,7 +143,8 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
     }
     mbar_init(smem_u32(&bar_s[0]), 1);
     mbar_init(smem_u32(&bar_s[1]), 1);
-    mbar_init(smem_u32(&bar_p), kSoftmaxWarps);
+    mbar_init(smem_u32(&bar_p[0]), kSoftmaxWarps);
+    mbar_init(smem_u32(&bar_p[1]), kSoftmaxWarps);
     mbar_init(smem_u32(&bar_o[0]), 1);
     mbar_init(smem_u32(&bar_o[1]), 1);
     fail_s = 0;
@@ -203,7 +204,9 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
       }
       for (int i = 0; ok && i < n_tiles; ++i) {
         // P(i) and V^T(i) are in shared memory, S(i) and O_tile(i - 2) have been read
-        if (!mbar_wait(smem_u32(&bar_p), i & 1)) {
+        // (one barrier per tile parity: with the scores two tiles ahead a fast pair of warps can be a
+        // whole tile in front of a slow one, and its arrival for tile i + 1 must not count for tile i)
+        if (!mbar_wait(smem_u32(&bar_p[i & 1]), (i >> 1) & 1)) {
           ok = false;
           break;
         }
@@ -312,7 +315,7 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
       m_run = m_new;
       fence_proxy_async();  // P and V^T (generic-proxy stores) -> visible to the tensor core
       __syncwarp();
-      if (lane == 0) mbar_arrive_cta(smem_u32(&bar_p));
+      if (lane == 0) mbar_arrive_cta(smem_u32(&bar_p[st]));
       // ---- O = alpha O + P V of the PREVIOUS tile: its product ran while this tile's softmax did
       if (i > 0) {
         if (ok) ok = mbar_poll(smem_u32(&bar_o[(i - 1) & 1]), ((i - 1) >> 1) & 1);

@@ -271,3 +271,33 @@ def test_prefill_attention_tensor_and_mma_kernels_agree_with_sdpa(lens, offs):
         assert torch.allclose(got, want, atol=ATOL), (n, o, (got - want).abs().max().item())
         ref = other[a:a + n].view(n, HEADS, HEAD_DIM).transpose(0, 1).float()
         assert torch.allclose(got, ref, atol=4e-3), (n, o, (got - ref).abs().max().item())
+
+
+def test_prefill_attention_gives_the_same_bits_every_run():
+    """The tcgen05 kernel's roles hand tiles to each other through mbarriers; a hand-off that lets
+    one pair of softmax warps run ahead of another shows up as a few rows that differ between
+    runs (it did, once: arrivals for tile i + 1 counted for tile i).  Thirty runs of a ragged
+    batch with a 4300-token sequence must be bit-identical, and so must the decode attention
+    with a cluster merge."""
+    from quic_cu_b200 import kernels as K
+
+    g = torch.Generator(device="cuda").manual_seed(99)
+    lens = [4300, 40, 700, 3000]
+    rows, s_max = sum(lens), 4352
+    q = torch.randn((HEADS, rows, HEAD_DIM), device="cuda", generator=g).half()
+    kc = torch.randn((4, 2, s_max, HEAD_DIM), device="cuda", generator=g).half()
+    vc = torch.randn((4, 2, s_max, HEAD_DIM), device="cuda", generator=g).half()
+    dev = dict(device="cuda", dtype=torch.int32)
+    starts = torch.tensor([sum(lens[:i]) for i in range(4)], **dev)
+    args = (q, kc, vc, starts, torch.tensor(lens, **dev), torch.arange(4, **dev), max(lens), SCALE)
+    first = K.attn_prefill(*args).clone()
+    for _ in range(30):
+        assert torch.equal(K.attn_prefill(*args), first)
+
+    qd = torch.randn((3, HEADS, 1, HEAD_DIM), device="cuda", generator=g).half()
+    pads = torch.tensor([0, 100, 4000], **dev)
+    kd, vd = kc[:3, :, :4096].contiguous(), vc[:3, :, :4096].contiguous()  # the longest cache that kernel takes
+    first = K.flash_attn_decode().forward(qd, kd, vd, SCALE, pads, cta_merge=True).clone()
+    for _ in range(30):
+        assert torch.equal(K.flash_attn_decode().forward(qd, kd, vd, SCALE, pads, cta_merge=True), first)
+    assert K.lib().quic_w4a16_tensor_status() == 0
