@@ -278,7 +278,7 @@ def run_gpu(args) -> None:
     step_gbs = step_bytes / (us_per_token * 1e-6) / 1e9
     layers_us = max(us_per_token - lm_us, 1e-3)           # all 5 x 24 layer kernels of a token
     layer_bytes = step_bytes - lm_bytes                     # W4 weights of 24 layers + K/V read and written
-    per_layer = {"qkv_kernel<1>": 536256 + 2304 + 1792 + 512, "attn_decode_warp_kernel": 512 * (mean_ctx + 1),
+    per_layer = {"qkv_kernel<1>": 536256 + 2304 + 1792 + 512, "attn_decode_cta_kernel<true>": 512 * (mean_ctx + 1),
                  "oproj_kernel<1>": 417088, "gateup_kernel<1>": 4528384 + 1792, "down_kernel<1>": 2264192}
     kernels = []
     for name, share in prof["layer_kernel_share"].items():
