@@ -63,22 +63,6 @@ __device__ __forceinline__ uint32_t pack2(float x, float y) {
 __device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// 32 consecutive fp32 columns of this thread's TMEM lane: two loads in flight, one wait
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-#pragma unroll
-  for (int q = 0; q < 2; ++q)
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
-          "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
-          "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]),
-          "=r"(r[16 * q + 14]), "=r"(r[16 * q + 15])
-        : "r"(taddr + 16u * q));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 // Bounded wait by polling (mbarrier.test_wait returns at once; try_wait may suspend the thread for a
 // scheduling quantum even when the phase completes a few cycles later): for the softmax warps, whose
 // barriers are normally complete, or about to be, when they look.

@@ -92,10 +92,20 @@ __global__ void set_slot_state_kernel(const int64_t* __restrict__ first, const i
   pos[slot] = seq_len[i] + (seq_off != nullptr ? seq_off[i] : 0);
 }
 
+// Rows per call of a linear: packed weights beyond kPrefillChunk rows never split K (their CTAs
+// fill the SMs many times over), so they need no workspace and one launch covers all rows --
+// fewer partial waves than a launch per 8192 rows.  Dense weights keep the chunks.
+int linear_chunk(const quic_w4_t& w, int rows) {
+  constexpr int kMaxRowsPerLaunch = 1 << 22;  // grid.z = rows / 256 stays far below 65535
+  if (w.w16 != nullptr || rows <= kPrefillChunk) return kPrefillChunk;
+  return rows < kMaxRowsPerLaunch ? rows : kMaxRowsPerLaunch;
+}
+
 // One W4A16 linear over all rows, in chunks that bound the split-K workspace.
 int linear_rows(const half* x, const quic_w4_t& w, half* y, int rows, void* ws, void* stream) {
-  for (int r0 = 0; r0 < rows; r0 += kPrefillChunk) {
-    const int m = rows - r0 < kPrefillChunk ? rows - r0 : kPrefillChunk;
+  const int chunk = linear_chunk(w, rows);
+  for (int r0 = 0; r0 < rows; r0 += chunk) {
+    const int m = rows - r0 < chunk ? rows - r0 : chunk;
     const int rc = quic_w4a16_linear(x + (size_t)r0 * w.k, &w, y + (size_t)r0 * w.n, m, 1, ws, stream);
     if (rc != QUIC_OK) return rc;
   }
@@ -164,8 +174,9 @@ extern "C" int quic_prefill(const quic_model_t* m, const quic_prefill_t* p, void
         QUIC_CUDA(launch_swiglu_fused(gu, act + (size_t)r0 * kInter, mrows, st));
       }
     } else if (rows >= 2) {  // gate|up GEMM with SwiGLU in its epilogue: the [rows, 9728] intermediate never exists
-      for (int r0 = 0; r0 < rows; r0 += kPrefillChunk) {
-        const int mrows = rows - r0 < kPrefillChunk ? rows - r0 : kPrefillChunk;
+      const int chunk = linear_chunk(L.gate_up, rows);
+      for (int r0 = 0; r0 < rows; r0 += chunk) {
+        const int mrows = rows - r0 < chunk ? rows - r0 : chunk;
         if ((rc = w4a16_gemm_tc_swiglu(xn + (size_t)r0 * kHidden, L.gate_up, act + (size_t)r0 * kInter, mrows, st)) !=
             QUIC_OK)
           return rc;

@@ -51,6 +51,7 @@ struct GemmArgs {
   // gate rows and the 64 up rows of the same columns (two 64-row TMA boxes per stage), and y
   // is the activation [m_total, N / 2] = silu(gate) * up.
   int fuse_swiglu;
+  int sc_groups;  // quantisation groups whose scales and zero points fit behind the operand ring
 };
 
 constexpr int kMaxGroupsPerCta = 40;            // K / 128 of the widest layer (4864) rounded up
@@ -59,22 +60,26 @@ constexpr int kGemmThreads = kConsumers + 64;   // + TMA warp + MMA warp (one la
 // A pipeline stage covers kSub swizzle atoms of K (2 x 64 = 128 = one quantisation group): the
 // fixed per-stage costs of every role (a barrier round trip, a fence, a commit) are paid
 // half as often as with one atom per stage.
+// Many rows over a short K (prefill: K = 896 is seven groups) turn this around: a CTA's prologue
+// and epilogue weigh as much as its main loop and a two-stage ring leaves the loads' latency
+// exposed, so there a stage is ONE atom (KS = 1), a CTA holds two of them, and two CTAs share
+// an SM -- one CTA's epilogue runs under the other's main loop.
 constexpr int kSub = 2;
 constexpr int kStageK = kBlockK * kSub;
-constexpr uint32_t kRawBytes = 8 * kSub * kTileN * 4;  // packed tile: 16 k-words x 128 rows
+constexpr int kScaleBytesPerGroup = kTileN * 3;  // fp16 scale + one byte of zero point per weight row
 
 // MTL = batch-row tiles per CTA: one dequantised weight tile feeds MTL MMAs groups, so the
 // dequantisation work per flop drops MTL-fold (large M: prefill).
-template <int MT, int MTL = 1>
+template <int MT, int MTL = 1, int KS = kSub>
 struct Smem {
+  static constexpr uint32_t kRaw = 8 * KS * kTileN * 4;                   // packed tile: 8 KS k-words x 128 rows
   static constexpr uint32_t kBTile = ((uint32_t)MT * 128u + 1023u) & ~1023u;  // one x tile (MT rows x 64 k), swizzled by TMA
-  static constexpr uint32_t kB = kBTile * MTL * kSub;
+  static constexpr uint32_t kB = kBTile * MTL * KS;
   static constexpr uint32_t kASub = kTileN * 128;                        // dequantised 128 rows x 64 k
-  static constexpr uint32_t kA = kASub * kSub;
-  static constexpr uint32_t kStage = kRawBytes + kB + kA;
-  // as many stages as fit beside ~16 KB of static shared memory
+  static constexpr uint32_t kA = kASub * KS;
+  static constexpr uint32_t kStage = kRaw + kB + kA;
+  // as many stages as fit beside ~16 KB of scales, zero points and barriers
   static constexpr int kStages = (int)((210u * 1024u) / kStage) > 4 ? 4 : (int)((210u * 1024u) / kStage);
-  static constexpr uint32_t kTotal = kStages * kStage + 1024;            // + alignment slack
 };
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -87,12 +92,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // once its A tile is complete and commits them to the stage's "empty" barrier, which lets
 // the TMA warp refill it.  No role ever waits for another role's instruction issue, only
 // for data.  Warps 0-15 read the accumulator back at the end.
-template <int MT, int kStages, int MTL>
+template <int MT, int kStages, int MTL, int KS>
 __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                      const __grid_constant__ CUtensorMap tm_x,
                                                                      const GemmArgs a) {
-  using L = Smem<MT, MTL>;
+  using L = Smem<MT, MTL, KS>;
   constexpr int kMaxStages = kStages;
+  constexpr int kSub = KS;                   // (shadows the default: atoms per stage of THIS kernel)
+  constexpr int kStageK = kBlockK * KS;
+  constexpr uint32_t kRawBytes = L::kRaw;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];    // packed weight tile landed (TMA bytes)
   __shared__ __align__(8) uint64_t bar_aready[kMaxStages];  // 16 consumer warps finished the A tile AND the x tile landed
@@ -100,8 +108,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
-  __shared__ half sc_s[kMaxGroupsPerCta][kTileN];
-  __shared__ uint8_t zp_s[kMaxGroupsPerCta][kTileN];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kTileN;
@@ -115,6 +121,9 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  // scales [groups][128] and zero points [groups][128] of this CTA's rows, behind the ring
+  half* sc_s = reinterpret_cast<half*>(gen_base + kStages * L::kStage);
+  uint8_t* zp_s = reinterpret_cast<uint8_t*>(sc_s + (size_t)a.sc_groups * kTileN);
 
   constexpr uint32_t kCols = MT * MTL < 32 ? 32 : MT * MTL;  // power of two >= 32
   if (tid == 0) {
@@ -144,9 +153,9 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
   if (tid < kTileN) {
     const half* scp = reinterpret_cast<const half*>(a.w.sc);
     const int n = tile_row_to_n(tid);
-    for (int g = g_first; g <= g_last && g - g_first < kMaxGroupsPerCta; ++g) {
-      sc_s[g - g_first][tid] = scp[(size_t)g * N + n];
-      zp_s[g - g_first][tid] = (a.w.zp[(size_t)g * (N >> 1) + (n >> 1)] >> (4 * (n & 1))) & 15;
+    for (int g = g_first; g <= g_last && g - g_first < a.sc_groups; ++g) {
+      sc_s[(g - g_first) * kTileN + tid] = scp[(size_t)g * N + n];
+      zp_s[(g - g_first) * kTileN + tid] = (a.w.zp[(size_t)g * (N >> 1) + (n >> 1)] >> (4 * (n & 1))) & 15;
     }
   }
   tc_fence_before();
@@ -259,8 +268,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       const uint32_t* raw_g = reinterpret_cast<const uint32_t*>(stage_g);
       unsigned char* a_g = stage_g + kRawBytes + L::kB;
       const int g = ((kb0 + it) * kStageK) / kGroup - g_first;
-      const half2 s2 = __half2half2(sc_s[g][row]);
-      const half2 zp = zp_to_half2(zp_s[g][row]);
+      const half2 s2 = __half2half2(sc_s[g * kTileN + row]);
+      const half2 zp = zp_to_half2(zp_s[g * kTileN + row]);
 #pragma unroll
       for (int jj = 0; jj < 2 * kSub; ++jj) {
         const int j = 2 * kSub * part + jj;  // k-word 0..15 of the stage: atom j / 8, 16-byte chunk j % 8
@@ -296,7 +305,79 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status[0], 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
-    if (a.fuse_swiglu) {
+    if (MTL == 2 && a.y != nullptr && gridDim.y == 1) {
+      // Many rows (two row tiles = 256 accumulator columns per CTA): every warp reads its lane
+      // quarter 32 columns at a time, the CTA's output tile is put together in shared memory --
+      // the operand ring is free once the accumulation is complete -- and leaves in 16-byte
+      // pieces, whole 128- or 256-byte rows at a time.  All 16 warps reach every barrier whether
+      // or not their waits succeeded.
+      const int quarter = warp & 3, cgroup = warp >> 2;  // cgroup: 64 of the 256 columns (= batch rows)
+      const uint32_t lane_addr = tmem_d + ((uint32_t)(quarter * 32) << 16);
+      float v[32];
+      if (a.fuse_swiglu) {
+        // TMEM lanes 0-63 hold the gate rows, 64-127 the up rows of the same 64 activation columns.
+        // Of a warp's 64 batch rows the up warps hand their first 32 to the gate warps and the gate
+        // warps their second 32 to the up warps (fp16-rounded, as the linear's output), so that
+        // every warp finishes silu(gate) * up for 32 batch rows.
+        float* ex = reinterpret_cast<float*>(gen_base);                               // [256][64] fp32
+        half* out_s = reinterpret_cast<half*>(gen_base + MT * MTL * 64 * sizeof(float));  // [256][64] fp16
+        const bool up = quarter >= 2;
+        const int row = (quarter & 1) * 32 + lane;  // 0..63 inside the gate (or up) half
+        const int c_send = cgroup * 64 + (up ? 0 : 32), c_fin = cgroup * 64 + (up ? 32 : 0);
+        if (ok && m0 + c_send < a.m_total) {
+          tmem_ld32(lane_addr + (uint32_t)c_send, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ex[(c_send + j) * 64 + row] = __half2float(__float2half_rn(v[j]));
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+        if (ok && m0 + c_fin < a.m_total) {
+          tmem_ld32(lane_addr + (uint32_t)c_fin, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float mine = __half2float(__float2half_rn(v[j])), other = ex[(c_fin + j) * 64 + row];
+            out_s[(c_fin + j) * 64 + row] = __float2half_rn(up ? silu_mul(other, mine) : silu_mul(mine, other));
+          }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+        if (ok) {
+#pragma unroll 1
+          for (int id = tid; id < MT * MTL * 8; id += kConsumers) {  // (batch row, 16-byte piece of its 128 bytes)
+            const int t = id >> 3, piece = id & 7, m = m0 + t;
+            if (m < a.m_total)
+              *reinterpret_cast<uint4*>(a.y + (size_t)m * half_n + (size_t)blockIdx.x * 64 + piece * 8) =
+                  *reinterpret_cast<const uint4*>(out_s + t * 64 + piece * 8);
+          }
+        }
+      } else {
+        half* out_s = reinterpret_cast<half*>(gen_base);  // [256][128] fp16
+        const int col_l = quarter * 32 + lane;
+        const bool has_bias = a.w.bias != nullptr;
+        const float bias = has_bias ? __half2float(reinterpret_cast<const half*>(a.w.bias)[n0 + col_l]) : 0.f;
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+          const int c0 = cgroup * 64 + hh * 32;
+          if (ok && m0 + c0 < a.m_total) {
+            tmem_ld32(lane_addr + (uint32_t)c0, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float o = __half2float(__float2half_rn(v[j]));
+              if (has_bias) o += bias;
+              out_s[(c0 + j) * kTileN + col_l] = __float2half_rn(o);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+        if (ok) {
+#pragma unroll 1
+          for (int id = tid; id < MT * MTL * 16; id += kConsumers) {  // (batch row, 16-byte piece of its 256 bytes)
+            const int t = id >> 4, piece = id & 15, m = m0 + t;
+            if (m < a.m_total)
+              *reinterpret_cast<uint4*>(a.y + (size_t)m * N + n0 + piece * 8) =
+                  *reinterpret_cast<const uint4*>(out_s + t * kTileN + piece * 8);
+          }
+        }
+      }
+    } else if (a.fuse_swiglu) {
       // TMEM lanes 0-63 hold the gate rows, 64-127 the up rows of the same 64 columns.  The up
       // warps park their (fp16-rounded) values in shared memory -- the operand ring is free once
       // the accumulation is complete -- and the gate warps finish silu(gate) * up.  Every one of
@@ -421,40 +502,46 @@ __global__ void tc_splitk_finish_kernel(const float* __restrict__ part, const ha
   *reinterpret_cast<uint2*>(y + idx) = out;
 }
 
-template <int MT>
-int run(const half* x, const GemmArgs& args, int splits, cudaStream_t st) {
-  GemmArgs a = args;
-  a.spin_limit = g_spin_limit;
-  a.skip_kblock = g_skip_kblock;
+template <int MT, int kDeep, int MTL, int KS>
+int run_variant(const half* x, GemmArgs a, int splits, cudaStream_t st) {
+  using L = Smem<MT, MTL, KS>;
   CUtensorMap tm_w, tm_x;
-  // packed weights int32 [K/8, N]: box = 8 k-words x 128 rows; x fp16 [m, K]: box = MT rows x 64 k,
+  // packed weights int32 [K/8, N]: box = 8 KS k-words x 128 rows; x fp16 [m, K]: box = MT rows x 64 k,
   // written with the 128-byte swizzle the UMMA descriptor expects (rows past m read as zero)
   // (fused SwiGLU: two boxes of 64 rows per stage, gate rows and up rows)
-  int rc = make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, a.w.qw, (uint64_t)a.w.k / 8, (uint64_t)a.w.n, 8 * kSub,
+  int rc = make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, a.w.qw, (uint64_t)a.w.k / 8, (uint64_t)a.w.n, 8 * KS,
                     a.fuse_swiglu ? kTileN / 2 : kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != QUIC_OK) return rc;
   rc = make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)a.m_total, (uint64_t)a.w.k, MT, kBlockK,
                 CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != QUIC_OK) return rc;
+  a.kblocks_per_split *= kSub / KS;  // planned in stages of kSub atoms
+  a.sc_groups = min(kMaxGroupsPerCta, a.w.k / kGroup);
   const int mtiles = (a.m_total + MT - 1) / MT;
+  const size_t smem = (size_t)kDeep * L::kStage + 1024 + (size_t)a.sc_groups * kScaleBytesPerGroup;
+  dim3 grid(a.w.n / kTileN, splits, (mtiles + MTL - 1) / MTL);
+  QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, MTL, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+  QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, MTL, KS>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
+  return QUIC_OK;
+}
+
+// K short enough (eight groups) for the two-CTAs-per-SM form of the two-row-tile kernel.
+constexpr int kShortK = 1024;
+
+template <int MT>
+int run(const half* x, const GemmArgs& args, int splits, cudaStream_t st) {
+  GemmArgs a = args;
+  a.spin_limit = g_spin_limit;
+  a.skip_kblock = g_skip_kblock;
   if (a.mtl == 2) {
     if constexpr (MT == 128) {
-      constexpr int kDeep = Smem<MT, 2>::kStages;
-      const size_t smem = Smem<MT, 2>::kTotal;
-      dim3 grid(a.w.n / kTileN, splits, (mtiles + 1) / 2);
-      QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
-      QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, 2>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
-      return QUIC_OK;
+      if (a.w.k <= kShortK && splits == 1 && g_skip_kblock < 0)
+        return run_variant<MT, 2, 2, 1>(x, a, splits, st);  // 2 x 52 KB + scales: two CTAs per SM
+      return run_variant<MT, Smem<MT, 2>::kStages, 2, kSub>(x, a, splits, st);
     }
   }
-  dim3 grid(a.w.n / kTileN, splits, mtiles);
-  constexpr int kDeep = Smem<MT>::kStages;
-  const size_t smem = Smem<MT>::kTotal;
-  QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-  QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, 1>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
-  return QUIC_OK;
+  return run_variant<MT, Smem<MT>::kStages, 1, kSub>(x, a, splits, st);
 }
 
 }  // namespace

@@ -72,25 +72,37 @@ def test_prefill_then_graph_decode_matches_oracle(tiny_model):
 
 
 def test_prefill_with_the_library_attention_kernel_matches_oracle(tiny_model):
-    """prefill_backend "quic": heads split + RoPE + KV write and causal attention by the
-    library's kernels for three ragged prompts at once; last-position logits and the greedy
-    continuation must follow the oracle like the SDPA backend does."""
+    """Heads split + RoPE + KV write and causal attention by the library's kernels for three
+    ragged prompts at once; last-position logits and the greedy continuation must follow the
+    oracle."""
     net, ref, _, _ = tiny_model
     gen = torch.Generator().manual_seed(21)
     prompts = [torch.randint(0, 2048, (n,), generator=gen) for n in (70, 1, 33)]
     want = [ref.greedy(p.tolist(), 5) for p in prompts]
-    try:
-        net.prefill_backend = "quic"
-        cache = net.new_cache(n_slots=4, s_max=128)
-        first, logits = net.prefill(cache, [2, 0, 3], prompts)
-    finally:
-        net.prefill_backend = "pytorch"
+    cache = net.new_cache(n_slots=4, s_max=128)
+    first, logits = net.prefill(cache, [2, 0, 3], prompts)
     for i in range(3):
         ok, err = _close(logits[i], want[i][1][0])
         assert ok, (i, err)
     rest = net.decode(cache, [2, 0, 3], 4)
     for i in range(3):
         _assert_greedy_matches([int(first[i])] + rest[i], want[i][0], want[i][1])
+
+
+def test_prefill_of_several_hundred_rows_matches_oracle(tiny_model):
+    """415 rows in one prefill: from 129 rows on the gate|up GEMM gives a CTA two row tiles and puts
+    its SwiGLU output together in shared memory (here: one full CTA and one whose second tile is
+    partly filled); the logits of every prompt's last position must follow the oracle."""
+    net, ref, _, _ = tiny_model
+    gen = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 2048, (n,), generator=gen) for n in (260, 150, 5)]
+    want = [ref.greedy(p.tolist(), 1) for p in prompts]
+    cache = net.new_cache(n_slots=4, s_max=320)
+    first, logits = net.prefill(cache, [1, 3, 0], prompts)
+    for i in range(3):
+        ok, err = _close(logits[i], want[i][1][0])
+        assert ok, (i, err)
+        _assert_greedy_matches([int(first[i])], want[i][0], want[i][1])
 
 
 def test_bursts_single_steps_and_host_fed_steps_agree(tiny_model):

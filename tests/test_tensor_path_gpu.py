@@ -29,7 +29,9 @@ def test_tensor_gemm_matches_gemv_and_oracle(name):
     w.bias = (torch.randn(n, generator=torch.Generator().manual_seed(1)) * 0.02).half().cuda()
     w16 = torch.from_numpy(quic_ref.dequantize_f16(layer["weight_packed"].numpy(), layer["weight_scale"].numpy(),
                                                    layer["weight_zero_point"].numpy()))
-    for m in (2, 3, 4, 5, 16, 17, 64, 100, 256, 300, 1000, 2500):
+    # (from 2049 / 2689 rows every shape gives a CTA two row tiles; 2600 and 3000 end in a CTA
+    # with one partly filled tile and with a full and a partly filled one)
+    for m in (2, 3, 4, 5, 16, 17, 64, 100, 256, 300, 1000, 2500, 2600, 3000):
         x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).half()
         y_tc = K.w4a16_linear(w, x.cuda(), use_tensor=True)
         y_gemv = K.w4a16_linear(w, x.cuda(), use_tensor=False)
