@@ -109,6 +109,14 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 // Byte offset of 16-byte chunk c (0..7) of row r inside a swizzled tile.
 __device__ __forceinline__ uint32_t sw128_offset(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16),
+// completing `bytes` of the barrier's transaction count.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }

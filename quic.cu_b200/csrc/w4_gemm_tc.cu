@@ -51,10 +51,8 @@ struct GemmArgs {
   // gate rows and the 64 up rows of the same columns (two 64-row TMA boxes per stage), and y
   // is the activation [m_total, N / 2] = silu(gate) * up.
   int fuse_swiglu;
-  int sc_groups;  // quantisation groups whose scales and zero points fit behind the operand ring
 };
 
-constexpr int kMaxGroupsPerCta = 40;            // K / 128 of the widest layer (4864) rounded up
 constexpr int kConsumers = 512;                 // 16 warps dequantise (4 per scheduler) and run the epilogue
 constexpr int kGemmThreads = kConsumers + 64;   // + TMA warp + MMA warp (one lane each)
 // A pipeline stage covers kSub swizzle atoms of K (2 x 64 = 128 = one quantisation group): the
@@ -66,7 +64,8 @@ constexpr int kGemmThreads = kConsumers + 64;   // + TMA warp + MMA warp (one la
 // an SM -- one CTA's epilogue runs under the other's main loop.
 constexpr int kSub = 2;
 constexpr int kStageK = kBlockK * kSub;
-constexpr int kScaleBytesPerGroup = kTileN * 3;  // fp16 scale + one byte of zero point per weight row
+// Scales (fp16) and zero points (a nibble) of a stage's 128 weight rows travel with the stage.
+constexpr uint32_t kScBytes = kTileN * 2, kZpBytes = kTileN / 2, kScArea = 1024;
 
 // MTL = batch-row tiles per CTA: one dequantised weight tile feeds MTL MMAs groups, so the
 // dequantisation work per flop drops MTL-fold (large M: prefill).
@@ -77,8 +76,8 @@ struct Smem {
   static constexpr uint32_t kB = kBTile * MTL * KS;
   static constexpr uint32_t kASub = kTileN * 128;                        // dequantised 128 rows x 64 k
   static constexpr uint32_t kA = kASub * KS;
-  static constexpr uint32_t kStage = kRaw + kB + kA;
-  // as many stages as fit beside ~16 KB of scales, zero points and barriers
+  static constexpr uint32_t kStage = kRaw + kB + kA + kScArea;        // [packed | x tiles | A | scales, zero points]
+  // as many stages as fit
   static constexpr int kStages = (int)((210u * 1024u) / kStage) > 4 ? 4 : (int)((210u * 1024u) / kStage);
 };
 
@@ -121,9 +120,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  // scales [groups][128] and zero points [groups][128] of this CTA's rows, behind the ring
-  half* sc_s = reinterpret_cast<half*>(gen_base + kStages * L::kStage);
-  uint8_t* zp_s = reinterpret_cast<uint8_t*>(sc_s + (size_t)a.sc_groups * kTileN);
 
   constexpr uint32_t kCols = MT * MTL < 32 ? 32 : MT * MTL;  // power of two >= 32
   if (tid == 0) {
@@ -143,21 +139,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // scales and zero points of this CTA's rows for its whole k range
-  const int g_first = (kb0 * kStageK) / kGroup, g_last = (kb1 * kStageK - 1) / kGroup;
-  // weight row of tile row r
   const int half_n = N >> 1;
-  auto tile_row_to_n = [&](int r) {
-    return a.fuse_swiglu ? (r < 64 ? (int)blockIdx.x * 64 + r : half_n + (int)blockIdx.x * 64 + (r - 64)) : n0 + r;
-  };
-  if (tid < kTileN) {
-    const half* scp = reinterpret_cast<const half*>(a.w.sc);
-    const int n = tile_row_to_n(tid);
-    for (int g = g_first; g <= g_last && g - g_first < a.sc_groups; ++g) {
-      sc_s[(g - g_first) * kTileN + tid] = scp[(size_t)g * N + n];
-      zp_s[(g - g_first) * kTileN + tid] = (a.w.zp[(size_t)g * (N >> 1) + (n >> 1)] >> (4 * (n & 1))) & 15;
-    }
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -173,17 +155,29 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int first = nkb < kStages ? nkb : kStages;
-      for (int it = 0; it < first; ++it) {
-        const uint32_t raw_s = base + it * L::kStage;
-        const uint32_t full = smem_u32(&bar_full[it]);
-        if (kb0 + it == a.skip_kblock) continue;  // test hook: the consumers' wait for this tile runs out
-        mbar_expect_tx(full, kRawBytes);
+      // weight side of k block `kb` into the stage at raw_s: packed tile, scales, zero points
+      const half* scp = reinterpret_cast<const half*>(a.w.sc);
+      auto load_weights = [&](uint32_t raw_s, int kb, uint32_t full) {
+        const uint32_t sc_s = raw_s + L::kStage - kScArea, zp_s = sc_s + kScBytes;
+        const size_t g = (size_t)((kb * kStageK) / kGroup);
+        mbar_expect_tx(full, kRawBytes + kScBytes + kZpBytes);
         if (a.fuse_swiglu) {  // two boxes of 64 rows: gate rows, then the up rows of the same columns
-          tma_load_2d(raw_s, &tm_w, (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
-          tma_load_2d(raw_s + kRawBytes / 2, &tm_w, half_n + (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
+          const int ng = (int)blockIdx.x * 64, nu = half_n + ng;
+          tma_load_2d(raw_s, &tm_w, ng, kb * 8 * kSub, full);
+          tma_load_2d(raw_s + kRawBytes / 2, &tm_w, nu, kb * 8 * kSub, full);
+          bulk_load(sc_s, scp + g * N + ng, kScBytes / 2, full);
+          bulk_load(sc_s + kScBytes / 2, scp + g * N + nu, kScBytes / 2, full);
+          bulk_load(zp_s, a.w.zp + g * half_n + (ng >> 1), kZpBytes / 2, full);
+          bulk_load(zp_s + kZpBytes / 2, a.w.zp + g * half_n + (nu >> 1), kZpBytes / 2, full);
         } else {
-          tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
+          tma_load_2d(raw_s, &tm_w, n0, kb * 8 * kSub, full);
+          bulk_load(sc_s, scp + g * N + n0, kScBytes, full);
+          bulk_load(zp_s, a.w.zp + g * half_n + (n0 >> 1), kZpBytes, full);
         }
+      };
+      for (int it = 0; it < first; ++it) {
+        if (kb0 + it == a.skip_kblock) continue;  // test hook: the consumers' wait for this tile runs out
+        load_weights(base + it * L::kStage, kb0 + it, smem_u32(&bar_full[it]));
       }
       pdl_wait();
       for (int it = 0; it < first; ++it) {
@@ -202,15 +196,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         }
         const uint32_t raw_s = base + stage * L::kStage, b_s = raw_s + kRawBytes;
         const uint32_t full = smem_u32(&bar_full[stage]), xfull = smem_u32(&bar_aready[stage]);
-        if (kb0 + it != a.skip_kblock) {  // (test hook: see the first pass)
-          mbar_expect_tx(full, kRawBytes);
-          if (a.fuse_swiglu) {
-            tma_load_2d(raw_s, &tm_w, (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
-            tma_load_2d(raw_s + kRawBytes / 2, &tm_w, half_n + (int)blockIdx.x * 64, (kb0 + it) * 8 * kSub, full);
-          } else {
-            tma_load_2d(raw_s, &tm_w, n0, (kb0 + it) * 8 * kSub, full);
-          }
-        }
+        if (kb0 + it != a.skip_kblock) load_weights(raw_s, kb0 + it, full);  // (test hook: see the first pass)
         mbar_expect_tx(xfull, (uint32_t)MT * 128u * MTL * kSub);
 #pragma unroll
         for (int i = 0; i < MTL * kSub; ++i)
@@ -267,9 +253,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
       unsigned char* stage_g = gen_base + stage * L::kStage;
       const uint32_t* raw_g = reinterpret_cast<const uint32_t*>(stage_g);
       unsigned char* a_g = stage_g + kRawBytes + L::kB;
-      const int g = ((kb0 + it) * kStageK) / kGroup - g_first;
-      const half2 s2 = __half2half2(sc_s[g * kTileN + row]);
-      const half2 zp = zp_to_half2(zp_s[g * kTileN + row]);
+      const half* sc_s = reinterpret_cast<const half*>(stage_g + L::kStage - kScArea);
+      const uint8_t* zp_s = reinterpret_cast<const uint8_t*>(sc_s) + kScBytes;  // byte r / 2: rows r (low nibble), r + 1
+      const half2 s2 = __half2half2(sc_s[row]);
+      const half2 zp = zp_to_half2((zp_s[row >> 1] >> (4 * (row & 1))) & 15);
 #pragma unroll
       for (int jj = 0; jj < 2 * kSub; ++jj) {
         const int j = 2 * kSub * part + jj;  // k-word 0..15 of the stage: atom j / 8, 16-byte chunk j % 8
@@ -516,18 +503,14 @@ int run_variant(const half* x, GemmArgs a, int splits, cudaStream_t st) {
                 CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != QUIC_OK) return rc;
   a.kblocks_per_split *= kSub / KS;  // planned in stages of kSub atoms
-  a.sc_groups = min(kMaxGroupsPerCta, a.w.k / kGroup);
   const int mtiles = (a.m_total + MT - 1) / MT;
-  const size_t smem = (size_t)kDeep * L::kStage + 1024 + (size_t)a.sc_groups * kScaleBytesPerGroup;
+  const size_t smem = (size_t)kDeep * L::kStage + 1024;
   dim3 grid(a.w.n / kTileN, splits, (mtiles + MTL - 1) / MTL);
   QUIC_CUDA(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<MT, kDeep, MTL, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
   QUIC_CUDA(launch(w4a16_gemm_tc_kernel<MT, kDeep, MTL, KS>, grid, dim3(kGemmThreads), smem, st, true, tm_w, tm_x, a));
   return QUIC_OK;
 }
-
-// K short enough (eight groups) for the two-CTAs-per-SM form of the two-row-tile kernel.
-constexpr int kShortK = 1024;
 
 template <int MT>
 int run(const half* x, const GemmArgs& args, int splits, cudaStream_t st) {
@@ -536,8 +519,14 @@ int run(const half* x, const GemmArgs& args, int splits, cudaStream_t st) {
   a.skip_kblock = g_skip_kblock;
   if (a.mtl == 2) {
     if constexpr (MT == 128) {
-      if (a.w.k <= kShortK && splits == 1 && g_skip_kblock < 0)
-        return run_variant<MT, 2, 2, 1>(x, a, splits, st);  // 2 x 52 KB + scales: two CTAs per SM
+      // Two CTAs per SM (2 x 53 KB, one-atom stages) when their waves take less time than the
+      // waves of one CTA per SM: a CTA that shares its SM was measured at 1.86 x the time of one
+      // that has it alone over a long K (4864) and about 1.5 x over a short one (896), where
+      // prologue and epilogue weigh more -- e.g. 896 CTAs are 7 waves of 148 or 4 of 296.
+      const int ctas = (a.w.n / kTileN) * (((a.m_total + MT - 1) / MT + 1) / 2);
+      const int waves1 = (ctas + 147) / 148, waves2 = (ctas + 295) / 296;
+      if (splits == 1 && g_skip_kblock < 0 && waves2 * (a.w.k <= 1024 ? 150 : 186) <= waves1 * 100)
+        return run_variant<MT, 2, 2, 1>(x, a, splits, st);
       return run_variant<MT, Smem<MT, 2>::kStages, 2, kSub>(x, a, splits, st);
     }
   }
@@ -578,7 +567,8 @@ int w4a16_gemm_tc(const half* x, const quic_w4_t& w, half* y, int m, float* work
                "w4a16_linear: the tensor path needs N and K multiples of 128");
   QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0), QUIC_E_ARG,
                "w4a16_linear: x and the packed weights must be 16-byte aligned");
-  QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16_linear: K beyond 5120 on the tensor path");
+  QUIC_REQUIRE(((uintptr_t)w.sc % 16 == 0) && ((uintptr_t)w.zp % 16 == 0), QUIC_E_ARG,
+               "w4a16_linear: scales and zero points must be 16-byte aligned");
   int mt, splits, per, mtl;
   tc_plan(m, w.n, w.k, &mt, &splits, &per, &mtl);
   QUIC_REQUIRE((splits == 1 && y != nullptr) || workspace != nullptr, QUIC_E_ARG,
@@ -617,7 +607,8 @@ int w4a16_gemm_tc_swiglu(const half* x, const quic_w4_t& w, half* act, int m, cu
                "w4a16 gate_up: N must be a multiple of 128 and K of 128");
   QUIC_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w.qw % 16 == 0) && act != nullptr, QUIC_E_ARG,
                "w4a16 gate_up: x and the packed weights must be 16-byte aligned");
-  QUIC_REQUIRE(w.k / kGroup <= kMaxGroupsPerCta, QUIC_E_LIMIT, "w4a16 gate_up: K beyond 5120 on the tensor path");
+  QUIC_REQUIRE(((uintptr_t)w.sc % 16 == 0) && ((uintptr_t)w.zp % 16 == 0), QUIC_E_ARG,
+               "w4a16 gate_up: scales and zero points must be 16-byte aligned");
   int mt, splits, per, mtl;
   tc_plan(m, w.n, w.k, &mt, &splits, &per, &mtl);
   GemmArgs a = {};
