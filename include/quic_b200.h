@@ -155,7 +155,8 @@ int quic_rope(const void *x_f16, const void *cos_f16, const void *sin_f16,
  * [14, rows, 64], and the rotated keys / plain values into the layer's cache
  * planes [n_slots, 2, s_max, 64] at (slot, head, position); a row whose slot
  * is outside 0..n_slots-1 or whose position is outside 0..s_max-1 appends
- * nothing (its query is still written).  Replaces
+ * nothing (its query is still written).  All tensors 16-byte aligned.
+ * Replaces
  * _heads + rope.forward x2 + DynamicCache.update of the reference's attention
  * (src/model.py:138-160). */
 int quic_qkv_rope_append(const void *qkv_f16, const int32_t *slots,

@@ -296,6 +296,58 @@ __global__ void qkv_post_kernel(const half* __restrict__ qkv, const float* __res
   dst[pair + 32] = __float2half_rn(hi);
 }
 
+// The same for many rows (prefill: every row brings its own slot and position, q is written
+// head-major): one thread per (row, head, 8 of the 64 dims), which reads the 8 stored pairs
+// its dims come from (32 bytes) with their cos / sin (16 bytes each) and writes 16 bytes.
+__global__ void __launch_bounds__(256) qkv_rope_rows_kernel(
+    const half* __restrict__ qkv, const int32_t* __restrict__ slots, const int32_t* __restrict__ row_pos,
+    const half* __restrict__ cos_t, const half* __restrict__ sin_t, int max_pos, half* __restrict__ qbuf,
+    half* __restrict__ kcache, half* __restrict__ vcache, int s_max, int rows, int n_slots) {
+  constexpr int kPerRow = (kHeads + 2 * kKvHeads) * 8;  // 144 threads per row
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (idx >= (size_t)rows * kPerRow) return;
+  const int b = (int)(idx / kPerRow), rem = (int)(idx % kPerRow);
+  const int head = rem >> 3, piece = rem & 7;   // piece: dims 8 piece .. 8 piece + 7
+  const int pair0 = (piece & 3) * 8;            // their pairs: dims d and d + 32 are stored side by side
+  const bool high = piece >= 4;                 // dims 32..63: the second element of the rotated pair
+  const int slot = slots[b], p = row_pos[b];
+  const half2* src = reinterpret_cast<const half2*>(qkv + (size_t)b * kQkvN + head * kHeadDim) + pair0;
+  const uint4 in0 = *reinterpret_cast<const uint4*>(src), in1 = *reinterpret_cast<const uint4*>(src + 4);
+  const half2 xy[8] = {*reinterpret_cast<const half2*>(&in0.x), *reinterpret_cast<const half2*>(&in0.y),
+                       *reinterpret_cast<const half2*>(&in0.z), *reinterpret_cast<const half2*>(&in0.w),
+                       *reinterpret_cast<const half2*>(&in1.x), *reinterpret_cast<const half2*>(&in1.y),
+                       *reinterpret_cast<const half2*>(&in1.z), *reinterpret_cast<const half2*>(&in1.w)};
+  half out[8];
+  if (head < kHeads + kKvHeads) {
+    const int pp = p < max_pos ? (p < 0 ? 0 : p) : max_pos - 1;
+    const uint4 c4 = *reinterpret_cast<const uint4*>(cos_t + (size_t)pp * 32 + pair0);
+    const uint4 s4 = *reinterpret_cast<const uint4*>(sin_t + (size_t)pp * 32 + pair0);
+    const half* ch = reinterpret_cast<const half*>(&c4);
+    const half* sh = reinterpret_cast<const half*>(&s4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 v = __half22float2(xy[i]);
+      const float c = __half2float(ch[i]), sn = __half2float(sh[i]);
+      out[i] = __float2half_rn(high ? v.x * sn + v.y * c : v.x * c - v.y * sn);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = high ? __high2half(xy[i]) : __low2half(xy[i]);
+  }
+  half* dst;
+  if (head < kHeads) {
+    dst = qbuf + ((size_t)head * rows + b) * kHeadDim;
+  } else {
+    if (p >= s_max || p < 0 || slot < 0 || slot >= n_slots) return;  // nothing is appended for such a row
+    const int kvh = (head - kHeads) & 1;
+    half* base = (head < kHeads + kKvHeads) ? kcache : vcache;
+    dst = base + (((size_t)slot * kKvHeads + kvh) * s_max + p) * kHeadDim;
+  }
+  *reinterpret_cast<uint4*>(dst + piece * 8) = *reinterpret_cast<const uint4*>(out);
+}
+
 // act[b][i] = silu(gu[b][i]) * gu[b][4864 + i] on the fused gate|up output, which comes
 // either as fp16 rows or as `splits` fp32 split-K partial sums [splits][batch][9728]; the
 // summed linear output is rounded to fp16 first, as the un-split epilogue does.
@@ -353,10 +405,9 @@ cudaError_t launch_qkv_post(const half* qkv, const int32_t* rows, const int32_t*
 cudaError_t launch_qkv_rope_append(const half* qkv, const int32_t* slots, const int32_t* positions, const half* cos_t,
                                    const half* sin_t, int max_pos, half* q_out, half* kcache, half* vcache, int s_max,
                                    int n_slots, int rows, cudaStream_t st, bool pdl) {
-  const int total = rows * (kQkvN / 2);
-  return launch(qkv_post_kernel, dim3((total + 255) / 256), dim3(256), 0, st, pdl, qkv, (const float*)nullptr, 0,
-                (const half*)nullptr, slots, (const int32_t*)nullptr, cos_t, sin_t, max_pos, q_out, kcache, vcache,
-                s_max, rows, positions, 1, n_slots);
+  const size_t total = (size_t)rows * (kHeads + 2 * kKvHeads) * 8;
+  return launch(qkv_rope_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, pdl, qkv, slots, positions,
+                cos_t, sin_t, max_pos, q_out, kcache, vcache, s_max, rows, n_slots);
 }
 cudaError_t launch_qkv_post_part(const float* part, int splits, const half* bias, const int32_t* rows,
                                  const int32_t* pos, const half* cos_t, const half* sin_t, int max_pos, half* qbuf,
@@ -445,6 +496,9 @@ extern "C" int quic_qkv_rope_append(const void* qkv, const int32_t* slots, const
                "qkv_rope_append: null tensor");
   QUIC_REQUIRE(rows >= 0 && rows <= (1 << 20) && s_max >= 1 && max_pos >= 1 && n_slots >= 1, QUIC_E_SHAPE,
                "qkv_rope_append: bad row count or cache geometry");
+  QUIC_REQUIRE(((uintptr_t)qkv | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)q_out | (uintptr_t)kcache |
+                (uintptr_t)vcache) % 16 == 0,
+               QUIC_E_ARG, "qkv_rope_append: tensors must be 16-byte aligned");
   if (rows == 0) return QUIC_OK;
   QUIC_CUDA(launch_qkv_rope_append((const half*)qkv, slots, positions, (const half*)cos_t, (const half*)sin_t,
                                    (int)max_pos, (half*)q_out, (half*)kcache, (half*)vcache, (int)s_max, (int)n_slots,
