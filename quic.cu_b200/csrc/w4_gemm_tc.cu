@@ -525,6 +525,8 @@ int run(const half* x, const GemmArgs& args, int splits, cudaStream_t st) {
       // prologue and epilogue weigh more -- e.g. 896 CTAs are 7 waves of 148 or 4 of 296.
       const int ctas = (a.w.n / kTileN) * (((a.m_total + MT - 1) / MT + 1) / 2);
       const int waves1 = (ctas + 147) / 148, waves2 = (ctas + 295) / 296;
+      static_assert(2 * (2 * Smem<MT, 2, 1>::kStage + 2048) <= 227 * 1024 && Smem<MT, 2, 1>::kStages >= 2,
+                    "two CTAs of two one-atom stages must fit one SM");
       if (splits == 1 && g_skip_kblock < 0 && waves2 * (a.w.k <= 1024 ? 150 : 186) <= waves1 * 100)
         return run_variant<MT, 2, 2, 1>(x, a, splits, st);
       return run_variant<MT, Smem<MT, 2>::kStages, 2, kSub>(x, a, splits, st);
