@@ -356,9 +356,9 @@ def run_gpu(args) -> None:
         dist.destroy_process_group()
 
 
-def linear_sweep(device: str = "cuda:0", shapes=None, ms=(1, 4, 16, 64, 256), reps: int = 20) -> list[dict]:
+def linear_sweep(device: str = "cuda:0", shapes=None, ms=(1, 4, 16, 64, 256, 8192), reps: int = 20) -> list[dict]:
     """The single W4A16 linear-op sweep of the benchmark configuration: the model's four
-    (K, N) shapes at M in {1, 4, 16, 64, 256}; int4 values and zero points uniform in 0..15,
+    (K, N) shapes at M in {1, 4, 16, 64, 256} (decode) and 8192 (prefill); int4 values and zero points uniform in 0..15,
     scales |N(0, 0.01)| + 1e-3, activations N(0, 1).  Each point is timed as a CUDA graph of
     ``reps`` launches (device time, no host overhead).  M = 1 runs the dequant GEMV, M >= 2
     the tcgen05 GEMM."""
