@@ -36,55 +36,6 @@ constexpr int kGroupHeads = kHeads / kKvHeads;  // 7
 constexpr int kWarps = 8;
 constexpr int kTile = 32;
 
-// The CTA that arrives last at the per-(row, kv head) counter merges the split partials of
-// the group's 7 heads, writes the fp16 output and re-arms the counter.  No CTA waits.
-// Partials are fetched 16 splits at a time with every load in flight before the first use.
-__device__ __forceinline__ void merge_splits_last_cta(const AttnArgs& a, int b, int kvh, int split, int* last_flag_s) {
-  const int tid = threadIdx.x;
-  int& last_flag = *last_flag_s;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(&a.counters[b * kKvHeads + kvh], 1);
-    last_flag = (old == a.splits - 1);
-  }
-  __syncthreads();
-  if (!last_flag) return;
-  __threadfence();
-  for (int idx = tid; idx < kGroupHeads * kHeadDim; idx += (int)blockDim.x) {
-    const int h = idx >> 6, d = idx & 63;
-    const int qh = kvh * kGroupHeads + h;
-    const size_t row = ((size_t)b * kHeads + qh) * a.splits;
-    float m = -INFINITY, num = 0.f, den = 0.f;
-    for (int s0 = 0; s0 < a.splits; s0 += 16) {
-      float ms[16], ls[16], os[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const bool in = s0 + j < a.splits;
-        ms[j] = in ? __ldcg(a.m_part + row + s0 + j) : -INFINITY;
-        ls[j] = in ? __ldcg(a.l_part + row + s0 + j) : 0.f;
-        os[j] = in ? __ldcg(a.o_part + (row + s0 + j) * kHeadDim + d) : 0.f;
-      }
-      float mc = m;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) mc = fmaxf(mc, ms[j]);
-      if (mc == -INFINITY) continue;
-      const float rescale = (m == -INFINITY) ? 0.f : __expf(m - mc);
-      num *= rescale;
-      den *= rescale;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float e = (ms[j] == -INFINITY) ? 0.f : __expf(ms[j] - mc);
-        den += e * ls[j];
-        num += e * os[j];
-      }
-      m = mc;
-    }
-    a.out[((size_t)b * kHeads + qh) * kHeadDim + d] = __float2half_rn(m == -INFINITY ? 0.f : num / den);
-  }
-  if (tid == 0) a.counters[b * kKvHeads + kvh] = 0;
-}
-
 // The same merge for single-warp CTAs and at most 32 splits.  Lane s owns split s for the
 // softmax statistics (one coalesced load per head), every lane owns two dims of the output;
 // all partial loads of four heads are in flight together, so the merge costs three memory

@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) attn_decode_cta_kernel(cons
   *reinterpret_cast<half2*>(out) = __floats2half2_rn(gnum.x * inv, gnum.y * inv);
 }
 
+
 }  // namespace
 
 int attn_cta_splits(int ctx) {

@@ -1,0 +1,223 @@
+// GQA decode attention for many rows (the tensor-core step beyond 32 rows): ONE CTA per
+// (row, KV head) streams that head's cached keys and values through a ring of shared-memory
+// stages filled by TMA (64-token tiles, 128-byte swizzle), four warps take the tiles in turn
+// -- the 64-token tile arithmetic of attn_warp.cuh on mma.sync, each warp keeping a running
+// softmax over its tiles -- and meet once in shared memory.  No partial results in global
+// memory, no counters, no second pass, and nothing is read beyond a row's own length.
+//
+// Why: with one-warp CTAs (attn_decode_warp_kernel) every warp requests its 16 KB tile with 32
+// loads per lane and then waits for it; at 64 rows of 200..1500 tokens that form reads 1.8 x
+// the algorithmic bytes (tiles beyond a row's length are fetched too), reaches a quarter of the
+// HBM bandwidth and takes 25 us per layer.  Here a single thread keeps kStages x 16 KB of bulk
+// copies in flight per SM and the copies cost the warps no instructions.
+//
+// Same mathematics as fad_decode_kernel + fad_combine_kernel of the reference
+// (kernels/cuda/flash_attn_decode.cu:12,104): fp32 softmax over the tokens [start_b, end_b) of
+// each row, rows without tokens give zeros (:118-121).
+#include "attn_warp.cuh"
+#include "decode_kernels.cuh"
+#include "tc_common.cuh"
+
+namespace quic {
+namespace {
+
+constexpr int kGroupHeads = kHeads / kKvHeads;  // 7
+constexpr int kStreamWarps = 4;                  // compute warps; warp 4 is the producer
+constexpr int kStreamStages = 8;                 // ring depth (a multiple of kStreamWarps)
+constexpr uint32_t kTileBytes = kWarpChunk * kHeadDim * 2;  // 8 KB: 64 tokens x 128 bytes
+constexpr uint32_t kStageBytes = 2 * kTileBytes;            // K tile, V tile
+constexpr size_t kStreamSmem = (size_t)kStreamStages * kStageBytes + 1024;
+
+__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// The fragments of warp_tile_request, from a swizzled tile pair in shared memory (conflict-free:
+// a quarter warp reads eight different 16-byte chunks of the 128-byte bank cycle).
+__device__ __forceinline__ void warp_tile_from_smem(WarpTile& t, uint32_t k_s, uint32_t v_s, int g, int c) {
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb) {
+    const int row = 8 * nb + g;
+    t.kr[nb][0] = lds128(k_s + sw128_offset(row, 2 * c));
+    t.kr[nb][1] = lds128(k_s + sw128_offset(row, 2 * c + 1));
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = 16 * j + 2 * c + (r & 1) + 8 * (r >> 1);
+      t.vr[j][r] = lds128(v_s + sw128_offset(row, g));
+    }
+  }
+}
+
+__global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
+    attn_decode_stream_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                              const AttnArgs a, int s_max, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStreamStages];   // a stage's two tiles landed
+  __shared__ __align__(8) uint64_t bar_empty[kStreamStages];  // its consumer warp holds them in registers
+  __shared__ float m_s[kStreamWarps][kGroupHeads];
+  __shared__ float l_s[kStreamWarps][kGroupHeads];
+  __shared__ __align__(16) float o_s[kStreamWarps][kGroupHeads][kHeadDim];
+  __shared__ int fail_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  if (tid == 0) {
+    for (int s = 0; s < kStreamStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    fail_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_trigger_early();
+  pdl_wait();  // the row appended by the preceding kernel and the positions are complete
+
+  int slot = b, t_begin = 0, t_end = a.s_cap;
+  if (a.pos != nullptr) {
+    slot = a.rows[b];
+    t_end = __ldcg(a.pos + slot) + 1;
+  } else {
+    if (a.start != nullptr) t_begin = a.start[b];
+    if (a.end != nullptr) t_end = a.end[b];
+  }
+  if (t_end > a.s_cap) t_end = a.s_cap;
+  if (t_begin < 0) t_begin = 0;
+  const int tile0 = t_begin / kWarpChunk;
+  const int n_tiles = t_end > t_begin ? (t_end + kWarpChunk - 1) / kWarpChunk - tile0 : 0;
+  const int row0 = (slot * kKvHeads + kvh) * s_max;  // first cache row of this (slot, KV head)
+
+  float m = -INFINITY, l = 0.f, o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  if (warp == kStreamWarps) {
+    // ---------------- producer: one thread keeps the ring full ----------------
+    if (lane == 0) {
+      for (int i = 0; i < n_tiles; ++i) {
+        const int s = i % kStreamStages;
+        if (i >= kStreamStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStreamStages) - 1) & 1)) {
+          fail_s = 1;
+          break;
+        }
+        const uint32_t full = smem_u32(&bar_full[s]), dst = base + s * kStageBytes;
+        const int row = row0 + (tile0 + i) * kWarpChunk;  // rows past the end of the cache read as zero
+        mbar_expect_tx(full, kStageBytes);
+        tma_load_2d(dst, &tm_k, 0, row, full);
+        tma_load_2d(dst + kTileBytes, &tm_v, 0, row, full);
+      }
+    }
+  } else if (n_tiles > 0) {
+    // ---------------- warps 0..3: tile i belongs to warp i % 4 ----------------
+    uint32_t qa0[4], qa2[4];
+    warp_q_fragments(qa0, qa2, a.q + ((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim, g, c);
+    for (int i = warp; i < n_tiles; i += kStreamWarps) {
+      const int s = i % kStreamStages;
+      bool ok = mbar_wait(smem_u32(&bar_full[s]), (i / kStreamStages) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) fail_s = 2;
+        break;
+      }
+      WarpTile tile;
+      warp_tile_from_smem(tile, base + s * kStageBytes, base + s * kStageBytes + kTileBytes, g, c);
+      __syncwarp();
+      if (lane == 0) mbar_arrive_local(smem_u32(&bar_empty[s]));  // the stage may be refilled
+      const int t0 = (tile0 + i) * kWarpChunk;
+      float m1, l1, o1[8][4];
+      warp_tile_attend(tile, qa0, qa2, t0, max(t_begin, t0), min(t_end, t0 + kWarpChunk), a.scale, c, m1, l1, o1);
+      // running softmax over this warp's tiles (m, l are equal in the four lanes of a head)
+      const float mx = fmaxf(m, m1);
+      if (mx != -INFINITY) {
+        const float e0 = (m == -INFINITY) ? 0.f : __expf(m - mx);
+        const float e1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mx);
+        l = e0 * l + e1 * l1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j][0] = e0 * o[j][0] + e1 * o1[j][0];
+          o[j][1] = e0 * o[j][1] + e1 * o1[j][1];
+        }
+        m = mx;
+      }
+    }
+  }
+  if (warp < kStreamWarps && g < kGroupHeads) {
+    // C columns 2c, 2c+1 of mma j are dims 16c + j and 16c + 8 + j of head g
+    float4* op = reinterpret_cast<float4*>(&o_s[warp][g][16 * c]);
+    op[0] = make_float4(o[0][0], o[1][0], o[2][0], o[3][0]);
+    op[1] = make_float4(o[4][0], o[5][0], o[6][0], o[7][0]);
+    op[2] = make_float4(o[0][1], o[1][1], o[2][1], o[3][1]);
+    op[3] = make_float4(o[4][1], o[5][1], o[6][1], o[7][1]);
+    if (c == 0) {
+      m_s[warp][g] = m;
+      l_s[warp][g] = l;
+    }
+  }
+  __syncthreads();
+  if (fail_s != 0) {  // a bounded wait gave up: say so, leave the row's output as it is
+    if (tid == 0) atomicCAS(status, 0, ((4 + fail_s) << 16) | 0x4000 | ((int)blockIdx.y & 0x3fff));
+    return;
+  }
+  // the four warps' results -> the row's heads; thread -> (head, pair of dims), 224 of them
+  for (int idx = tid; idx < kGroupHeads * 32; idx += (kStreamWarps + 1) * 32) {
+    const int h = idx >> 5, d2 = idx & 31;
+    float mx = -INFINITY, den = 0.f;
+    float2 num = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < kStreamWarps; ++w) mx = fmaxf(mx, m_s[w][h]);
+    if (mx != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kStreamWarps; ++w) {
+        const float e = (m_s[w][h] == -INFINITY) ? 0.f : __expf(m_s[w][h] - mx);
+        const float2 v = *reinterpret_cast<const float2*>(&o_s[w][h][2 * d2]);
+        den = fmaf(e, l_s[w][h], den);
+        num.x = fmaf(e, v.x, num.x);
+        num.y = fmaf(e, v.y, num.y);
+      }
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    *reinterpret_cast<half2*>(a.out + ((size_t)b * kHeads + kvh * kGroupHeads + h) * kHeadDim + 2 * d2) =
+        __floats2half2_rn(num.x * inv, num.y * inv);
+  }
+}
+
+}  // namespace
+
+// The cache planes must be the decode step's: [n_slots][2][s_max][64] fp16, 16-byte aligned.
+// a.s_cap bounds the tokens of a row; `status`: error word of the bounded waits.
+int launch_attn_stream(const AttnArgs& a, int batch, int n_slots, int s_max, int* status, cudaStream_t stream,
+                       bool pdl) {
+  QUIC_REQUIRE(a.stride_h == (int64_t)s_max * kHeadDim && a.stride_b == (int64_t)kKvHeads * s_max * kHeadDim,
+               QUIC_E_ARG, "attn_decode_stream: the cache must be [slots][2][s_max][64]");
+  QUIC_REQUIRE(status != nullptr && batch >= 1 && batch <= 65535 && n_slots >= 1, QUIC_E_ARG,
+               "attn_decode_stream: bad batch, slots or status word");
+  CUtensorMap tm_k, tm_v;
+  const uint64_t rows = (uint64_t)n_slots * kKvHeads * s_max;
+  int rc = make_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.k, rows, kHeadDim, kWarpChunk, kHeadDim,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != QUIC_OK) return rc;
+  rc = make_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.v, rows, kHeadDim, kWarpChunk, kHeadDim,
+                CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != QUIC_OK) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    QUIC_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)kStreamSmem));
+    attr_set = true;
+  }
+  QUIC_CUDA(launch(attn_decode_stream_kernel, dim3(kKvHeads, batch), dim3((kStreamWarps + 1) * 32), kStreamSmem, stream,
+                   pdl, tm_k, tm_v, a, s_max, status));
+  return QUIC_OK;
+}
+
+}  // namespace quic

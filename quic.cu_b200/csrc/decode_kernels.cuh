@@ -105,6 +105,8 @@ struct AttnArgs {
 constexpr int kAttnCtaMaxSplits = 8;
 int attn_cta_splits(int ctx);
 cudaError_t launch_attn_cta(const AttnArgs& a, int batch, cudaStream_t stream, bool pdl);
+// Many rows: one CTA per (row, KV head) streaming the cache through a TMA ring (attn_decode_stream.cu).
+int launch_attn_stream(const AttnArgs& a, int batch, int n_slots, int s_max, int* status, cudaStream_t stream, bool pdl);
 
 struct LmHeadArgs {
   const half* embed;  // [vocab][896]

@@ -378,6 +378,11 @@ int enqueue_step_rows16(const quic_model_t* m, const quic_decode_t* d, cudaStrea
 // Batch > 16: every linear is the tcgen05 GEMM; norms, RoPE/KV append and SwiGLU are
 // separate small kernels (at these sizes each kernel does microseconds of real work, so
 // the launch chain is no longer what bounds the step).
+// Up to 20 rows the cluster kernel, whose tiles are requested before the dependency wait (17 rows of
+// 200..1500 tokens: 791 us per step against 865 streamed; 24 rows: 963 against 872).
+constexpr int kCtaAttnMaxRows = 20;
+constexpr int kStreamMaxCtx = 2048;  // beyond: the split kernel (a row of 2048 tokens is 8 rounds of the four warps)
+
 int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int ctx, half* qbuf, half* kc, half* vc,
                       half* attn_out, cudaStream_t st);
 
@@ -469,14 +474,20 @@ int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int c
   aa.use_mma = 1;
   aa.consumer_merge = 0;
   aa.epoch = d->step_counter;
-  // (measured at 512 tokens: 9 and 7 % off the step at 17 and 32 rows, 3 % slower at 64, where its
-  // 128 CTAs of 512 tokens each leave less room per SM than 1024 single-warp CTAs)
-  if (attn_cta_splits(ctx) <= kAttnCtaMaxSplits && B <= 32) {
+  // few rows: CTAs of 512 tokens, clusters beyond, no scratch
+  if (attn_cta_splits(ctx) <= kAttnCtaMaxSplits && B <= kCtaAttnMaxRows) {
     aa.splits = attn_cta_splits(ctx);
     aa.chunk = 512;
     aa.prefetch = d->step_counter != nullptr ? 1 : 0;
     QUIC_CUDA(launch_attn_cta(aa, B, st, true));
     return QUIC_OK;
+  }
+  if (ctx <= kStreamMaxCtx) {
+    // more rows: one CTA per (row, KV head) streams the row's cache through a TMA ring
+    // (64 rows of 200..1500 tokens: 1266 -> 1022 us per step; 64 rows of 512: 1050 -> 932)
+    aa.splits = 1;
+    aa.chunk = ctx;
+    return launch_attn_stream(aa, B, d->n_slots, d->s_max, tc_status_words(), st, true);
   }
   aa.splits = splits;
   aa.chunk = (ctx + splits - 1) / splits;
