@@ -1,6 +1,6 @@
-// GQA decode attention for many rows (the tensor-core step beyond 32 rows): ONE CTA per
+// GQA decode attention for many rows (the tensor-core step beyond 20 rows): ONE CTA per
 // (row, KV head) streams that head's cached keys and values through a ring of shared-memory
-// stages filled by TMA (64-token tiles, 128-byte swizzle), four warps take the tiles in turn
+// stages filled by TMA (64-token tiles, 128-byte swizzle), six warps take the tiles in turn
 // -- the 64-token tile arithmetic of attn_warp.cuh on mma.sync, each warp keeping a running
 // softmax over its tiles -- and meet once in shared memory.  No partial results in global
 // memory, no counters, no second pass, and nothing is read beyond a row's own length.
@@ -8,8 +8,10 @@
 // Why: with one-warp CTAs (attn_decode_warp_kernel) every warp requests its 16 KB tile with 32
 // loads per lane and then waits for it; at 64 rows of 200..1500 tokens that form reads 1.8 x
 // the algorithmic bytes (tiles beyond a row's length are fetched too), reaches a quarter of the
-// HBM bandwidth and takes 25 us per layer.  Here a single thread keeps kStages x 16 KB of bulk
-// copies in flight per SM and the copies cost the warps no instructions.
+// HBM bandwidth and takes 25 us per layer (12 us here).  Here a single thread keeps kStreamStages x
+// 16 KB of bulk copies in flight per SM and the copies cost the warps no instructions.  Measured
+// per 64-row step of 200..1500 tokens: 1266 us with one-warp CTAs, 1022 with four warps and eight
+// stages.
 //
 // Same mathematics as fad_decode_kernel + fad_combine_kernel of the reference
 // (kernels/cuda/flash_attn_decode.cu:12,104): fp32 softmax over the tokens [start_b, end_b) of
@@ -22,8 +24,14 @@ namespace quic {
 namespace {
 
 constexpr int kGroupHeads = kHeads / kKvHeads;  // 7
-constexpr int kStreamWarps = 4;                  // compute warps; warp 4 is the producer
-constexpr int kStreamStages = 8;                 // ring depth (a multiple of kStreamWarps)
+constexpr int kStreamWarps = 6;                  // compute warps; the next warp is the producer
+constexpr int kStreamStages = 12;                // ring depth: 192 KB of copies in flight per SM
+// Tile i lives in stage i % kStreamStages and belongs to warp i % kStreamWarps.  The depth must be
+// a multiple of the warp count: then every stage is always consumed by the same warp, in order,
+// and a parity wait can never be answered by the phase of two uses earlier.  (With 8 warps and 12
+// stages, stage 0 holds tiles 0, 12, 24 of warps 0, 4, 0: warp 0 could find the parity of tile 24
+// already 'complete' -- it is tile 0's -- while tile 12 was still being consumed.)
+static_assert(kStreamStages % kStreamWarps == 0, "every stage must belong to one warp");
 constexpr uint32_t kTileBytes = kWarpChunk * kHeadDim * 2;  // 8 KB: 64 tokens x 128 bytes
 constexpr uint32_t kStageBytes = 2 * kTileBytes;            // K tile, V tile
 constexpr size_t kStreamSmem = (size_t)kStreamStages * kStageBytes + 1024;
@@ -118,7 +126,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
       }
     }
   } else if (n_tiles > 0) {
-    // ---------------- warps 0..3: tile i belongs to warp i % 4 ----------------
+    // ---------------- compute warps: tile i belongs to warp i % kStreamWarps ----------------
     uint32_t qa0[4], qa2[4];
     warp_q_fragments(qa0, qa2, a.q + ((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim, g, c);
     for (int i = warp; i < n_tiles; i += kStreamWarps) {
@@ -168,7 +176,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
     if (tid == 0) atomicCAS(status, 0, ((4 + fail_s) << 16) | 0x4000 | ((int)blockIdx.y & 0x3fff));
     return;
   }
-  // the four warps' results -> the row's heads; thread -> (head, pair of dims), 224 of them
+  // the warps' results -> the row's heads; thread -> (head, pair of dims), 224 of them
   for (int idx = tid; idx < kGroupHeads * 32; idx += (kStreamWarps + 1) * 32) {
     const int h = idx >> 5, d2 = idx & 31;
     float mx = -INFINITY, den = 0.f;

@@ -243,6 +243,40 @@ def test_single_row_long_context_matches_the_batched_step(tiny_model):
         nxt = logits.argmax(dim=-1, keepdim=True)
 
 
+def test_many_ragged_rows_streamed_attention_matches_the_small_batch_chain(tiny_model):
+    """24 rows of 5..1900 tokens in one tensor-core step: from 21 rows on, up to 2048 tokens of
+    context, a CTA per (row, KV head) streams the row's cache through an eight-stage ring (rows
+    beyond 512 tokens wrap it, the longest four times) and four warps keep running softmaxes.
+    The same rows as two batches of 12 run the mma.sync chain with the cluster attention; fed the
+    same tokens, the logits of the two must agree."""
+    net, _, _, _ = tiny_model
+    gen = torch.Generator().manual_seed(79)
+    lens = [5, 63, 64, 65, 127, 128, 129, 300, 511, 512, 513, 700, 1023, 1024, 1025, 1300, 1536, 1700, 1900, 1, 2,
+            450, 900, 33]
+    prompts = [torch.randint(0, 2048, (n,), generator=gen) for n in lens]
+    steps = 3
+
+    halves = net.new_cache(n_slots=24, s_max=2048)
+    firsts, _ = net.prefill(halves, list(range(24)), prompts)
+    fed, chain = [firsts.view(24, 1).clone()], []
+    for _ in range(steps):
+        rows = []
+        for lo in (0, 12):
+            halves.batch_slots = list(range(lo, lo + 12))
+            rows.append(net(fed[-1][lo:lo + 12], past_key_values=halves).logits[:, 0].clone())
+        chain.append(torch.cat(rows))
+        fed.append(chain[-1].argmax(dim=-1, keepdim=True))
+
+    whole = net.new_cache(n_slots=24, s_max=2048)
+    firsts24, _ = net.prefill(whole, list(range(24)), prompts)
+    assert firsts24.tolist() == firsts.tolist()
+    whole.batch_slots = list(range(24))
+    for i in range(steps):
+        logits = net(fed[i], past_key_values=whole).logits[:, 0]
+        ok, err = _close(logits, chain[i])
+        assert ok, (i, err)
+
+
 def test_three_ragged_rows_long_context_match_the_batched_step(tiny_model):
     """Three rows of 4300 / 40 / 2500 tokens on the GEMV chain (3-row kernels, throughput
     attention kernel, splits without tokens for the short rows, o_proj merging 64 splits)

@@ -171,7 +171,7 @@ def test_a_gemm_wait_that_runs_out_is_reported_and_the_next_call_works(tiny_mode
     assert lib.quic_w4a16_tensor_status() == 0
 
 
-@pytest.mark.parametrize("rows", [1, 3, 8, 16, 20])
+@pytest.mark.parametrize("rows", [1, 3, 8, 16, 20, 40])
 def test_decode_gives_the_same_bits_every_run(tiny_model, rows):
     """Cross-CTA hand-offs (arrival counters, cluster merges, split-K planes) must not make the
     result depend on timing: the same prompts decoded from scratch five times leave bit-identical
