@@ -571,7 +571,7 @@ def measure_batch64(net, device, world, dist):
     peak, kind = peaks()
     step_bytes = net.weight_bytes() + B * 12288 * (ctx + steps / 2 + 1)
     return {"value": world * B / (us_step * 1e-6), "unit": UNIT, "batch": B, "context": ctx, "us_per_step": us_step,
-            "kernels": "tcgen05 W4A16 GEMM + tcgen05 lm_head/argmax + split-K attention",
+            "kernels": "tcgen05 W4A16 GEMM + tcgen05 lm_head/argmax + attention streamed through a TMA ring",
             "hbm_frac": step_bytes / (us_step * 1e-6) / 1e9 / peak, "peak_kind": f"of {kind}",
             "algorithmic_bytes_per_step": step_bytes}
 

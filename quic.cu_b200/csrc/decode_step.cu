@@ -381,7 +381,11 @@ int enqueue_step_rows16(const quic_model_t* m, const quic_decode_t* d, cudaStrea
 // Up to 20 rows the cluster kernel, whose tiles are requested before the dependency wait (17 rows of
 // 200..1500 tokens: 791 us per step against 865 streamed; 24 rows: 963 against 872).
 constexpr int kCtaAttnMaxRows = 20;
-constexpr int kStreamMaxCtx = 2048;  // beyond: the split kernel (a row of 2048 tokens is 8 rounds of the four warps)
+// One CTA per (row, KV head) is a serial walk over the row: with few rows and very long rows the
+// split kernel, which spreads a row over many CTAs, wins (us per step, streamed / split: 24 rows of
+// 4000..8000 tokens 1430 / 1555, of 8000..16000 2157 / 1822; 64 rows of 16000..32000 4079 / 4598).
+constexpr int kStreamMaxCtx = 8192;
+constexpr int kStreamAnyCtxRows = 48;
 
 int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int ctx, half* qbuf, half* kc, half* vc,
                       half* attn_out, cudaStream_t st);
@@ -482,9 +486,9 @@ int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int c
     QUIC_CUDA(launch_attn_cta(aa, B, st, true));
     return QUIC_OK;
   }
-  if (ctx <= kStreamMaxCtx) {
+  if (B > kCtaAttnMaxRows && (ctx <= kStreamMaxCtx || B >= kStreamAnyCtxRows)) {
     // more rows: one CTA per (row, KV head) streams the row's cache through a TMA ring
-    // (64 rows of 200..1500 tokens: 1266 -> 1022 us per step; 64 rows of 512: 1050 -> 932)
+    // (64 rows of 200..1500 tokens: 1266 -> 1015 us per step; of 512: 1050 -> 924; of 2000..4000: 1622 -> 1307)
     aa.splits = 1;
     aa.chunk = ctx;
     return launch_attn_stream(aa, B, d->n_slots, d->s_max, tc_status_words(), st, true);

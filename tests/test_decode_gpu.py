@@ -277,6 +277,34 @@ def test_many_ragged_rows_streamed_attention_matches_the_small_batch_chain(tiny_
         assert ok, (i, err)
 
 
+def test_many_rows_beyond_2048_tokens_streamed_attention_matches_the_split_kernel(tiny_model):
+    """22 rows, one of 4300 tokens: the streamed attention walks 68 tiles of that row through its
+    twelve-stage ring.  The same rows as two batches of 11 run the mma.sync chain, whose attention
+    beyond 4096 tokens is the split kernel; fed the same tokens, the logits must agree."""
+    net, _, _, _ = tiny_model
+    gen = torch.Generator().manual_seed(80)
+    lens = [4300, 2049, 2048, 3000] + [17 * (i + 1) for i in range(18)]
+    prompts = [torch.randint(0, 2048, (n,), generator=gen) for n in lens]
+    halves = net.new_cache(n_slots=22, s_max=4608)
+    firsts, _ = net.prefill(halves, list(range(22)), prompts)
+    fed, chain = [firsts.view(22, 1).clone()], []
+    for _ in range(2):
+        rows = []
+        for lo in (0, 11):
+            halves.batch_slots = list(range(lo, lo + 11))
+            rows.append(net(fed[-1][lo:lo + 11], past_key_values=halves).logits[:, 0].clone())
+        chain.append(torch.cat(rows))
+        fed.append(chain[-1].argmax(dim=-1, keepdim=True))
+    whole = net.new_cache(n_slots=22, s_max=4608)
+    firsts22, _ = net.prefill(whole, list(range(22)), prompts)
+    assert firsts22.tolist() == firsts.tolist()
+    whole.batch_slots = list(range(22))
+    for i in range(2):
+        logits = net(fed[i], past_key_values=whole).logits[:, 0]
+        ok, err = _close(logits, chain[i])
+        assert ok, (i, err)
+
+
 def test_three_ragged_rows_long_context_match_the_batched_step(tiny_model):
     """Three rows of 4300 / 40 / 2500 tokens on the GEMV chain (3-row kernels, throughput
     attention kernel, splits without tokens for the short rows, o_proj merging 64 splits)
