@@ -710,7 +710,7 @@ def measure_serving(net, device, n_requests, world, dist, rank):
     n_chunks = len(chunks_of(reqs, chunk))
     store = group_store(dist) if dist is not None else tdist.HashStore()
     module = SimpleNamespace(load=lambda **options: (net, None))
-    engine = Engine(config=EngineConfig(batching="continuous", max_context=2048, decode_burst=8,
+    engine = Engine(config=EngineConfig(batching="continuous", max_context=2048, decode_burst=16,
                                         prefill_backend="quic"),
                     max_batch_size=64, model_module=module)
     # First pass: the engine captures one CUDA graph per (rows, context bound, burst) it meets
@@ -746,7 +746,7 @@ def measure_serving(net, device, n_requests, world, dist, rank):
                      "the queue size is fixed as N grows (strong scaling)",
             "note": "value: second pass over the same queue on the same engine (decode graphs captured); "
                     "first_pass_*: fresh engine, captures included",
-            "slots_per_gpu": 64, "replicas": world}
+            "slots_per_gpu": 64, "decode_burst": 16, "replicas": world}
 
 
 def main() -> None:
