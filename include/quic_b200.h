@@ -125,6 +125,12 @@ int quic_w4a16_tensor_status(void);
  * with (0, -1) to restore normal operation. */
 void quic_w4a16_tensor_test_hook(uint32_t spin_limit, int32_t skip_kblock);
 
+/* Test hook for the streamed decode attention (more than 20 rows): launches and graph captures
+ * that follow repeat the tile requests made before the dependency wait, as the kernel does when
+ * the step counter moved between request and wait.  0 restores the normal behaviour.  No
+ * reference counterpart. */
+void quic_attn_stream_test_hook(int32_t force_reload);
+
 /* ------------------------------------------------------------------------
  * Stand-alone operators with the reference's per-op signatures.
  * ---------------------------------------------------------------------- */

@@ -13,6 +13,14 @@
 // per 64-row step of 200..1500 tokens: 1266 us with one-warp CTAs, 1022 with four warps and eight
 // stages.
 //
+// Inside the decode chain (a.prefetch) the producer requests, BEFORE the dependency wait, the
+// tiles that hold only tokens of earlier steps (up to the ring's depth): those rows are complete
+// once the step counter shows the current step.  The counter is read (acquire) before the
+// requests and again after the wait; if it moved, the previous step was still finishing when
+// the tiles were requested, and they are requested again (a second phase of the same stages'
+// barriers, which their consumers then wait for).  The tile of the row that the preceding
+// kernel appends is never requested early.
+//
 // Same mathematics as fad_decode_kernel + fad_combine_kernel of the reference
 // (kernels/cuda/flash_attn_decode.cu:12,104): fp32 softmax over the tokens [start_b, end_b) of
 // each row, rows without tokens give zeros (:118-121).
@@ -66,14 +74,14 @@ __device__ __forceinline__ void warp_tile_from_smem(WarpTile& t, uint32_t k_s, u
 
 __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
     attn_decode_stream_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                              const AttnArgs a, int s_max, int* status) {
+                              const AttnArgs a, int s_max, int* status, int force_reload) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStreamStages];   // a stage's two tiles landed
   __shared__ __align__(8) uint64_t bar_empty[kStreamStages];  // its consumer warp holds them in registers
   __shared__ float m_s[kStreamWarps][kGroupHeads];
   __shared__ float l_s[kStreamWarps][kGroupHeads];
   __shared__ __align__(16) float o_s[kStreamWarps][kGroupHeads][kHeadDim];
-  __shared__ int fail_s;
+  __shared__ int fail_s, pre_s, epoch_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -85,11 +93,31 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     fail_s = 0;
+    pre_s = 0;
+    epoch_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
   pdl_trigger_early();
+  if (warp == kStreamWarps && lane == 0 && a.prefetch != 0 && a.epoch != nullptr && a.pos != nullptr) {
+    const int e0 = ld_acquire_s32(a.epoch);
+    const int slot0 = a.rows[b];  // (the row -> slot map is not written inside the chain)
+    const int p0 = min(__ldcg(a.pos + slot0), a.s_cap);  // tokens below p0 were appended by earlier steps
+    const int pre = min(p0 > 0 ? p0 / kWarpChunk : 0, kStreamStages);
+    const int row0p = (slot0 * kKvHeads + kvh) * s_max;
+    for (int i = 0; i < pre; ++i) {
+      const uint32_t full = smem_u32(&bar_full[i]), dst = base + i * kStageBytes;
+      mbar_expect_tx(full, kStageBytes);
+      tma_load_2d(dst, &tm_k, 0, row0p + i * kWarpChunk, full);
+      tma_load_2d(dst + kTileBytes, &tm_v, 0, row0p + i * kWarpChunk, full);
+    }
+    pre_s = pre;
+    epoch_s = e0;
+  }
   pdl_wait();  // the row appended by the preceding kernel and the positions are complete
+  __syncthreads();
+  const int pre = pre_s;  // tiles requested before the wait (they start at token 0: positions mode)
+  const bool stale = pre > 0 && (__ldcg(a.epoch) != epoch_s || force_reload != 0);
 
   int slot = b, t_begin = 0, t_end = a.s_cap;
   if (a.pos != nullptr) {
@@ -112,7 +140,19 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
   if (warp == kStreamWarps) {
     // ---------------- producer: one thread keeps the ring full ----------------
     if (lane == 0) {
-      for (int i = 0; i < n_tiles; ++i) {
+      if (stale) {  // wait for the early copies to land, then fetch the same tiles again
+        for (int i = 0; i < pre; ++i) {
+          const uint32_t full = smem_u32(&bar_full[i]), dst = base + i * kStageBytes;
+          if (!mbar_wait(full, 0)) {
+            fail_s = 1;
+            break;
+          }
+          mbar_expect_tx(full, kStageBytes);
+          tma_load_2d(dst, &tm_k, 0, row0 + i * kWarpChunk, full);
+          tma_load_2d(dst + kTileBytes, &tm_v, 0, row0 + i * kWarpChunk, full);
+        }
+      }
+      for (int i = pre; i < n_tiles && fail_s == 0; ++i) {
         const int s = i % kStreamStages;
         if (i >= kStreamStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStreamStages) - 1) & 1)) {
           fail_s = 1;
@@ -131,7 +171,9 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
     warp_q_fragments(qa0, qa2, a.q + ((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim, g, c);
     for (int i = warp; i < n_tiles; i += kStreamWarps) {
       const int s = i % kStreamStages;
-      bool ok = mbar_wait(smem_u32(&bar_full[s]), (i / kStreamStages) & 1);
+      // (a stage whose early copy was repeated is one phase ahead for the rest of the kernel)
+      const int shift = (stale && s < pre) ? 1 : 0;
+      bool ok = mbar_wait(smem_u32(&bar_full[s]), ((i / kStreamStages) + shift) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) fail_s = 2;
@@ -203,6 +245,8 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
 
 // The cache planes must be the decode step's: [n_slots][2][s_max][64] fp16, 16-byte aligned.
 // a.s_cap bounds the tokens of a row; `status`: error word of the bounded waits.
+int g_stream_force_reload = 0;
+
 int launch_attn_stream(const AttnArgs& a, int batch, int n_slots, int s_max, int* status, cudaStream_t stream,
                        bool pdl) {
   QUIC_REQUIRE(a.stride_h == (int64_t)s_max * kHeadDim && a.stride_b == (int64_t)kKvHeads * s_max * kHeadDim,
@@ -224,8 +268,13 @@ int launch_attn_stream(const AttnArgs& a, int batch, int n_slots, int s_max, int
     attr_set = true;
   }
   QUIC_CUDA(launch(attn_decode_stream_kernel, dim3(kKvHeads, batch), dim3((kStreamWarps + 1) * 32), kStreamSmem, stream,
-                   pdl, tm_k, tm_v, a, s_max, status));
+                   pdl, tm_k, tm_v, a, s_max, status, g_stream_force_reload));
   return QUIC_OK;
 }
 
 }  // namespace quic
+
+// Test hook: the streamed decode attention of the launches (and graph captures) that follow treats
+// its early tile requests as made too early and repeats them, as it does when the step counter
+// moved between the request and the dependency wait.  0 restores the normal behaviour.
+extern "C" void quic_attn_stream_test_hook(int32_t force_reload) { quic::g_stream_force_reload = force_reload != 0; }

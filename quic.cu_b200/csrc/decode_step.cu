@@ -491,6 +491,7 @@ int enqueue_attention(const quic_decode_t* d, const Arena& ar, int splits, int c
     // (64 rows of 200..1500 tokens: 1266 -> 1015 us per step; of 512: 1050 -> 924; of 2000..4000: 1622 -> 1307)
     aa.splits = 1;
     aa.chunk = ctx;
+    aa.prefetch = d->step_counter != nullptr ? 1 : 0;
     return launch_attn_stream(aa, B, d->n_slots, d->s_max, tc_status_words(), st, true);
   }
   aa.splits = splits;

@@ -130,6 +130,7 @@ SIGNATURES = {
     "quic_w4a16_workspace_bytes": (_I64, [_I32, _I32, _I32]),
     "quic_w4a16_tensor_status": (C.c_int, []),
     "quic_w4a16_tensor_test_hook": (None, [C.c_uint32, _I32]),
+    "quic_attn_stream_test_hook": (None, [_I32]),
     "quic_rmsnorm": (C.c_int, [_P, _P, _P, _F, _P, _P, _I32, _P]),
     "quic_rope_table_init": (C.c_int, [_P, _I32, _P, _P, _P]),
     "quic_rope": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P]),

@@ -243,12 +243,16 @@ def test_single_row_long_context_matches_the_batched_step(tiny_model):
         nxt = logits.argmax(dim=-1, keepdim=True)
 
 
-def test_many_ragged_rows_streamed_attention_matches_the_small_batch_chain(tiny_model):
+@pytest.mark.parametrize("repeat_early_requests", [False, True])
+def test_many_ragged_rows_streamed_attention_matches_the_small_batch_chain(tiny_model, repeat_early_requests):
     """24 rows of 5..1900 tokens in one tensor-core step: from 21 rows on, up to 2048 tokens of
     context, a CTA per (row, KV head) streams the row's cache through an eight-stage ring (rows
     beyond 512 tokens wrap it, the longest four times) and four warps keep running softmaxes.
     The same rows as two batches of 12 run the mma.sync chain with the cluster attention; fed the
-    same tokens, the logits of the two must agree."""
+    same tokens, the logits of the two must agree.  Second form: the kernel repeats the tile requests
+    it made before the dependency wait (its path for a step counter that moved meanwhile)."""
+    from quic_cu_b200 import kernels as K
+
     net, _, _, _ = tiny_model
     gen = torch.Generator().manual_seed(79)
     lens = [5, 63, 64, 65, 127, 128, 129, 300, 511, 512, 513, 700, 1023, 1024, 1025, 1300, 1536, 1700, 1900, 1, 2,
@@ -271,10 +275,16 @@ def test_many_ragged_rows_streamed_attention_matches_the_small_batch_chain(tiny_
     firsts24, _ = net.prefill(whole, list(range(24)), prompts)
     assert firsts24.tolist() == firsts.tolist()
     whole.batch_slots = list(range(24))
-    for i in range(steps):
-        logits = net(fed[i], past_key_values=whole).logits[:, 0]
-        ok, err = _close(logits, chain[i])
-        assert ok, (i, err)
+    K.lib().quic_attn_stream_test_hook(int(repeat_early_requests))
+    try:
+        for i in range(steps):
+            logits = net(fed[i], past_key_values=whole).logits[:, 0]
+            ok, err = _close(logits, chain[i])
+            assert ok, (i, err)
+        torch.cuda.synchronize()
+    finally:
+        K.lib().quic_attn_stream_test_hook(0)
+    assert K.lib().quic_w4a16_tensor_status() == 0
 
 
 def test_many_rows_beyond_2048_tokens_streamed_attention_matches_the_split_kernel(tiny_model):
