@@ -369,7 +369,7 @@ int64_t quic_prefill_scratch_bytes(int32_t rows, int32_t n_seq, int32_t vocab);
 int quic_prefill(const quic_model_t *m, const quic_prefill_t *p, void *stream);
 
 /* Which of the three forms of the decode step a batch takes.  Batches of at
- * least quic_set_tensor_min_batch rows (default 17, range 2..17) run every
+ * least quic_set_tensor_min_batch rows (default 16, range 2..17) run every
  * linear on the tcgen05 GEMM and the tensor lm_head; below that, batches of at
  * least quic_set_mma_chain_min_batch rows (default 3, range 2..17) run the
  * five-kernel layer chain with the rows on the M side of mma.sync, whose cost

@@ -124,7 +124,8 @@ int enqueue_step_rows16(const quic_model_t* m, const quic_decode_t* d, cudaStrea
 // and smallest batch that takes the mma.sync chain (quic_set_mma_chain_min_batch): 2..17.
 // Below both, the rows run the GEMV chain (FMA; its cost grows with every row, measured 352,
 // 491 and 683 us per step at 1, 2 and 3 rows against 565 and 580 us of the mma.sync chain).
-int g_tensor_min_batch = kMmaChainMaxRows + 1;
+// (the tensor-core step, 731..759 us at 6..16 rows of 512 tokens, meets the mma.sync chain, 642..776, at 16 rows)
+int g_tensor_min_batch = kMmaChainMaxRows;
 int g_mma_chain_min_batch = 3;
 
 int enqueue_step_f16(const quic_model_t* m, const quic_decode_t* d, cudaStream_t st, bool chain_head);
