@@ -66,6 +66,7 @@ class SlotCache:
         self._row_bufs: dict[int, torch.Tensor] = {}    # per batch size: the buffer captured graphs read
         self._scratch: dict[tuple, torch.Tensor] = {}
         self._graphs: dict[tuple, int] = {}
+        self.max_graphs = 512                      # captured graphs kept; beyond that all are dropped and rebuilt
         self._plans: dict[tuple, tuple] = {}       # decode(): per (rows, steps) launch plan
         self._rows_loaded: dict[int, torch.Tensor] = {}  # row->slot map now on the device, per batch size
         self.host_steps = 0                        # host mirror of step_counter
@@ -120,9 +121,13 @@ class SlotCache:
         return t
 
     def release_graphs(self) -> None:
+        """Destroys every captured graph with what only graphs refer to (launch plans, scratch
+        arenas).  The caller makes sure that none of them is still running."""
         for g in self._graphs.values():
             K.lib().quic_graph_destroy(g)
         self._graphs.clear()
+        self._plans.clear()
+        self._scratch.clear()
 
     def __del__(self):
         try:
@@ -301,10 +306,17 @@ class QUICForCausalLM:
     def _graph(self, cache: SlotCache, batch: int, ctx: int, steps: int, logits: torch.Tensor | None):
         key = (batch, ctx, steps, K.ptr(logits))
         g = cache._graphs.get(key)
+        if g is None and len(cache._graphs) >= cache.max_graphs:
+            # a long-lived engine with ragged batches meets ever new (rows, context bound, steps):
+            # start over rather than keep thousands of graphs and their scratch arenas
+            torch.cuda.synchronize(self.device)
+            cache.release_graphs()
         d, rows = self._decode_struct(cache, batch, ctx, logits)
         if g is None:
             if not hasattr(self, "_capture_stream"):
-                self._capture_stream = torch.cuda.Stream(device=self.device)
+                # kernel nodes keep the priority of the stream they were captured on: decode steps go
+                # ahead of a prefill that runs beside them on another stream
+                self._capture_stream = torch.cuda.Stream(device=self.device, priority=-1)
             out = C.c_void_p()
             K.check(K.lib().quic_decode_graph_create(C.byref(self._c_model), C.byref(d), steps,
                                                      self._capture_stream.cuda_stream, C.byref(out)),

@@ -105,6 +105,25 @@ def test_prefill_of_several_hundred_rows_matches_oracle(tiny_model):
         _assert_greedy_matches([int(first[i])], want[i][0], want[i][1])
 
 
+def test_the_graph_cache_is_bounded_and_rebuilds(tiny_model):
+    """A cache keeps at most ``max_graphs`` captured graphs; when another one is needed all are
+    destroyed (with their launch plans and scratch arenas) and decoding goes on, same tokens."""
+    net, _, _, _ = tiny_model
+    prompt = torch.tensor([5, 6, 7, 8, 9, 10, 11])
+    want_cache = net.new_cache(n_slots=2, s_max=128)
+    first, _ = net.prefill(want_cache, [0], [prompt])
+    want = [int(first[0])] + net.decode(want_cache, [0], 12)[0]
+
+    cache = net.new_cache(n_slots=2, s_max=128)
+    cache.max_graphs = 2
+    first, _ = net.prefill(cache, [0], [prompt])
+    got = [int(first[0])]
+    for steps in (1, 2, 3, 1, 2, 3):  # three graph shapes through two places, twice
+        got += net.decode(cache, [0], steps)[0]
+        assert len(cache._graphs) <= 2
+    assert got == want
+
+
 def test_bursts_single_steps_and_host_fed_steps_agree(tiny_model):
     """150 tokens three ways: graph bursts of 64 steps (the ring of generated tokens wraps),
     single-step calls, and single-step calls that feed the previous token back from pinned
