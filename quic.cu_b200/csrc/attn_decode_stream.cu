@@ -21,6 +21,14 @@
 // barriers, which their consumers then wait for).  The tile of the row that the preceding
 // kernel appends is never requested early.
 //
+// With `fin.part` set the CTA first finishes the fused QKV linear for its row and KV head, which a
+// separate kernel (qkv_post_kernel) would otherwise do between the GEMM and the attention: the
+// compute warps sum the split-K partial sums of their seven q heads, their k head and their v head,
+// add the bias with the GEMM epilogue's roundings, rotate q and k (rope.forward of the reference,
+// kernels/cuda/rope.cu), keep q in shared memory for the fragments, append k and v to the cache for
+// later steps, and the warp that owns the row's last tile writes the new k and v into that tile in
+// shared memory once TMA has landed it -- whatever TMA read at that position is overwritten.
+//
 // Same mathematics as fad_decode_kernel + fad_combine_kernel of the reference
 // (kernels/cuda/flash_attn_decode.cu:12,104): fp32 softmax over the tokens [start_b, end_b) of
 // each row, rows without tokens give zeros (:118-121).
@@ -74,7 +82,8 @@ __device__ __forceinline__ void warp_tile_from_smem(WarpTile& t, uint32_t k_s, u
 
 __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
     attn_decode_stream_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                              const AttnArgs a, int s_max, int* status, int force_reload) {
+                              const AttnArgs a, const QkvFinish fin, int n_slots, int s_max, int* status,
+                              int force_reload) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStreamStages];   // a stage's two tiles landed
   __shared__ __align__(8) uint64_t bar_empty[kStreamStages];  // its consumer warp holds them in registers
@@ -82,6 +91,8 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
   __shared__ float l_s[kStreamWarps][kGroupHeads];
   __shared__ __align__(16) float o_s[kStreamWarps][kGroupHeads][kHeadDim];
   __shared__ int fail_s, pre_s, epoch_s;
+  __shared__ __align__(16) half q_s[kGroupHeads][kHeadDim];  // finished q heads (fin.part set)
+  __shared__ __align__(16) half kn_s[kHeadDim], vn_s[kHeadDim];  // this step's k and v of the KV head
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -120,9 +131,11 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
   const bool stale = pre > 0 && (__ldcg(a.epoch) != epoch_s || force_reload != 0);
 
   int slot = b, t_begin = 0, t_end = a.s_cap;
+  int p_new = -1;  // position of this step's token (positions mode)
   if (a.pos != nullptr) {
     slot = a.rows[b];
-    t_end = __ldcg(a.pos + slot) + 1;
+    p_new = __ldcg(a.pos + slot);
+    t_end = p_new + 1;
   } else {
     if (a.start != nullptr) t_begin = a.start[b];
     if (a.end != nullptr) t_end = a.end[b];
@@ -136,6 +149,57 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
   float m = -INFINITY, l = 0.f, o[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  const bool finish = fin.part != nullptr;
+  if (finish && warp < kStreamWarps) {
+    // thread -> (head of the CTA: 7 q, k, v; rotation pair): stored columns (2 pair, 2 pair + 1) are dims (pair, pair + 32)
+    const bool slot_ok = slot >= 0 && slot < n_slots;
+    const int p = slot_ok ? p_new : 0;
+    const int pp = p < fin.max_pos ? (p < 0 ? 0 : p) : fin.max_pos - 1;
+    for (int idx = tid; idx < (kGroupHeads + 2) * 32; idx += kStreamWarps * 32) {
+      const int hl = idx >> 5, pair = idx & 31;
+      const int head = hl < kGroupHeads ? kvh * kGroupHeads + hl : (hl == kGroupHeads ? kHeads + kvh : kHeads + kKvHeads + kvh);
+      const int col = head * kHeadDim + 2 * pair;
+      float2 acc = make_float2(0.f, 0.f);
+      for (int s0 = 0; s0 < fin.splits; s0 += 8) {  // eight partial sums in flight
+        float2 ps[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          ps[j] = s0 + j < fin.splits
+                      ? __ldcg(reinterpret_cast<const float2*>(fin.part + ((size_t)(s0 + j) * gridDim.y + b) * kQkvN + col))
+                      : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc.x += ps[j].x;
+          acc.y += ps[j].y;
+        }
+      }
+      const float2 bb = __half22float2(*reinterpret_cast<const half2*>(fin.bias + col));
+      const float x = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.x)) + bb.x));
+      const float y = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.y)) + bb.y));
+      float lo = x, hi = y;
+      if (hl <= kGroupHeads) {  // q and k are rotated
+        const float cs = __half2float(fin.cos_t[(size_t)pp * 32 + pair]), sn = __half2float(fin.sin_t[(size_t)pp * 32 + pair]);
+        lo = x * cs - y * sn;
+        hi = x * sn + y * cs;
+      }
+      const half hlo = __float2half_rn(lo), hhi = __float2half_rn(hi);
+      if (hl < kGroupHeads) {
+        q_s[hl][pair] = hlo;
+        q_s[hl][pair + 32] = hhi;
+      } else {
+        half* mine = hl == kGroupHeads ? kn_s : vn_s;
+        mine[pair] = hlo;
+        mine[pair + 32] = hhi;
+        if (slot_ok && p >= 0 && p < s_max) {  // for the steps to come
+          half* dst = const_cast<half*>(hl == kGroupHeads ? a.k : a.v) + ((size_t)row0 + p) * kHeadDim;
+          dst[pair] = hlo;
+          dst[pair + 32] = hhi;
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kStreamWarps * 32) : "memory");  // the compute warps only
+  }
 
   if (warp == kStreamWarps) {
     // ---------------- producer: one thread keeps the ring full ----------------
@@ -168,7 +232,19 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
   } else if (n_tiles > 0) {
     // ---------------- compute warps: tile i belongs to warp i % kStreamWarps ----------------
     uint32_t qa0[4], qa2[4];
-    warp_q_fragments(qa0, qa2, a.q + ((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim, g, c);
+    if (finish) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        qa0[ks] = qa2[ks] = 0u;
+        if (g < kGroupHeads) {
+          const uint2 u = *reinterpret_cast<const uint2*>(&q_s[g][16 * c + 4 * ks]);
+          qa0[ks] = u.x;
+          qa2[ks] = u.y;
+        }
+      }
+    } else {
+      warp_q_fragments(qa0, qa2, a.q + ((size_t)b * kHeads + kvh * kGroupHeads) * kHeadDim, g, c);
+    }
     for (int i = warp; i < n_tiles; i += kStreamWarps) {
       const int s = i % kStreamStages;
       // (a stage whose early copy was repeated is one phase ahead for the rest of the kernel)
@@ -179,11 +255,22 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
         if (lane == 0) fail_s = 2;
         break;
       }
+      const int t0 = (tile0 + i) * kWarpChunk;
+      if (finish && p_new >= t0 && p_new < t0 + kWarpChunk && p_new < t_end) {
+        // this step's k and v take their row of the tile (16 chunks of 16 bytes: lanes 0-7 k, 8-15 v)
+        if (lane < 16) {
+          const int chunk = lane & 7;
+          const uint32_t dst = base + s * kStageBytes + (lane < 8 ? 0u : kTileBytes) + sw128_offset(p_new - t0, chunk);
+          const uint4 val = *reinterpret_cast<const uint4*>((lane < 8 ? kn_s : vn_s) + 8 * chunk);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
+                       : "memory");
+        }
+        __syncwarp();
+      }
       WarpTile tile;
       warp_tile_from_smem(tile, base + s * kStageBytes, base + s * kStageBytes + kTileBytes, g, c);
       __syncwarp();
       if (lane == 0) mbar_arrive_local(smem_u32(&bar_empty[s]));  // the stage may be refilled
-      const int t0 = (tile0 + i) * kWarpChunk;
       float m1, l1, o1[8][4];
       warp_tile_attend(tile, qa0, qa2, t0, max(t_begin, t0), min(t_end, t0 + kWarpChunk), a.scale, c, m1, l1, o1);
       // running softmax over this warp's tiles (m, l are equal in the four lanes of a head)
@@ -247,12 +334,19 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
 // a.s_cap bounds the tokens of a row; `status`: error word of the bounded waits.
 int g_stream_force_reload = 0;
 
-int launch_attn_stream(const AttnArgs& a, int batch, int n_slots, int s_max, int* status, cudaStream_t stream,
-                       bool pdl) {
+int launch_attn_stream(const AttnArgs& a, const QkvFinish* fuse, int batch, int n_slots, int s_max, int* status,
+                       cudaStream_t stream, bool pdl) {
   QUIC_REQUIRE(a.stride_h == (int64_t)s_max * kHeadDim && a.stride_b == (int64_t)kKvHeads * s_max * kHeadDim,
                QUIC_E_ARG, "attn_decode_stream: the cache must be [slots][2][s_max][64]");
   QUIC_REQUIRE(status != nullptr && batch >= 1 && batch <= 65535 && n_slots >= 1, QUIC_E_ARG,
                "attn_decode_stream: bad batch, slots or status word");
+  QkvFinish fin = {};
+  if (fuse != nullptr) {
+    QUIC_REQUIRE(fuse->part && fuse->bias && fuse->cos_t && fuse->sin_t && fuse->splits >= 1 && fuse->max_pos >= 1 &&
+                     a.pos != nullptr && a.rows != nullptr,
+                 QUIC_E_ARG, "attn_decode_stream: incomplete QKV finish");
+    fin = *fuse;
+  }
   CUtensorMap tm_k, tm_v;
   const uint64_t rows = (uint64_t)n_slots * kKvHeads * s_max;
   int rc = make_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.k, rows, kHeadDim, kWarpChunk, kHeadDim,
@@ -268,7 +362,7 @@ int launch_attn_stream(const AttnArgs& a, int batch, int n_slots, int s_max, int
     attr_set = true;
   }
   QUIC_CUDA(launch(attn_decode_stream_kernel, dim3(kKvHeads, batch), dim3((kStreamWarps + 1) * 32), kStreamSmem, stream,
-                   pdl, tm_k, tm_v, a, s_max, status, g_stream_force_reload));
+                   pdl, tm_k, tm_v, a, fin, n_slots, s_max, status, g_stream_force_reload));
   return QUIC_OK;
 }
 

@@ -106,7 +106,19 @@ constexpr int kAttnCtaMaxSplits = 8;
 int attn_cta_splits(int ctx);
 cudaError_t launch_attn_cta(const AttnArgs& a, int batch, cudaStream_t stream, bool pdl);
 // Many rows: one CTA per (row, KV head) streaming the cache through a TMA ring (attn_decode_stream.cu).
-int launch_attn_stream(const AttnArgs& a, int batch, int n_slots, int s_max, int* status, cudaStream_t stream, bool pdl);
+// `fuse` (or nullptr): the kernel also finishes the fused QKV linear for its row -- sums the split-K
+// partial sums, adds the bias, rotates q and k, appends k and v to the cache -- so that no separate
+// kernel stands between the QKV GEMM and the attention.
+struct QkvFinish {
+  const float* part;  // [splits][batch][1152] fp32 partial sums of the QKV linear (columns in the prepacked order)
+  int32_t splits;
+  const half* bias;   // [1152]
+  const half* cos_t;  // [max_pos][32]
+  const half* sin_t;
+  int32_t max_pos;
+};
+int launch_attn_stream(const AttnArgs& a, const QkvFinish* fuse, int batch, int n_slots, int s_max, int* status,
+                       cudaStream_t stream, bool pdl);
 
 struct LmHeadArgs {
   const half* embed;  // [vocab][896]
