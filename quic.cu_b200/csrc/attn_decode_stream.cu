@@ -150,7 +150,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-  const bool finish = fin.part != nullptr;
+  const bool finish = fin.part != nullptr || fin.qkv != nullptr;
   if (finish && warp < kStreamWarps) {
     // thread -> (head of the CTA: 7 q, k, v; rotation pair): stored columns (2 pair, 2 pair + 1) are dims (pair, pair + 32)
     const bool slot_ok = slot >= 0 && slot < n_slots;
@@ -160,6 +160,12 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
       const int hl = idx >> 5, pair = idx & 31;
       const int head = hl < kGroupHeads ? kvh * kGroupHeads + hl : (hl == kGroupHeads ? kHeads + kvh : kHeads + kKvHeads + kvh);
       const int col = head * kHeadDim + 2 * pair;
+      float x, y;
+      if (fin.qkv != nullptr) {  // the dense GEMM's own output, bias included
+        const float2 v = __half22float2(*reinterpret_cast<const half2*>(fin.qkv + (size_t)b * kQkvN + col));
+        x = v.x;
+        y = v.y;
+      } else {
       float2 acc = make_float2(0.f, 0.f);
       for (int s0 = 0; s0 < fin.splits; s0 += 8) {  // eight partial sums in flight
         float2 ps[8];
@@ -175,8 +181,9 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
         }
       }
       const float2 bb = __half22float2(*reinterpret_cast<const half2*>(fin.bias + col));
-      const float x = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.x)) + bb.x));
-      const float y = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.y)) + bb.y));
+      x = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.x)) + bb.x));
+      y = __half2float(__float2half_rn(__half2float(__float2half_rn(acc.y)) + bb.y));
+      }
       float lo = x, hi = y;
       if (hl <= kGroupHeads) {  // q and k are rotated
         const float cs = __half2float(fin.cos_t[(size_t)pp * 32 + pair]), sn = __half2float(fin.sin_t[(size_t)pp * 32 + pair]);
@@ -342,8 +349,8 @@ int launch_attn_stream(const AttnArgs& a, const QkvFinish* fuse, int batch, int 
                "attn_decode_stream: bad batch, slots or status word");
   QkvFinish fin = {};
   if (fuse != nullptr) {
-    QUIC_REQUIRE(fuse->part && fuse->bias && fuse->cos_t && fuse->sin_t && fuse->splits >= 1 && fuse->max_pos >= 1 &&
-                     a.pos != nullptr && a.rows != nullptr,
+    QUIC_REQUIRE(((fuse->part && fuse->bias && fuse->splits >= 1) || fuse->qkv) && fuse->cos_t && fuse->sin_t &&
+                     fuse->max_pos >= 1 && a.pos != nullptr && a.rows != nullptr,
                  QUIC_E_ARG, "attn_decode_stream: incomplete QKV finish");
     fin = *fuse;
   }

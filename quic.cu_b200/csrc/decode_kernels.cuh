@@ -113,6 +113,7 @@ struct QkvFinish {
   const float* part;  // [splits][batch][1152] fp32 partial sums of the QKV linear (columns in the prepacked order)
   int32_t splits;
   const half* bias;   // [1152]
+  const half* qkv;    // instead of part / splits / bias: the linear's finished fp16 output [batch][1152]
   const half* cos_t;  // [max_pos][32]
   const half* sin_t;
   int32_t max_pos;

@@ -429,7 +429,8 @@ int enqueue_step_batched(const quic_model_t* m, const quic_decode_t* d, cudaStre
     if (attention_streams(B, ctx)) {
       // the attention CTAs sum the partial sums, rotate and append themselves: one launch less
       // (64 rows of 512 tokens: 934 -> 883 us per step, same bits)
-      QkvFinish fin = {part, sp, (const half*)L.qkv.bias, (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos};
+      QkvFinish fin = {part, sp, (const half*)L.qkv.bias, nullptr, (const half*)m->rope_cos, (const half*)m->rope_sin,
+                       m->max_pos};
       rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st, &fin);
     } else {
       QUIC_CUDA(launch_qkv_post_part(part, sp, (const half*)L.qkv.bias, d->rows, d->pos, (const half*)m->rope_cos,
@@ -605,9 +606,14 @@ int enqueue_step_batched_f16(const quic_model_t* m, const quic_decode_t* d, cuda
     half* vc = kc + kv_plane;
     int rc = gemm_f16_tc(xn, (const half*)L.qkv.w16, (const half*)L.qkv.bias, qkv, B, kQkvN, kHidden, ws, st, true);
     if (rc != QUIC_OK) return rc;
-    QUIC_CUDA(launch_qkv_post(qkv, d->rows, d->pos, (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos,
-                              qbuf, kc, vc, d->s_max, d->n_slots, B, st));
-    rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st);
+    if (attention_streams(B, ctx)) {  // the attention CTAs rotate and append themselves
+      QkvFinish fin = {nullptr, 0, nullptr, qkv, (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos};
+      rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st, &fin);
+    } else {
+      QUIC_CUDA(launch_qkv_post(qkv, d->rows, d->pos, (const half*)m->rope_cos, (const half*)m->rope_sin, m->max_pos,
+                                qbuf, kc, vc, d->s_max, d->n_slots, B, st));
+      rc = enqueue_attention(d, ar, splits, ctx, qbuf, kc, vc, attn_out, st);
+    }
     if (rc != QUIC_OK) return rc;
     rc = gemm_f16_tc(attn_out, (const half*)L.o.w16, nullptr, qkv, B, kHidden, kHidden, ws, st, true);
     if (rc != QUIC_OK) return rc;
@@ -676,7 +682,11 @@ extern "C" int64_t quic_decode_scratch_bytes(int32_t batch, int32_t vocab, int32
 extern "C" int32_t quic_decode_launch_count(const quic_model_t* m, const quic_decode_t* d) {
   if (!m) return 0;
   if (m->layers && m->layers[0].qkv.w16 != nullptr) {
-    if (d && d->batch > kF16ChainMaxRows) return 9 * m->n_layers + 3;
+    if (d && d->batch > kF16ChainMaxRows) {
+      int ctx = d->ctx_hint > 0 ? d->ctx_hint : d->s_max;
+      if (ctx > d->s_max) ctx = d->s_max;
+      return (attention_streams(d->batch, ctx) ? 8 : 9) * m->n_layers + 3;
+    }
     return 5 * m->n_layers + 1;
   }
   if (d && d->batch >= g_tensor_min_batch) {

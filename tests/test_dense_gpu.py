@@ -55,7 +55,7 @@ def test_dense_linear_matches_torch(m, n, k):
     assert K.lib().quic_w4a16_tensor_status() == 0
 
 
-@pytest.mark.parametrize("rows", [1, 2, 3, 4, 6, 20])
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 6, 20, 24])
 def test_dense_decode_matches_oracle(dense_model, rows):
     """Prefill + greedy bursts: the chain of decode_layers_f16.cu up to 2 rows, the GEMM step
     beyond; tokens against the oracle row by row (up to a near-tie)."""
