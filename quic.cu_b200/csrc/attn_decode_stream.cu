@@ -211,8 +211,9 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
   if (warp == kStreamWarps) {
     // ---------------- producer: one thread keeps the ring full ----------------
     if (lane == 0) {
+      int repeated = 0, issued = pre;  // early copies fetched again; tiles requested so far
       if (stale) {  // wait for the early copies to land, then fetch the same tiles again
-        for (int i = 0; i < pre; ++i) {
+        for (int i = 0; i < pre; ++i, ++repeated) {
           const uint32_t full = smem_u32(&bar_full[i]), dst = base + i * kStageBytes;
           if (!mbar_wait(full, 0)) {
             fail_s = 1;
@@ -223,7 +224,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
           tma_load_2d(dst + kTileBytes, &tm_v, 0, row0 + i * kWarpChunk, full);
         }
       }
-      for (int i = pre; i < n_tiles && fail_s == 0; ++i) {
+      for (int i = pre; i < n_tiles && fail_s == 0; ++i, ++issued) {
         const int s = i % kStreamStages;
         if (i >= kStreamStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStreamStages) - 1) & 1)) {
           fail_s = 1;
@@ -234,6 +235,14 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
         mbar_expect_tx(full, kStageBytes);
         tma_load_2d(dst, &tm_k, 0, row, full);
         tma_load_2d(dst + kTileBytes, &tm_v, 0, row, full);
+      }
+      // No copy may still be on its way into this CTA's shared memory when the CTA ends, whatever
+      // became of its consumer: wait (with the usual bound) for the last copy into every stage.
+      // In the normal course the consumers needed these phases anyway.
+      for (int i = issued > kStreamStages ? issued - kStreamStages : 0; i < issued; ++i) {
+        const int s = i % kStreamStages;
+        const int phase = i / kStreamStages + ((i < pre ? i < repeated : (stale && s < pre)) ? 1 : 0);
+        if (!mbar_wait(smem_u32(&bar_full[s]), phase & 1)) fail_s = 1;
       }
     }
   } else if (n_tiles > 0) {
