@@ -125,11 +125,13 @@ int quic_w4a16_tensor_status(void);
  * with (0, -1) to restore normal operation. */
 void quic_w4a16_tensor_test_hook(uint32_t spin_limit, int32_t skip_kblock);
 
-/* Test hook for the streamed decode attention (more than 20 rows): launches and graph captures
- * that follow repeat the tile requests made before the dependency wait, as the kernel does when
- * the step counter moved between request and wait.  0 restores the normal behaviour.  No
- * reference counterpart. */
-void quic_attn_stream_test_hook(int32_t force_reload);
+/* Test hook for the streamed decode attention (more than 20 rows), for the launches and graph
+ * captures that follow.  1: repeat the tile requests made before the dependency wait, as the
+ * kernel does when the step counter moved between request and wait.  2: never request the
+ * first tile of a row and probe 20000 times at most, so that the bounded waits run out, the
+ * kernel sets the error word read by quic_w4a16_tensor_status (code 5 or 6 in bits 16..,
+ * bit 14 set) and returns.  0 restores the normal behaviour.  No reference counterpart. */
+void quic_attn_stream_test_hook(int32_t mode);
 
 /* ------------------------------------------------------------------------
  * Stand-alone operators with the reference's per-op signatures.

@@ -83,7 +83,7 @@ __device__ __forceinline__ void warp_tile_from_smem(WarpTile& t, uint32_t k_s, u
 __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
     attn_decode_stream_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                               const AttnArgs a, const QkvFinish fin, int n_slots, int s_max, int* status,
-                              int force_reload) {
+                              int force_reload, int skip_tile0, uint32_t spin_limit) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStreamStages];   // a stage's two tiles landed
   __shared__ __align__(8) uint64_t bar_empty[kStreamStages];  // its consumer warp holds them in registers
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
     const int p0 = min(__ldcg(a.pos + slot0), a.s_cap);  // tokens below p0 were appended by earlier steps
     const int pre = min(p0 > 0 ? p0 / kWarpChunk : 0, kStreamStages);
     const int row0p = (slot0 * kKvHeads + kvh) * s_max;
-    for (int i = 0; i < pre; ++i) {
+    for (int i = skip_tile0 ? 1 : 0; i < pre; ++i) {  // (test hook: the wait for tile 0 runs out)
       const uint32_t full = smem_u32(&bar_full[i]), dst = base + i * kStageBytes;
       mbar_expect_tx(full, kStageBytes);
       tma_load_2d(dst, &tm_k, 0, row0p + i * kWarpChunk, full);
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
       if (stale) {  // wait for the early copies to land, then fetch the same tiles again
         for (int i = 0; i < pre; ++i, ++repeated) {
           const uint32_t full = smem_u32(&bar_full[i]), dst = base + i * kStageBytes;
-          if (!mbar_wait(full, 0)) {
+          if (!mbar_wait(full, 0, spin_limit)) {
             fail_s = 1;
             break;
           }
@@ -226,10 +226,11 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
       }
       for (int i = pre; i < n_tiles && fail_s == 0; ++i, ++issued) {
         const int s = i % kStreamStages;
-        if (i >= kStreamStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStreamStages) - 1) & 1)) {
+        if (i >= kStreamStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStreamStages) - 1) & 1, spin_limit)) {
           fail_s = 1;
           break;
         }
+        if (i == 0 && skip_tile0) continue;  // (test hook)
         const uint32_t full = smem_u32(&bar_full[s]), dst = base + s * kStageBytes;
         const int row = row0 + (tile0 + i) * kWarpChunk;  // rows past the end of the cache read as zero
         mbar_expect_tx(full, kStageBytes);
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
       for (int i = issued > kStreamStages ? issued - kStreamStages : 0; i < issued; ++i) {
         const int s = i % kStreamStages;
         const int phase = i / kStreamStages + ((i < pre ? i < repeated : (stale && s < pre)) ? 1 : 0);
-        if (!mbar_wait(smem_u32(&bar_full[s]), phase & 1)) fail_s = 1;
+        if (!mbar_wait(smem_u32(&bar_full[s]), phase & 1, spin_limit)) fail_s = 1;
       }
     }
   } else if (n_tiles > 0) {
@@ -265,7 +266,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
       const int s = i % kStreamStages;
       // (a stage whose early copy was repeated is one phase ahead for the rest of the kernel)
       const int shift = (stale && s < pre) ? 1 : 0;
-      bool ok = mbar_wait(smem_u32(&bar_full[s]), ((i / kStreamStages) + shift) & 1);
+      bool ok = mbar_wait(smem_u32(&bar_full[s]), ((i / kStreamStages) + shift) & 1, spin_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) fail_s = 2;
@@ -348,7 +349,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
 
 // The cache planes must be the decode step's: [n_slots][2][s_max][64] fp16, 16-byte aligned.
 // a.s_cap bounds the tokens of a row; `status`: error word of the bounded waits.
-int g_stream_force_reload = 0;
+int g_stream_hook = 0;  // quic_attn_stream_test_hook: 1 repeat the early requests, 2 never request tile 0
 
 int launch_attn_stream(const AttnArgs& a, const QkvFinish* fuse, int batch, int n_slots, int s_max, int* status,
                        cudaStream_t stream, bool pdl) {
@@ -378,13 +379,16 @@ int launch_attn_stream(const AttnArgs& a, const QkvFinish* fuse, int batch, int 
     attr_set = true;
   }
   QUIC_CUDA(launch(attn_decode_stream_kernel, dim3(kKvHeads, batch), dim3((kStreamWarps + 1) * 32), kStreamSmem, stream,
-                   pdl, tm_k, tm_v, a, fin, n_slots, s_max, status, g_stream_force_reload));
+                   pdl, tm_k, tm_v, a, fin, n_slots, s_max, status, g_stream_hook == 1 ? 1 : 0, g_stream_hook == 2 ? 1 : 0,
+                   g_stream_hook == 2 ? 20000u : kSpinLimit));
   return QUIC_OK;
 }
 
 }  // namespace quic
 
-// Test hook: the streamed decode attention of the launches (and graph captures) that follow treats
-// its early tile requests as made too early and repeats them, as it does when the step counter
-// moved between the request and the dependency wait.  0 restores the normal behaviour.
-extern "C" void quic_attn_stream_test_hook(int32_t force_reload) { quic::g_stream_force_reload = force_reload != 0; }
+// Test hook for the launches (and graph captures) that follow.  1: the kernel treats its early tile
+// requests as made too early and repeats them, as it does when the step counter moved between the
+// request and the dependency wait.  2: the first tile of every row is never requested and the
+// waits probe 20000 times at most, so the wait for that tile runs out, the other roles' waits
+// follow, the CTA sets the error word (code 5 or 6, bit 14) and returns; nothing faults.  0: normal.
+extern "C" void quic_attn_stream_test_hook(int32_t mode) { quic::g_stream_hook = (mode == 1 || mode == 2) ? mode : 0; }

@@ -171,6 +171,37 @@ def test_a_gemm_wait_that_runs_out_is_reported_and_the_next_call_works(tiny_mode
     assert lib.quic_w4a16_tensor_status() == 0
 
 
+def test_a_streamed_attention_wait_that_runs_out_is_reported_and_the_next_call_works(tiny_model):
+    """The bounded waits of the streamed decode attention: under the library's test hook the first
+    tile of every row is never requested and the waits probe 20000 times at most; the consumer
+    warp's wait runs out, the producer's wait for that stage follows, the CTA reports and returns.
+    decode() raises; with the hook cleared a fresh cache decodes what the oracle gives."""
+    from quic_cu_b200 import kernels as K
+
+    net, ref, _, _ = tiny_model
+    lib = K.lib()
+    gen = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 2048, (70 + i,), generator=gen) for i in range(24)]
+    slots = list(range(24))
+    assert lib.quic_w4a16_tensor_status() == 0
+    cache = net.new_cache(n_slots=24, s_max=128)
+    net.prefill(cache, slots, prompts)
+    lib.quic_attn_stream_test_hook(2)
+    try:
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            net.decode(cache, slots, 2)
+    finally:
+        lib.quic_attn_stream_test_hook(0)
+    assert lib.quic_w4a16_tensor_status() == 0          # decode() took the word
+    cache = net.new_cache(n_slots=24, s_max=128)
+    first, _ = net.prefill(cache, slots, prompts)
+    rest = net.decode(cache, slots, 3)
+    for i in (0, 11, 23):
+        ref_tokens, ref_logits = ref.greedy(prompts[i].tolist(), 4)
+        _near_tie_ok([int(first[i])] + rest[i], ref_tokens, ref_logits)
+    assert lib.quic_w4a16_tensor_status() == 0
+
+
 @pytest.mark.parametrize("rows", [1, 3, 8, 16, 20, 40])
 def test_decode_gives_the_same_bits_every_run(tiny_model, rows):
     """Cross-CTA hand-offs (arrival counters, cluster merges, split-K planes) must not make the
