@@ -548,7 +548,11 @@ static void tc_plan(int m, int n, int k, int* mt_out, int* splits_out, int* per_
   // split K while it at most fills the SMs once, at most 16 ways, at least one stage per CTA
   int splits = 1;
   while (splits < 16 && ctas * splits * 2 <= 148 && kb_total / (splits * 2) >= 1) splits *= 2;
-  const int per = (kb_total + splits - 1) / splits;
+  int per = (kb_total + splits - 1) / splits;
+  // a short K (seven stages) in single stages while that still fits one wave: the loop's length,
+  // not the work, bounds a small GEMM
+  // (64-row step 889 -> 881 us, 32 rows 781 -> 758)
+  if (per == 2 && ctas * kb_total <= 148) per = 1;
   *mt_out = mt;
   *per_out = per;
   *splits_out = (kb_total + per - 1) / per;
