@@ -61,6 +61,31 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// N (2, 4 or a multiple of 8) consecutive fp32 columns of this thread's TMEM lane: all loads in
+// flight, one wait
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[N]) {
+  static_assert(N == 2 || N == 4 || (N % 8 == 0 && N >= 8), "2, 4 or whole 8-column loads");
+  uint32_t r[N];
+  if constexpr (N == 2) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr));
+  } else if constexpr (N == 4) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr));
+  } else {
+#pragma unroll
+    for (int q = 0; q < N / 8; ++q)
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(r[8 * q + 0]), "=r"(r[8 * q + 1]), "=r"(r[8 * q + 2]), "=r"(r[8 * q + 3]), "=r"(r[8 * q + 4]),
+                     "=r"(r[8 * q + 5]), "=r"(r[8 * q + 6]), "=r"(r[8 * q + 7])
+                   : "r"(taddr + 8u * q));
+  }
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < N; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane: two loads in flight, one wait
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];

@@ -292,35 +292,37 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     if (!ok && tid == 0 && nkb > 0) atomicCAS(&g_tc_status[0], 0, ((fail_s ? fail_s : 3) << 16) | (int)blockIdx.x);
-    if (MTL == 2 && a.y != nullptr && gridDim.y == 1) {
-      // Many rows (two row tiles = 256 accumulator columns per CTA): every warp reads its lane
-      // quarter 32 columns at a time, the CTA's output tile is put together in shared memory --
-      // the operand ring is free once the accumulation is complete -- and leaves in 16-byte
-      // pieces, whole 128- or 256-byte rows at a time.  All 16 warps reach every barrier whether
-      // or not their waits succeeded.
-      const int quarter = warp & 3, cgroup = warp >> 2;  // cgroup: 64 of the 256 columns (= batch rows)
+    constexpr int kOutCols = MT * MTL;       // accumulator columns = batch rows of the CTA
+    constexpr int kWarpCols = kOutCols / 4;  // per warp of a lane quarter
+    if (a.y != nullptr && gridDim.y == 1) {
+      // A finished fp16 output (no K split): every warp reads its lane quarter kWarpCols / 2 columns at
+      // a time, the CTA's output tile is put together in shared memory -- the operand ring is free
+      // once the accumulation is complete -- and leaves in 16-byte pieces, whole 128- or 256-byte
+      // rows at a time.  All 16 warps reach every barrier whether or not their waits succeeded.
+      constexpr int kHalf = kWarpCols / 2;  // 2 (16 batch rows per CTA) .. 32 (256)
+      const int quarter = warp & 3, cgroup = warp >> 2;  // cgroup: a quarter of the columns (= batch rows)
       const uint32_t lane_addr = tmem_d + ((uint32_t)(quarter * 32) << 16);
-      float v[32];
+      float v[kHalf];
       if (a.fuse_swiglu) {
         // TMEM lanes 0-63 hold the gate rows, 64-127 the up rows of the same 64 activation columns.
-        // Of a warp's 64 batch rows the up warps hand their first 32 to the gate warps and the gate
-        // warps their second 32 to the up warps (fp16-rounded, as the linear's output), so that
-        // every warp finishes silu(gate) * up for 32 batch rows.
-        float* ex = reinterpret_cast<float*>(gen_base);                               // [256][64] fp32
-        half* out_s = reinterpret_cast<half*>(gen_base + MT * MTL * 64 * sizeof(float));  // [256][64] fp16
+        // Of a warp's batch rows the up warps hand the first half to the gate warps and the gate
+        // warps the second half to the up warps (fp16-rounded, as the linear's output), so that
+        // every warp finishes silu(gate) * up for half of them.
+        float* ex = reinterpret_cast<float*>(gen_base);                            // [kOutCols][64] fp32
+        half* out_s = reinterpret_cast<half*>(gen_base + kOutCols * 64 * sizeof(float));  // [kOutCols][64] fp16
         const bool up = quarter >= 2;
         const int row = (quarter & 1) * 32 + lane;  // 0..63 inside the gate (or up) half
-        const int c_send = cgroup * 64 + (up ? 0 : 32), c_fin = cgroup * 64 + (up ? 32 : 0);
+        const int c_send = cgroup * kWarpCols + (up ? 0 : kHalf), c_fin = cgroup * kWarpCols + (up ? kHalf : 0);
         if (ok && m0 + c_send < a.m_total) {
-          tmem_ld32(lane_addr + (uint32_t)c_send, v);
+          tmem_ld_cols<kHalf>(lane_addr + (uint32_t)c_send, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) ex[(c_send + j) * 64 + row] = __half2float(__float2half_rn(v[j]));
+          for (int j = 0; j < kHalf; ++j) ex[(c_send + j) * 64 + row] = __half2float(__float2half_rn(v[j]));
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
         if (ok && m0 + c_fin < a.m_total) {
-          tmem_ld32(lane_addr + (uint32_t)c_fin, v);
+          tmem_ld_cols<kHalf>(lane_addr + (uint32_t)c_fin, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
+          for (int j = 0; j < kHalf; ++j) {
             const float mine = __half2float(__float2half_rn(v[j])), other = ex[(c_fin + j) * 64 + row];
             out_s[(c_fin + j) * 64 + row] = __float2half_rn(up ? silu_mul(other, mine) : silu_mul(mine, other));
           }
@@ -328,7 +330,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
         if (ok) {
 #pragma unroll 1
-          for (int id = tid; id < MT * MTL * 8; id += kConsumers) {  // (batch row, 16-byte piece of its 128 bytes)
+          for (int id = tid; id < kOutCols * 8; id += kConsumers) {  // (batch row, 16-byte piece of its 128 bytes)
             const int t = id >> 3, piece = id & 7, m = m0 + t;
             if (m < a.m_total)
               *reinterpret_cast<uint4*>(a.y + (size_t)m * half_n + (size_t)blockIdx.x * 64 + piece * 8) =
@@ -336,17 +338,17 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
           }
         }
       } else {
-        half* out_s = reinterpret_cast<half*>(gen_base);  // [256][128] fp16
+        half* out_s = reinterpret_cast<half*>(gen_base);  // [kOutCols][128] fp16
         const int col_l = quarter * 32 + lane;
         const bool has_bias = a.w.bias != nullptr;
         const float bias = has_bias ? __half2float(reinterpret_cast<const half*>(a.w.bias)[n0 + col_l]) : 0.f;
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh) {
-          const int c0 = cgroup * 64 + hh * 32;
+          const int c0 = cgroup * kWarpCols + hh * kHalf;
           if (ok && m0 + c0 < a.m_total) {
-            tmem_ld32(lane_addr + (uint32_t)c0, v);
+            tmem_ld_cols<kHalf>(lane_addr + (uint32_t)c0, v);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < kHalf; ++j) {
               float o = __half2float(__float2half_rn(v[j]));
               if (has_bias) o += bias;
               out_s[(c0 + j) * kTileN + col_l] = __float2half_rn(o);
@@ -356,56 +358,13 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
         if (ok) {
 #pragma unroll 1
-          for (int id = tid; id < MT * MTL * 16; id += kConsumers) {  // (batch row, 16-byte piece of its 256 bytes)
+          for (int id = tid; id < kOutCols * 16; id += kConsumers) {  // (batch row, 16-byte piece of its 256 bytes)
             const int t = id >> 4, piece = id & 15, m = m0 + t;
             if (m < a.m_total)
               *reinterpret_cast<uint4*>(a.y + (size_t)m * N + n0 + piece * 8) =
                   *reinterpret_cast<const uint4*>(out_s + t * kTileN + piece * 8);
           }
         }
-      }
-    } else if (a.fuse_swiglu) {
-      // TMEM lanes 0-63 hold the gate rows, 64-127 the up rows of the same 64 columns.  The up
-      // warps park their (fp16-rounded) values in shared memory -- the operand ring is free once
-      // the accumulation is complete -- and the gate warps finish silu(gate) * up.  Every one of
-      // the 16 warps reaches the barrier whether or not its waits succeeded.
-      const int quarter = warp & 3, cgroup = warp >> 2;
-      constexpr int kColsPerGroup = MT >= 32 ? MT / 4 : 8;
-      float* ex = reinterpret_cast<float*>(gen_base);  // [MT * MTL columns][64 rows]
-#pragma unroll 1
-      for (int phase = 0; phase < 2; ++phase) {
-        const bool mine = ok && ((phase == 0) == (quarter >= 2));
-        if (mine) {
-#pragma unroll 1
-          for (int i = 0; i < MTL; ++i) {
-            if (m0 + i * MT >= a.m_total) break;
-#pragma unroll 1
-            for (int c = cgroup * kColsPerGroup; c < min(MT, (cgroup + 1) * kColsPerGroup); c += 8) {
-              const int c0 = i * MT + c;
-              if (m0 + c0 >= a.m_total) break;
-              uint32_t r[8];
-              const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-              asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                           : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                             "=r"(r[7])
-                           : "r"(taddr));
-              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-              const int row = (quarter & 1) * 32 + lane;  // 0..63 inside the gate (or up) half
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int m = m0 + c0 + j;
-                const float v = __half2float(__float2half_rn(__uint_as_float(r[j])));  // the linear's fp16 output
-                if (phase == 0) {
-                  ex[(c0 + j) * 64 + row] = v;
-                } else if (m < a.m_total) {
-                  const float u = ex[(c0 + j) * 64 + row];
-                  a.y[(size_t)m * half_n + (size_t)blockIdx.x * 64 + row] = __float2half_rn(silu_mul(v, u));
-                }
-              }
-            }
-          }
-        }
-        if (phase == 0) asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
       }
     } else if (ok) {
       // TMEM lane = tile row; a warp may read lanes 32*(warp % 4)..+31, so the four warps that
