@@ -367,41 +367,22 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
         }
       }
     } else if (ok) {
-      // TMEM lane = tile row; a warp may read lanes 32*(warp % 4)..+31, so the four warps that
-      // share a lane quarter split the batch columns between them
+      // fp32 partial sums of this K split for a fused consumer.  TMEM lane = tile row; a warp may
+      // read lanes 32*(warp % 4)..+31, so the four warps that share a lane quarter split the batch
+      // columns between them and read theirs in one go.
       const int quarter = warp & 3, cgroup = warp >> 2;
       const int col = n0 + quarter * 32 + lane;
-      constexpr int kColsPerGroup = MT >= 32 ? MT / 4 : 8;
-      const float bias = (a.w.bias != nullptr && gridDim.y == 1 && a.y != nullptr)
-                             ? __half2float(reinterpret_cast<const half*>(a.w.bias)[col])
-                             : 0.f;
+      constexpr int kPer = MT >= 32 ? MT / 4 : 8;
 #pragma unroll 1
       for (int i = 0; i < MTL; ++i) {
-        if (m0 + i * MT >= a.m_total) break;
-#pragma unroll 1
-        for (int c = cgroup * kColsPerGroup; c < min(MT, (cgroup + 1) * kColsPerGroup); c += 8) {
-          const int c0 = i * MT + c;  // accumulator column = tile * MT + row inside the tile
-          if (m0 + c0 >= a.m_total) break;
-          uint32_t r[8];
-          const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                         "=r"(r[7])
-                       : "r"(taddr));
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int c0 = i * MT + cgroup * kPer;  // accumulator column = tile * MT + row inside the tile
+        if (cgroup * kPer >= MT || m0 + c0 >= a.m_total) continue;
+        float v[kPer];
+        tmem_ld_cols<kPer>(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int m = m0 + c0 + j;
-            if (m >= a.m_total) continue;
-            const float v = __uint_as_float(r[j]);
-            if (gridDim.y == 1 && a.y != nullptr) {
-              float o = __half2float(__float2half_rn(v));
-              if (a.w.bias != nullptr) o += bias;
-              a.y[(size_t)m * N + col] = __float2half_rn(o);
-            } else {
-              a.part[((size_t)split * a.m_total + m) * N + col] = v;
-            }
-          }
+        for (int j = 0; j < kPer; ++j) {
+          const int m = m0 + c0 + j;
+          if (m < a.m_total) a.part[((size_t)split * a.m_total + m) * N + col] = v[j];
         }
       }
     }
