@@ -124,6 +124,23 @@ def test_the_graph_cache_is_bounded_and_rebuilds(tiny_model):
     assert got == want
 
 
+def test_prefill_beyond_8192_rows_goes_out_in_one_launch_per_linear(tiny_model):
+    """Five prompts of 2000 tokens are 10000 rows: beyond 8192 rows a packed linear covers all rows in
+    one launch (no K split at that size, so no workspace).  The same prompts prefilled as 6000 and
+    4000 rows must leave the same first tokens, the same logits and the same cache."""
+    net, _, _, _ = tiny_model
+    gen = torch.Generator().manual_seed(81)
+    prompts = [torch.randint(0, 2048, (2000,), generator=gen) for _ in range(5)]
+    whole = net.new_cache(n_slots=5, s_max=2048)
+    first, logits = net.prefill(whole, [0, 1, 2, 3, 4], prompts)
+    parts = net.new_cache(n_slots=5, s_max=2048)
+    first_a, logits_a = net.prefill(parts, [0, 1, 2], prompts[:3])
+    first_b, logits_b = net.prefill(parts, [3, 4], prompts[3:])
+    assert first.tolist() == first_a.tolist() + first_b.tolist()
+    assert torch.equal(logits, torch.cat([logits_a, logits_b]))
+    assert torch.equal(whole.kv[:, :, :, :, :2000], parts.kv[:, :, :, :, :2000])
+
+
 def test_bursts_single_steps_and_host_fed_steps_agree(tiny_model):
     """150 tokens three ways: graph bursts of 64 steps (the ring of generated tokens wraps),
     single-step calls, and single-step calls that feed the previous token back from pinned
