@@ -770,6 +770,8 @@ def main() -> None:
                     help="also serve a queue of this many synthetic requests with continuous batching (64 slots "
                          "per GPU, pulled by all replicas from one FIFO, two passes: about 35 s each on one GPU); "
                          "4096 is the benchmark configuration; 0 skips it")
+    ap.add_argument("--batch64-only", action="store_true",
+                    help="run only the 64-row decode measurement and print its block (profiler captures)")
     ap.add_argument("--serving-order", default="longest", choices=["longest", "fifo"],
                     help="order of the serving queue: by token budget, largest first (default), or as generated")
     ap.add_argument("--layers", type=int, default=24,
@@ -804,6 +806,10 @@ def main() -> None:
     if args.linear_sweep:
         for row in linear_sweep():
             print(json.dumps(row))
+        return
+    if args.batch64_only:
+        net, _ = build_model("cuda:0", args.layers)
+        print(json.dumps(measure_batch64(net, "cuda:0", 1, None)))
         return
     if args.impl == "reference":
         run_reference(args)
