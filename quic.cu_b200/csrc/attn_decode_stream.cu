@@ -11,7 +11,7 @@
 // HBM bandwidth and takes 25 us per layer (12 us here).  Here a single thread keeps kStreamStages x
 // 16 KB of bulk copies in flight per SM and the copies cost the warps no instructions.  Measured
 // per 64-row step of 200..1500 tokens: 1266 us with one-warp CTAs, 1022 with four warps and eight
-// stages.
+// stages, 1015 with six warps and twelve stages, 973 with the QKV finish below.
 //
 // Inside the decode chain (a.prefetch) the producer requests, BEFORE the dependency wait, the
 // tiles that hold only tokens of earlier steps (up to the ring's depth): those rows are complete
@@ -21,7 +21,7 @@
 // barriers, which their consumers then wait for).  The tile of the row that the preceding
 // kernel appends is never requested early.
 //
-// With `fin.part` set the CTA first finishes the fused QKV linear for its row and KV head, which a
+// With `fin.part` (or `fin.qkv`, a finished fp16 output) set the CTA first finishes the fused QKV linear for its row and KV head, which a
 // separate kernel (qkv_post_kernel) would otherwise do between the GEMM and the attention: the
 // compute warps sum the split-K partial sums of their seven q heads, their k head and their v head,
 // add the bias with the GEMM epilogue's roundings, rotate q and k (rope.forward of the reference,
