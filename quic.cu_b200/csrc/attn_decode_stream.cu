@@ -99,6 +99,8 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32, 1)
   const int kvh = blockIdx.x, b = blockIdx.y;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   if (tid == 0) {
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
     for (int s = 0; s < kStreamStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);

@@ -120,6 +120,9 @@ __global__ void __launch_bounds__(kAttThreads, 2) attn_prefill_tc_kernel(const _
   unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
 
   if (tid == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
     mbar_init(smem_u32(&bar_q), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);

@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(kDenseThreads) gemm_f16_tc_kernel(const __grid
   constexpr uint32_t kCols = MT < 32 ? 32 : MT;
 
   if (tid == 0) {
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
     for (int s = 0; s < kDenseStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);

@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_tc_kernel(const __grid_con
   constexpr uint32_t kCols = MT < 32 ? 32 : MT;
 
   if (tid == 0) {
+    tma_prefetch_desc(&tm_e);
+    tma_prefetch_desc(&tm_x);
     for (int s = 0; s < kLmStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);

@@ -123,6 +123,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_tc_kernel(const __gri
 
   constexpr uint32_t kCols = MT * MTL < 32 ? 32 : MT * MTL;  // power of two >= 32
   if (tid == 0) {
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_aready[s]), kConsumers / 32 + 1);
