@@ -595,7 +595,8 @@ def _flash_attn_decode_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                                          ptr(pad_lens), None, s, scale, ptr(out), b, stream_ptr()),
               "attn_decode_cta")
         return out
-    if splits <= 0:
+    asked = splits
+    if splits <= 0:  # the library chooses (the same count, or its streamed kernel, which needs no scratch)
         splits = lib().quic_attn_pick_splits(b, s)
     scratch = None
     if splits > 1:
@@ -606,7 +607,7 @@ def _flash_attn_decode_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
             scratch = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=q.device)
             _attn_scratch[key] = scratch
     check(lib().quic_attn_decode(ptr(q), ptr(k), ptr(v), KV_HEADS * s * HEAD_DIM, s * HEAD_DIM,
-                                 ptr(pad_lens), None, s, scale, ptr(out), b, splits, ptr(scratch),
+                                 ptr(pad_lens), None, s, scale, ptr(out), b, splits if asked > 0 else 0, ptr(scratch),
                                  stream_ptr()), "attn_decode")
     return out
 
