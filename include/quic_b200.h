@@ -242,7 +242,10 @@ int64_t quic_lm_head_scratch_bytes(int32_t b, int32_t vocab);
  * (flash_attn_decode.cu:118-121).  `scratch` holds the split partials and the
  * arrival counters: quic_attn_scratch_bytes(b, splits) bytes, whose first
  * b*2*4 bytes (the counters) must be zero before the first call; the kernel
- * leaves them zero.  `splits` 0 lets the library choose. */
+ * leaves them zero.  `splits` 0 lets the library choose: quic_attn_pick_splits(b,
+ * s_max) splits (size the scratch for that count), or, for 21..128 rows of up to
+ * 8192 tokens whose K and V are contiguous [b][2][s_max][64] planes, the streamed
+ * kernel of the decode step, which uses no scratch. */
 int quic_attn_decode(const void *q_f16, const void *k_f16, const void *v_f16,
                      int64_t stride_b, int64_t stride_h, const int32_t *start,
                      const int32_t *end, int32_t s_max, float scale,
